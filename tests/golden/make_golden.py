@@ -1,0 +1,300 @@
+"""Generate golden vectors by running the reference implementation on CPU.
+
+Run where the reference checkout is available:
+
+    python tests/golden/make_golden.py --reference /path/to/reference [--cases small_fp32,...]
+
+The reference's certified path is Python + Triton.  It runs on CPU tensors
+with the Triton interpreter (TRITON_INTERPRET=1) and with `pin_memory`
+turned into a no-op (there is no CUDA driver on the generating machine).
+Inputs come from `cqa_b200.synth` (numpy RNG, seeded), so the tests can
+rebuild them without the reference.  Intermediate tensors are captured by
+wrapping the functions `certified_attention_layer` calls.
+
+Each case is written to tests/golden/<case>.npz.  Large byte arrays are
+stored as SHA-256 digests plus a strided sample; small tensors in full.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+os.environ.setdefault("TRITON_INTERPRET", "1")
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT / "certified-quantised-attention_b200"))
+
+from cqa_b200 import synth  # noqa: E402
+
+PAPER_KNOBS = dict(
+    v_tolerance=0.05, top_k_fp16_keys=4, ranking_fallback=True, ranking_r=1,
+    ranking_fallback_mode="full", tau_cov=0.995, k_min=2, k_max=128,
+    rung1_threshold=0.02, rung1_multiplier=2.0, score_consistency_check=True,
+    eps_guard=0.01, exploration_rate=0.02, value_error_mode="tight",
+)
+
+CASES = {
+    # name: dict(inputs=..., appends=[...], calls at ..., knobs overrides)
+    "small_fp32": dict(
+        seed=11, n_tokens=1029, kv_heads=2, gqa_group=4, dtype="float32",
+        planted=0, appends=0, call_after=[0], knobs={},
+    ),
+    "small_vtol0": dict(
+        seed=12, n_tokens=1024, kv_heads=2, gqa_group=4, dtype="float32",
+        planted=0, appends=0, call_after=[0], knobs={"v_tolerance": 0.0},
+    ),
+    "planted_bf16_append": dict(
+        seed=13, n_tokens=2048, kv_heads=2, gqa_group=4, dtype="bfloat16",
+        planted=8, appends=20, call_after=[0, 5, 16, 20], knobs={},
+    ),
+    "planted_fp16_g2": dict(
+        seed=14, n_tokens=1552, kv_heads=3, gqa_group=2, dtype="float16",
+        planted=6, appends=3, call_after=[3], knobs={"score_consistency_check": False},
+    ),
+    "config1_8k": dict(
+        seed=0, n_tokens=8192, kv_heads=8, gqa_group=4, dtype="float32",
+        planted=0, appends=0, call_after=[0], knobs={},
+    ),
+    "planted_8k_bf16": dict(
+        seed=21, n_tokens=8192, kv_heads=8, gqa_group=4, dtype="bfloat16",
+        planted=32, appends=0, call_after=[0], knobs={},
+    ),
+}
+
+TORCH_DTYPE = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+
+
+def _install_cpu_shims():
+    """No CUDA driver here: make pinned-memory requests plain CPU allocations."""
+    torch.Tensor.pin_memory = lambda self, *a, **k: self
+    torch.Tensor.is_pinned = lambda self, *a, **k: True
+    for name in ("zeros", "empty", "ones"):
+        orig = getattr(torch, name)
+
+        def wrapped(*args, _orig=orig, **kwargs):
+            kwargs.pop("pin_memory", None)
+            return _orig(*args, **kwargs)
+
+        setattr(torch, name, wrapped)
+
+
+def sha(t) -> str:
+    a = t.detach().cpu().contiguous()
+    if a.dtype == torch.bfloat16:
+        a = a.view(torch.int16)
+    return hashlib.sha256(a.numpy().tobytes()).hexdigest()
+
+
+def npy(t):
+    a = t.detach().cpu().contiguous()
+    if a.dtype == torch.bfloat16:
+        return a.view(torch.int16).numpy()
+    return a.numpy()
+
+
+def cache_snapshot(cache, tag: str, out: dict):
+    nt = cache.num_tokens
+    nq = cache.num_quantized_blocks
+    bs = cache.block_size
+    big = {
+        "keys_int8": cache.keys_int8[:, : nq * bs],
+        "keys_scale": cache.keys_scale[:, :nq],
+        "keys_zero_points": cache.keys_zero_points[:, :nq],
+        "values_int4_packed": cache.values_int4_packed[:, : nq * bs],
+        "values_int4_scales": cache.values_int4_scales[:, : nq * bs],
+        "values_int4_zeros": cache.values_int4_zeros[:, : nq * bs],
+    }
+    for name, t in big.items():
+        out[f"{tag}/sha/{name}"] = np.array(sha(t))
+    small = {
+        "correction": cache.correction[:, :nq],
+        "values_int4_errors": cache.values_int4_errors[:, :nq],
+        "values_int4_error_sums": cache.values_int4_error_sums[:, :nq],
+        "values_norm_max_per_block": cache.values_norm_max_per_block[:, : cache.num_blocks],
+    }
+    for name, t in small.items():
+        out[f"{tag}/{name}"] = npy(t)
+    out[f"{tag}/num_tokens"] = np.array(nt)
+    out[f"{tag}/num_quantized_blocks"] = np.array(nq)
+    # Strided samples of the big arrays so a mismatch can be localised.
+    out[f"{tag}/sample/keys_int8"] = npy(cache.keys_int8[:, : nq * bs : 37, ::5])
+    out[f"{tag}/sample/keys_scale"] = npy(cache.keys_scale[:, :nq:7, ::3])
+    out[f"{tag}/sample/values_int4_packed"] = npy(cache.values_int4_packed[:, : nq * bs : 37, ::5])
+
+
+def run_case(name: str, spec: dict, ref_mods) -> dict:
+    ca, tkc = ref_mods
+    t0 = time.time()
+    base = synth.make_layer_inputs(
+        spec["seed"], spec["n_tokens"], kv_heads=spec["kv_heads"], gqa_group=spec["gqa_group"],
+        dtype=spec["dtype"], n_planted_blocks=spec["planted"],
+    )
+    td = TORCH_DTYPE[spec["dtype"]]
+    K = torch.from_numpy(base.k).to(td)
+    V = torch.from_numpy(base.v).to(td)
+    n = spec["n_tokens"]
+    aligned = (n // 16) * 16
+    max_new = spec["appends"] + 16
+    # Same construction as create_tiered_cache_int4v_from_model with both
+    # FP16 capacities None (full mirrors, deferred INT4 append quantisation).
+    cache = tkc.TieredKeyCacheLayer.from_fp16_cache_int4v(
+        K[:, :aligned].contiguous(), V[:, :aligned].contiguous(),
+        block_size=16, group_size=16, max_new_tokens=max_new + (n - aligned),
+        fp16_key_cache_capacity=None, fp16_value_cache_capacity=None,
+        defer_int4_append_quantization=True,
+    )
+    for t in range(aligned, n):
+        cache.append_token(K[:, t:t + 1], V[:, t:t + 1])
+    at, nt = cache.aligned_tokens, cache.num_tokens
+    if at > nt:
+        cache.keys_int8[:, nt:at, :] = -127
+
+    out: dict = {"spec": np.array(json.dumps(spec))}
+    cache_snapshot(cache, "prefill", out)
+
+    knobs = dict(PAPER_KNOBS)
+    knobs.update(spec["knobs"])
+    q_scale = 1.0 / (128 ** 0.5)
+    H = spec["kv_heads"] * spec["gqa_group"]
+
+    captured: dict = {}
+
+    def wrap(modname, fn_name, recorder):
+        orig = getattr(ca, fn_name)
+
+        def w(*args, **kwargs):
+            res = orig(*args, **kwargs)
+            recorder(args, kwargs, res)
+            return res
+
+        setattr(ca, fn_name, w)
+        return orig
+
+    def rec_score(args, kwargs, res):
+        captured["m_b"] = npy(res[0])
+        captured["S_b"] = npy(res[1])
+
+    def rec_topk(args, kwargs, res):
+        # (mask, k_star, tail, tau_actual, mass_frac, sorted_idx, sel_k, cumsum)
+        if len(res) == 8:
+            captured["sel_k_star_expanded"] = npy(res[1])
+            captured["mass_frac"] = npy(res[4])
+            captured["sorted_idx"] = npy(res[5]).astype(np.int32)
+            captured["sorted_cumsum"] = npy(res[7])
+
+    def rec_fp16(args, kwargs, res):
+        captured["top_block_indices"] = npy(args[2]).astype(np.int32)
+        captured["fp16_block_scores"] = npy(res[0])
+        captured["fp16_block_log_masses"] = npy(res[1])
+
+    def rec_delta(args, kwargs, res):
+        captured["delta_per_head"] = npy(res)
+
+    def rec_phase2(args, kwargs, res):
+        captured["phase2_fn"] = np.array(kwargs.get("_fn", ""))
+        captured["topk_mask_attend"] = np.packbits(npy(kwargs["topk_mask"]).astype(bool), axis=1)
+        captured["topk_mask_shape"] = np.array(kwargs["topk_mask"].shape)
+        if "value_fp16_mask" in kwargs:
+            captured["value_fp16_mask"] = np.packbits(
+                npy(kwargs["value_fp16_mask"]).astype(bool), axis=1)
+        captured["last_block_valid"] = np.array(int(kwargs["last_block_valid"]))
+        captured["phase2_out"] = npy(res).copy()
+
+    def rec_rung3(args, kwargs, res):
+        captured["rung3_heads"] = npy(kwargs["head_indices"]).astype(np.int32)
+
+    def rec_explore(args, kwargs, res):
+        captured["exploration_mask"] = np.packbits(npy(res[1]).astype(bool), axis=1)
+
+    origs = {}
+    origs["fused_score_certify_multihead"] = wrap(ca, "fused_score_certify_multihead", rec_score)
+    origs["compute_adaptive_topk_mask"] = wrap(ca, "compute_adaptive_topk_mask", rec_topk)
+    origs["compute_fp16_block_scores"] = wrap(ca, "compute_fp16_block_scores", rec_fp16)
+    origs["compute_delta_bound"] = wrap(ca, "compute_delta_bound", rec_delta)
+    origs["recompute_heads_dense_fp16"] = wrap(ca, "recompute_heads_dense_fp16", rec_rung3)
+    origs["augment_mask_with_exploration"] = wrap(ca, "augment_mask_with_exploration", rec_explore)
+    for fn in (
+        "selective_attend_multihead_hybrid_int4v",
+        "selective_attend_multihead_hybrid_mixedv",
+        "selective_attend_multihead_hybrid_mixedv_split_k",
+    ):
+        origs[fn] = wrap(ca, fn, rec_phase2)
+
+    try:
+        step = 0
+        for target in spec["call_after"]:
+            while step < target:
+                qt, kn, vn = synth.decode_step_inputs(base, step, dtype=spec["dtype"])
+                cache.append_token(torch.from_numpy(kn).to(td), torch.from_numpy(vn).to(td))
+                step += 1
+            if target == 0:
+                q_np = base.q
+            else:
+                q_np, _, _ = synth.decode_step_inputs(base, target - 1, dtype=spec["dtype"])
+            q_all = torch.from_numpy(q_np).to(td)
+            tag = f"call{target}"
+            cache_snapshot(cache, f"{tag}/cache", out)
+            gen = torch.Generator(device="cpu")
+            gen.manual_seed(1000 + spec["seed"] * 100 + target)
+            # The uniforms the reference will draw (same generator state).
+            g2 = torch.Generator(device="cpu")
+            g2.manual_seed(1000 + spec["seed"] * 100 + target)
+            nq = cache.num_quantized_blocks
+            u = torch.rand((H, nq), generator=g2)
+            captured.clear()
+            with torch.inference_mode():
+                output, stats = ca.certified_attention_layer(
+                    cache, q_all, spec["gqa_group"], q_scale, collect_stats=True,
+                    exploration_generator=gen, **knobs,
+                )
+            out[f"{tag}/exploration_u_sha"] = np.array(sha(u))
+            out[f"{tag}/output"] = npy(output).copy()
+            out[f"{tag}/stats"] = np.array(json.dumps(
+                {k: (v if isinstance(v, (int, float, str, bool)) else float(v)) for k, v in stats.items()}
+            ))
+            for k, v in captured.items():
+                out[f"{tag}/{k}"] = v
+            print(f"  [{name}] {tag}: nt={cache.num_tokens} nq={nq} "
+                  f"k*={stats.get('k_star_mean')} v_format={stats.get('v_format')} "
+                  f"rung1={stats.get('rung1_fired')} rung2={stats.get('rung2_fired')} "
+                  f"rung3={stats.get('rung3_fired')} vfb={stats.get('value_fallback_blocks')} "
+                  f"({time.time() - t0:.0f}s)", flush=True)
+    finally:
+        for fn, o in origs.items():
+            setattr(ca, fn, o)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--cases", default="small_fp32,small_vtol0,planted_bf16_append,planted_fp16_g2")
+    ap.add_argument("--out", default=str(HERE))
+    args = ap.parse_args()
+
+    _install_cpu_shims()
+    sys.path.insert(0, args.reference)
+    import dotcache.kernels.certified_attention as ca
+    import dotcache.kernels.tiered_kv_cache as tkc
+    assert str(Path(ca.__file__).resolve()).startswith(str(Path(args.reference).resolve()))
+
+    for name in args.cases.split(","):
+        spec = CASES[name]
+        print(f"[golden] {name}: {spec}", flush=True)
+        res = run_case(name, spec, (ca, tkc))
+        path = Path(args.out) / f"{name}.npz"
+        np.savez_compressed(path, **res)
+        print(f"[golden] wrote {path} ({path.stat().st_size / 1024:.0f} KiB)", flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,158 @@
+"""The CPU oracle against the golden vectors produced by the reference's own code.
+
+Bytes, masks, index sets and flags must match exactly; floats within the
+stated tolerances (the reference fixes no summation order, so its float32
+results are only defined up to rounding)."""
+from __future__ import annotations
+
+import json
+
+import numpy as np
+import pytest
+
+import golden_cases as gc
+from oracle import cqa_oracle as orc
+
+RTOL_STAT = 1e-5     # m_b, S_b, mass fractions, eta, nu, delta
+ATOL_STAT = 2e-6
+OUT_RTOL = 1e-3      # attention output (north-star tolerance)
+
+
+def _make_cache(k, v, dtype, max_new):
+    return orc.OracleCache.from_fp16_cache_int4v(k, v, dtype, max_new_tokens=max_new)
+
+
+def _append(cache, k, v):
+    cache.append_token(k, v)
+
+
+def check_cache_snapshot(cache, z, tag):
+    nq = int(z[f"{tag}/num_quantized_blocks"])
+    assert cache.num_quantized_blocks == nq
+    assert cache.num_tokens == int(z[f"{tag}/num_tokens"])
+    T = nq * 16
+    exact = {
+        "keys_int8": cache.keys_int8[:, :T],
+        "keys_scale": cache.keys_scale[:, :nq],
+        "keys_zero_points": cache.keys_zero_points[:, :nq],
+        "values_int4_packed": cache.values_int4_packed[:, :T],
+        "values_int4_scales": cache.values_int4_scales[:, :T],
+        "values_int4_zeros": cache.values_int4_zeros[:, :T],
+    }
+    for name, arr in exact.items():
+        assert gc.sha_np(arr) == str(z[f"{tag}/sha/{name}"]), f"{tag}: {name} bytes differ"
+    np.testing.assert_allclose(cache.correction[:, :nq], z[f"{tag}/correction"], rtol=1e-6)
+    np.testing.assert_allclose(cache.values_int4_errors[:, :nq], z[f"{tag}/values_int4_errors"],
+                               rtol=RTOL_STAT)
+    np.testing.assert_allclose(cache.values_int4_error_sums[:, :nq],
+                               z[f"{tag}/values_int4_error_sums"], rtol=RTOL_STAT)
+    np.testing.assert_allclose(cache.values_norm_max_per_block[:, :cache.num_blocks],
+                               z[f"{tag}/values_norm_max_per_block"], rtol=RTOL_STAT)
+
+
+def check_call(R, z, tag, H, nq, nact):
+    stats = json.loads(str(z[f"{tag}/stats"]))
+    np.testing.assert_allclose(R["m_b"], z[f"{tag}/m_b"], rtol=RTOL_STAT, atol=ATOL_STAT * 10)
+    np.testing.assert_allclose(R["S_b"], z[f"{tag}/S_b"], rtol=RTOL_STAT * 2)
+    if f"{tag}/mass_frac" in z:
+        np.testing.assert_allclose(R["mass_frac"], z[f"{tag}/mass_frac"], rtol=5e-5, atol=1e-9)
+        assert np.array_equal(R["sorted_idx"], z[f"{tag}/sorted_idx"]), "sorted block order differs"
+        np.testing.assert_allclose(R["sorted_cumsum"], z[f"{tag}/sorted_cumsum"], rtol=2e-5)
+    if f"{tag}/exploration_mask" in z:
+        ref = gc.unpack_mask(z[f"{tag}/exploration_mask"], nq)
+        assert np.array_equal(R["exploration_mask"], ref), "exploration mask differs"
+    ref_topk = gc.unpack_mask(z[f"{tag}/topk_mask_attend"], nact)
+    assert np.array_equal(R["topk_mask_active"], ref_topk), "FP16-key (top-K*) mask differs"
+    if f"{tag}/value_fp16_mask" in z:
+        ref_v = gc.unpack_mask(z[f"{tag}/value_fp16_mask"], nact)
+        assert np.array_equal(R["value_fp16_mask"], ref_v), "FP16-value mask differs"
+    assert int(z[f"{tag}/last_block_valid"]) == R["last_block_valid"]
+    # ranking check: same top-4 set per head; per-block FP16 scores agree
+    ref_idx = z[f"{tag}/top_block_indices"]
+    for h in range(H):
+        assert set(ref_idx[h].tolist()) == set(R["top_block_indices"][h].tolist())
+        pos = {int(b): i for i, b in enumerate(R["top_block_indices"][h])}
+        perm = [pos[int(b)] for b in ref_idx[h]]
+        np.testing.assert_allclose(R["fp16_block_scores"][h][perm], z[f"{tag}/fp16_block_scores"][h],
+                                   rtol=RTOL_STAT, atol=ATOL_STAT * 10)
+        np.testing.assert_allclose(R["fp16_block_log_masses"][h][perm],
+                                   z[f"{tag}/fp16_block_log_masses"][h], rtol=RTOL_STAT,
+                                   atol=ATOL_STAT * 10)
+    np.testing.assert_allclose(R["delta_per_head"], z[f"{tag}/delta_per_head"], rtol=RTOL_STAT)
+    ref_r3 = z[f"{tag}/rung3_heads"] if f"{tag}/rung3_heads" in z else np.zeros(0, np.int32)
+    assert np.array_equal(np.sort(R["rung3_heads"]), np.sort(ref_r3)), "Rung-3 head set differs"
+    # certificate flags / counters from the reference's stats dict
+    assert bool(stats["rung1_fired"]) == bool(R["rung1_trigger"].any())
+    assert bool(stats["rung3_fired"]) == bool(R["rung3_heads"].size > 0)
+    assert bool(stats["rung4_fired"]) == bool(R["rung4"])
+    assert stats["k_star_min"] == int(R["k_star"].min())
+    assert stats["k_star_max"] == int(R["k_star"].max())
+    assert stats["rung1_triggered_heads"] == int(R["rung1_trigger"].sum())
+    assert stats["exploration_blocks"] == int(R["exploration_mask"].sum())
+    assert stats.get("value_fallback_head_blocks", 0) == int(R["value_unsafe_mask"].sum())
+    assert stats.get("value_fallback_blocks", 0) == int(R["value_unsafe_mask"].any(axis=0).sum())
+    if "ranking_disagree_r1" in stats:
+        assert stats["ranking_disagree_r1"] == R["ranking_disagree_r1"]
+        assert stats["ranking_disagree_r3"] == R["ranking_disagree_r3"]
+        assert stats["boundary_check_triggered_heads"] == int(R["boundary_mask"].sum())
+    if "score_consistency_violation_heads" in stats:
+        assert stats["score_consistency_violation_heads"] == int(
+            R["score_consistency_violation_mask"].sum())
+    np.testing.assert_allclose(float(R["e_val"].max()), stats["e_val_max"], rtol=1e-4, atol=1e-7)
+    np.testing.assert_allclose(float(R["e_pre"].max()), stats["e_val_pre_rung2_max"], rtol=1e-4)
+    np.testing.assert_allclose(float(R["tail_mass"].max()), stats["tail_mass_int8_est_max"],
+                               rtol=1e-3, atol=1e-6)
+    # output: 1e-3 relative to the row scale
+    ref_out = z[f"{tag}/output"].astype(np.float64)
+    scale = np.abs(ref_out).max(axis=1, keepdims=True)
+    assert np.all(np.abs(R["output"] - ref_out) <= OUT_RTOL * scale), "attention output out of tolerance"
+    ref_p2 = z[f"{tag}/phase2_out"].astype(np.float64)
+    scale2 = np.abs(ref_p2).max(axis=1, keepdims=True)
+    assert np.all(np.abs(R["phase2_output"] - ref_p2) <= OUT_RTOL * scale2)
+
+
+def run_golden_case(name):
+    spec, z = gc.load(name)
+    H = spec["kv_heads"] * spec["gqa_group"]
+
+    def call(cache, q, target, knobs):
+        check_cache_snapshot(cache, z, f"call{target}/cache")
+        nq = cache.num_quantized_blocks
+        u = gc.exploration_uniforms(spec, target, H, nq)
+        assert gc.sha_np(u) == str(z[f"call{target}/exploration_u_sha"])
+        return orc.layer_step(cache, q, spec["gqa_group"], exploration_u=u, **knobs)
+
+    n_calls = 0
+    for target, cache, R in gc.replay(spec, _make_cache, _append, call):
+        if target == "prefill":
+            check_cache_snapshot(cache, z, "prefill")
+            continue
+        check_call(R, z, f"call{target}", H, cache.num_quantized_blocks, cache.active_blocks)
+        n_calls += 1
+    assert n_calls == len(spec["call_after"])
+
+
+@pytest.mark.parametrize("name", gc.available(gc.SMALL_CASES))
+def test_oracle_matches_reference_small(name):
+    run_golden_case(name)
+
+
+@pytest.mark.parametrize("name", gc.available(gc.LARGE_CASES))
+def test_oracle_matches_reference_8k(name):
+    run_golden_case(name)
+
+
+def test_goldens_present():
+    assert len(gc.available(gc.SMALL_CASES)) == len(gc.SMALL_CASES)
+
+
+def test_custom_exp_log_accuracy():
+    xs = np.linspace(-80, 20, 4001).astype(np.float32)
+    mine = np.array([orc.exp32(x) for x in xs], dtype=np.float64)
+    ref = np.exp(xs.astype(np.float64))
+    assert np.max(np.abs(mine - ref) / ref) < 2.5e-7
+    xs = np.logspace(-20, 20, 4001).astype(np.float32)
+    mine = np.array([orc.log32(x) for x in xs], dtype=np.float64)
+    ref = np.log(xs.astype(np.float64))
+    assert np.max(np.abs(mine - ref)) < 8e-6
+    assert orc.exp32(-200.0) == 0.0 and orc.exp32(0.0) == 1.0 and orc.log32(1.0) == 0.0
