@@ -1,0 +1,450 @@
+"""Benchmark: certified quantised decode attention, µs per layer per decode step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--context 32768] [--layers 8] [--planted 64]
+
+Workload (N=1): the single-GPU configuration of the headline metric — Llama-3.1-8B
+attention geometry (32 query heads, 8 KV heads, head_dim 128), batch 1,
+context 32768, bf16 Q/K/V ~ N(0,1) with 4 outlier key channels per head (x8)
+and 64 planted key blocks (cosine 0.9 to the query), INT8 keys / INT4 g16
+values, paper certification knobs; every decode step appends one seeded token
+and runs the certified attention chain.  A "step" is one token through
+`--layers` independent layer caches (distinct caches, so the working set
+between two visits of the same cache is far larger than L2, as in a real
+32-layer decode); the metric is step time / layers.
+
+The default run prints ONE JSON line on rank 0.  `value` is the device-timed
+number with inputs resident in HBM; `e2e` is the same metric through the public
+Python API with host buffers (pinned q/k/v copied in, output copied out every
+layer-step).  `roofline` is for the dominant kernel, `cpu_baseline` times the CPU
+oracle (a port of the reference's algorithm) on this host.
+
+--impl reference times the reference's own algorithm on the host cores.  The
+reference is Python + Triton with no CPU implementation that can travel to this
+box, so that arm runs the CPU oracle port (oracle/cqa_oracle.*) with all host
+threads on the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (str(ROOT), str(ROOT / "certified-quantised-attention_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np
+
+PAPER_KNOBS = dict(
+    v_tolerance=0.05, top_k_fp16_keys=4, ranking_fallback=True, ranking_r=1,
+    ranking_fallback_mode="full", tau_cov=0.995, k_min=2, k_max=128,
+    rung1_threshold=0.02, rung1_multiplier=2.0, score_consistency_check=False,
+    eps_guard=0.01, exploration_rate=0.02, value_error_mode="tight",
+)
+METRIC = "certified_decode_attention_us_per_layer_step"
+KERNELS_PER_LAYER_STEP = 7  # append, score, select, certify, attend, dense recompute, merge
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--planted", type=int, default=64)
+    ap.add_argument("--seed", type=int, default=2)
+    ap.add_argument("--e2e-steps", type=int, default=64)
+    ap.add_argument("--kernel-steps", type=int, default=32)
+    ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------- workload
+
+def build_inputs(args, n_layers, rank=0):
+    from cqa_b200 import synth
+
+    bases = []
+    for l in range(n_layers):
+        bases.append(synth.make_layer_inputs(args.seed + 1000 * rank + l, args.context, dtype="bfloat16",
+                                             n_planted_blocks=args.planted))
+    return bases
+
+
+def step_tensors(bases, n_steps):
+    """[steps][layers] numpy arrays of (q, k_new, v_new)."""
+    from cqa_b200 import synth
+
+    out = []
+    for s in range(n_steps):
+        out.append([synth.decode_step_inputs(b, s, dtype="bfloat16") for b in bases])
+    return out
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+def cpu_baseline(args, base, n_steps, max_new):
+    """The CPU oracle port of the reference's algorithm on the host cores:
+    append + Phase 1 + selector + certificate + Phase 2 (float32) per step."""
+    from cqa_b200 import synth
+    from oracle import cqa_oracle as orc
+
+    n = args.context
+    aligned = (n // 16) * 16
+    oc = orc.OracleCache.from_fp16_cache_int4v(base.k[:, :aligned], base.v[:, :aligned], "bfloat16",
+                                               max_new_tokens=max_new)
+    for t in range(aligned, n):
+        oc.append_token(base.k[:, t:t + 1], base.v[:, t:t + 1])
+    vs = oc.values_int4_scales.astype(np.float32)
+    vz = oc.values_int4_zeros.astype(np.float32)
+    knobs = dict(PAPER_KNOBS)
+    times = []
+    rng = np.random.default_rng(0)
+    for s in range(n_steps + 1):
+        q, kn, vn = synth.decode_step_inputs(base, s, dtype="bfloat16")
+        t0 = time.perf_counter()
+        oc.append_token(kn, vn)
+        if (oc.num_tokens - 1) % 16 == 15:
+            vs = oc.values_int4_scales.astype(np.float32)
+            vz = oc.values_int4_zeros.astype(np.float32)
+        nq = oc.num_quantized_blocks
+        nact = oc.active_blocks
+        m_b, S_b, tok = orc.score_blocks(oc, q, 4, 1.0 / math.sqrt(128.0))
+        sel = orc.adaptive_select(m_b, S_b, knobs["tau_cov"], knobs["k_min"], knobs["k_max"],
+                                  knobs["rung1_threshold"], knobs["rung1_multiplier"])
+        mask = sel["topk_mask"]
+        u = rng.random(mask.shape, dtype=np.float32)
+        mask = mask | ((~mask) & (u < np.float32(knobs["exploration_rate"])))
+        H = mask.shape[0]
+        top_idx = np.stack([np.argsort(-m_b[h], kind="stable")[:4] for h in range(H)]).astype(np.int32)
+        orc.fp16_block_scores(oc, q, top_idx, 4, 1.0 / math.sqrt(128.0), nq)
+        orc.delta_bound(q, oc.sigma_max, 4)
+        vc = orc.value_check(sel["mass_frac"], oc.values_int4_errors[:, :nq], 4, knobs["v_tolerance"])
+        tk = np.zeros((H, nact), dtype=np.int32)
+        tk[:, :nq] = mask
+        vm = np.zeros((H, nact), dtype=np.int32)
+        vm[:, :nq] = vc["unsafe"]
+        trailing = oc.has_trailing_partial_block
+        if trailing:
+            tk[:, nq:] = 1
+            vm[:, nq:] = 1
+        lv = 16 if not trailing else oc.num_tokens - nq * 16
+        orc.attend_mixed_f32(oc, q, 4, 1.0 / math.sqrt(128.0), tok, tk, vm, nact, lv, vs, vz)
+        dt = time.perf_counter() - t0
+        if s > 0:
+            times.append(dt)
+    return float(np.median(times)) * 1e6
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def run_ours(args, rank, world, device_index):
+    import torch
+    import torch.distributed as dist
+
+    from cqa_b200 import roofline
+    from dotcache.kernels import certified_attention as ca
+    from dotcache.kernels.tiered_kv_cache import TieredKeyCacheLayer
+
+    torch.cuda.set_device(device_index)
+    dev = torch.device("cuda", device_index)
+    K, W, NL = args.steps, args.warmup, args.layers
+    total_steps = W + K + args.e2e_steps + args.kernel_steps + 4
+    bases = build_inputs(args, NL, rank)
+    n = args.context
+    aligned = (n // 16) * 16
+    caches = []
+    for b in bases:
+        kd = torch.from_numpy(b.k[:, :aligned]).to(torch.bfloat16).to(dev)
+        vd = torch.from_numpy(b.v[:, :aligned]).to(torch.bfloat16).to(dev)
+        c = TieredKeyCacheLayer.from_fp16_cache_int4v(kd, vd, max_new_tokens=total_steps + (n - aligned) + 16,
+                                                      defer_int4_append_quantization=True)
+        for t in range(aligned, n):
+            c.append_token(torch.from_numpy(b.k[:, t:t + 1]).to(torch.bfloat16).to(dev),
+                           torch.from_numpy(b.v[:, t:t + 1]).to(torch.bfloat16).to(dev))
+        caches.append(c)
+        del kd, vd
+    steps = step_tensors(bases, total_steps)
+    H = 32
+    q_host = torch.empty(total_steps, NL, H, 128, dtype=torch.bfloat16).pin_memory()
+    k_host = torch.empty(total_steps, NL, 8, 128, dtype=torch.bfloat16).pin_memory()
+    v_host = torch.empty(total_steps, NL, 8, 128, dtype=torch.bfloat16).pin_memory()
+    for s in range(total_steps):
+        for l in range(NL):
+            q, kn, vn = steps[s][l]
+            q_host[s, l] = torch.from_numpy(q).to(torch.bfloat16)
+            k_host[s, l] = torch.from_numpy(kn.reshape(8, 128)).to(torch.bfloat16)
+            v_host[s, l] = torch.from_numpy(vn.reshape(8, 128)).to(torch.bfloat16)
+    q_dev, k_dev, v_dev = q_host.to(dev), k_host.to(dev), v_host.to(dev)
+    knobs = dict(PAPER_KNOBS)
+    q_scale = 1.0 / math.sqrt(128.0)
+
+    def layer_step(s, l, collect=False, timings=None):
+        c = caches[l]
+        c.append_token(k_dev[s, l], v_dev[s, l])
+        return ca.certified_attention_layer(c, q_dev[s, l], 4, q_scale, collect, phase_timings=timings, **knobs)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    s_idx = 0
+    for _ in range(W):
+        for l in range(NL):
+            layer_step(s_idx, l)
+        s_idx += 1
+    # ---- timed region: inputs resident in HBM
+    sampler = ClockSampler(device_index)
+    sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        for l in range(NL):
+            layer_step(s_idx, l)
+        s_idx += 1
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / K
+    # whole-job aggregate: layer-steps of all ranks per unit time (ranks run independent sequences)
+    us_per_layer = ms_per_step * 1e3 / (NL * world)
+
+    # ---- end to end: host buffers in, output out, every layer-step
+    out_host = torch.empty(H, 128, dtype=torch.float32).pin_memory()
+    qd = torch.empty(H, 128, dtype=torch.bfloat16, device=dev)
+    kd = torch.empty(8, 128, dtype=torch.bfloat16, device=dev)
+    vd = torch.empty(8, 128, dtype=torch.bfloat16, device=dev)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        for l in range(NL):
+            qd.copy_(q_host[s_idx, l], non_blocking=True)
+            kd.copy_(k_host[s_idx, l], non_blocking=True)
+            vd.copy_(v_host[s_idx, l], non_blocking=True)
+            c = caches[l]
+            c.append_token(kd, vd)
+            out, _ = ca.certified_attention_layer(c, qd, 4, q_scale, False, **knobs)
+            out_host.copy_(out, non_blocking=True)
+            torch.cuda.synchronize()
+        s_idx += 1
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_us = e2e_s * 1e6 / (args.e2e_steps * NL)
+    h2d = (H * 128 + 2 * 8 * 128) * 2
+    d2h = H * 128 * 4
+
+    # ---- per-kernel timing (staged calls, CUDA events on the launching stream) and algorithmic bytes
+    phase = {}
+    bytes_acc = {"score": 0, "attend": 0, "dense": 0, "total": 0, "floor": 0}
+    n_meas = 0
+    sel_stats = {"k_star_mean": [], "value_fallback_blocks": [], "rung3": 0, "fp16_key_bytes": 0,
+                 "fp16_value_bytes": 0}
+    for _ in range(args.kernel_steps):
+        for l in range(NL):
+            layer_step(s_idx, l, collect=False, timings=phase)
+            c = caches[l]
+            ws = c._certified_workspace["cqa_ws"]
+            nq, nact = c.num_quantized_blocks, c.active_blocks
+            cert, flags = ws.read_cert()
+            lv = 16 if nact == nq else c.num_tokens - nq * 16
+            b = roofline.step_bytes(ws.topk_mask[:, :nact].cpu().numpy(), ws.value_mask[:, :nact].cpu().numpy(),
+                                    nq, nact, lv, 4, cert["dense"], 2, cert["top_blocks"][:, :4])
+            for key in ("score", "attend", "dense", "total"):
+                bytes_acc[key] += b[key]
+            bytes_acc["floor"] += roofline.tier1_floor_bytes(c.num_tokens)
+            sel_stats["k_star_mean"].append(float(cert["k_star"].mean()))
+            sel_stats["value_fallback_blocks"].append(int((ws.value_mask[:, :nq].amax(dim=0) > 0).sum().item()))
+            sel_stats["rung3"] += int(cert["dense"].sum())
+            sel_stats["fp16_key_bytes"] += b["fp16_key_bytes"]
+            sel_stats["fp16_value_bytes"] += b["fp16_value_bytes"]
+            n_meas += 1
+        s_idx += 1
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    kern_us = {k[:-3]: v / n_meas for k, v in phase.items()}
+    stage_of = {"phase1_int8_scoring": "score", "phase2_fused_attend": "attend"}
+    dominant = max(stage_of, key=lambda k: kern_us.get(k, 0.0))
+    dom_bytes = bytes_acc[stage_of[dominant]] / n_meas
+    if dominant == "phase2_fused_attend":
+        dom_bytes += bytes_acc["dense"] / n_meas
+    achieved = dom_bytes / (kern_us[dominant] * 1e-6) / 1e9
+    chain_bytes = bytes_acc["total"] / n_meas
+    chain_gbs = chain_bytes / (us_per_layer * 1e-6) / 1e9
+    roof = {
+        "bound": "hbm", "kernel": {"phase1_int8_scoring": "score_blocks_kernel",
+                                   "phase2_fused_attend": "attend_mixed_kernel(+dense,+merge)"}[dominant],
+        "achieved": round(achieved, 1), "peak": peak_gbs, "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
+        "peak_source": peak_src, "traffic": None,
+        "algorithmic_bytes_per_launch": int(dom_bytes), "kernel_us": round(kern_us[dominant], 2),
+        "chain": {"algorithmic_bytes_per_layer_step": int(chain_bytes), "us_per_layer_step": round(us_per_layer, 2),
+                  "achieved_gbs": round(chain_gbs, 1), "frac": round(chain_gbs / peak_gbs, 4),
+                  "frac_of_nominal_8000": round(chain_gbs / 8000.0, 4),
+                  "tier1_floor_bytes": int(bytes_acc["floor"] / n_meas)},
+        "stage_us": {k: round(v, 2) for k, v in kern_us.items()},
+    }
+    result = {
+        "metric": METRIC, "value": round(us_per_layer, 3), "unit": "us", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_per_step, 5), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"llama3.1-8b attention geometry, batch 1, context {args.context}, bf16 KV, "
+                               f"INT8K/INT4V g16, {args.planted} planted blocks, one appended token per step",
+                   "context": args.context, "layers_per_step": NL, "kv_heads": 8, "q_heads": 32, "head_dim": 128,
+                   "knobs": "tau_cov 0.995, k 2..128, r 1, eps_guard 0.01, exploration 0.02, rung1 0.02 x2.0, "
+                            "v_tol 0.05", "l2": "working set per step (layers x Tier-1) larger than L2",
+                   "parallelism": "independent sequences per GPU" if world > 1 else "single GPU"},
+        "tokens_per_s_32layer_equiv": round(1e6 / (32.0 * us_per_layer), 2),
+        "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": h2d * NL, "d2h_bytes_per_step": d2h * NL,
+                "tokens_per_s_32layer_equiv": round(1e6 / (32.0 * e2e_us), 2)},
+        "gpu_launches": KERNELS_PER_LAYER_STEP * NL * K,
+        "clocks": clocks,
+        "roofline": roof,
+        "selection": {"k_star_mean": round(float(np.mean(sel_stats["k_star_mean"])), 2),
+                      "value_fallback_blocks_mean": round(float(np.mean(sel_stats["value_fallback_blocks"])), 2),
+                      "rung3_heads_total": sel_stats["rung3"], "layer_steps_measured": n_meas},
+    }
+    return result, bases
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    max_new = args.warmup + args.steps + args.e2e_steps + args.kernel_steps + 64
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        from cqa_b200 import synth
+
+        base = synth.make_layer_inputs(args.seed, args.context, dtype="bfloat16", n_planted_blocks=args.planted)
+        n_cpu = max(1, min(args.steps, 8))
+        t0 = time.perf_counter()
+        us = cpu_baseline(args, base, n_cpu, max_new)
+        cores = os.cpu_count() or 1
+        line = {
+            "impl": "reference", "metric": METRIC, "value": round(us, 1), "unit": "us", "n_gpus": args.gpus,
+            "steps": n_cpu, "warmup": 1, "ms_per_step": round(us / 1e3, 3), "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"llama3.1-8b attention geometry, batch 1, context {args.context}, bf16 KV, "
+                                   f"INT8K/INT4V g16, {args.planted} planted blocks, one appended token per step",
+                       "context": args.context, "layers_per_step": 1},
+            "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
+                             "sample": f"{n_cpu} decode steps of one layer at context {args.context} "
+                                       f"(median), OpenMP over {cores} host threads, after 1 warm-up step"},
+            "e2e": {"value": round(us, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference has no CPU implementation that runs outside its Python/Triton stack; this arm "
+                    "times the CPU oracle port of its algorithm",
+            "wall_s": round(time.perf_counter() - t0, 1),
+        }
+        print(json.dumps(line), flush=True)
+        return 0
+
+    import torch
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: bench.py --impl ours needs a B200; there is no CPU fallback"}))
+        return 1
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    result, bases = run_ours(args, rank, world, local)
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            us = cpu_baseline(args, bases[0], args.cpu_steps, max_new)
+            cores = os.cpu_count() or 1
+            result["cpu_baseline"] = {
+                "value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
+                "sample": f"{args.cpu_steps} decode steps of one layer at context {args.context} (median), "
+                          f"OpenMP over {cores} host threads, after 1 warm-up step"}
+        print(json.dumps(result), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,156 @@
+"""ctypes binding of libcqa_b200.so (the C ABI declared in include/cqa_b200.h).
+
+The library is the only compute path: there is no CPU or PyTorch fallback.
+`lib()` raises if the shared object is missing or does not export every
+declared symbol.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libcqa_b200.so"
+
+CQA_F32, CQA_F16, CQA_BF16 = 0, 1, 2
+MAX_RANKING_K = 32
+MAX_SORT_BLOCKS = 16384
+
+SYMBOLS = [
+    "cqa_version", "cqa_last_error", "cqa_quantize_blocks", "cqa_append_token", "cqa_int4_quantise",
+    "cqa_score_blocks", "cqa_select", "cqa_fp16_block_scores", "cqa_delta_bound", "cqa_certify",
+    "cqa_attend", "cqa_layer_step", "cqa_suggest_splits",
+]
+
+vp = C.c_void_p
+
+
+class CqaCache(C.Structure):
+    _fields_ = [
+        ("kv_heads", C.c_int32), ("gqa_group", C.c_int32), ("t2_dtype", C.c_int32), ("reserved", C.c_int32),
+        ("cap_tokens", C.c_int64), ("max_blocks", C.c_int64),
+        ("keys_int8", vp), ("keys_scale", vp), ("keys_zero_points", vp), ("correction", vp),
+        ("sigma_max", vp), ("values_int4_packed", vp), ("values_int4_scales", vp),
+        ("values_int4_zeros", vp), ("values_int4_errors", vp), ("values_int4_error_sums", vp),
+        ("values_int4_error_counts", vp), ("values_norm_max", vp),
+        ("keys_t2", vp), ("keys_t2_rows", C.c_int64), ("values_t2", vp), ("values_t2_rows", C.c_int64),
+        ("key_slots", vp), ("value_slots", vp),
+    ]
+
+
+class CqaKnobs(C.Structure):
+    _fields_ = [
+        ("q_scale", C.c_float), ("tau_cov", C.c_float), ("rung1_threshold", C.c_float),
+        ("rung1_multiplier", C.c_float), ("eps_guard", C.c_float), ("exploration_rate", C.c_float),
+        ("v_tolerance", C.c_float),
+        ("k_min", C.c_int32), ("k_max", C.c_int32), ("ranking_r", C.c_int32),
+        ("top_k_fp16_keys", C.c_int32), ("ranking_fallback", C.c_int32), ("rung3_recompute", C.c_int32),
+        ("score_consistency", C.c_int32), ("value_mode_tight", C.c_int32),
+        ("force_trailing_value_fp16", C.c_int32),
+    ]
+
+
+class CqaHeadCert(C.Structure):
+    _fields_ = [
+        ("k_star", C.c_int32), ("k_star_base", C.c_int32), ("k_star_expanded", C.c_int32),
+        ("rung1_triggered", C.c_int32), ("exploration_blocks", C.c_int32),
+        ("ranking_disagree", C.c_int32), ("ranking_disagree_r1", C.c_int32),
+        ("ranking_disagree_r3", C.c_int32), ("boundary_triggered", C.c_int32), ("rung3", C.c_int32),
+        ("consistency_violation", C.c_int32), ("value_promoted_blocks", C.c_int32), ("dense", C.c_int32),
+        ("reserved", C.c_int32 * 3),
+        ("tail_mass", C.c_float), ("tau_actual", C.c_float), ("m_global", C.c_float),
+        ("total_mass", C.c_float), ("delta", C.c_float), ("e_pre", C.c_float), ("e_val", C.c_float),
+        ("boundary_ub", C.c_float), ("ell_fp16_r", C.c_float), ("fp16_top1", C.c_float),
+        ("fp16_top2", C.c_float), ("int8_top1", C.c_float),
+        ("top_blocks", C.c_int32 * MAX_RANKING_K), ("fp16_scores", C.c_float * MAX_RANKING_K),
+        ("fp16_logmass", C.c_float * MAX_RANKING_K),
+    ]
+
+
+class CqaWorkspace(C.Structure):
+    _fields_ = [
+        ("ld", C.c_int64),
+        ("m_b", vp), ("s_b", vp), ("token_scores", vp), ("mass_frac", vp),
+        ("topk_mask", vp), ("value_mask", vp), ("explore_mask", vp),
+        ("sorted_idx", vp), ("sorted_cumsum", vp),
+        ("sel_width", C.c_int32), ("num_splits", C.c_int32), ("dense_splits", C.c_int32),
+        ("reserved", C.c_int32),
+        ("part_m", vp), ("part_l", vp), ("part_acc", vp),
+        ("dense_m", vp), ("dense_l", vp), ("dense_acc", vp),
+        ("cert", vp), ("any_flags", vp), ("out", vp),
+    ]
+
+
+CERT_BYTES = C.sizeof(CqaHeadCert)
+
+_lib = None
+
+
+class CqaError(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """Load the CUDA library (once).  Fails loudly when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise CqaError(
+            f"{LIB_PATH} is missing: build it with "
+            "`python certified-quantised-attention_b200/build.py` (needs nvcc); "
+            "this package has no CPU fallback"
+        )
+    L = C.CDLL(str(LIB_PATH))
+    missing = [s for s in SYMBOLS if not hasattr(L, s)]
+    if missing:
+        raise CqaError(f"{LIB_PATH} does not export {missing}")
+    L.cqa_version.restype = C.c_char_p
+    L.cqa_last_error.restype = C.c_char_p
+    i64, i32, f32 = C.c_int64, C.c_int, C.c_float
+    pc, pk, pw = C.POINTER(CqaCache), C.POINTER(CqaKnobs), C.POINTER(CqaWorkspace)
+    L.cqa_quantize_blocks.argtypes = [pc, vp, vp, i32, i64, i64, i64, vp]
+    L.cqa_append_token.argtypes = [pc, vp, vp, i32, i64, i32, vp]
+    L.cqa_int4_quantise.argtypes = [vp, i32, i64, vp, vp, vp, vp, vp, vp]
+    L.cqa_score_blocks.argtypes = [pc, vp, i32, i64, f32, vp, vp, i64, vp, vp]
+    L.cqa_select.argtypes = [pc, pk, pw, i64, i64, vp, i64, vp]
+    L.cqa_fp16_block_scores.argtypes = [pc, vp, i32, vp, i32, i64, f32, vp, vp, vp]
+    L.cqa_delta_bound.argtypes = [pc, vp, i32, vp, vp]
+    L.cqa_certify.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp]
+    L.cqa_attend.argtypes = [pc, pw, vp, i32, i64, i64, i64, i32, f32, vp]
+    L.cqa_layer_step.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp, i64, vp]
+    L.cqa_suggest_splits.argtypes = [i32, i32, i64, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    for s in SYMBOLS[2:]:
+        getattr(L, s).restype = C.c_int
+    _lib = L
+    return L
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc != 0:
+        msg = lib().cqa_last_error().decode("utf-8", "replace")
+        if rc in (-1, -3, -4):
+            raise ValueError(f"{what}: {msg} (status {rc})")
+        raise CqaError(f"{what}: {msg} (status {rc})")
+
+
+def dtype_code(torch_dtype) -> int:
+    import torch
+
+    if torch_dtype == torch.float32:
+        return CQA_F32
+    if torch_dtype == torch.float16:
+        return CQA_F16
+    if torch_dtype == torch.bfloat16:
+        return CQA_BF16
+    raise ValueError(f"unsupported dtype {torch_dtype}; expected float32, float16 or bfloat16")
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def current_stream(device) -> int:
+    import torch
+
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,152 @@
+// C ABI glue: error text, argument checks, the fused per-layer chain.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace cqa {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+}
+
+int check_cuda(cudaError_t e, const char *what)
+{
+    if (e == cudaSuccess) return CQA_OK;
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return CQA_ERR_CUDA;
+}
+
+int check_launch(const char *what) { return check_cuda(cudaGetLastError(), what); }
+
+int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
+                        float *s_b, long ld, float *tok, cudaStream_t st);
+int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq, long nact,
+                  const float *u, long u_ld, cudaStream_t st);
+int certify_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
+                   long nq, long nact, cudaStream_t st);
+int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
+                  long num_tokens, int last_valid, float q_scale, cudaStream_t st);
+
+static int check_common(const cqa_cache *c, const cqa_workspace *ws, const char *who)
+{
+    if (!c || !ws) { set_error("%s: NULL cache or workspace", who); return CQA_ERR_INVALID; }
+    if (c->kv_heads <= 0 || (c->gqa_group != 1 && c->gqa_group != 2 && c->gqa_group != 4 && c->gqa_group != 8)) {
+        set_error("%s: unsupported head layout kv=%d group=%d", who, c->kv_heads, c->gqa_group);
+        return CQA_ERR_UNSUPPORTED;
+    }
+    if (c->t2_dtype < 0 || c->t2_dtype > 2) { set_error("%s: unknown Tier-2 dtype %d", who, c->t2_dtype); return CQA_ERR_INVALID; }
+    if (ws->ld <= 0) { set_error("%s: workspace ld must be positive", who); return CQA_ERR_INVALID; }
+    return CQA_OK;
+}
+
+static int check_select_ws(const cqa_workspace *ws, const char *who)
+{
+    if (!ws->m_b || !ws->s_b || !ws->mass_frac || !ws->topk_mask || !ws->explore_mask || !ws->sorted_idx ||
+        !ws->sorted_cumsum || !ws->cert || !ws->any_flags) {
+        set_error("%s: workspace is missing selector buffers", who);
+        return CQA_ERR_INVALID;
+    }
+    return CQA_OK;
+}
+
+}  // namespace cqa
+
+using namespace cqa;
+
+extern "C" const char *cqa_version(void) { return "cqa_b200 0.1 (sm_100a)"; }
+extern "C" const char *cqa_last_error(void) { return g_err; }
+
+extern "C" int cqa_select(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, int64_t nq,
+                          int64_t nact, const float *exploration_u, int64_t u_ld, void *stream)
+{
+    int rc = check_common(c, ws, "cqa_select");
+    if (rc) return rc;
+    if (!knobs) { set_error("cqa_select: NULL knobs"); return CQA_ERR_INVALID; }
+    rc = check_select_ws(ws, "cqa_select");
+    if (rc) return rc;
+    if (nact < nq || nact > nq + 1 || nact > ws->ld) {
+        set_error("cqa_select: nact=%ld inconsistent with nq=%ld (ld=%ld)", (long)nact, (long)nq, (long)ws->ld);
+        return CQA_ERR_INVALID;
+    }
+    if (!(knobs->tau_cov > 0.0f)) { set_error("cqa_select: tau_cov must be positive"); return CQA_ERR_INVALID; }
+    if (exploration_u && u_ld < nq) { set_error("cqa_select: exploration_u leading dimension too small"); return CQA_ERR_INVALID; }
+    return select_launch(c, knobs, ws, nq, nact, exploration_u, u_ld, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_certify(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *q,
+                           int q_dtype, int64_t nq, int64_t nact, void *stream)
+{
+    int rc = check_common(c, ws, "cqa_certify");
+    if (rc) return rc;
+    if (!knobs || !q) { set_error("cqa_certify: NULL knobs or q"); return CQA_ERR_INVALID; }
+    rc = check_select_ws(ws, "cqa_certify");
+    if (rc) return rc;
+    if (!ws->value_mask) { set_error("cqa_certify: value_mask missing"); return CQA_ERR_INVALID; }
+    if (nact < nq || nact > nq + 1 || nact > ws->ld) { set_error("cqa_certify: bad nact"); return CQA_ERR_INVALID; }
+    return certify_launch(c, knobs, ws, q, q_dtype, nq, nact, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,
+                          int64_t nact, int64_t num_tokens, int last_block_valid, float q_scale, void *stream)
+{
+    int rc = check_common(c, ws, "cqa_attend");
+    if (rc) return rc;
+    if (!q) { set_error("cqa_attend: NULL q"); return CQA_ERR_INVALID; }
+    return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_block_valid, q_scale, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *q,
+                              int q_dtype, int64_t num_tokens, int64_t nq, const float *exploration_u,
+                              int64_t u_ld, void *stream)
+{
+    int rc = check_common(c, ws, "cqa_layer_step");
+    if (rc) return rc;
+    if (!knobs || !q) { set_error("cqa_layer_step: NULL knobs or q"); return CQA_ERR_INVALID; }
+    rc = check_select_ws(ws, "cqa_layer_step");
+    if (rc) return rc;
+    if (nq <= 0 || num_tokens < nq * BS || num_tokens >= (nq + 1) * BS) {
+        set_error("cqa_layer_step: num_tokens=%ld does not match %ld quantised blocks", (long)num_tokens, (long)nq);
+        return CQA_ERR_INVALID;
+    }
+    const long nact = (num_tokens + BS - 1) / BS;
+    const int last_valid = nact == nq ? BS : (int)(num_tokens - nq * BS);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!ws->token_scores) { set_error("cqa_layer_step: token_scores missing"); return CQA_ERR_INVALID; }
+    rc = score_blocks_launch(c, q, q_dtype, nq, knobs->q_scale, ws->m_b, ws->s_b, ws->ld, ws->token_scores, st);
+    if (rc) return rc;
+    rc = cqa_select(c, knobs, ws, nq, nact, exploration_u, u_ld, stream);
+    if (rc) return rc;
+    rc = cqa_certify(c, knobs, ws, q, q_dtype, nq, nact, stream);
+    if (rc) return rc;
+    return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, knobs->q_scale, st);
+}
+
+extern "C" int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int *num_splits, int *dense_splits)
+{
+    if (kv_heads <= 0 || gqa_group <= 0 || !num_splits || !dense_splits) {
+        set_error("cqa_suggest_splits: bad arguments");
+        return CQA_ERR_INVALID;
+    }
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    // Phase 2: about four resident CTAs per SM, at least 8 blocks (one per warp) per split.
+    long target = ((long)sms * 4 + kv_heads - 1) / kv_heads;
+    long by_work = (nact + 7) / 8;
+    long ns = target < by_work ? target : by_work;
+    if (ns < 1) ns = 1;
+    *num_splits = (int)ns;
+    long H = (long)kv_heads * gqa_group;
+    long dtarget = ((long)sms * 2 + H - 1) / H;
+    long ds = dtarget < by_work ? dtarget : by_work;
+    if (ds < 1) ds = 1;
+    *dense_splits = (int)ds;
+    return CQA_OK;
+}

@@ -1,0 +1,210 @@
+// Shared device helpers: canonical binary32 arithmetic, loads, error plumbing.
+//
+// "Canonical" functions fix the exact sequence of IEEE-754 binary32 operations
+// (round to nearest even, explicit fused multiply-adds, no contraction, no
+// approximate intrinsics) for every value that can change a block selection or
+// a certificate flag.  The CPU checker used by the tests follows the same
+// sequence, so those values are reproducible bit for bit.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/cqa_b200.h"
+
+namespace cqa {
+
+constexpr int D = 128;   // head_dim == d_v
+constexpr int BS = 16;   // tokens per block
+constexpr int GS = 16;   // INT4 group size
+constexpr int NG = 8;    // groups per token
+constexpr unsigned FULL = 0xffffffffu;
+
+// ---------------------------------------------------------------- exp / log
+
+// exp(x): Cody-Waite reduction, degree-5 polynomial (Cephes coefficients),
+// exact power-of-two scaling.  x <= -104 (or NaN) gives 0.
+__device__ __forceinline__ float cexp(float x)
+{
+    if (!(x > -104.0f)) return 0.0f;
+    if (x > 88.0f) x = 88.0f;
+    float t = __fmul_rn(x, 1.44269504088896341f);
+    float n = rintf(t);
+    float r = __fmaf_rn(n, -0.693145751953125f, x);
+    r = __fmaf_rn(n, -1.42860682030941723212e-6f, r);
+    float p = 1.9875691500e-4f;
+    p = __fmaf_rn(p, r, 1.3981999507e-3f);
+    p = __fmaf_rn(p, r, 8.3334519073e-3f);
+    p = __fmaf_rn(p, r, 4.1665795894e-2f);
+    p = __fmaf_rn(p, r, 1.6666665459e-1f);
+    p = __fmaf_rn(p, r, 5.0000001201e-1f);
+    float r2 = __fmul_rn(r, r);
+    p = __fmaf_rn(p, r2, r);
+    p = __fadd_rn(p, 1.0f);
+    int ni = (int)n;
+    if (ni < -126) {
+        p = __fmul_rn(p, __int_as_float((ni + 64 + 127) << 23));
+        return __fmul_rn(p, 5.42101086242752217e-20f);  // 2^-64
+    }
+    return __fmul_rn(p, __int_as_float((ni + 127) << 23));
+}
+
+// log(x) for positive normal x (Cephes logf layout).
+__device__ __forceinline__ float clog(float x)
+{
+    unsigned ix = __float_as_uint(x);
+    int e = (int)(ix >> 23) - 126;
+    float m = __uint_as_float((ix & 0x007FFFFFu) | 0x3F000000u);
+    if (m < 0.707106781186547524f) {
+        e -= 1;
+        m = __fadd_rn(__fadd_rn(m, m), -1.0f);
+    } else {
+        m = __fadd_rn(m, -1.0f);
+    }
+    float z = __fmul_rn(m, m);
+    float y = 7.0376836292e-2f;
+    y = __fmaf_rn(y, m, -1.1514610310e-1f);
+    y = __fmaf_rn(y, m, 1.1676998740e-1f);
+    y = __fmaf_rn(y, m, -1.2420140846e-1f);
+    y = __fmaf_rn(y, m, 1.4249322787e-1f);
+    y = __fmaf_rn(y, m, -1.6668057665e-1f);
+    y = __fmaf_rn(y, m, 2.0000714765e-1f);
+    y = __fmaf_rn(y, m, -2.4999993993e-1f);
+    y = __fmaf_rn(y, m, 3.3333331174e-1f);
+    y = __fmul_rn(y, m);
+    y = __fmul_rn(y, z);
+    float fe = (float)e;
+    y = __fmaf_rn(fe, -2.12194440e-4f, y);
+    y = __fmaf_rn(z, -0.5f, y);
+    float r = __fadd_rn(m, y);
+    r = __fmaf_rn(fe, 0.693359375f, r);
+    return r;
+}
+
+// ------------------------------------------------------------ canonical sums
+
+// Partial of a 128-wide dot product for the 8 channels a lane owns: two fused
+// chains (even / odd channels) added at the end.
+__device__ __forceinline__ float chain8(const float (&a)[8], const float (&b)[8])
+{
+    float e = __fmaf_rn(a[0], b[0], 0.0f);
+    float o = __fmaf_rn(a[1], b[1], 0.0f);
+    e = __fmaf_rn(a[2], b[2], e);
+    o = __fmaf_rn(a[3], b[3], o);
+    e = __fmaf_rn(a[4], b[4], e);
+    o = __fmaf_rn(a[5], b[5], o);
+    e = __fmaf_rn(a[6], b[6], e);
+    o = __fmaf_rn(a[7], b[7], o);
+    return __fadd_rn(e, o);
+}
+
+// Butterfly all-reduce over the 16 lanes of a half warp (strides 8,4,2,1).
+__device__ __forceinline__ float hw_sum(float p)
+{
+    p = __fadd_rn(p, __shfl_xor_sync(FULL, p, 8));
+    p = __fadd_rn(p, __shfl_xor_sync(FULL, p, 4));
+    p = __fadd_rn(p, __shfl_xor_sync(FULL, p, 2));
+    p = __fadd_rn(p, __shfl_xor_sync(FULL, p, 1));
+    return p;
+}
+__device__ __forceinline__ float hw_max(float p)
+{
+    p = fmaxf(p, __shfl_xor_sync(FULL, p, 8));
+    p = fmaxf(p, __shfl_xor_sync(FULL, p, 4));
+    p = fmaxf(p, __shfl_xor_sync(FULL, p, 2));
+    p = fmaxf(p, __shfl_xor_sync(FULL, p, 1));
+    return p;
+}
+// Butterfly all-reduce over a full warp (strides 16,8,4,2,1).
+__device__ __forceinline__ float warp_sum(float p)
+{
+    p = __fadd_rn(p, __shfl_xor_sync(FULL, p, 16));
+    return hw_sum(p);
+}
+__device__ __forceinline__ float warp_max(float p)
+{
+    p = fmaxf(p, __shfl_xor_sync(FULL, p, 16));
+    return hw_max(p);
+}
+
+// ------------------------------------------------------------------- loads
+
+template <typename T> struct Cvt;
+template <> struct Cvt<float> {
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct Cvt<__half> {
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Cvt<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// 8 consecutive elements of type T -> float[8] (16-byte or 32-byte vector loads).
+template <typename T>
+__device__ __forceinline__ void load8(const T *p, float (&out)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float *p, float (&out)[8])
+{
+    float4 a = *reinterpret_cast<const float4 *>(p);
+    float4 b = *reinterpret_cast<const float4 *>(p + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half *p, float (&out)[8])
+{
+    uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16 *p, float (&out)[8])
+{
+    uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const unsigned *w = reinterpret_cast<const unsigned *>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// Scalar read of q in its runtime dtype.
+__device__ __forceinline__ float load_q(const void *q, int dtype, long idx)
+{
+    if (dtype == CQA_F32) return reinterpret_cast<const float *>(q)[idx];
+    if (dtype == CQA_F16) return __half2float(reinterpret_cast<const __half *>(q)[idx]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(q)[idx]);
+}
+__device__ __forceinline__ void load_q8(const void *q, int dtype, long idx, float (&out)[8])
+{
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = load_q(q, dtype, idx + i);
+}
+
+// 8 signed bytes -> float[8]
+__device__ __forceinline__ void i8x8_to_f(uint2 w, float (&out)[8])
+{
+    const int8_t *b = reinterpret_cast<const int8_t *>(&w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = (float)b[i];
+}
+
+// ----------------------------------------------------------------- errors
+
+void set_error(const char *fmt, ...);
+int check_cuda(cudaError_t e, const char *what);
+int check_launch(const char *what);
+
+}  // namespace cqa

@@ -1,0 +1,77 @@
+// FP16-key block re-score and Delta bound, shared by the stand-alone entry
+// points and the certifier kernel.
+#pragma once
+#include "common.cuh"
+
+namespace cqa {
+
+// ------------------------------------------------------ FP16 block re-score
+
+// One warp scores one (head, block): 16 token logits from Tier-2 keys, then
+// m = max, logmass = m + log(max(sum exp(logit - m), 1e-30)).  Tokens with
+// block*16+t >= n_scoring_tokens, slot < 0 or slot row out of range are -inf.
+template <typename T2>
+__device__ __forceinline__ void fp16_block_score_warp(const cqa_cache &c, const void *q, int q_dtype, int h,
+                                                      long bid, long n_scoring_tokens, float q_scale,
+                                                      float &score_out, float &logmass_out)
+{
+    const int lane = threadIdx.x & 31, L = lane & 15, hw = lane >> 4;
+    const int kv = h / c.gqa_group;
+    const bool valid_block = bid >= 0 && bid * BS < n_scoring_tokens;
+    long slot = -1;
+    if (valid_block) slot = c.key_slots ? (long)c.key_slots[bid] : bid;
+    float qv[8];
+    load_q8(q, q_dtype, (long)h * D + 8 * L, qv);
+    const T2 *base = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
+    float lg[8];  // this half warp's tokens hw*8 .. hw*8+7 (all lanes hold all 8)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int t = hw * 8 + i;
+        const long ti = slot * BS + t;
+        const bool valid = valid_block && (bid * BS + t) < n_scoring_tokens && slot >= 0 && ti < c.keys_t2_rows;
+        float kf[8];
+        if (valid) load8<T2>(base + ti * D + 8 * L, kf);
+        else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) kf[k] = 0.0f;
+        }
+        float d = hw_sum(chain8(kf, qv));
+        lg[i] = valid ? __fmul_rn(d, q_scale) : -INFINITY;
+    }
+    float mx = lg[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) mx = fmaxf(mx, lg[i]);
+    mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, 16));
+    float e[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = lg[i] == -INFINITY ? 0.0f : cexp(__fsub_rn(lg[i], mx));
+    // butterfly over the 16 tokens: stride 8 pairs token i with i+8 (other half warp)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = __fadd_rn(e[i], __shfl_xor_sync(FULL, e[i], 16));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = __fadd_rn(e[i], e[i + 4]);
+    e[0] = __fadd_rn(e[0], e[2]);
+    e[1] = __fadd_rn(e[1], e[3]);
+    float l = fmaxf(__fadd_rn(e[0], e[1]), 1e-30f);
+    score_out = mx;
+    logmass_out = mx == -INFINITY ? -INFINITY : __fadd_rn(mx, clog(l));
+}
+
+// Delta[h] = dot(|q_h|, sigma_max[kv]) / (2 sqrt(128))
+__device__ __forceinline__ float delta_bound_warp(const cqa_cache &c, const void *q, int q_dtype, int h)
+{
+    const int L = threadIdx.x & 15;
+    const int kv = h / c.gqa_group;
+    float qa[8], sg[8];
+    load_q8(q, q_dtype, (long)h * D + 8 * L, qa);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        qa[i] = fabsf(qa[i]);
+        sg[i] = c.sigma_max[kv * D + 8 * L + i];
+    }
+    const float denom = 22.627416997969522f;  // 2*sqrt(128) rounded to binary32
+    return __fdiv_rn(hw_sum(chain8(qa, sg)), denom);
+}
+
+
+}  // namespace cqa

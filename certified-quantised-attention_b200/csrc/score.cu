@@ -1,0 +1,270 @@
+// Phase 1: per-block INT8 Q.K scores (m_b, S_b and the 16 token scores per
+// head), the FP16-key block re-score and the Delta bound.
+//
+// score_blocks_kernel: one CTA = (kv head, run of blocks); each half warp
+// owns one 16-token block at a time.  Lane L of the half warp owns channels
+// 8L..8L+7 with q*sigma for the G heads of the group in registers, so one
+// key byte feeds G fused multiply-adds.  Key rows, scales and zero points are
+// staged in shared memory by 16-byte asynchronous copies (warp-private double
+// buffer, no CTA barrier).  Lane L walks the tokens in the order j^L, which
+// makes the shared-memory reads conflict free and lets the 16-lane
+// reduce-scatter run without selects: afterwards lane L holds token L.
+//
+// Per token and head:  score = (dot(k_int8, q*sigma) + dot(q, zero)) * q_scale
+// with the canonical dot order (two chains per lane, butterfly 8,4,2,1).
+#include "common.cuh"
+#include "rescore.cuh"
+
+namespace cqa {
+
+constexpr int SCORE_WARPS = 8;
+constexpr int BLOCK_BYTES = BS * D;                       // 2048 INT8 key bytes
+constexpr int STAGE_HALF = BLOCK_BYTES + 2 * D * 4;       // + scale + zero point = 3072
+constexpr int STAGE_WARP = 2 * STAGE_HALF;                // two half warps
+constexpr int SCORE_SMEM = SCORE_WARPS * 2 * STAGE_WARP;  // double buffered: 98304
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
+{
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// Issue the copies of one warp stage: blocks b0 (lanes 0-15) and b0+1 (lanes 16-31).
+__device__ __forceinline__ void score_issue(const cqa_cache &c, int kv, long b_first, long b_end, char *stage,
+                                            int lane)
+{
+    // 6144 bytes = 384 chunks of 16 B; chunk i belongs to half (i / 192).
+#pragma unroll
+    for (int r = 0; r < 12; ++r) {
+        const int i = r * 32 + lane;
+        const int half = i / 192, j = i % 192;
+        const long b = b_first + half;
+        if (b < b_end) {
+            const char *src;
+            if (j < 128)
+                src = reinterpret_cast<const char *>(c.keys_int8) + ((long)kv * c.cap_tokens + b * BS) * D + j * 16;
+            else if (j < 160)
+                src = reinterpret_cast<const char *>(c.keys_scale + ((long)kv * c.max_blocks + b) * D) + (j - 128) * 16;
+            else
+                src = reinterpret_cast<const char *>(c.keys_zero_points + ((long)kv * c.max_blocks + b) * D) + (j - 160) * 16;
+            cp_async16(stage + half * STAGE_HALF + j * 16, src);
+        }
+    }
+    cp_async_commit();
+}
+
+template <int G>
+__global__ void __launch_bounds__(SCORE_WARPS * 32) score_blocks_kernel(cqa_cache c, const void *q, int q_dtype,
+                                                                       long nq, float q_scale, float *m_b,
+                                                                       float *s_b, long ld, float *tok,
+                                                                       int blocks_per_cta)
+{
+    extern __shared__ __align__(16) char smem[];
+    constexpr int GH = G >= 4 ? 4 : G;  // heads per register pass
+    const int kv = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int L = lane & 15, hw = lane >> 4;
+    const long b_begin = (long)blockIdx.x * blocks_per_cta;
+    const long b_end = min(nq, b_begin + (long)blocks_per_cta);
+    char *wbuf = smem + warp * 2 * STAGE_WARP;
+
+    // Blocks of this warp: b_begin + 2*(warp + 8*it) + hw
+    const long stride = 2 * SCORE_WARPS;
+    long b0 = b_begin + 2 * warp;
+    int stage = 0;
+    if (b0 < b_end) score_issue(c, kv, b0, b_end, wbuf, lane);
+
+    for (; b0 < b_end; b0 += stride) {
+        const long bn = b0 + stride;
+        if (bn < b_end) {
+            score_issue(c, kv, bn, b_end, wbuf + (stage ^ 1) * STAGE_WARP, lane);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        const long b = b0 + hw;
+        const bool live = b < b_end;
+        const char *kb = wbuf + stage * STAGE_WARP + hw * STAGE_HALF;
+        const float *sc = reinterpret_cast<const float *>(kb + BLOCK_BYTES);
+        const float *zp = sc + D;
+        float sg[8], zz[8];
+        if (live) {
+            load8<float>(sc + 8 * L, sg);
+            load8<float>(zp + 8 * L, zz);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { sg[i] = 0.0f; zz[i] = 0.0f; }
+        }
+#pragma unroll
+        for (int pass = 0; pass < G / GH; ++pass) {
+            float qs[GH][8], zq[GH];
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+                float qv[8];
+                load_q8(q, q_dtype, ((long)(kv * G + pass * GH + g)) * D + 8 * L, qv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) qs[g][i] = __fmul_rn(qv[i], sg[i]);
+                zq[g] = hw_sum(chain8(qv, zz));
+            }
+            float acc[GH][BS];
+#pragma unroll
+            for (int j = 0; j < BS; ++j) {
+                const int t = j ^ L;
+                float kf[8];
+                if (live) {
+                    uint2 w = *reinterpret_cast<const uint2 *>(kb + t * D + 8 * L);
+                    i8x8_to_f(w, kf);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) kf[i] = 0.0f;
+                }
+#pragma unroll
+                for (int g = 0; g < GH; ++g) acc[g][j] = chain8(kf, qs[g]);
+            }
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[g][j] = __fadd_rn(acc[g][j], __shfl_xor_sync(FULL, acc[g][j + 8], 8));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[g][j] = __fadd_rn(acc[g][j], __shfl_xor_sync(FULL, acc[g][j + 4], 4));
+#pragma unroll
+                for (int j = 0; j < 2; ++j) acc[g][j] = __fadd_rn(acc[g][j], __shfl_xor_sync(FULL, acc[g][j + 2], 2));
+                acc[g][0] = __fadd_rn(acc[g][0], __shfl_xor_sync(FULL, acc[g][1], 1));
+                const float score = __fmul_rn(__fadd_rn(acc[g][0], zq[g]), q_scale);
+                const float mx = hw_max(score);
+                const float e = cexp(__fsub_rn(score, mx));
+                const float ssum = hw_sum(e);
+                if (live) {
+                    const int gg = pass * GH + g;
+                    if (tok) tok[(((long)kv * nq + b) * G + gg) * BS + L] = score;
+                    if (L == 0) {
+                        const long o = (long)(kv * G + gg) * ld + b;
+                        m_b[o] = mx;
+                        s_b[o] = ssum;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        stage ^= 1;
+    }
+}
+
+template <typename T2>
+__global__ void __launch_bounds__(32) fp16_block_scores_kernel(cqa_cache c, const void *q, int q_dtype,
+                                                              const int32_t *idx, int K, long n_scoring_tokens,
+                                                              float q_scale, float *scores, float *logmass)
+{
+    const int h = blockIdx.y, kk = blockIdx.x;
+    float s, lm;
+    fp16_block_score_warp<T2>(c, q, q_dtype, h, (long)idx[h * K + kk], n_scoring_tokens, q_scale, s, lm);
+    if (threadIdx.x == 0) {
+        scores[h * K + kk] = s;
+        logmass[h * K + kk] = lm;
+    }
+}
+
+__global__ void __launch_bounds__(32) delta_bound_kernel(cqa_cache c, const void *q, int q_dtype, float *delta)
+{
+    float d = delta_bound_warp(c, q, q_dtype, blockIdx.x);
+    if (threadIdx.x == 0) delta[blockIdx.x] = d;
+}
+
+int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
+                        float *s_b, long ld, float *tok, cudaStream_t st)
+{
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    // two resident CTAs per SM; runs of blocks in multiples of 16 (one per half warp)
+    long target_ctas = (long)sm_count * 2;
+    long per_kv = (target_ctas + c->kv_heads - 1) / c->kv_heads;
+    long bpc = (nq + per_kv - 1) / per_kv;
+    bpc = ((bpc + 15) / 16) * 16;
+    if (bpc < 16) bpc = 16;
+    dim3 grid((unsigned)((nq + bpc - 1) / bpc), (unsigned)c->kv_heads);
+#define CQA_SCORE_LAUNCH(GV)                                                                                  \
+    do {                                                                                                      \
+        static bool attr_set = false;                                                                         \
+        if (!attr_set) {                                                                                      \
+            int rc = check_cuda(cudaFuncSetAttribute(score_blocks_kernel<GV>,                                 \
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SCORE_SMEM), \
+                                "cudaFuncSetAttribute(score_blocks_kernel)");                                 \
+            if (rc) return rc;                                                                                \
+            attr_set = true;                                                                                  \
+        }                                                                                                     \
+        score_blocks_kernel<GV><<<grid, SCORE_WARPS * 32, SCORE_SMEM, st>>>(*c, q, q_dtype, nq, q_scale, m_b, \
+                                                                            s_b, ld, tok, (int)bpc);          \
+    } while (0)
+    switch (c->gqa_group) {
+    case 1: CQA_SCORE_LAUNCH(1); break;
+    case 2: CQA_SCORE_LAUNCH(2); break;
+    case 4: CQA_SCORE_LAUNCH(4); break;
+    case 8: CQA_SCORE_LAUNCH(8); break;
+    default: set_error("score_blocks: unsupported gqa_group %d", c->gqa_group); return CQA_ERR_UNSUPPORTED;
+    }
+#undef CQA_SCORE_LAUNCH
+    return check_launch("score_blocks_kernel");
+}
+
+}  // namespace cqa
+
+using namespace cqa;
+
+extern "C" int cqa_score_blocks(const cqa_cache *c, const void *q, int q_dtype, int64_t nq, float q_scale,
+                                float *m_b, float *s_b, int64_t ld, float *token_scores, void *stream)
+{
+    if (!c || !q || !m_b || !s_b || !c->keys_int8 || !c->keys_scale || !c->keys_zero_points) {
+        set_error("cqa_score_blocks: NULL pointer");
+        return CQA_ERR_INVALID;
+    }
+    if (nq == 0) return CQA_OK;
+    if (nq < 0 || nq > c->max_blocks || nq * BS > c->cap_tokens || ld < nq) {
+        set_error("cqa_score_blocks: nq=%ld out of range (max_blocks=%ld, ld=%ld)", (long)nq, (long)c->max_blocks,
+                  (long)ld);
+        return CQA_ERR_INVALID;
+    }
+    if (q_dtype < 0 || q_dtype > 2) { set_error("cqa_score_blocks: unknown q dtype"); return CQA_ERR_INVALID; }
+    return score_blocks_launch(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, token_scores, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_fp16_block_scores(const cqa_cache *c, const void *q, int q_dtype, const int32_t *idx, int K,
+                                     int64_t n_scoring_blocks, float q_scale, float *scores, float *logmass,
+                                     void *stream)
+{
+    if (!c || !q || !idx || !scores || !logmass || !c->keys_t2) {
+        set_error("cqa_fp16_block_scores: NULL pointer");
+        return CQA_ERR_INVALID;
+    }
+    if (K <= 0) return CQA_OK;
+    const int H = c->kv_heads * c->gqa_group;
+    dim3 grid((unsigned)K, (unsigned)H);
+    cudaStream_t st = (cudaStream_t)stream;
+    const long nst = n_scoring_blocks * BS;
+    switch (c->t2_dtype) {
+    case CQA_F32: fp16_block_scores_kernel<float><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); break;
+    case CQA_F16: fp16_block_scores_kernel<__half><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); break;
+    case CQA_BF16: fp16_block_scores_kernel<__nv_bfloat16><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); break;
+    default: set_error("cqa_fp16_block_scores: unknown Tier-2 dtype"); return CQA_ERR_INVALID;
+    }
+    return check_launch("fp16_block_scores_kernel");
+}
+
+extern "C" int cqa_delta_bound(const cqa_cache *c, const void *q, int q_dtype, float *delta, void *stream)
+{
+    if (!c || !q || !delta || !c->sigma_max) { set_error("cqa_delta_bound: NULL pointer"); return CQA_ERR_INVALID; }
+    const int H = c->kv_heads * c->gqa_group;
+    delta_bound_kernel<<<H, 32, 0, (cudaStream_t)stream>>>(*c, q, q_dtype, delta);
+    return check_launch("delta_bound_kernel");
+}

@@ -1,0 +1,439 @@
+"""Tiered KV cache for certified decode attention, B200-native.
+
+Mirrors the public surface of the reference's
+`dotcache/kernels/tiered_kv_cache.py` (TieredKeyCacheLayer:29-132,
+from_fp16_cache:135-286, from_fp16_cache_int4v:289-405, append_token:545-708,
+create_tiered_cache*_from_model:1579-1701): same field names, shapes, dtypes
+and counters, so callers that read the tensors keep working.  All
+quantisation and append work runs in hand-written CUDA through the C ABI of
+libcqa_b200.so; there is no PyTorch or CPU compute path.
+
+Tier 1 (INT8 per-channel keys, INT4 per-group values) and Tier 2 (the
+model-dtype originals) both live in HBM: a B200 has room for the full-context
+originals, so `keys_fp16_gpu` / `values_fp16_gpu` are full mirrors addressed
+through identity slot tables.  A bounded hot tier (capacity smaller than the
+context) is not built yet and raises NotImplementedError.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from cqa_b200 import _lib
+
+BLOCK = 16
+HEAD_DIM = 128
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"{what} must be a CUDA tensor: this cache runs only on the GPU library "
+            "(libcqa_b200.so); there is no CPU fallback"
+        )
+
+
+@dataclass
+class TieredKeyCacheLayer:
+    """One layer's tiered cache (all KV heads)."""
+
+    keys_int8: torch.Tensor           # [kv, cap, 128] int8
+    keys_scale: torch.Tensor          # [kv, max_blocks, 128] f32
+    keys_zero_points: torch.Tensor    # [kv, max_blocks, 128] f32
+    correction: torch.Tensor          # [kv, max_blocks] f32
+    values_fp16: torch.Tensor | None  # [kv, cap, 128] model dtype (FP16-value caches only)
+    keys_fp16_cpu: torch.Tensor | None
+    kv_heads: int
+    num_tokens: int
+    head_dim: int
+    d_v: int
+    block_size: int
+    num_blocks: int
+    num_quantized_blocks: int = 0
+    _pagein_buffer: torch.Tensor | None = None
+    _keys_deq_f32: torch.Tensor | None = None
+    _values_f32: torch.Tensor | None = None
+    values_int4_packed: torch.Tensor | None = None   # [kv, cap, 64] u8
+    values_int4_scales: torch.Tensor | None = None   # [kv, cap, 8] f16
+    values_int4_zeros: torch.Tensor | None = None    # [kv, cap, 8] f16
+    values_int4_errors: torch.Tensor | None = None   # eta_b [kv, max_blocks] f32
+    values_int4_error_sums: torch.Tensor | None = None
+    values_int4_error_counts: torch.Tensor | None = None
+    values_int4_group_size: int = 16
+    defer_int4_append_quantization: bool = False
+    values_norm_max_per_block: torch.Tensor | None = None  # nu_b [kv, max_blocks] f32
+    values_fp16_cpu: torch.Tensor | None = None
+    values_fp16_gpu: torch.Tensor | None = None
+    fp16_value_cache_capacity: int | None = None
+    _fp16_value_resident: "OrderedDict[int, int]" = field(default_factory=OrderedDict)
+    _fp16_value_free_slots: list = field(default_factory=list)
+    static_resident_value_cache: bool = False
+    static_resident_value_prepare_bytes: int = 0
+    keys_fp16_gpu: torch.Tensor | None = None
+    fp16_key_cache_capacity: int | None = None
+    _fp16_key_resident: "OrderedDict[int, int]" = field(default_factory=OrderedDict)
+    _fp16_key_free_slots: list = field(default_factory=list)
+    static_resident_key_cache: bool = False
+    static_resident_key_prepare_bytes: int = 0
+    # Running per-channel max of keys_scale over quantised blocks, [kv, 128] f32
+    # (what compute_delta_bound reduces every step in the reference,
+    # certified_attention.py:938; here the quantisers maintain it).
+    keys_scale_max: torch.Tensor | None = None
+    gqa_group_hint: int = 1
+    _certified_workspace: dict = field(default_factory=dict, repr=False)
+
+    # ------------------------------------------------------------------ C ABI view
+
+    def _desc(self, gqa_group: int | None = None) -> _lib.CqaCache:
+        """The cqa_cache struct over this layer's tensors."""
+        d = _lib.CqaCache()
+        d.kv_heads = self.kv_heads
+        d.gqa_group = int(gqa_group if gqa_group is not None else self.gqa_group_hint)
+        t2 = self.keys_fp16_gpu
+        d.t2_dtype = _lib.dtype_code(t2.dtype) if t2 is not None else _lib.CQA_F16
+        d.cap_tokens = int(self.keys_int8.shape[1])
+        d.max_blocks = int(self.keys_scale.shape[1])
+        d.keys_int8 = _lib.ptr(self.keys_int8)
+        d.keys_scale = _lib.ptr(self.keys_scale)
+        d.keys_zero_points = _lib.ptr(self.keys_zero_points)
+        d.correction = _lib.ptr(self.correction)
+        d.sigma_max = _lib.ptr(self.keys_scale_max)
+        d.values_int4_packed = _lib.ptr(self.values_int4_packed)
+        d.values_int4_scales = _lib.ptr(self.values_int4_scales)
+        d.values_int4_zeros = _lib.ptr(self.values_int4_zeros)
+        d.values_int4_errors = _lib.ptr(self.values_int4_errors)
+        d.values_int4_error_sums = _lib.ptr(self.values_int4_error_sums)
+        d.values_int4_error_counts = _lib.ptr(self.values_int4_error_counts)
+        d.values_norm_max = _lib.ptr(self.values_norm_max_per_block)
+        d.keys_t2 = _lib.ptr(t2)
+        d.keys_t2_rows = int(t2.shape[1]) if t2 is not None else 0
+        vt2 = self.values_fp16 if self.values_fp16 is not None else self.values_fp16_gpu
+        d.values_t2 = _lib.ptr(vt2)
+        d.values_t2_rows = int(vt2.shape[1]) if vt2 is not None else 0
+        d.key_slots = None      # identity: full mirrors
+        d.value_slots = None
+        return d
+
+    # ------------------------------------------------------------------ construction
+
+    @classmethod
+    def _allocate(cls, keys: torch.Tensor, values: torch.Tensor, block_size: int, max_pagein_blocks: int,
+                  max_new_tokens: int, int4: bool, group_size: int) -> "TieredKeyCacheLayer":
+        _require_cuda(keys, "keys")
+        _require_cuda(values, "values")
+        if block_size != BLOCK:
+            raise ValueError("block_size must be 16 (fixed by the kernels)")
+        if int4 and group_size != 16:
+            raise ValueError("INT4 group_size must be 16 (fixed by the kernels)")
+        kv, N, hd = keys.shape
+        dv = values.shape[2]
+        if hd != HEAD_DIM or dv != HEAD_DIM:
+            raise ValueError(f"head_dim and d_v must be 128 (got {hd}, {dv})")
+        if N % BLOCK != 0:
+            raise ValueError("N must be block aligned; append the remainder with append_token")
+        if keys.dtype != values.dtype:
+            values = values.to(keys.dtype)
+        _lib.dtype_code(keys.dtype)
+        dev = keys.device
+        nb = N // BLOCK
+        cap = N + max_new_tokens
+        maxblk = nb + (max_new_tokens + BLOCK - 1) // BLOCK
+        kvd = keys.dtype
+        z = torch.zeros
+        self = cls(
+            keys_int8=z(kv, cap, hd, dtype=torch.int8, device=dev),
+            keys_scale=z(kv, maxblk, hd, dtype=torch.float32, device=dev),
+            keys_zero_points=z(kv, maxblk, hd, dtype=torch.float32, device=dev),
+            correction=torch.ones(kv, maxblk, dtype=torch.float32, device=dev),
+            values_fp16=None,
+            keys_fp16_cpu=None,
+            kv_heads=kv, num_tokens=N, head_dim=hd, d_v=dv, block_size=BLOCK, num_blocks=nb,
+            num_quantized_blocks=nb,
+            _pagein_buffer=torch.empty(max_pagein_blocks * BLOCK, hd, dtype=kvd, device=dev),
+            values_norm_max_per_block=z(kv, maxblk, dtype=torch.float32, device=dev),
+            keys_fp16_gpu=z(kv, cap, hd, dtype=kvd, device=dev),
+            keys_scale_max=z(kv, hd, dtype=torch.float32, device=dev),
+        )
+        vbuf = z(kv, cap, dv, dtype=kvd, device=dev)
+        if int4:
+            self.values_int4_packed = z(kv, cap, dv // 2, dtype=torch.uint8, device=dev)
+            self.values_int4_scales = z(kv, cap, dv // 16, dtype=torch.float16, device=dev)
+            self.values_int4_zeros = z(kv, cap, dv // 16, dtype=torch.float16, device=dev)
+            self.values_int4_errors = z(kv, maxblk, dtype=torch.float32, device=dev)
+            self.values_int4_error_sums = z(kv, maxblk, dtype=torch.float32, device=dev)
+            self.values_int4_error_counts = z(kv, maxblk, dtype=torch.int32, device=dev)
+            self.values_int4_group_size = 16
+            self.values_fp16_gpu = vbuf
+        else:
+            self.values_fp16 = vbuf
+        self._fp16_key_resident = OrderedDict((i, i) for i in range(nb))
+        return self
+
+    def _quantize_prefill(self, keys: torch.Tensor, values: torch.Tensor) -> None:
+        N = keys.shape[1]
+        if N == 0:
+            return
+        keys = keys.contiguous()
+        values = values.to(keys.dtype).contiguous()
+        with torch.cuda.device(keys.device):
+            rc = _lib.lib().cqa_quantize_blocks(
+                C.byref(self._desc()), keys.data_ptr(), values.data_ptr(), _lib.dtype_code(keys.dtype),
+                N, 0, N // BLOCK, _lib.current_stream(keys.device))
+        _lib.check(rc, "cqa_quantize_blocks")
+
+    @staticmethod
+    def _check_capacity(cap, max_blocks: int, what: str):
+        if cap is None:
+            return None
+        cap = max(int(cap), 0)
+        if cap < max_blocks:
+            raise NotImplementedError(
+                f"{what}={cap} is smaller than the reserved {max_blocks} blocks: the bounded hot tier "
+                "(LRU scratch with page-in) is not built yet; pass None (full HBM mirror) or a capacity "
+                "that covers the reserved context (static-resident)")
+        return cap
+
+    @classmethod
+    def from_fp16_cache(cls, keys_fp16: torch.Tensor, values_fp16: torch.Tensor, block_size: int = 16,
+                        max_pagein_blocks: int = 64, max_new_tokens: int = 512,
+                        fp16_key_cache_capacity: int | None = None) -> "TieredKeyCacheLayer":
+        """INT8 keys + model-dtype values (reference: tiered_kv_cache.py:135-286)."""
+        self = cls._allocate(keys_fp16, values_fp16, block_size, max_pagein_blocks, max_new_tokens,
+                             int4=False, group_size=16)
+        cap = cls._check_capacity(fp16_key_cache_capacity, self.keys_scale.shape[1], "fp16_key_cache_capacity")
+        self._quantize_prefill(keys_fp16, values_fp16)
+        if cap is not None:
+            self.fp16_key_cache_capacity = cap
+            self.static_resident_key_cache = True
+            self._fp16_key_resident = OrderedDict((i, i) for i in range(self.keys_scale.shape[1]))
+        return self
+
+    @classmethod
+    def from_fp16_cache_int4v(cls, keys_fp16: torch.Tensor, values_fp16: torch.Tensor, block_size: int = 16,
+                              group_size: int = 16, max_pagein_blocks: int = 64, max_new_tokens: int = 512,
+                              fp16_key_cache_capacity: int | None = None,
+                              fp16_value_cache_capacity: int | None = None,
+                              defer_int4_append_quantization: bool = False) -> "TieredKeyCacheLayer":
+        """INT8 keys + INT4 g16 values (reference: tiered_kv_cache.py:289-405)."""
+        self = cls._allocate(keys_fp16, values_fp16, block_size, max_pagein_blocks, max_new_tokens,
+                             int4=True, group_size=group_size)
+        maxblk = self.keys_scale.shape[1]
+        kcap = cls._check_capacity(fp16_key_cache_capacity, maxblk, "fp16_key_cache_capacity")
+        vcap = cls._check_capacity(fp16_value_cache_capacity, maxblk, "fp16_value_cache_capacity")
+        self.defer_int4_append_quantization = bool(defer_int4_append_quantization)
+        self._quantize_prefill(keys_fp16, values_fp16)
+        if kcap is not None:
+            self.fp16_key_cache_capacity = kcap
+            self.static_resident_key_cache = True
+            self._fp16_key_resident = OrderedDict((i, i) for i in range(maxblk))
+        if vcap is not None:
+            # A capacity that covers the reserved context is the reference's
+            # "static resident" mode, which also defers INT4 append
+            # quantisation to block completion (tiered_kv_cache.py:947-952).
+            self.fp16_value_cache_capacity = vcap
+            self.static_resident_value_cache = True
+            self.defer_int4_append_quantization = True
+            self._fp16_value_resident = OrderedDict((i, i) for i in range(maxblk))
+        return self
+
+    # ------------------------------------------------------------------ append
+
+    def append_token(self, key_fp16: torch.Tensor, value_fp16: torch.Tensor) -> None:
+        """Append one token ([kv, 1, 128] each); one fused kernel launch.
+
+        Reference: tiered_kv_cache.py:545-708 (append_token, _quantize_block,
+        _quantize_value_block)."""
+        pos = self.num_tokens
+        if pos >= self.keys_int8.shape[1]:
+            raise ValueError(
+                f"cache capacity {self.keys_int8.shape[1]} exhausted; build the cache with a larger max_new_tokens")
+        _require_cuda(key_fp16, "key")
+        k = key_fp16.reshape(self.kv_heads, self.head_dim)
+        v = value_fp16.reshape(self.kv_heads, self.d_v)
+        if v.dtype != k.dtype:
+            v = v.to(k.dtype)
+        k = k.contiguous()
+        v = v.contiguous()
+        defer = bool(
+            self.defer_int4_append_quantization
+            and self.values_fp16_gpu is not None
+            and (self.fp16_value_cache_capacity is None or self.static_resident_value_cache)
+        )
+        with torch.cuda.device(k.device):
+            rc = _lib.lib().cqa_append_token(
+                C.byref(self._desc()), k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype), pos,
+                1 if defer else 0, _lib.current_stream(k.device))
+        _lib.check(rc, "cqa_append_token")
+        self.num_tokens = pos + 1
+        self.num_blocks = (self.num_tokens + BLOCK - 1) // BLOCK
+        if pos % BLOCK == BLOCK - 1:
+            self.num_quantized_blocks = pos // BLOCK + 1
+
+    # ------------------------------------------------------------------ views / accounting
+
+    @property
+    def has_trailing_partial_block(self) -> bool:
+        return self.num_tokens > 0 and self.num_tokens % self.block_size != 0
+
+    @property
+    def trailing_block_idx(self) -> int | None:
+        return self.num_tokens // self.block_size if self.has_trailing_partial_block else None
+
+    @property
+    def active_tokens(self) -> int:
+        return self.num_tokens
+
+    @property
+    def aligned_tokens(self) -> int:
+        return ((self.num_tokens + self.block_size - 1) // self.block_size) * self.block_size
+
+    @property
+    def active_blocks(self) -> int:
+        return (self.num_tokens + self.block_size - 1) // self.block_size
+
+    def keys_int8_active(self) -> torch.Tensor:
+        return self.keys_int8[:, :self.aligned_tokens, :]
+
+    def keys_scale_active(self) -> torch.Tensor:
+        return self.keys_scale[:, :self.active_blocks, :]
+
+    def keys_zero_points_active(self) -> torch.Tensor:
+        return self.keys_zero_points[:, :self.active_blocks, :]
+
+    def correction_active(self) -> torch.Tensor:
+        return self.correction[:, :self.active_blocks]
+
+    def values_fp16_active(self):
+        return None if self.values_fp16 is None else self.values_fp16[:, :self.aligned_tokens, :]
+
+    def v_max_global(self) -> float:
+        if self.values_norm_max_per_block is None:
+            return 0.0
+        a = self.values_norm_max_per_block[:, :self.active_blocks]
+        return float(a.max().item()) if a.numel() else 0.0
+
+    def refresh_keys_scale_max(self) -> None:
+        """Recompute keys_scale_max from keys_scale (needed only after a caller
+        edits keys_scale by hand)."""
+        nq = self.num_quantized_blocks
+        if nq:
+            self.keys_scale_max.copy_(self.keys_scale[:, :nq].amax(dim=1))
+        else:
+            self.keys_scale_max.zero_()
+
+    def vram_bytes(self) -> int:
+        total = self.keys_int8.nelement()
+        total += self.keys_scale.nelement() * 4 + self.keys_zero_points.nelement() * 4
+        total += self.correction.nelement() * 4
+        if self.values_fp16 is not None:
+            total += self.values_fp16.nelement() * self.values_fp16.element_size()
+        if self._pagein_buffer is not None:
+            total += self._pagein_buffer.nelement() * self._pagein_buffer.element_size()
+        if self.values_int4_packed is not None:
+            total += self.values_int4_packed.nelement()
+            total += self.values_int4_scales.nelement() * 2 + self.values_int4_zeros.nelement() * 2
+            total += self.values_int4_errors.nelement() * 4
+            total += self.values_int4_error_sums.nelement() * 4
+            total += self.values_int4_error_counts.nelement() * 4
+        if self.values_fp16_gpu is not None:
+            total += self.values_fp16_gpu.nelement() * self.values_fp16_gpu.element_size()
+        if self.keys_fp16_gpu is not None:
+            total += self.keys_fp16_gpu.nelement() * self.keys_fp16_gpu.element_size()
+        return int(total)
+
+    def cpu_bytes(self) -> int:
+        total = 0
+        if self.keys_fp16_cpu is not None:
+            total += self.keys_fp16_cpu.nelement() * self.keys_fp16_cpu.element_size()
+        if self.values_fp16_cpu is not None:
+            total += self.values_fp16_cpu.nelement() * self.values_fp16_cpu.element_size()
+        return int(total)
+
+    def fp16_key_block_slots_gpu(self, n_blocks: int) -> torch.Tensor:
+        return self._identity_slots(n_blocks)
+
+    def fp16_value_block_slots_gpu(self, n_blocks: int) -> torch.Tensor:
+        return self._identity_slots(n_blocks)
+
+    def _identity_slots(self, n_blocks: int) -> torch.Tensor:
+        t = self._certified_workspace.get("identity_slots")
+        n = int(self.keys_scale.shape[1])
+        if t is None or t.numel() < n:
+            t = torch.arange(n, dtype=torch.int32, device=self.keys_int8.device)
+            self._certified_workspace["identity_slots"] = t
+        return t[: int(n_blocks)]
+
+    def dequantise_int4_values(self) -> torch.Tensor:
+        """All INT4 values as float32 [kv, cap, 128] (debug helper; torch ops)."""
+        p = self.values_int4_packed
+        lo = (p & 0x0F).to(torch.float32)
+        hi = ((p >> 4) & 0x0F).to(torch.float32)
+        codes = torch.stack([lo, hi], dim=-1).reshape(p.shape[0], p.shape[1], -1)
+        s = self.values_int4_scales.float().repeat_interleave(16, dim=-1)
+        z = self.values_int4_zeros.float().repeat_interleave(16, dim=-1)
+        return codes * s + z
+
+
+def _layer_kv(past_kv, layer_id: int):
+    if hasattr(past_kv, "layers"):
+        return past_kv.layers[layer_id].keys[0], past_kv.layers[layer_id].values[0]
+    return past_kv[layer_id][0][0], past_kv[layer_id][1][0]
+
+
+def _poison_padding(cache: TieredKeyCacheLayer) -> None:
+    at, nt = cache.aligned_tokens, cache.num_tokens
+    if at > nt:
+        cache.keys_int8[:, nt:at, :] = -127
+
+
+def create_tiered_cache_int4v_from_model(past_kv, layer_ids: list, block_size: int = 16, group_size: int = 16,
+                                         max_new_tokens: int = 512,
+                                         fp16_key_cache_capacity: int | None = None,
+                                         fp16_value_cache_capacity: int | None = None,
+                                         defer_int4_append_quantization: bool | None = None) -> dict:
+    """Per-layer INT8K/INT4V caches from HF past_key_values
+    (reference: tiered_kv_cache.py:1579-1641)."""
+    if defer_int4_append_quantization is None:
+        defer_int4_append_quantization = fp16_value_cache_capacity is None
+    caches = {}
+    for layer_id in layer_ids:
+        keys, values = _layer_kv(past_kv, layer_id)
+        seq_len = keys.shape[1]
+        aligned = (seq_len // block_size) * block_size
+        cache = TieredKeyCacheLayer.from_fp16_cache_int4v(
+            keys[:, :aligned, :].contiguous(), values[:, :aligned, :].contiguous(),
+            block_size=block_size, group_size=group_size,
+            max_new_tokens=max_new_tokens + (seq_len - aligned),
+            fp16_key_cache_capacity=fp16_key_cache_capacity,
+            fp16_value_cache_capacity=fp16_value_cache_capacity,
+            defer_int4_append_quantization=bool(defer_int4_append_quantization),
+        )
+        for t in range(aligned, seq_len):
+            cache.append_token(keys[:, t:t + 1, :], values[:, t:t + 1, :])
+        _poison_padding(cache)
+        caches[layer_id] = cache
+    return caches
+
+
+def create_tiered_cache_from_model(past_kv, layer_ids: list, block_size: int = 16, max_new_tokens: int = 512,
+                                   fp16_key_cache_capacity: int | None = None) -> dict:
+    """Per-layer INT8-key / model-dtype-value caches (reference: tiered_kv_cache.py:1644-1701)."""
+    caches = {}
+    for layer_id in layer_ids:
+        keys, values = _layer_kv(past_kv, layer_id)
+        seq_len = keys.shape[1]
+        aligned = (seq_len // block_size) * block_size
+        cache = TieredKeyCacheLayer.from_fp16_cache(
+            keys[:, :aligned, :].contiguous(), values[:, :aligned, :].contiguous(),
+            block_size=block_size, max_new_tokens=max_new_tokens + (seq_len - aligned),
+            fp16_key_cache_capacity=fp16_key_cache_capacity,
+        )
+        for t in range(aligned, seq_len):
+            cache.append_token(keys[:, t:t + 1, :], values[:, t:t + 1, :])
+        _poison_padding(cache)
+        caches[layer_id] = cache
+    return caches

@@ -1,0 +1,252 @@
+/*
+ * cqa_b200 — C ABI of the B200 (sm_100a) certified quantised decode-attention path.
+ *
+ * One shared library, `extern "C"`, plain pointers and sizes.  Unless a
+ * parameter is documented as host memory, every pointer is a DEVICE pointer.
+ * Every call that launches work takes a `cudaStream_t` passed as `void*`
+ * (NULL = legacy default stream), returns 0 on success or a negative
+ * `cqa_status`, never throws and never allocates or frees device memory:
+ * all buffers, including scratch, belong to the caller.
+ *
+ * Geometry is fixed to what the reference's native kernels hard-wire
+ * (dotcache/backends/cuda_kernels/certified_blackwell.cpp:110,226): head_dim =
+ * d_v = 128, 16 tokens per block ("page"), INT4 group size 16.  gqa_group may
+ * be 1, 2, 4 or 8.
+ *
+ * Citations below name the reference interface each entry point replaces, as
+ * file:line inside the reference project (DeanoC/certified-quantised-attention).
+ */
+#ifndef CQA_B200_H
+#define CQA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CQA_HEAD_DIM 128
+#define CQA_BLOCK 16
+#define CQA_GROUP 16
+#define CQA_NGROUPS 8
+#define CQA_MAX_RANKING_K 32
+#define CQA_MAX_SORT_BLOCKS 16384 /* selector limit: quantised blocks per call */
+
+typedef enum cqa_status {
+    CQA_OK = 0,
+    CQA_ERR_INVALID = -1,   /* bad argument (NULL pointer, unsupported size or dtype) */
+    CQA_ERR_CUDA = -2,      /* a CUDA runtime call failed; see cqa_last_error() */
+    CQA_ERR_UNSUPPORTED = -3,
+    CQA_ERR_TOO_LARGE = -4, /* request exceeds a documented limit */
+    CQA_ERR_TIMEOUT = -5    /* a bounded device-side wait ran out */
+} cqa_status;
+
+typedef enum cqa_dtype { CQA_F32 = 0, CQA_F16 = 1, CQA_BF16 = 2 } cqa_dtype;
+
+/* One layer's cache arrays (the fields of the reference's TieredKeyCacheLayer,
+ * dotcache/kernels/tiered_kv_cache.py:29-132).  Row-major; `cap_tokens` and
+ * `max_blocks` are the per-KV-head strides (in token rows / blocks) so the
+ * active prefix is addressed in place, without copies. */
+typedef struct cqa_cache {
+    int32_t kv_heads;
+    int32_t gqa_group;
+    int32_t t2_dtype;                /* cqa_dtype of keys_t2 / values_t2 */
+    int32_t reserved;
+    int64_t cap_tokens;              /* rows per KV head in the per-token arrays */
+    int64_t max_blocks;              /* blocks per KV head in the per-block arrays */
+    int8_t *keys_int8;               /* [KV][cap][128] */
+    float *keys_scale;               /* [KV][max_blocks][128] */
+    float *keys_zero_points;         /* [KV][max_blocks][128] */
+    float *correction;               /* [KV][max_blocks] */
+    float *sigma_max;                /* [KV][128] running max of keys_scale over quantised blocks */
+    uint8_t *values_int4_packed;     /* [KV][cap][64], low nibble = even channel */
+    uint16_t *values_int4_scales;    /* [KV][cap][8] IEEE half bits */
+    uint16_t *values_int4_zeros;     /* [KV][cap][8] IEEE half bits */
+    float *values_int4_errors;       /* eta_b [KV][max_blocks] */
+    float *values_int4_error_sums;   /* [KV][max_blocks] */
+    int32_t *values_int4_error_counts; /* [KV][max_blocks] */
+    float *values_norm_max;          /* nu_b [KV][max_blocks] */
+    void *keys_t2;                   /* Tier-2 keys, [KV][keys_t2_rows][128] of t2_dtype */
+    int64_t keys_t2_rows;
+    void *values_t2;                 /* Tier-2 values, [KV][values_t2_rows][128] */
+    int64_t values_t2_rows;
+    const int32_t *key_slots;        /* block -> 16-row slot in keys_t2; NULL = identity */
+    const int32_t *value_slots;      /* block -> slot in values_t2; NULL = identity */
+} cqa_cache;
+
+/* Certification knobs (the keyword arguments of certified_attention_layer,
+ * dotcache/kernels/certified_attention.py:1065-1097). */
+typedef struct cqa_knobs {
+    float q_scale;
+    float tau_cov;
+    float rung1_threshold;       /* < 0 disables Rung-1 expansion */
+    float rung1_multiplier;
+    float eps_guard;
+    float exploration_rate;
+    float v_tolerance;
+    int32_t k_min;
+    int32_t k_max;               /* <= 0: no cap */
+    int32_t ranking_r;
+    int32_t top_k_fp16_keys;
+    int32_t ranking_fallback;    /* bool */
+    int32_t rung3_recompute;     /* bool: ranking_fallback_mode == "full" */
+    int32_t score_consistency;   /* bool */
+    int32_t value_mode_tight;    /* bool: "tight" (1) or "loose" (0) */
+    int32_t force_trailing_value_fp16; /* bool */
+} cqa_knobs;
+
+/* Per-head results of selection and certification (device memory, one per q head). */
+typedef struct cqa_head_cert {
+    int32_t k_star;
+    int32_t k_star_base;
+    int32_t k_star_expanded;
+    int32_t rung1_triggered;
+    int32_t exploration_blocks;
+    int32_t ranking_disagree;    /* top-r ranking disagreement (before the boundary check) */
+    int32_t ranking_disagree_r1;
+    int32_t ranking_disagree_r3;
+    int32_t boundary_triggered;
+    int32_t rung3;               /* ranking_disagree | boundary_triggered */
+    int32_t consistency_violation;
+    int32_t value_promoted_blocks;
+    int32_t dense;               /* this head's output comes from the dense FP16 recompute */
+    int32_t reserved[3];
+    float tail_mass;
+    float tau_actual;
+    float m_global;
+    float total_mass;
+    float delta;
+    float e_pre;
+    float e_val;
+    float boundary_ub;           /* max over tail blocks of ell_int8 + delta */
+    float ell_fp16_r;            /* r-th largest FP16 log-mass among the re-scored blocks */
+    float fp16_top1;             /* largest FP16 block score */
+    float fp16_top2;
+    float int8_top1;             /* m_b of the best INT8 block */
+    int32_t top_blocks[CQA_MAX_RANKING_K];
+    float fp16_scores[CQA_MAX_RANKING_K];
+    float fp16_logmass[CQA_MAX_RANKING_K];
+} cqa_head_cert;
+
+/* Caller-owned scratch and outputs of one layer step.  H = kv_heads*gqa_group,
+ * nq = fully quantised blocks, nact = active blocks (nq or nq+1),
+ * ld = leading dimension (>= nact) of the [H][ld] arrays. */
+typedef struct cqa_workspace {
+    int64_t ld;
+    float *m_b;                  /* [H][ld] */
+    float *s_b;                  /* [H][ld] */
+    float *token_scores;         /* [KV][nq][G][16] */
+    float *mass_frac;            /* [H][ld] */
+    uint8_t *topk_mask;          /* [H][ld] 1 = FP16 keys for this (head, block) */
+    uint8_t *value_mask;         /* [H][ld] 1 = FP16 values */
+    uint8_t *explore_mask;       /* [H][ld] */
+    int32_t *sorted_idx;         /* [H][sel_width] */
+    float *sorted_cumsum;        /* [H][sel_width] */
+    int32_t sel_width;           /* >= min(expanded k_max, nq); ignored if k_max <= 0 (then ld) */
+    int32_t num_splits;          /* Phase-2 splits per KV head */
+    int32_t dense_splits;        /* dense recompute splits per head */
+    int32_t reserved;
+    float *part_m;               /* [H][num_splits] */
+    float *part_l;               /* [H][num_splits] */
+    float *part_acc;             /* [H][num_splits][128] */
+    float *dense_m;              /* [H][dense_splits] */
+    float *dense_l;
+    float *dense_acc;            /* [H][dense_splits][128] */
+    cqa_head_cert *cert;         /* [H] */
+    int32_t *any_flags;          /* [4]: any rung1, any rung3, any rung4 (violation), any value promotion */
+    float *out;                  /* [H][128] float32 */
+} cqa_workspace;
+
+const char *cqa_version(void);
+/* Text of the last error on the calling thread (host memory, valid until the next call). */
+const char *cqa_last_error(void);
+
+/* Quantise `n_blocks` complete blocks starting at block `first_block` from
+ * K/V in `src_dtype` ([KV][src_rows][128], token 0 of the source = token
+ * first_block*16 of the cache): INT8 keys (scale, zero point, correction,
+ * sigma_max), INT4 values (packed, scales, zeros, eta_b = max over the block,
+ * error sums/counts), nu_b, and copies the rows into the Tier-2 arrays
+ * (converted to t2_dtype).  Replaces TieredKeyCacheLayer.from_fp16_cache /
+ * from_fp16_cache_int4v (tiered_kv_cache.py:135-405) and
+ * quantise_int4_grouped_block (int4_group_quantise.py:123-151). */
+int cqa_quantize_blocks(const cqa_cache *c, const void *k_src, const void *v_src, int src_dtype,
+                        int64_t src_rows, int64_t first_block, int64_t n_blocks, void *stream);
+
+/* Fused append-and-quantise of one token at position `pos` for every KV head:
+ * Tier-2 rows, nu_b, per-token INT4 (unless `defer_int4`), and, when the token
+ * completes a block, the block's INT8 keys and (deferred) INT4 values with
+ * eta_b = mean of the 16 token errors; poisons the unused INT8 rows of a newly
+ * opened block with -127.  k_new/v_new: [KV][128] of `src_dtype`.
+ * Replaces TieredKeyCacheLayer.append_token / _quantize_block /
+ * _quantize_value_block (tiered_kv_cache.py:545-708, 480-543, 407-453). */
+int cqa_append_token(const cqa_cache *c, const void *k_new, const void *v_new, int src_dtype,
+                     int64_t pos, int defer_int4, void *stream);
+
+/* Per-token per-group INT4 quantisation of x [T][128] (src_dtype): packed
+ * [T][64], scales/zeros [T][8] half, rel_err/abs_err [T] float32.
+ * Replaces quantise_int4_grouped (int4_group_quantise.py:22-88). */
+int cqa_int4_quantise(const void *x, int src_dtype, int64_t T, uint8_t *packed, uint16_t *scales,
+                      uint16_t *zeros, float *rel_err, float *abs_err, void *stream);
+
+/* Phase 1: m_b, S_b [H][ld] for blocks [0, nq) and, if token_scores != NULL,
+ * the 16 token scores per (kv, block, head).  q: [H][128] of q_dtype.
+ * Replaces score_blocks_cuda (backends/certified_blackwell.py:64-87) and
+ * fused_score_certify_multihead (kernels/fused_score_certify.py:398-456). */
+int cqa_score_blocks(const cqa_cache *c, const void *q, int q_dtype, int64_t nq, float q_scale,
+                     float *m_b, float *s_b, int64_t ld, float *token_scores, void *stream);
+
+/* Adaptive top-K* selection with the Rung-1 expansion and the exploration
+ * draw: fills mass_frac, sorted_idx, sorted_cumsum, topk_mask (blocks >= nq up
+ * to nact are forced to 1), explore_mask and the selection fields of cert[].
+ * exploration_u: [H][u_ld] uniforms in [0,1) or NULL.
+ * Replaces adaptive_topk_cuda (backends/certified_blackwell.py:90-107),
+ * compute_adaptive_topk_mask and augment_mask_with_exploration
+ * (kernels/certified_attention.py:245-444, 882-909, 1299-1535). */
+int cqa_select(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, int64_t nq,
+               int64_t nact, const float *exploration_u, int64_t u_ld, void *stream);
+
+/* FP16-key block re-score: scores/logmass [H][K] for block ids idx [H][K].
+ * Replaces fp16_block_scores_triton (kernels/fp16_block_scores_triton.py:73-146). */
+int cqa_fp16_block_scores(const cqa_cache *c, const void *q, int q_dtype, const int32_t *idx, int K,
+                          int64_t n_scoring_blocks, float q_scale, float *scores, float *logmass,
+                          void *stream);
+
+/* Delta[h] = sum_c |q[h][c]| * sigma_max[kv(h)][c] / (2*sqrt(128)).
+ * Replaces compute_delta_bound (kernels/certified_attention.py:912-945) with
+ * sigma_max maintained by the quantisers. */
+int cqa_delta_bound(const cqa_cache *c, const void *q, int q_dtype, float *delta, void *stream);
+
+/* Ranking / boundary / score-consistency checks and the Rung-2 value check:
+ * fills the certificate fields of cert[], value_mask and any_flags.  Must run
+ * after cqa_select on the same workspace.
+ * Replaces certified_attention.py:1563-1727 and :1940-2034. */
+int cqa_certify(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *q,
+                int q_dtype, int64_t nq, int64_t nact, void *stream);
+
+/* Phase 2: mixed INT8/FP16-key, INT4/FP16-value split-K attend over blocks
+ * [0, nact) with `last_block_valid` valid tokens in the last block, the dense
+ * FP16 recompute of heads whose cert[h].dense is set, and the LSE merge into
+ * ws->out.  INT8 blocks reuse ws->token_scores.
+ * Replaces hybrid_mixedv_split_k_cuda (backends/certified_blackwell.py:138-224),
+ * selective_attend_multihead_hybrid_{int4v,mixedv,mixedv_split_k}
+ * (kernels/selective_attend_triton.py:633-708, 1448-1576),
+ * recompute_heads_dense_fp16 and sdpa_attend_with_skip
+ * (kernels/certified_attention.py:789-879, 989-1062). */
+int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,
+               int64_t nact, int64_t num_tokens, int last_block_valid, float q_scale, void *stream);
+
+/* The whole per-layer chain on one stream: score -> select -> certify ->
+ * attend.  No host synchronisation; results stay on the device.
+ * Replaces certified_attention_layer (kernels/certified_attention.py:1065-2790)
+ * for the adaptive-K*, INT4-value configuration. */
+int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *q,
+                   int q_dtype, int64_t num_tokens, int64_t nq, const float *exploration_u,
+                   int64_t u_ld, void *stream);
+
+/* Suggested split counts for a context of `nact` blocks on the current device. */
+int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int *num_splits, int *dense_splits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CQA_B200_H */

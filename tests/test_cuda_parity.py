@@ -1,0 +1,257 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle on
+the same seeded inputs, and against the golden vectors from the reference."""
+from __future__ import annotations
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import golden_cases as gc
+from cqa_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    import cuda_harness as hz
+    from oracle import cqa_oracle as orc
+    from test_oracle_golden import check_cache_snapshot, check_call
+
+
+def _knobs(**over):
+    k = dict(gc.PAPER_KNOBS)
+    k.update(over)
+    return k
+
+
+def _oracle_knobs(knobs, u):
+    k = dict(knobs)
+    k["exploration_u"] = u
+    return k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+def test_prefill_quantisation_bit_exact(dtype):
+    base = synth.make_layer_inputs(101, 2048, kv_heads=2, gqa_group=4, dtype=dtype)
+    cc = hz.make_cuda_cache(base.k, base.v, dtype, 64)
+    oc = hz.make_oracle_cache(base.k, base.v, dtype, 64)
+    hz.compare_caches(cc, oc, f"prefill[{dtype}]")
+
+
+@pytest.mark.parametrize("dtype,defer", [("bfloat16", True), ("float16", False), ("float32", True)])
+def test_append_sequence_bit_exact(dtype, defer):
+    base = synth.make_layer_inputs(102, 512, kv_heads=3, gqa_group=2, dtype=dtype)
+    cc = hz.make_cuda_cache(base.k, base.v, dtype, 64, defer=defer)
+    oc = hz.make_oracle_cache(base.k, base.v, dtype, 64, defer=defer)
+    for step in range(37):
+        _, kn, vn = synth.decode_step_inputs(base, step, dtype=dtype)
+        cc.append_token(hz.to_dev(kn, dtype), hz.to_dev(vn, dtype))
+        oc.append_token(kn, vn)
+        if step in (0, 4, 15, 16, 31, 36):
+            torch.cuda.synchronize()
+            hz.compare_caches(cc, oc, f"append[{dtype},defer={defer}] step {step}")
+    with pytest.raises(ValueError):
+        for _ in range(64):
+            cc.append_token(hz.to_dev(kn, dtype), hz.to_dev(vn, dtype))
+
+
+def test_empty_prefill_then_appends():
+    """A cache that starts empty: every block arrives through append_token."""
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(103, 16, kv_heads=2, gqa_group=4, dtype=dtype)
+    cc = hz.make_cuda_cache(base.k[:, :0], base.v[:, :0], dtype, 80)
+    oc = hz.make_oracle_cache(base.k[:, :0], base.v[:, :0], dtype, 80)
+    knobs = _knobs(exploration_rate=0.0)
+    for step in range(50):
+        q, kn, vn = synth.decode_step_inputs(base, step, dtype=dtype)
+        cc.append_token(hz.to_dev(kn, dtype), hz.to_dev(vn, dtype))
+        oc.append_token(kn, vn)
+        if step in (15, 16, 30, 31, 47, 49):   # nq = 1, 1, 1, 2, 3, 3 with trailing 0,1,15,0,0,2
+            hz.compare_caches(cc, oc, f"step {step}")
+            R = orc.layer_step(oc, q, 4, **_oracle_knobs(knobs, None))
+            out, _ = hz.cuda_step(cc, q, dtype, 4, knobs)
+            hz.compare_step(cc, R, out, f"empty-start step {step}")
+
+
+@pytest.mark.parametrize("name", gc.available(gc.SMALL_CASES + gc.LARGE_CASES))
+def test_golden_case_cuda(name):
+    """CUDA against the oracle (bit-exact) and against the reference's stored results."""
+    spec, z = gc.load(name)
+    H = spec["kv_heads"] * spec["gqa_group"]
+    dtype = spec["dtype"]
+    oracle_cache = {}
+
+    def mk(k, v, dt, max_new):
+        oracle_cache["c"] = hz.make_oracle_cache(k, v, dt, max_new)
+        return hz.make_cuda_cache(k, v, dt, max_new)
+
+    def app(cache, k, v):
+        cache.append_token(hz.to_dev(k, dtype), hz.to_dev(v, dtype))
+        oracle_cache["c"].append_token(k, v)
+
+    def call(cache, q, target, knobs):
+        oc = oracle_cache["c"]
+        hz.compare_caches(cache, oc, f"{name} call{target}")
+        check_cache_snapshot(oc, z, f"call{target}/cache")
+        u = gc.exploration_uniforms(spec, target, H, cache.num_quantized_blocks)
+        R = orc.layer_step(oc, q, spec["gqa_group"], **_oracle_knobs(knobs, u))
+        out, stats = hz.cuda_step(cache, q, dtype, spec["gqa_group"], knobs, u)
+        hz.compare_step(cache, R, out, f"{name} call{target}")
+        # the oracle result is itself pinned to the reference's golden values
+        check_call(R, z, f"call{target}", H, cache.num_quantized_blocks, cache.active_blocks)
+        ref_stats = json.loads(str(z[f"call{target}/stats"]))
+        for key in ("k_star_min", "k_star_max", "rung1_fired", "rung2_fired", "rung3_fired", "rung4_fired",
+                    "v_format", "exploration_blocks", "skipped_blocks", "attended_blocks", "total_blocks",
+                    "rung1_triggered_heads", "ranking_k", "boundary_check_triggered_heads"):
+            if key in ref_stats:
+                assert stats[key] == ref_stats[key], f"stats[{key}]: {stats[key]} vs reference {ref_stats[key]}"
+        for key in ("value_fallback_blocks", "value_fallback_head_blocks"):
+            assert stats.get(key, 0) == ref_stats.get(key, 0), key
+        ref_out = z[f"call{target}/output"].astype(np.float64)
+        scale = np.abs(ref_out).max(axis=1, keepdims=True)
+        assert np.all(np.abs(out - ref_out) <= hz.OUT_RTOL * scale), "output vs reference out of tolerance"
+        return R
+
+    for target, cache, R in gc.replay(spec, mk, app, call):
+        pass
+
+
+@pytest.mark.parametrize("n_tokens,planted,dtype,seed", [
+    (32768 + 5, 64, "bfloat16", 7),      # the 32K single-GPU configuration plus a trailing partial block
+    (16384, 0, "float16", 8),            # diffuse attention: K* pinned, nearly every value block promoted
+])
+def test_layer_step_vs_oracle_large(n_tokens, planted, dtype, seed):
+    base = synth.make_layer_inputs(seed, n_tokens, dtype=dtype, n_planted_blocks=planted)
+    aligned = (n_tokens // 16) * 16
+    cc = hz.make_cuda_cache(base.k[:, :aligned], base.v[:, :aligned], dtype, 64)
+    oc = hz.make_oracle_cache(base.k[:, :aligned], base.v[:, :aligned], dtype, 64)
+    for t in range(aligned, n_tokens):
+        cc.append_token(hz.to_dev(base.k[:, t:t + 1], dtype), hz.to_dev(base.v[:, t:t + 1], dtype))
+        oc.append_token(base.k[:, t:t + 1], base.v[:, t:t + 1])
+    hz.compare_caches(cc, oc, "large prefill")
+    rng = np.random.default_rng(seed)
+    u = rng.random((32, oc.num_quantized_blocks), dtype=np.float32)
+    knobs = _knobs()
+    R = orc.layer_step(oc, base.q, 4, **_oracle_knobs(knobs, u))
+    out, stats = hz.cuda_step(cc, base.q, dtype, 4, knobs, u)
+    err = hz.compare_step(cc, R, out, f"large N={n_tokens}")
+    print(f"N={n_tokens} planted={planted}: k*={stats['k_star_mean']:.1f} rung1={stats['rung1_triggered_heads']} "
+          f"value_fallback_blocks={stats.get('value_fallback_blocks', 0)} out_err={err:.2e}")
+
+
+def test_decode_loop_bit_exact_selections():
+    """48 decode steps (3 block completions) at 4K context: every step's
+    selections, flags and appended bytes match the oracle."""
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(9, 4096, dtype=dtype, n_planted_blocks=16)
+    cc = hz.make_cuda_cache(base.k, base.v, dtype, 64)
+    oc = hz.make_oracle_cache(base.k, base.v, dtype, 64)
+    knobs = _knobs()
+    rng = np.random.default_rng(9)
+    for step in range(48):
+        q, kn, vn = synth.decode_step_inputs(base, step, dtype=dtype)
+        cc.append_token(hz.to_dev(kn, dtype), hz.to_dev(vn, dtype))
+        oc.append_token(kn, vn)
+        u = rng.random((32, oc.num_quantized_blocks), dtype=np.float32)
+        R = orc.layer_step(oc, q, 4, **_oracle_knobs(knobs, u))
+        out, _ = hz.cuda_step(cc, q, dtype, 4, knobs, u, collect_stats=(step % 8 == 0))
+        hz.compare_step(cc, R, out, f"decode step {step}")
+    hz.compare_caches(cc, oc, "after decode loop")
+
+
+def test_rung3_dense_recompute():
+    """ranking_r=4 makes INT8/FP16 ranking disagreements common: the flagged
+    heads must come from the dense FP16 recompute, the others from Phase 2."""
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(10, 4096 + 7, dtype=dtype)
+    al = 4096
+    cc = hz.make_cuda_cache(base.k[:, :al], base.v[:, :al], dtype, 32)
+    oc = hz.make_oracle_cache(base.k[:, :al], base.v[:, :al], dtype, 32)
+    for t in range(al, al + 7):
+        cc.append_token(hz.to_dev(base.k[:, t:t + 1], dtype), hz.to_dev(base.v[:, t:t + 1], dtype))
+        oc.append_token(base.k[:, t:t + 1], base.v[:, t:t + 1])
+    knobs = _knobs(ranking_r=4, exploration_rate=0.0)
+    R = orc.layer_step(oc, base.q, 4, **_oracle_knobs(knobs, None))
+    assert R["rung3_heads"].size > 0, "test needs at least one flagged head"
+    assert R["rung3_heads"].size < 32
+    out, stats = hz.cuda_step(cc, base.q, dtype, 4, knobs)
+    hz.compare_step(cc, R, out, "rung3")
+    assert stats["rung3_fired"] and stats["ranking_fallback_triggered"] == R["rung3_heads"].size
+    # "measure" mode detects but does not recompute
+    knobs_m = _knobs(ranking_r=4, exploration_rate=0.0, ranking_fallback_mode="measure")
+    Rm = orc.layer_step(oc, base.q, 4, **_oracle_knobs(knobs_m, None))
+    outm, statsm = hz.cuda_step(cc, base.q, dtype, 4, knobs_m)
+    hz.compare_step(cc, Rm, outm, "rung3-measure")
+    assert not statsm["rung3_fired"]
+
+
+def test_rung4_dense_for_all_heads():
+    """A negative eps_guard makes the score-consistency check fail on every
+    head (host-side fault injection): all heads are recomputed densely."""
+    dtype = "float16"
+    base = synth.make_layer_inputs(11, 2048, dtype=dtype)
+    cc = hz.make_cuda_cache(base.k, base.v, dtype, 32)
+    oc = hz.make_oracle_cache(base.k, base.v, dtype, 32)
+    knobs = _knobs(eps_guard=-10.0)
+    u = np.random.default_rng(1).random((32, 128), dtype=np.float32)
+    R = orc.layer_step(oc, base.q, 4, **_oracle_knobs(knobs, u))
+    assert R["rung4"]
+    out, stats = hz.cuda_step(cc, base.q, dtype, 4, knobs, u)
+    hz.compare_step(cc, R, out, "rung4")
+    assert stats["rung4_fired"] is True and stats["v_format"] == "fp16" and stats["rung3_fired"] is False
+
+
+def test_loose_value_mode_and_no_ranking():
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(12, 3072, dtype=dtype, n_planted_blocks=8)
+    cc = hz.make_cuda_cache(base.k, base.v, dtype, 32)
+    oc = hz.make_oracle_cache(base.k, base.v, dtype, 32)
+    for kn in (_knobs(value_error_mode="loose", v_tolerance=0.07),
+               _knobs(ranking_fallback=False, score_consistency_check=False),
+               _knobs(k_max=None, rung1_threshold=0.02),
+               _knobs(k_max=16, k_min=4, rung1_multiplier=3.0, tau_cov=0.9)):
+        u = np.random.default_rng(2).random((32, 192), dtype=np.float32)
+        R = orc.layer_step(oc, base.q, 4, **_oracle_knobs(kn, u))
+        out, _ = hz.cuda_step(cc, base.q, dtype, 4, kn, u)
+        hz.compare_step(cc, R, out, f"knobs {kn}")
+
+
+def test_no_stats_path_returns_same_output():
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(13, 2048 + 3, dtype=dtype, n_planted_blocks=8)
+    cc = hz.make_cuda_cache(base.k[:, :2048], base.v[:, :2048], dtype, 32)
+    for t in range(2048, 2051):
+        cc.append_token(hz.to_dev(base.k[:, t:t + 1], dtype), hz.to_dev(base.v[:, t:t + 1], dtype))
+    knobs = _knobs(exploration_rate=0.0)
+    out1, stats = hz.cuda_step(cc, base.q, dtype, 4, knobs, collect_stats=True)
+    out2, empty = hz.cuda_step(cc, base.q, dtype, 4, knobs, collect_stats=False)
+    assert empty == {} and np.array_equal(out1, out2)
+    timings = {}
+    out3, _ = hz.cuda_step(cc, base.q, dtype, 4, dict(knobs, phase_timings=timings), collect_stats=False)
+    assert np.array_equal(out1, out3)
+    assert {"phase1_int8_scoring_us", "adaptive_selection_us", "ranking_check_us", "phase2_fused_attend_us"} <= set(timings)
+    for key in ("total_blocks", "skipped_blocks", "skip_rate", "attended_blocks", "v_format", "h2d_total_bytes",
+                "vram_fp16_key_cache_bytes", "rung1_fired", "rung2_fired", "rung3_fired", "rung4_fired", "rho_max",
+                "eta_int4", "int4_error_bound", "e_val_max", "e_val_pre_rung2_max", "k_star_mean", "tau_cov",
+                "tau_cov_actual_mean", "tail_mass_int8_est_max", "exploration_blocks", "v_max_layer",
+                "e_key_step_max", "score_consistency_violation_heads", "delta_bound_mean", "ranking_heads_total",
+                "ranking_disagree_r1", "ranking_fallback_triggered", "ranking_k", "boundary_check_fired",
+                "score_gap_top12_mean", "s_int8_top1_mean", "s_fp16_top1_mean"):
+        assert key in stats, key
+
+
+def test_naive_baseline_matches_oracle_all_int8_int4():
+    """Plain INT8K/INT4V attend (no certification) equals Phase 2 with empty masks."""
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(14, 2048, dtype=dtype)
+    cc = hz.make_cuda_cache(base.k, base.v, dtype, 32)
+    oc = hz.make_oracle_cache(base.k, base.v, dtype, 32)
+    q = hz.to_dev(base.q, dtype)
+    from dotcache.kernels import certified_attention as ca
+    out, stats = ca.certified_attention_layer(cc, q, 4, None, False, v_tolerance=0.05, score_consistency_check=False)
+    torch.cuda.synchronize()
+    z = np.zeros((32, 128), dtype=np.int32)
+    ref, _ = orc.attend_mixed(oc, base.q, 4, 1.0 / np.sqrt(128.0), z, z, 128, 16)
+    scale = np.abs(ref).max(axis=1, keepdims=True)
+    assert stats == {} and np.all(np.abs(out.cpu().numpy() - ref) <= 1e-3 * scale)

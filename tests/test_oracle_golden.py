@@ -56,7 +56,14 @@ def check_call(R, z, tag, H, nq, nact):
     np.testing.assert_allclose(R["S_b"], z[f"{tag}/S_b"], rtol=RTOL_STAT * 2)
     if f"{tag}/mass_frac" in z:
         np.testing.assert_allclose(R["mass_frac"], z[f"{tag}/mass_frac"], rtol=5e-5, atol=1e-9)
-        assert np.array_equal(R["sorted_idx"], z[f"{tag}/sorted_idx"]), "sorted block order differs"
+        # Same selected set in the same order, except that two blocks whose
+        # reference masses agree to 2e-6 relative (a few float32 ulps: the
+        # reference fixes no summation order) may swap places.
+        ref_idx, ref_mf = z[f"{tag}/sorted_idx"], z[f"{tag}/mass_frac"]
+        for h, j in np.argwhere(R["sorted_idx"] != ref_idx):
+            a, b = ref_mf[h, ref_idx[h, j]], ref_mf[h, R["sorted_idx"][h, j]]
+            assert abs(a - b) <= 2e-6 * max(a, b), f"sorted order differs at head {h} pos {j}: {a} vs {b}"
+        assert np.array_equal(np.sort(R["sorted_idx"], axis=1), np.sort(ref_idx, axis=1)), "selected set differs"
         np.testing.assert_allclose(R["sorted_cumsum"], z[f"{tag}/sorted_cumsum"], rtol=2e-5)
     if f"{tag}/exploration_mask" in z:
         ref = gc.unpack_mask(z[f"{tag}/exploration_mask"], nq)
