@@ -19,7 +19,7 @@ MAX_SORT_BLOCKS = 16384
 SYMBOLS = [
     "cqa_version", "cqa_last_error", "cqa_quantize_blocks", "cqa_append_token", "cqa_int4_quantise",
     "cqa_score_blocks", "cqa_select", "cqa_fp16_block_scores", "cqa_delta_bound", "cqa_certify",
-    "cqa_attend", "cqa_layer_step", "cqa_suggest_splits",
+    "cqa_attend", "cqa_attend_static", "cqa_layer_step", "cqa_suggest_splits",
 ]
 
 vp = C.c_void_p
@@ -118,6 +118,7 @@ def lib() -> C.CDLL:
     L.cqa_delta_bound.argtypes = [pc, vp, i32, vp, vp]
     L.cqa_certify.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp]
     L.cqa_attend.argtypes = [pc, pw, vp, i32, i64, i64, i64, i32, f32, vp]
+    L.cqa_attend_static.argtypes = [pc, pw, vp, i32, i64, i64, i64, i32, f32, vp]
     L.cqa_layer_step.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp, i64, vp]
     L.cqa_suggest_splits.argtypes = [i32, i32, i64, C.POINTER(C.c_int), C.POINTER(C.c_int)]
     for s in SYMBOLS[2:]:

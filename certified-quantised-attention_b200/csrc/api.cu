@@ -34,6 +34,9 @@ int certify_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace 
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
                   long num_tokens, int last_valid, float q_scale, cudaStream_t st);
 
+int attend_static_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
+                         long num_tokens, int last_valid, float q_scale, cudaStream_t st);
+
 static int check_common(const cqa_cache *c, const cqa_workspace *ws, const char *who)
 {
     if (!c || !ws) { set_error("%s: NULL cache or workspace", who); return CQA_ERR_INVALID; }
@@ -100,6 +103,16 @@ extern "C" int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const voi
     if (rc) return rc;
     if (!q) { set_error("cqa_attend: NULL q"); return CQA_ERR_INVALID; }
     return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_block_valid, q_scale, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_attend_static(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,
+                                 int64_t nact, int64_t num_tokens, int last_block_valid, float q_scale, void *stream)
+{
+    int rc = check_common(c, ws, "cqa_attend_static");
+    if (rc) return rc;
+    if (!q) { set_error("cqa_attend_static: NULL q"); return CQA_ERR_INVALID; }
+    return attend_static_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_block_valid, q_scale,
+                                (cudaStream_t)stream);
 }
 
 extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *q,

@@ -12,6 +12,8 @@
 //
 // Nothing computed here can change a selection or a certificate flag, so fast
 // exponentials are used.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cqa {
@@ -358,6 +360,66 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
     }
     set_error("cqa_attend: unknown Tier-2 dtype %d", c->t2_dtype);
     return CQA_ERR_INVALID;
+}
+
+// ---------------------------------------------------------------------------
+// Built-in scratch for cqa_attend_static: split partials for callers that
+// cannot allocate device memory.  Layout: [Phase-2 m | l | acc][dense m | l | acc].
+constexpr long STATIC_P2 = (long)CQA_STATIC_MAX_HEADS * CQA_STATIC_MAX_SPLITS;
+constexpr long STATIC_DN = (long)CQA_STATIC_MAX_HEADS * CQA_STATIC_MAX_DENSE_SPLITS;
+constexpr long STATIC_FLOATS = STATIC_P2 * (D + 2) + STATIC_DN * (D + 2);
+static __device__ __align__(256) float g_static_partials[STATIC_FLOATS];
+
+// Device address of g_static_partials per device.  In host code the symbol is
+// only a handle; the address a kernel can use comes from cudaGetSymbolAddress,
+// looked up once per device with that device current.
+static float *static_partials_for_current_device(int *rc_out)
+{
+    constexpr int MAX_DEV = 64;
+    static float *addr[MAX_DEV] = {nullptr};
+    static std::mutex mu;
+    int dev = -1;
+    *rc_out = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (*rc_out) return nullptr;
+    if (dev < 0 || dev >= MAX_DEV) {
+        set_error("cqa_attend_static: device index %d out of range", dev);
+        *rc_out = CQA_ERR_UNSUPPORTED;
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void *p = nullptr;
+        *rc_out = check_cuda(cudaGetSymbolAddress(&p, g_static_partials), "cudaGetSymbolAddress(g_static_partials)");
+        if (*rc_out) return nullptr;
+        addr[dev] = static_cast<float *>(p);
+    }
+    return addr[dev];
+}
+
+int attend_static_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
+                         long num_tokens, int last_valid, float q_scale, cudaStream_t st)
+{
+    const long H = (long)c->kv_heads * c->gqa_group;
+    if (H > CQA_STATIC_MAX_HEADS || ws->num_splits > CQA_STATIC_MAX_SPLITS ||
+        ws->dense_splits > CQA_STATIC_MAX_DENSE_SPLITS) {
+        set_error("cqa_attend_static: %ld heads / %d splits / %d dense splits exceed the built-in scratch "
+                  "(limits %d / %d / %d); use cqa_attend with caller-provided partial buffers",
+                  H, ws->num_splits, ws->dense_splits, CQA_STATIC_MAX_HEADS, CQA_STATIC_MAX_SPLITS,
+                  CQA_STATIC_MAX_DENSE_SPLITS);
+        return CQA_ERR_TOO_LARGE;
+    }
+    int rc = CQA_OK;
+    float *base = static_partials_for_current_device(&rc);
+    if (rc) return rc;
+    cqa_workspace w = *ws;
+    w.part_m = base;
+    w.part_l = base + STATIC_P2;
+    w.part_acc = base + 2 * STATIC_P2;
+    float *dn = base + STATIC_P2 * (D + 2);
+    w.dense_m = dn;
+    w.dense_l = dn + STATIC_DN;
+    w.dense_acc = dn + 2 * STATIC_DN;
+    return attend_launch(c, &w, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
 }
 
 }  // namespace cqa

@@ -235,6 +235,38 @@ int cqa_certify(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace 
 int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,
                int64_t nact, int64_t num_tokens, int last_block_valid, float q_scale, void *stream);
 
+/* Limits of cqa_attend_static (the size of its built-in scratch). */
+#define CQA_STATIC_MAX_HEADS 64
+#define CQA_STATIC_MAX_SPLITS 128
+#define CQA_STATIC_MAX_DENSE_SPLITS 64
+
+/* Same work and same result as cqa_attend, for callers that cannot hand over
+ * scratch buffers because they are not able to allocate device memory at all:
+ * for example a plugin loaded into a serving engine that has already claimed
+ * the whole GPU for its own memory pool, or a decode loop in which calling
+ * the driver's allocator is off limits because it stalls the device.  This
+ * entry point has no counterpart in the reference project.
+ *
+ * The split partials (m, l, acc[128] per head and split, for Phase 2 and for
+ * the dense recompute) live in an array that is part of the library image
+ * (about 6.3 MB of device memory on every GPU that loads the library, held
+ * until the process exits).  ws->part_m/part_l/part_acc and
+ * ws->dense_m/dense_l/dense_acc are ignored and may be NULL; every other
+ * field of ws, the inputs and ws->out are the caller's as usual.
+ * Limits: kv_heads*gqa_group <= CQA_STATIC_MAX_HEADS, ws->num_splits <=
+ * CQA_STATIC_MAX_SPLITS, ws->dense_splits <= CQA_STATIC_MAX_DENSE_SPLITS;
+ * anything larger returns CQA_ERR_TOO_LARGE and launches nothing.
+ * The call performs no device allocation or free, directly or through a
+ * library.  The first call on each device looks up the device address of
+ * the array (with that device current); make that first call outside any
+ * stream capture.  All calls on a device share the one array and it keeps
+ * whatever the previous call left there; nothing in it has to start at zero
+ * (each call overwrites every partial it later reads), but two calls whose
+ * kernels can overlap on the GPU (different streams) would overwrite each
+ * other's partials: serialise them. */
+int cqa_attend_static(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,
+                      int64_t nact, int64_t num_tokens, int last_block_valid, float q_scale, void *stream);
+
 /* The whole per-layer chain on one stream: score -> select -> certify ->
  * attend.  No host synchronisation; results stay on the device.
  * Replaces certified_attention_layer (kernels/certified_attention.py:1065-2790)
