@@ -45,6 +45,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         "-prec-div=true", "-prec-sqrt=true", "-ftz=false",
         "-I", str(INCLUDE), "-o", str(LIB),
     ] + [str(CSRC / s) for s in SOURCES]
+    extra = os.environ.get("CQA_NVCC_FLAGS")
+    if extra:
+        cmd[1:1] = extra.split()
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     res = subprocess.run(cmd, capture_output=True, text=True)

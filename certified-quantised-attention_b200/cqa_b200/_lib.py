@@ -77,7 +77,7 @@ class CqaWorkspace(C.Structure):
         ("reserved", C.c_int32),
         ("part_m", vp), ("part_l", vp), ("part_acc", vp),
         ("dense_m", vp), ("dense_l", vp), ("dense_acc", vp),
-        ("cert", vp), ("any_flags", vp), ("out", vp),
+        ("cert", vp), ("any_flags", vp), ("out", vp), ("tickets", vp),
     ]
 
 

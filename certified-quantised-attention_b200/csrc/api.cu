@@ -31,6 +31,8 @@ int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *
                   const float *u, long u_ld, cudaStream_t st);
 int certify_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
                    long nq, long nact, cudaStream_t st);
+int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
+                   long nq, long nact, const float *u, long u_ld, int phases, cudaStream_t st);
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
                   long num_tokens, int last_valid, float q_scale, cudaStream_t st);
 
@@ -134,9 +136,11 @@ extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const 
     if (!ws->token_scores) { set_error("cqa_layer_step: token_scores missing"); return CQA_ERR_INVALID; }
     rc = score_blocks_launch(c, q, q_dtype, nq, knobs->q_scale, ws->m_b, ws->s_b, ws->ld, ws->token_scores, st);
     if (rc) return rc;
-    rc = cqa_select(c, knobs, ws, nq, nact, exploration_u, u_ld, stream);
-    if (rc) return rc;
-    rc = cqa_certify(c, knobs, ws, q, q_dtype, nq, nact, stream);
+    if (!(knobs->tau_cov > 0.0f)) { set_error("cqa_layer_step: tau_cov must be positive"); return CQA_ERR_INVALID; }
+    if (!ws->value_mask) { set_error("cqa_layer_step: value_mask missing"); return CQA_ERR_INVALID; }
+    if (nact > ws->ld) { set_error("cqa_layer_step: workspace ld too small"); return CQA_ERR_INVALID; }
+    if (exploration_u && u_ld < nq) { set_error("cqa_layer_step: exploration_u leading dimension too small"); return CQA_ERR_INVALID; }
+    rc = selcert_launch(c, knobs, ws, q, q_dtype, nq, nact, exploration_u, u_ld, 3, st);   // select + certify, one launch
     if (rc) return rc;
     return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, knobs->q_scale, st);
 }
@@ -150,15 +154,17 @@ extern "C" int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
-    // Phase 2: about four resident CTAs per SM, at least 8 blocks (one per warp) per split.
-    long target = ((long)sms * 4 + kv_heads - 1) / kv_heads;
+    // Phase 2: two resident CTAs per SM, at least 8 blocks (one per warp) per split.
+    long target = ((long)sms * 2) / kv_heads;
+    if (target < 1) target = 1;
     long by_work = (nact + 7) / 8;
     long ns = target < by_work ? target : by_work;
+    if (ns > CQA_MAX_SPLITS) ns = CQA_MAX_SPLITS;
     if (ns < 1) ns = 1;
     *num_splits = (int)ns;
-    long H = (long)kv_heads * gqa_group;
-    long dtarget = ((long)sms * 2 + H - 1) / H;
-    long ds = dtarget < by_work ? dtarget : by_work;
+    // dense recompute: chunks of about 16 blocks per (flagged head), at most CQA_MAX_DENSE_SPLITS
+    long ds = (nact + 15) / 16;
+    if (ds > CQA_MAX_DENSE_SPLITS) ds = CQA_MAX_DENSE_SPLITS;
     if (ds < 1) ds = 1;
     *dense_splits = (int)ds;
     return CQA_OK;

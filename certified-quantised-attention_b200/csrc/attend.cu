@@ -1,14 +1,25 @@
 // Phase 2: mixed INT8/FP16-key, INT4/FP16-value split-K attend, the dense
-// FP16 recompute of flagged heads, and the log-sum-exp merge.
+// FP16 recompute of flagged heads, and the log-sum-exp merge — one launch.
 //
-// attend_mixed_kernel: one CTA = (kv head, split of blocks); the G query heads
-// of the group share every value load.  A warp owns one 16-token block at a
-// time: lane L (mod 16) owns output channels 8L..8L+7, the two half warps take
-// 8 tokens each.  Blocks whose (head, block) bit in topk_mask is clear reuse
-// the Phase-1 token scores (no second pass over the INT8 keys); promoted
-// blocks recompute their scores from the Tier-2 keys.  INT4 values are
-// unpacked and dequantised in registers straight into the softmax.V
-// accumulation; (head, block) pairs flagged in value_mask read Tier-2 values.
+// attend_kernel, grid (8 + splits, KV):
+//   * CTAs x >= 8: one (kv head, split of blocks).  The G query heads of the
+//     group share every value load.  A warp owns one 16-token block at a time;
+//     the block's INT4 codes, scales, zeros and cached Phase-1 token scores
+//     (1.5 KB + 64 B per head) arrive in a warp-private 4-stage shared-memory
+//     ring through 16-byte asynchronous copies, so several blocks per warp are
+//     in flight and no CTA barrier sits in the loop.  Lane L (mod 16) owns
+//     output channels 8L..8L+7; half warp 0 takes the even tokens, half warp 1
+//     the odd ones (conflict-free shared-memory reads).  INT4 codes become
+//     floats with one logic op and one exact fused multiply-add each (magic
+//     number 2^23), scale and zero are folded into the softmax weights, and
+//     the accumulation uses packed f32x2 fused multiply-adds.  (head, block)
+//     pairs flagged in topk_mask recompute their scores from Tier-2 keys;
+//     pairs flagged in value_mask read Tier-2 values.
+//   * CTAs x < 8 (dispatched first): a pool of 8*KV CTAs for the dense FP16
+//     recompute.  Work units are (flagged head, chunk of blocks), taken from the
+//     list the certifier wrote; with no flagged head the pool exits at once.
+//   * The last CTA to finish for a kv head (a head, for the dense role) merges
+//     the split partials and writes the output rows; no separate merge launch.
 //
 // Nothing computed here can change a selection or a certificate flag, so fast
 // exponentials are used.
@@ -19,17 +30,87 @@
 namespace cqa {
 
 constexpr int ATT_WARPS = 8;
+constexpr int ATT_THREADS = ATT_WARPS * 32;
+constexpr int ATT_STAGES = 4;
 
 __device__ __forceinline__ float fexp(float x) { return __expf(x); }
 
-// Merge (m, l, acc) partials across the warps of a CTA and write one partial.
+__device__ __forceinline__ void att_cp16(void *smem, const void *gmem)
+{
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void att_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void att_wait()
+{
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+template <int G>
+struct AttLayout {
+    static constexpr int PACKED = 0;
+    static constexpr int SCALES = BS * (D / 2);               // 1024
+    static constexpr int ZEROS = SCALES + BS * NG * 2;        // 1280
+    static constexpr int SCORES = ZEROS + BS * NG * 2;        // 1536
+    static constexpr int STAGE = SCORES + G * BS * 4;         // + 64 B per head
+    static constexpr int RING = ATT_WARPS * ATT_STAGES * STAGE;
+    // cross-warp merge buffers and final-merge scratch (both alias the ring)
+    static constexpr int MERGE_A = ATT_WARPS * G * (D + 2) * 4;
+    static constexpr int MERGE_B = (2 * G * CQA_MAX_SPLITS + G + 4 + ATT_WARPS * D) * 4;
+    static constexpr int MERGE = MERGE_A > MERGE_B ? MERGE_A : MERGE_B;
+    static constexpr int RING_BYTES = RING > MERGE ? RING : MERGE;
+};
+
+// Per-lane source pointers of the next block to stage.  A block's stage is 1536 + 64*G bytes = packed codes
+// (two 512-byte rounds), scales+zeros (one round: lanes 0-15 scales, 16-31 zeros) and G*64 bytes of token scores.
+template <int G>
+struct AttIssuer {
+    const char *pk, *sz, *sc;   // global sources for this lane
+    long b, b_end, nq;          // block to issue next
+    bool have4;
+
+    __device__ __forceinline__ void init(const cqa_cache &c, const float *tok, long nq_, int kv, long b0, long bend,
+                                         int lane)
+    {
+        b = b0;
+        b_end = bend;
+        nq = nq_;
+        have4 = c.values_int4_packed != nullptr;
+        const long row0 = (long)kv * c.cap_tokens + b0 * BS;
+        pk = reinterpret_cast<const char *>(c.values_int4_packed) + row0 * (D / 2) + lane * 16;
+        const char *szb = lane < 16 ? reinterpret_cast<const char *>(c.values_int4_scales)
+                                    : reinterpret_cast<const char *>(c.values_int4_zeros);
+        sz = szb + row0 * NG * 2 + (lane & 15) * 16;
+        sc = reinterpret_cast<const char *>(tok + ((long)kv * nq_ + b0) * G * BS) + lane * 16;
+    }
+    // Stage the block `b` (if any) and advance by one warp stride; always commits one group.
+    __device__ __forceinline__ void issue(char *stage, int lane)
+    {
+        using LY = AttLayout<G>;
+        if (b < b_end) {
+            if (have4) {
+                att_cp16(stage + lane * 16, pk);
+                att_cp16(stage + 512 + lane * 16, pk + 512);
+                att_cp16(stage + LY::SCALES + lane * 16, sz);
+            }
+            if (b < nq && lane < 4 * G) att_cp16(stage + LY::SCORES + lane * 16, sc);
+        }
+        att_commit();
+        b += ATT_WARPS;
+        pk += ATT_WARPS * BS * (D / 2);
+        sz += ATT_WARPS * BS * NG * 2;
+        sc += ATT_WARPS * G * BS * 4;
+    }
+};
+
+// Cross-warp merge of (m, l, acc) inside the CTA, then one partial per head to global memory.
 template <int G>
 __device__ __forceinline__ void cta_merge_store(float (&m)[G], float (&l)[G], float (&acc)[G][8], float *sm_m,
                                                 float *sm_l, float *sm_acc, float *out_m, float *out_l,
                                                 float *out_acc, int head0, int split, int nsplits)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, L = lane & 15;
-    // the two half warps hold partial sums over disjoint tokens
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
@@ -45,7 +126,7 @@ __device__ __forceinline__ void cta_merge_store(float (&m)[G], float (&l)[G], fl
         for (int g = 0; g < G; ++g) { sm_m[warp * G + g] = m[g]; sm_l[warp * G + g] = l[g]; }
     }
     __syncthreads();
-    for (int item = threadIdx.x; item < G * D; item += ATT_WARPS * 32) {
+    for (int item = threadIdx.x; item < G * D; item += ATT_THREADS) {
         const int g = item / D, ch = item % D;
         float M = -INFINITY;
 #pragma unroll
@@ -64,174 +145,98 @@ __device__ __forceinline__ void cta_merge_store(float (&m)[G], float (&l)[G], fl
     }
 }
 
-template <int G, typename T2>
-__global__ void __launch_bounds__(ATT_WARPS * 32) attend_mixed_kernel(cqa_cache c, cqa_workspace ws, const void *q,
-                                                                     int q_dtype, long nq, long nact,
-                                                                     int last_valid, float q_scale,
-                                                                     int blocks_per_split)
+// Final merge of `ns` split partials of heads [head0, head0+nh) by the last CTA to arrive.
+// All 256 threads take part; `sm` is 16-byte aligned scratch of at least 2*nh*ns + nh + 3 + 8*128 floats.
+// Step 1 brings the (m, l) partials into shared memory in one round of loads, step 2 (one warp per head)
+// computes the scale of every split, step 3 streams the acc rows with the warps of a head striding over the
+// splits (float4 per lane, all loads independent), step 4 adds the per-warp sums and normalises.
+__device__ __forceinline__ void final_merge(const float *pm, const float *pl, const float *pa, int ns, int head0,
+                                            int nh, const cqa_workspace &ws, bool dense_role, float *sm)
 {
-    __shared__ float s_q[G * D];
-    __shared__ float s_w[ATT_WARPS][BS][G];        // softmax weights of the current block, [token][head]
-    __shared__ float s_sc[ATT_WARPS][G][BS];       // FP16-key logits of the current block
-    __shared__ float sm_m[ATT_WARPS * G], sm_l[ATT_WARPS * G];
-    __shared__ float sm_acc[ATT_WARPS * G * D];
-    const int kv = blockIdx.y, split = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, L = lane & 15, hw = lane >> 4;
-    const long b_begin = (long)split * blocks_per_split;
-    const long b_end = min(nact, b_begin + (long)blocks_per_split);
-    for (int i = threadIdx.x; i < G * D; i += ATT_WARPS * 32) s_q[i] = load_q(q, q_dtype, (long)kv * G * D + i);
+    float *s_m = sm, *s_sc = sm + nh * ns, *s_l = s_sc + nh * ns;
+    float *s_part = sm + ((2 * nh * ns + nh + 3) & ~3);  // 16-byte aligned for float4 stores
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     __syncthreads();
-
-    float m[G], l[G], acc[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        m[g] = -INFINITY;
-        l[g] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[g][i] = 0.0f;
+    for (int i = tid; i < nh * ns; i += ATT_THREADS) {
+        s_m[i] = __ldcg(pm + (long)head0 * ns + i);
+        s_sc[i] = __ldcg(pl + (long)head0 * ns + i);
     }
-    const T2 *kt2 = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
-    const T2 *vt2 = reinterpret_cast<const T2 *>(c.values_t2) + (long)kv * c.values_t2_rows * D;
-    constexpr int NP = (G + 1) / 2;  // score passes: two heads (one per half warp) at a time
-
-    for (long b = b_begin + warp; b < b_end; b += ATT_WARPS) {
-        unsigned km = 0, vm = 0;  // bit g: head g uses FP16 keys / FP16 values for this block
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const long o = (long)(kv * G + g) * ws.ld + b;
-            km |= (ws.topk_mask[o] || b >= nq) ? (1u << g) : 0u;
-            vm |= ws.value_mask[o] ? (1u << g) : 0u;
+    __syncthreads();
+    if (warp < nh) {
+        float M = -INFINITY;
+        for (int s = lane; s < ns; s += 32) M = fmaxf(M, s_m[warp * ns + s]);
+        M = warp_max(M);
+        float lsum = 0.0f;
+        for (int s = lane; s < ns; s += 32) {
+            const float mi = s_m[warp * ns + s];
+            const float sc = mi == -INFINITY ? 0.0f : fexp(mi - M);
+            lsum = fmaf(s_sc[warp * ns + s], sc, lsum);
+            s_sc[warp * ns + s] = sc;
         }
-        const int n_valid = (b == nact - 1) ? last_valid : BS;
-        // FP16-key logits for promoted heads
-        if (km) {
-            long kslot = c.key_slots ? (long)c.key_slots[b] : b;
-            if (kslot < 0) kslot = 0;
-            float kf[8][8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int t = hw * 8 + i;
-                if (t < n_valid) load8<T2>(kt2 + (kslot * BS + t) * D + 8 * L, kf[i]);
-                else {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) kf[i][k] = 0.0f;
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                if (km & (1u << g)) {
-                    float qv[8];
-                    load8<float>(s_q + g * D + 8 * L, qv);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        float d = hw_sum(chain8(kf[i], qv));
-                        if (L == i) s_sc[warp][g][hw * 8 + i] = d * q_scale;
-                    }
-                }
-            }
-            __syncwarp();
-        }
-        // softmax bookkeeping, two heads per pass
-        float alpha[G];
-#pragma unroll
-        for (int p = 0; p < NP; ++p) {
-            const int g = 2 * p + hw;
-            const bool gvalid = g < G;
-            float s = -INFINITY;
-            if (gvalid && L < n_valid) {
-                if (km & (1u << g)) s = s_sc[warp][g][L];
-                else s = ws.token_scores[(((long)kv * nq + b) * G + g) * BS + L];
-            }
-            const float bm = hw_max(s);
-            const float bm_o = __shfl_xor_sync(FULL, bm, 16);
-            // new running max for this lane's head (and the other half's head)
-            const int g_o = 2 * p + (hw ^ 1);
-            float m_old_mine = 0.0f, m_new_mine = 0.0f;
-#pragma unroll
-            for (int gg = 0; gg < G; ++gg) {
-                if (gg == g || gg == g_o) {
-                    const float bmg = (gg == g) ? bm : bm_o;
-                    const float mn = fmaxf(m[gg], bmg);
-                    alpha[gg] = (mn == -INFINITY || m[gg] == mn) ? 1.0f : fexp(m[gg] - mn);
-                    if (gg == g) { m_old_mine = m[gg]; m_new_mine = mn; }
-                    m[gg] = mn;
-                }
-            }
-            (void)m_old_mine;
-            const float w = (gvalid && s != -INFINITY) ? fexp(s - m_new_mine) : 0.0f;
-            if (gvalid) s_w[warp][L][g] = w;
-            const float ls = hw_sum(w);
-            const float ls_o = __shfl_xor_sync(FULL, ls, 16);
-#pragma unroll
-            for (int gg = 0; gg < G; ++gg) {
-                if (gg == g || gg == g_o) l[gg] = fmaf(l[gg], alpha[gg], (gg == g) ? ls : ls_o);
-            }
-        }
-        __syncwarp();
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            if (alpha[g] != 1.0f) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g][i] *= alpha[g];
-            }
-        }
-        // values
-        const bool need4 = (vm != ((1u << G) - 1u));
-        const bool need16 = vm != 0;
-        long vslot = c.value_slots ? (long)c.value_slots[b] : b;
-        if (vslot < 0) vslot = 0;
-        const long row_base = (long)kv * c.cap_tokens + b * BS;
-#pragma unroll 2
-        for (int i = 0; i < 8; ++i) {
-            const int t = hw * 8 + i;
-            if (t >= n_valid) continue;
-            float v4[8], v16[8];
-            if (need4) {
-                const long row = row_base + t;
-                const unsigned pk = *reinterpret_cast<const unsigned *>(c.values_int4_packed + row * (D / 2) + 4 * L);
-                const float s = __half2float(__ushort_as_half(c.values_int4_scales[row * NG + (L >> 1)]));
-                const float z = __half2float(__ushort_as_half(c.values_int4_zeros[row * NG + (L >> 1)]));
-#pragma unroll
-                for (int k = 0; k < 8; ++k) v4[k] = fmaf((float)((pk >> (4 * k)) & 0xFu), s, z);
-            }
-            if (need16) load8<T2>(vt2 + (vslot * BS + t) * D + 8 * L, v16);
-            float wv[G];
-#pragma unroll
-            for (int g = 0; g < G; ++g) wv[g] = s_w[warp][t][g];
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                if (vm & (1u << g)) {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) acc[g][k] = fmaf(wv[g], v16[k], acc[g][k]);
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) acc[g][k] = fmaf(wv[g], v4[k], acc[g][k]);
-                }
-            }
-        }
-        __syncwarp();
+        lsum = warp_sum(lsum);
+        if (lane == 0) s_l[warp] = lsum;
     }
-    cta_merge_store<G>(m, l, acc, sm_m, sm_l, sm_acc, ws.part_m, ws.part_l, ws.part_acc, kv * G, split,
-                       ws.num_splits);
+    __syncthreads();
+    const int wph = ATT_WARPS / nh;  // warps per head (nh is 1, 2, 4 or 8)
+    {
+        const int g = warp / wph, part = warp % wph;
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float4 *rows = reinterpret_cast<const float4 *>(pa + (long)(head0 + g) * ns * D) + lane;
+#pragma unroll 8
+        for (int s = part; s < ns; s += wph) {
+            const float4 v = __ldcg(rows + (long)s * (D / 4));
+            const float sc = s_sc[g * ns + s];
+            a.x = fmaf(v.x, sc, a.x);
+            a.y = fmaf(v.y, sc, a.y);
+            a.z = fmaf(v.z, sc, a.z);
+            a.w = fmaf(v.w, sc, a.w);
+        }
+        reinterpret_cast<float4 *>(s_part + warp * D)[lane] = a;
+    }
+    __syncthreads();
+    for (int item = tid; item < nh * D; item += ATT_THREADS) {
+        const int g = item / D, ch = item % D, h = head0 + g;
+        const bool flagged = ws.cert != nullptr && (ws.cert[h].dense || ws.any_flags[2]);
+        if (flagged != dense_role) continue;
+        float a = 0.0f;
+        for (int p = 0; p < wph; ++p) a += s_part[(g * wph + p) * D + ch];
+        const float l = s_l[g];
+        ws.out[(long)h * D + ch] = a / (l > 0.0f ? l : 1.0f);
+    }
+    __syncthreads();
 }
 
-// Dense attention over the Tier-2 keys/values of heads flagged for recompute
-// (per-head Rung 3, or every head when a score-consistency violation was
-// raised).  Grid (dense_splits, H); CTAs of unflagged heads return at once.
-template <typename T2>
-__global__ void __launch_bounds__(ATT_WARPS * 32) dense_attend_kernel(cqa_cache c, cqa_workspace ws, const void *q,
-                                                                     int q_dtype, long num_tokens, float q_scale,
-                                                                     int blocks_per_split)
+// Returns true in every thread of the CTA that took the last ticket.
+__device__ __forceinline__ bool take_ticket(int *ticket, int total, int *s_flag)
 {
-    const int h = blockIdx.y, split = blockIdx.x;
-    if (!(ws.cert[h].dense || ws.any_flags[2])) return;
-    __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS];
-    __shared__ float sm_acc[ATT_WARPS * D];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int t = atomicAdd(ticket, 1);
+        *s_flag = (t == total - 1) ? 1 : 0;
+        if (t == total - 1) *ticket = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    const bool last = *s_flag != 0;
+    if (last) __threadfence();
+    return last;
+}
+
+// Dense FP16 attention of one (head, chunk of blocks) unit; the last unit of a head merges and writes the row.
+template <typename T2>
+__device__ void dense_unit(const cqa_cache &c, const cqa_workspace &ws, const void *q, int q_dtype, long num_tokens,
+                           float q_scale, int h, int chunk, char *smem_raw, int *s_flag)
+{
+    float *sm_m = reinterpret_cast<float *>(smem_raw);
+    float *sm_l = sm_m + ATT_WARPS;
+    float *sm_acc = sm_l + ATT_WARPS;
     const int kv = h / c.gqa_group;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, L = lane & 15, hw = lane >> 4;
     const long nblk = (num_tokens + BS - 1) / BS;
-    const long b_begin = (long)split * blocks_per_split;
-    const long b_end = min(nblk, b_begin + (long)blocks_per_split);
+    const int ds = ws.dense_splits;
+    const long bps = (nblk + ds - 1) / ds;
+    const long b_begin = (long)chunk * bps;
+    const long b_end = min(nblk, b_begin + bps);
     float qv[8];
     load_q8(q, q_dtype, (long)h * D + 8 * L, qv);
     const T2 *kt2 = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
@@ -243,17 +248,26 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) dense_attend_kernel(cqa_cache 
         long kslot = c.key_slots ? (long)c.key_slots[b] : b;
         long vslot = c.value_slots ? (long)c.value_slots[b] : b;
         if (kslot < 0 || vslot < 0) continue;
+        // all key and value rows of this half warp's 8 tokens are requested before anything is consumed
+        Raw8<T2> kr[8], vr[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const long t = b * BS + hw * 8 + i;
+            if (t < num_tokens) {
+                kr[i] = raw_load8<T2>(kt2 + (kslot * BS + hw * 8 + i) * D + 8 * L);
+                vr[i] = raw_load8<T2>(vt2 + (vslot * BS + hw * 8 + i) * D + 8 * L);
+            } else {
+                kr[i] = raw_zero8<T2>();
+                vr[i] = raw_zero8<T2>();
+            }
+        }
         float lg[8];
         float bm = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const long t = b * BS + hw * 8 + i;
             float kf[8];
-            if (t < num_tokens) load8<T2>(kt2 + (kslot * BS + hw * 8 + i) * D + 8 * L, kf);
-            else {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) kf[k] = 0.0f;
-            }
+            raw_to_f(kr[i], kf);
             const float d = hw_sum(chain8(kf, qv));
             lg[i] = t < num_tokens ? d * q_scale : -INFINITY;
             bm = fmaxf(bm, lg[i]);
@@ -269,78 +283,332 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) dense_attend_kernel(cqa_cache 
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            if (lg[i] == -INFINITY) continue;
-            const float w = fexp(lg[i] - mn);
+            const float w = lg[i] == -INFINITY ? 0.0f : fexp(lg[i] - mn);
             ls += w;
             float vf[8];
-            load8<T2>(vt2 + (vslot * BS + hw * 8 + i) * D + 8 * L, vf);
+            raw_to_f(vr[i], vf);
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[0][k] = fmaf(w, vf[k], acc[0][k]);
         }
         ls += __shfl_xor_sync(FULL, ls, 16);
         l[0] = fmaf(l[0], alpha, ls);
     }
-    cta_merge_store<1>(m, l, acc, sm_m, sm_l, sm_acc, ws.dense_m, ws.dense_l, ws.dense_acc, h, split,
-                       ws.dense_splits);
+    __syncthreads();
+    cta_merge_store<1>(m, l, acc, sm_m, sm_l, sm_acc, ws.dense_m, ws.dense_l, ws.dense_acc, h, chunk, ds);
+    if (take_ticket(ws.tickets + c.kv_heads + h, ds, s_flag))
+        final_merge(ws.dense_m, ws.dense_l, ws.dense_acc, ds, h, 1, ws, true, reinterpret_cast<float *>(smem_raw));
 }
 
-// Final merge of the split partials; picks the dense partials for flagged heads.
-__global__ void __launch_bounds__(D) lse_reduce_kernel(cqa_workspace ws)
+constexpr int DENSE_POOL_X = 8;  // dense-recompute CTAs per KV row of the grid
+
+template <int G, typename T2>
+__global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa_workspace ws, const void *q,
+                                                               int q_dtype, long nq, long nact, long num_tokens,
+                                                               int last_valid, float q_scale, int blocks_per_split)
 {
-    const int h = blockIdx.x, ch = threadIdx.x;
-    const bool dense = ws.cert != nullptr && (ws.cert[h].dense || ws.any_flags[2]);
-    const int ns = dense ? ws.dense_splits : ws.num_splits;
-    const float *pm = dense ? ws.dense_m : ws.part_m;
-    const float *pl = dense ? ws.dense_l : ws.part_l;
-    const float *pa = dense ? ws.dense_acc : ws.part_acc;
-    float M = -INFINITY;
-    for (int s = 0; s < ns; ++s) M = fmaxf(M, pm[(long)h * ns + s]);
-    float a = 0.0f, l = 0.0f;
-    for (int s = 0; s < ns; ++s) {
-        const long p = (long)h * ns + s;
-        const float mi = pm[p];
-        const float sc = mi == -INFINITY ? 0.0f : fexp(mi - M);
-        a = fmaf(pa[p * D + ch], sc, a);
-        l = fmaf(pl[p], sc, l);
+    using LY = AttLayout<G>;
+    extern __shared__ __align__(16) char dsm[];
+    __shared__ int s_flag;
+    const int kv = blockIdx.y;
+    const int ns = ws.num_splits;
+    const int pool_x = ws.dense_splits > 0 ? DENSE_POOL_X : 0;
+    if ((int)blockIdx.x < pool_x) {
+        // Dense-recompute pool: units are (flagged head, chunk); unflagged steps leave at once.
+        const int H = c.kv_heads * G;
+        const bool all = ws.any_flags[2] != 0;
+        const int n_heads = all ? H : ws.any_flags[4];
+        if (n_heads == 0) return;
+        const int ds = ws.dense_splits;
+        const int pool = c.kv_heads * DENSE_POOL_X;
+        for (int u = kv * DENSE_POOL_X + (int)blockIdx.x; u < n_heads * ds; u += pool) {
+            const int h = all ? u / ds : ws.any_flags[5 + u / ds];
+            dense_unit<T2>(c, ws, q, q_dtype, num_tokens, q_scale, h, u % ds, dsm, &s_flag);
+        }
+        return;
     }
-    ws.out[(long)h * D + ch] = a / (l > 0.0f ? l : 1.0f);
+    // ---- shared memory carve-up
+    char *ring = dsm;
+    float *s_q = reinterpret_cast<float *>(dsm + LY::RING_BYTES);              // [G][128]
+    float2 *s_w = reinterpret_cast<float2 *>(s_q + G * D);                      // [warps][16][G] (w, w)
+    float *s_sc = reinterpret_cast<float *>(s_w + ATT_WARPS * BS * G);          // [warps][G][16]
+    unsigned char *s_km = reinterpret_cast<unsigned char *>(s_sc + ATT_WARPS * G * BS);  // [bps]
+    unsigned char *s_vm = s_km + blocks_per_split;
+
+    const int split = (int)blockIdx.x - pool_x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, L = lane & 15, hw = lane >> 4;
+    const long b_begin = (long)split * blocks_per_split;
+    const long b_end = min(nact, b_begin + (long)blocks_per_split);
+    char *wring = ring + warp * ATT_STAGES * LY::STAGE;
+
+    // start the pipeline before anything else
+    AttIssuer<G> issuer;
+    issuer.init(c, ws.token_scores, nq, kv, b_begin + warp, b_end, lane);
+#pragma unroll
+    for (int s = 0; s < ATT_STAGES - 1; ++s) issuer.issue(wring + s * LY::STAGE, lane);
+    for (int i = threadIdx.x; i < G * D; i += ATT_THREADS) s_q[i] = load_q(q, q_dtype, (long)kv * G * D + i);
+    for (int i = threadIdx.x; i < blocks_per_split; i += ATT_THREADS) {
+        const long b = b_begin + i;
+        unsigned km = 0, vm = 0;
+        if (b < b_end) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const long o = (long)(kv * G + g) * ws.ld + b;
+                km |= (ws.topk_mask[o] || b >= nq) ? (1u << g) : 0u;
+                vm |= ws.value_mask[o] ? (1u << g) : 0u;
+            }
+        }
+        s_km[i] = (unsigned char)km;
+        s_vm[i] = (unsigned char)vm;
+    }
+    __syncthreads();
+
+    // Softmax bookkeeping layout: LPH lanes per head, each lane holds TPL tokens of its head `gl`.
+    constexpr int LPH = G >= 8 ? 4 : (G == 4 ? 8 : 16);
+    constexpr int TPL = BS / LPH;
+    const int gl = lane / LPH, sub = lane % LPH;
+    const bool gl_valid = gl < G;
+
+    float m[G], l[G];
+    float2 acc2[G][4];
+    float m_mine = -INFINITY;   // running max of head gl (same value as m[gl])
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc2[g][k] = make_float2(0.0f, 0.0f);
+    }
+    const T2 *kt2 = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
+    const T2 *vt2 = reinterpret_cast<const T2 *>(c.values_t2) + (long)kv * c.values_t2_rows * D;
+    float2 *w_tile = s_w + warp * BS * G;
+    float *sc_tile = s_sc + warp * G * BS;
+    const unsigned all = (1u << G) - 1u;
+
+    int it = 0;
+    for (long b = b_begin + warp; b < b_end; b += ATT_WARPS, ++it) {
+        issuer.issue(wring + ((it + ATT_STAGES - 1) % ATT_STAGES) * LY::STAGE, lane);
+        att_wait<ATT_STAGES - 1>();
+        __syncwarp();
+        const char *st = wring + (it % ATT_STAGES) * LY::STAGE;
+        const unsigned km = s_km[b - b_begin], vm = s_vm[b - b_begin];
+        const int n_valid = (b == nact - 1) ? last_valid : BS;
+        // ---- FP16-key logits for promoted heads
+        if (km) {
+            long kslot = c.key_slots ? (long)c.key_slots[b] : b;
+            if (kslot < 0) kslot = 0;
+#pragma unroll 1
+            for (int g = 0; g < G; ++g) {
+                if (!(km & (1u << g))) continue;
+                float qv[8];
+                load8<float>(s_q + g * D + 8 * L, qv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int t = hw * 8 + i;
+                    float kf[8];
+                    if (t < n_valid) load8<T2>(kt2 + (kslot * BS + t) * D + 8 * L, kf);
+                    else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) kf[k] = 0.0f;
+                    }
+                    const float d = hw_sum(chain8(kf, qv));
+                    if (L == i) sc_tile[g * BS + t] = d * q_scale;
+                }
+            }
+            __syncwarp();
+        }
+        // ---- softmax bookkeeping: every lane owns TPL tokens of head gl
+        const float *st_sc = reinterpret_cast<const float *>(st + LY::SCORES);
+        float sv_[TPL];
+        float bm = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < TPL; ++i) {
+            const int t = sub * TPL + i;
+            float x = -INFINITY;
+            if (gl_valid && t < n_valid) x = ((km >> gl) & 1u) ? sc_tile[gl * BS + t] : st_sc[gl * BS + t];
+            sv_[i] = x;
+            bm = fmaxf(bm, x);
+        }
+#pragma unroll
+        for (int o = LPH / 2; o >= 1; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(FULL, bm, o));
+        const float m_new_mine = fmaxf(m_mine, bm);
+        m_mine = m_new_mine;
+        float ls = 0.0f;
+#pragma unroll
+        for (int i = 0; i < TPL; ++i) {
+            const float w = sv_[i] == -INFINITY ? 0.0f : fexp(sv_[i] - m_new_mine);
+            ls += w;
+            if (gl_valid) w_tile[(sub * TPL + i) * G + gl] = make_float2(w, w);
+        }
+#pragma unroll
+        for (int o = LPH / 2; o >= 1; o >>= 1) ls += __shfl_xor_sync(FULL, ls, o);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float bmg = __shfl_sync(FULL, bm, g * LPH);
+            const float lsg = __shfl_sync(FULL, ls, g * LPH);
+            const float mn = fmaxf(m[g], bmg);
+            const float alpha = (mn == -INFINITY || m[g] == mn) ? 1.0f : fexp(m[g] - mn);
+            m[g] = mn;
+            l[g] = fmaf(l[g], alpha, lsg);
+            if (alpha != 1.0f) {
+                const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc2[g][k] = __fmul2_rn(acc2[g][k], a2);
+            }
+        }
+        __syncwarp();
+        // ---- values: this half warp takes tokens t = 2i + hw
+        long vslot = c.value_slots ? (long)c.value_slots[b] : b;
+        if (vslot < 0) vslot = 0;
+        const unsigned *st_pk = reinterpret_cast<const unsigned *>(st + LY::PACKED);
+        const __half *st_s = reinterpret_cast<const __half *>(st + LY::SCALES);
+        const __half *st_z = reinterpret_cast<const __half *>(st + LY::ZEROS);
+        // codes -> floats: (bits | 2^(23-4j)) is 2^(23-4j) + code; one exact add removes the offset
+        const float2 o01 = make_float2(-8388608.0f, -524288.0f), o23 = make_float2(-32768.0f, -2048.0f);
+        if (vm == 0 && n_valid == BS) {
+            // common case: a full block whose values are INT4 for every head of the group
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int t = 2 * i + hw;
+                const unsigned pk = st_pk[t * 16 + L];
+                const float sv = __half2float(st_s[t * NG + (L >> 1)]);
+                const float zv = __half2float(st_z[t * NG + (L >> 1)]);
+                const float2 s2 = make_float2(sv, sv), z2 = make_float2(zv, zv);
+                const unsigned lo = pk & 0xFFFFu, hi = pk >> 16;
+                float2 v[4];
+                v[0] = make_float2(__uint_as_float((lo & 0x000Fu) | 0x4B000000u), __uint_as_float((lo & 0x00F0u) | 0x49000000u));
+                v[1] = make_float2(__uint_as_float((lo & 0x0F00u) | 0x47000000u), __uint_as_float((lo & 0xF000u) | 0x45000000u));
+                v[2] = make_float2(__uint_as_float((hi & 0x000Fu) | 0x4B000000u), __uint_as_float((hi & 0x00F0u) | 0x49000000u));
+                v[3] = make_float2(__uint_as_float((hi & 0x0F00u) | 0x47000000u), __uint_as_float((hi & 0xF000u) | 0x45000000u));
+                v[0] = __ffma2_rn(__fadd2_rn(v[0], o01), s2, z2);
+                v[1] = __ffma2_rn(__fadd2_rn(v[1], o23), s2, z2);
+                v[2] = __ffma2_rn(__fadd2_rn(v[2], o01), s2, z2);
+                v[3] = __ffma2_rn(__fadd2_rn(v[3], o23), s2, z2);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float2 w2 = w_tile[t * G + g];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc2[g][k] = __ffma2_rn(w2, v[k], acc2[g][k]);
+                }
+            }
+        } else {
+            if (vm != all) {
+#pragma unroll 2
+                for (int i = 0; i < 8; ++i) {
+                    const int t = 2 * i + hw;
+                    if (t >= n_valid) continue;
+                    const unsigned pk = st_pk[t * 16 + L];
+                    const float sv = __half2float(st_s[t * NG + (L >> 1)]);
+                    const float zv = __half2float(st_z[t * NG + (L >> 1)]);
+                    const float2 s2 = make_float2(sv, sv), z2 = make_float2(zv, zv);
+                    const unsigned lo = pk & 0xFFFFu, hi = pk >> 16;
+                    float2 v[4];
+                    v[0] = make_float2(__uint_as_float((lo & 0x000Fu) | 0x4B000000u), __uint_as_float((lo & 0x00F0u) | 0x49000000u));
+                    v[1] = make_float2(__uint_as_float((lo & 0x0F00u) | 0x47000000u), __uint_as_float((lo & 0xF000u) | 0x45000000u));
+                    v[2] = make_float2(__uint_as_float((hi & 0x000Fu) | 0x4B000000u), __uint_as_float((hi & 0x00F0u) | 0x49000000u));
+                    v[3] = make_float2(__uint_as_float((hi & 0x0F00u) | 0x47000000u), __uint_as_float((hi & 0xF000u) | 0x45000000u));
+                    v[0] = __ffma2_rn(__fadd2_rn(v[0], o01), s2, z2);
+                    v[1] = __ffma2_rn(__fadd2_rn(v[1], o23), s2, z2);
+                    v[2] = __ffma2_rn(__fadd2_rn(v[2], o01), s2, z2);
+                    v[3] = __ffma2_rn(__fadd2_rn(v[3], o23), s2, z2);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        if (vm & (1u << g)) continue;
+                        const float2 w2 = w_tile[t * G + g];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) acc2[g][k] = __ffma2_rn(w2, v[k], acc2[g][k]);
+                    }
+                }
+            }
+            if (vm) {
+#pragma unroll 2
+                for (int i = 0; i < 8; ++i) {
+                    const int t = 2 * i + hw;
+                    if (t >= n_valid) continue;
+                    float v16[8];
+                    load8<T2>(vt2 + (vslot * BS + t) * D + 8 * L, v16);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        if (!(vm & (1u << g))) continue;
+                        const float2 w2 = w_tile[t * G + g];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            acc2[g][k] = __ffma2_rn(w2, make_float2(v16[2 * k], v16[2 * k + 1]), acc2[g][k]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+    att_wait<0>();
+    float acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { acc[g][2 * k] = acc2[g][k].x; acc[g][2 * k + 1] = acc2[g][k].y; }
+    __syncthreads();  // the ring is reused as merge buffers
+    float *sm_m = reinterpret_cast<float *>(ring);
+    float *sm_l = sm_m + ATT_WARPS * G;
+    float *sm_acc = sm_l + ATT_WARPS * G;
+    cta_merge_store<G>(m, l, acc, sm_m, sm_l, sm_acc, ws.part_m, ws.part_l, ws.part_acc, kv * G, split, ns);
+    if (take_ticket(ws.tickets + kv, ns, &s_flag))
+        final_merge(ws.part_m, ws.part_l, ws.part_acc, ns, kv * G, G, ws, false, reinterpret_cast<float *>(ring));
+}
+
+template <int G>
+static size_t attend_smem(int bps)
+{
+    using LY = AttLayout<G>;
+    size_t dense_bytes = (size_t)(2 * CQA_MAX_DENSE_SPLITS + 8 + 8 * D + 2 * ATT_WARPS + ATT_WARPS * D) * 4;
+    size_t mixed = (size_t)LY::RING_BYTES + (size_t)G * D * 4 + (size_t)ATT_WARPS * BS * G * 8 +
+                   (size_t)ATT_WARPS * G * BS * 4 + 2 * (size_t)bps;
+    mixed = (mixed + 15) & ~(size_t)15;
+    return mixed > dense_bytes ? mixed : dense_bytes;
+}
+
+template <int G, typename T2>
+static int attend_launch_gt(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq,
+                            long nact, long num_tokens, int last_valid, float q_scale, cudaStream_t st)
+{
+    const int ns = ws->num_splits;
+    const int bps = (int)((nact + ns - 1) / ns);
+    const bool dense = ws->cert && ws->dense_splits > 0 && ws->dense_m && ws->dense_l && ws->dense_acc;
+    cqa_workspace w = *ws;
+    if (!dense) w.dense_splits = 0;
+    const size_t smem = attend_smem<G>(bps);
+    static size_t attr = 0;
+    if (smem > attr) {
+        int rc = check_cuda(cudaFuncSetAttribute(attend_kernel<G, T2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem),
+                            "cudaFuncSetAttribute(attend_kernel)");
+        if (rc) return rc;
+        attr = smem;
+    }
+    dim3 grid((unsigned)(ns + (dense ? DENSE_POOL_X : 0)), (unsigned)c->kv_heads);
+    attend_kernel<G, T2><<<grid, ATT_THREADS, smem, st>>>(*c, w, q, q_dtype, nq, nact, num_tokens, last_valid,
+                                                         q_scale, bps);
+    return check_launch("attend_kernel");
 }
 
 template <typename T2>
 static int attend_launch_t(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq,
                            long nact, long num_tokens, int last_valid, float q_scale, cudaStream_t st)
 {
-    const int H = c->kv_heads * c->gqa_group;
-    const int ns = ws->num_splits;
-    const int bps = (int)((nact + ns - 1) / ns);
-    dim3 grid((unsigned)ns, (unsigned)c->kv_heads);
     switch (c->gqa_group) {
-    case 1: attend_mixed_kernel<1, T2><<<grid, ATT_WARPS * 32, 0, st>>>(*c, *ws, q, q_dtype, nq, nact, last_valid, q_scale, bps); break;
-    case 2: attend_mixed_kernel<2, T2><<<grid, ATT_WARPS * 32, 0, st>>>(*c, *ws, q, q_dtype, nq, nact, last_valid, q_scale, bps); break;
-    case 4: attend_mixed_kernel<4, T2><<<grid, ATT_WARPS * 32, 0, st>>>(*c, *ws, q, q_dtype, nq, nact, last_valid, q_scale, bps); break;
-    case 8: attend_mixed_kernel<8, T2><<<grid, ATT_WARPS * 32, 0, st>>>(*c, *ws, q, q_dtype, nq, nact, last_valid, q_scale, bps); break;
-    default: set_error("cqa_attend: unsupported gqa_group %d", c->gqa_group); return CQA_ERR_UNSUPPORTED;
+    case 1: return attend_launch_gt<1, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
+    case 2: return attend_launch_gt<2, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
+    case 4: return attend_launch_gt<4, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
+    case 8: return attend_launch_gt<8, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
     }
-    int rc = check_launch("attend_mixed_kernel");
-    if (rc) return rc;
-    if (ws->cert && ws->dense_splits > 0 && ws->dense_m && c->keys_t2 && c->values_t2) {
-        const long nblk = (num_tokens + BS - 1) / BS;
-        const int dbps = (int)((nblk + ws->dense_splits - 1) / ws->dense_splits);
-        dim3 dgrid((unsigned)ws->dense_splits, (unsigned)H);
-        dense_attend_kernel<T2><<<dgrid, ATT_WARPS * 32, 0, st>>>(*c, *ws, q, q_dtype, num_tokens, q_scale, dbps);
-        rc = check_launch("dense_attend_kernel");
-        if (rc) return rc;
-    }
-    lse_reduce_kernel<<<H, D, 0, st>>>(*ws);
-    return check_launch("lse_reduce_kernel");
+    set_error("cqa_attend: unsupported gqa_group %d", c->gqa_group);
+    return CQA_ERR_UNSUPPORTED;
 }
 
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
                   long num_tokens, int last_valid, float q_scale, cudaStream_t st)
 {
     if (ws->num_splits <= 0 || !ws->part_m || !ws->part_l || !ws->part_acc || !ws->out || !ws->topk_mask ||
-        !ws->value_mask) {
-        set_error("cqa_attend: workspace is missing partial buffers, masks or the output");
+        !ws->value_mask || !ws->tickets) {
+        set_error("cqa_attend: workspace is missing partial buffers, tickets, masks or the output");
         return CQA_ERR_INVALID;
     }
     if (nq > 0 && !ws->token_scores) { set_error("cqa_attend: token_scores missing"); return CQA_ERR_INVALID; }
@@ -348,6 +616,11 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
         set_error("cqa_attend: nact=%ld out of range (ld=%ld)", nact, (long)ws->ld);
         return CQA_ERR_INVALID;
     }
+    if (ws->num_splits > CQA_MAX_SPLITS || ws->dense_splits > CQA_MAX_DENSE_SPLITS) {
+        set_error("cqa_attend: at most %d splits and %d dense splits", CQA_MAX_SPLITS, CQA_MAX_DENSE_SPLITS);
+        return CQA_ERR_TOO_LARGE;
+    }
+    if (ws->num_splits > nact) { set_error("cqa_attend: more splits (%d) than blocks (%ld)", ws->num_splits, nact); return CQA_ERR_INVALID; }
     if (last_valid < 1 || last_valid > BS) { set_error("cqa_attend: last_block_valid=%d", last_valid); return CQA_ERR_INVALID; }
     if (!c->keys_t2 || !c->values_t2) {
         set_error("cqa_attend: Tier-2 key/value arrays are required (promoted and trailing blocks read them)");
@@ -363,11 +636,13 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
 }
 
 // ---------------------------------------------------------------------------
-// Built-in scratch for cqa_attend_static: split partials for callers that
-// cannot allocate device memory.  Layout: [Phase-2 m | l | acc][dense m | l | acc].
+// Built-in scratch for cqa_attend_static: split partials and merge tickets for
+// callers that cannot allocate device memory.
+// Layout: [Phase-2 m | l | acc][dense m | l | acc][tickets (int32)].
 constexpr long STATIC_P2 = (long)CQA_STATIC_MAX_HEADS * CQA_STATIC_MAX_SPLITS;
 constexpr long STATIC_DN = (long)CQA_STATIC_MAX_HEADS * CQA_STATIC_MAX_DENSE_SPLITS;
-constexpr long STATIC_FLOATS = STATIC_P2 * (D + 2) + STATIC_DN * (D + 2);
+constexpr long STATIC_TICKETS = 2 * CQA_STATIC_MAX_HEADS;
+constexpr long STATIC_FLOATS = STATIC_P2 * (D + 2) + STATIC_DN * (D + 2) + STATIC_TICKETS;
 static __device__ __align__(256) float g_static_partials[STATIC_FLOATS];
 
 // Device address of g_static_partials per device.  In host code the symbol is
@@ -419,6 +694,10 @@ int attend_static_launch(const cqa_cache *c, const cqa_workspace *ws, const void
     w.dense_m = dn;
     w.dense_l = dn + STATIC_DN;
     w.dense_acc = dn + 2 * STATIC_DN;
+    w.tickets = reinterpret_cast<int32_t *>(dn + STATIC_DN * (D + 2));
+    // The merge tickets are the only part of the shared array that must start at zero.
+    rc = check_cuda(cudaMemsetAsync(w.tickets, 0, STATIC_TICKETS * sizeof(int32_t), st), "cudaMemsetAsync(tickets)");
+    if (rc) return rc;
     return attend_launch(c, &w, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
 }
 

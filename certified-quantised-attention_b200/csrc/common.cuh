@@ -180,6 +180,65 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16 *p, flo
     }
 }
 
+
+// Raw (unconverted) 8-element loads, so many rows can be in flight in few registers.
+template <typename T> struct Raw8 { uint4 v; };
+template <> struct Raw8<float> { float4 a, b; };
+template <typename T>
+__device__ __forceinline__ Raw8<T> raw_load8(const T *p)
+{
+    Raw8<T> r;
+    r.v = *reinterpret_cast<const uint4 *>(p);
+    return r;
+}
+template <>
+__device__ __forceinline__ Raw8<float> raw_load8<float>(const float *p)
+{
+    Raw8<float> r;
+    r.a = *reinterpret_cast<const float4 *>(p);
+    r.b = *reinterpret_cast<const float4 *>(p + 4);
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ Raw8<T> raw_zero8()
+{
+    Raw8<T> r;
+    r.v = make_uint4(0u, 0u, 0u, 0u);
+    return r;
+}
+template <>
+__device__ __forceinline__ Raw8<float> raw_zero8<float>()
+{
+    Raw8<float> r;
+    r.a = make_float4(0.f, 0.f, 0.f, 0.f);
+    r.b = r.a;
+    return r;
+}
+__device__ __forceinline__ void raw_to_f(const Raw8<float> &r, float (&out)[8])
+{
+    out[0] = r.a.x; out[1] = r.a.y; out[2] = r.a.z; out[3] = r.a.w;
+    out[4] = r.b.x; out[5] = r.b.y; out[6] = r.b.z; out[7] = r.b.w;
+}
+__device__ __forceinline__ void raw_to_f(const Raw8<__half> &r, float (&out)[8])
+{
+    const __half2 *h = reinterpret_cast<const __half2 *>(&r.v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void raw_to_f(const Raw8<__nv_bfloat16> &r, float (&out)[8])
+{
+    const unsigned *w = reinterpret_cast<const unsigned *>(&r.v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
 // Scalar read of q in its runtime dtype.
 __device__ __forceinline__ float load_q(const void *q, int dtype, long idx)
 {

@@ -24,17 +24,22 @@ __device__ __forceinline__ void fp16_block_score_warp(const cqa_cache &c, const 
     load_q8(q, q_dtype, (long)h * D + 8 * L, qv);
     const T2 *base = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
     float lg[8];  // this half warp's tokens hw*8 .. hw*8+7 (all lanes hold all 8)
+    // issue the eight row loads together, then reduce (small code: this runs once per launch)
+    Raw8<T2> raw[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int t = hw * 8 + i;
+        const long ti = slot * BS + t;
+        const bool valid = valid_block && (bid * BS + t) < n_scoring_tokens && slot >= 0 && ti < c.keys_t2_rows;
+        raw[i] = valid ? raw_load8<T2>(base + ti * D + 8 * L) : raw_zero8<T2>();
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int t = hw * 8 + i;
         const long ti = slot * BS + t;
         const bool valid = valid_block && (bid * BS + t) < n_scoring_tokens && slot >= 0 && ti < c.keys_t2_rows;
         float kf[8];
-        if (valid) load8<T2>(base + ti * D + 8 * L, kf);
-        else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) kf[k] = 0.0f;
-        }
+        raw_to_f(raw[i], kf);
         float d = hw_sum(chain8(kf, qv));
         lg[i] = valid ? __fmul_rn(d, q_scale) : -INFINITY;
     }

@@ -59,11 +59,36 @@ __device__ __forceinline__ void score_issue(const cqa_cache &c, int kv, long b_f
     cp_async_commit();
 }
 
+// 8 signed bytes -> four float pairs, exactly: flip the sign bit (u = k + 128), drop each byte into the
+// mantissa of 2^23 with one logic op, and remove offset and scale with one fused multiply-add per pair.
+__device__ __forceinline__ void i8x8_to_f2(uint2 w, float2 (&k)[4])
+{
+    const unsigned M = 0x4B000000u;
+    const float2 cs = make_float2(1.0f, 0.00390625f);
+    const float2 off = make_float2(-8388736.0f, -32896.0f);   // -(2^23 + 128), -(2^15 + 128)
+    const unsigned x0 = w.x ^ 0x80808080u, x1 = w.y ^ 0x80808080u;
+    const unsigned x0h = x0 >> 16, x1h = x1 >> 16;
+    k[0] = __ffma2_rn(make_float2(__uint_as_float((x0 & 0xFFu) | M), __uint_as_float((x0 & 0xFF00u) | M)), cs, off);
+    k[1] = __ffma2_rn(make_float2(__uint_as_float((x0h & 0xFFu) | M), __uint_as_float((x0h & 0xFF00u) | M)), cs, off);
+    k[2] = __ffma2_rn(make_float2(__uint_as_float((x1 & 0xFFu) | M), __uint_as_float((x1 & 0xFF00u) | M)), cs, off);
+    k[3] = __ffma2_rn(make_float2(__uint_as_float((x1h & 0xFFu) | M), __uint_as_float((x1h & 0xFF00u) | M)), cs, off);
+}
+
+// chain8 on packed operands: the .x lanes are the even-channel chain, the .y lanes the odd one.
+__device__ __forceinline__ float chain8_f2(const float2 (&a)[4], const float2 (&b)[4])
+{
+    float2 p = __ffma2_rn(a[0], b[0], make_float2(0.0f, 0.0f));
+    p = __ffma2_rn(a[1], b[1], p);
+    p = __ffma2_rn(a[2], b[2], p);
+    p = __ffma2_rn(a[3], b[3], p);
+    return __fadd_rn(p.x, p.y);
+}
+
 template <int G>
-__global__ void __launch_bounds__(SCORE_WARPS * 32) score_blocks_kernel(cqa_cache c, const void *q, int q_dtype,
-                                                                       long nq, float q_scale, float *m_b,
-                                                                       float *s_b, long ld, float *tok,
-                                                                       int blocks_per_cta)
+__global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_cache c, const void *q, int q_dtype,
+                                                                          long nq, float q_scale, float *m_b,
+                                                                          float *s_b, long ld, float *tok,
+                                                                          int blocks_per_cta)
 {
     extern __shared__ __align__(16) char smem[];
     constexpr int GH = G >= 4 ? 4 : G;  // heads per register pass
@@ -73,12 +98,15 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32) score_blocks_kernel(cqa_cach
     const long b_begin = (long)blockIdx.x * blocks_per_cta;
     const long b_end = min(nq, b_begin + (long)blocks_per_cta);
     char *wbuf = smem + warp * 2 * STAGE_WARP;
+    float *s_q = reinterpret_cast<float *>(smem + SCORE_SMEM);   // [G][128] query rows of this KV group
 
     // Blocks of this warp: b_begin + 2*(warp + 8*it) + hw
     const long stride = 2 * SCORE_WARPS;
     long b0 = b_begin + 2 * warp;
     int stage = 0;
     if (b0 < b_end) score_issue(c, kv, b0, b_end, wbuf, lane);
+    for (int i = threadIdx.x; i < G * D; i += SCORE_WARPS * 32) s_q[i] = load_q(q, q_dtype, (long)kv * G * D + i);
+    __syncthreads();
 
     for (; b0 < b_end; b0 += stride) {
         const long bn = b0 + stride;
@@ -94,44 +122,52 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32) score_blocks_kernel(cqa_cach
         const char *kb = wbuf + stage * STAGE_WARP + hw * STAGE_HALF;
         const float *sc = reinterpret_cast<const float *>(kb + BLOCK_BYTES);
         const float *zp = sc + D;
-        float sg[8], zz[8];
-        if (live) {
-            load8<float>(sc + 8 * L, sg);
-            load8<float>(zp + 8 * L, zz);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { sg[i] = 0.0f; zz[i] = 0.0f; }
-        }
 #pragma unroll
         for (int pass = 0; pass < G / GH; ++pass) {
-            float qs[GH][8], zq[GH];
-#pragma unroll
-            for (int g = 0; g < GH; ++g) {
-                float qv[8];
-                load_q8(q, q_dtype, ((long)(kv * G + pass * GH + g)) * D + 8 * L, qv);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) qs[g][i] = __fmul_rn(qv[i], sg[i]);
-                zq[g] = hw_sum(chain8(qv, zz));
-            }
-            float acc[GH][BS];
-#pragma unroll
-            for (int j = 0; j < BS; ++j) {
-                const int t = j ^ L;
-                float kf[8];
+            float2 qs[GH][4];
+            float zq[GH];
+            {
+                float sg[8], zz[8];
                 if (live) {
-                    uint2 w = *reinterpret_cast<const uint2 *>(kb + t * D + 8 * L);
-                    i8x8_to_f(w, kf);
+                    load8<float>(sc + 8 * L, sg);
+                    load8<float>(zp + 8 * L, zz);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) kf[i] = 0.0f;
+                    for (int i = 0; i < 8; ++i) { sg[i] = 0.0f; zz[i] = 0.0f; }
                 }
 #pragma unroll
-                for (int g = 0; g < GH; ++g) acc[g][j] = chain8(kf, qs[g]);
+                for (int g = 0; g < GH; ++g) {
+                    float qv[8];
+                    load8<float>(s_q + (pass * GH + g) * D + 8 * L, qv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        qs[g][i] = make_float2(__fmul_rn(qv[2 * i], sg[2 * i]), __fmul_rn(qv[2 * i + 1], sg[2 * i + 1]));
+                    zq[g] = hw_sum(chain8(qv, zz));
+                }
+            }
+            // Tokens are visited in pairs (j^L, (j+8)^L): the first step of the 16-lane reduce-scatter
+            // (stride 8) is applied at once, so only 8 partial sums per head stay live.
+            float acc[GH][8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = j ^ L;
+                float2 klo[4], khi[4];
+                uint2 wlo = make_uint2(0x80808080u, 0x80808080u), whi = wlo;   // bytes that decode to 0
+                if (live) {
+                    wlo = *reinterpret_cast<const uint2 *>(kb + t * D + 8 * L);
+                    whi = *reinterpret_cast<const uint2 *>(kb + (t ^ 8) * D + 8 * L);
+                }
+                i8x8_to_f2(wlo, klo);
+                i8x8_to_f2(whi, khi);
+#pragma unroll
+                for (int g = 0; g < GH; ++g) {
+                    const float lo = chain8_f2(klo, qs[g]);
+                    const float hi = chain8_f2(khi, qs[g]);
+                    acc[g][j] = __fadd_rn(lo, __shfl_xor_sync(FULL, hi, 8));
+                }
             }
 #pragma unroll
             for (int g = 0; g < GH; ++g) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[g][j] = __fadd_rn(acc[g][j], __shfl_xor_sync(FULL, acc[g][j + 8], 8));
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[g][j] = __fadd_rn(acc[g][j], __shfl_xor_sync(FULL, acc[g][j + 4], 4));
 #pragma unroll
@@ -177,6 +213,23 @@ __global__ void __launch_bounds__(32) delta_bound_kernel(cqa_cache c, const void
     if (threadIdx.x == 0) delta[blockIdx.x] = d;
 }
 
+template <int G>
+static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
+                          float *s_b, long ld, float *tok, dim3 grid, int bpc, cudaStream_t st)
+{
+    constexpr int SMEM = SCORE_SMEM + G * D * 4;
+    static bool attr_set = false;
+    if (!attr_set) {
+        int rc = check_cuda(cudaFuncSetAttribute(score_blocks_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 SMEM),
+                            "cudaFuncSetAttribute(score_blocks_kernel)");
+        if (rc) return rc;
+        attr_set = true;
+    }
+    score_blocks_kernel<G><<<grid, SCORE_WARPS * 32, SMEM, st>>>(*c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, bpc);
+    return check_launch("score_blocks_kernel");
+}
+
 int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
                         float *s_b, long ld, float *tok, cudaStream_t st)
 {
@@ -187,35 +240,20 @@ int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq,
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
-    // two resident CTAs per SM; runs of blocks in multiples of 16 (one per half warp)
+    // two resident CTAs per SM
     long target_ctas = (long)sm_count * 2;
     long per_kv = (target_ctas + c->kv_heads - 1) / c->kv_heads;
     long bpc = (nq + per_kv - 1) / per_kv;
-    bpc = ((bpc + 15) / 16) * 16;
-    if (bpc < 16) bpc = 16;
+    if (bpc < 2) bpc = 2;
     dim3 grid((unsigned)((nq + bpc - 1) / bpc), (unsigned)c->kv_heads);
-#define CQA_SCORE_LAUNCH(GV)                                                                                  \
-    do {                                                                                                      \
-        static bool attr_set = false;                                                                         \
-        if (!attr_set) {                                                                                      \
-            int rc = check_cuda(cudaFuncSetAttribute(score_blocks_kernel<GV>,                                 \
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SCORE_SMEM), \
-                                "cudaFuncSetAttribute(score_blocks_kernel)");                                 \
-            if (rc) return rc;                                                                                \
-            attr_set = true;                                                                                  \
-        }                                                                                                     \
-        score_blocks_kernel<GV><<<grid, SCORE_WARPS * 32, SCORE_SMEM, st>>>(*c, q, q_dtype, nq, q_scale, m_b, \
-                                                                            s_b, ld, tok, (int)bpc);          \
-    } while (0)
     switch (c->gqa_group) {
-    case 1: CQA_SCORE_LAUNCH(1); break;
-    case 2: CQA_SCORE_LAUNCH(2); break;
-    case 4: CQA_SCORE_LAUNCH(4); break;
-    case 8: CQA_SCORE_LAUNCH(8); break;
-    default: set_error("score_blocks: unsupported gqa_group %d", c->gqa_group); return CQA_ERR_UNSUPPORTED;
+    case 1: return score_launch_g<1>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, st);
+    case 2: return score_launch_g<2>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, st);
+    case 4: return score_launch_g<4>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, st);
+    case 8: return score_launch_g<8>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, st);
     }
-#undef CQA_SCORE_LAUNCH
-    return check_launch("score_blocks_kernel");
+    set_error("score_blocks: unsupported gqa_group %d", c->gqa_group);
+    return CQA_ERR_UNSUPPORTED;
 }
 
 }  // namespace cqa

@@ -199,10 +199,15 @@ def hybrid_mixedv_split_k_cuda(*, keys_int8: Any, keys_scale: Any, keys_zero_poi
     part_m, part_l = buf("mixedv_m_part", (H, nsplit)), buf("mixedv_l_part", (H, nsplit))
     part_acc = buf("mixedv_acc_part", (H, nsplit, 128))
     out = buf("mixedv_output", (H, 128))
+    tickets = wsd.get("cqa_tickets")
+    if tickets is None or tickets.numel() != kv + H or tickets.device != dev:
+        tickets = torch.zeros(kv + H, dtype=torch.int32, device=dev)
+        wsd["cqa_tickets"] = tickets
     w.m_b, w.s_b, w.token_scores = m_b.data_ptr(), s_b.data_ptr(), tok.data_ptr()
     w.topk_mask, w.value_mask = tk.data_ptr(), vm.data_ptr()
     w.num_splits, w.dense_splits = nsplit, 0
     w.part_m, w.part_l, w.part_acc, w.out = part_m.data_ptr(), part_l.data_ptr(), part_acc.data_ptr(), out.data_ptr()
+    w.tickets = tickets.data_ptr()
     q = q_all.contiguous()
     qd = _lib.dtype_code(q.dtype)
     L = _lib.lib()

@@ -68,10 +68,12 @@ class _Workspace:
         self.dense_m = torch.empty(H, self.dense_splits, **f32)
         self.dense_l = torch.empty(H, self.dense_splits, **f32)
         self.dense_acc = torch.empty(H, self.dense_splits, 128, **f32)
-        # certificate structs followed by the four "any" flags: one D2H copy reads both
+        # certificate structs followed by the flag words (4 flags, dense-head count and list):
+        # one D2H copy reads both
         self.cert_bytes = H * _lib.CERT_BYTES
-        self.cert_buf = torch.zeros(self.cert_bytes + 16, **u8)
+        self.cert_buf = torch.zeros(self.cert_bytes + 4 * (5 + H), **u8)
         self.out = torch.empty(H, 128, **f32)
+        self.tickets = torch.zeros(cache.kv_heads + H, dtype=torch.int32, device=device)
         self.cert_host = None
         self.struct = _lib.CqaWorkspace()
 
@@ -96,13 +98,14 @@ class _Workspace:
         if nact is not None:
             # never more splits than eight-block groups of work
             ns = max(1, min(ns, (nact + 7) // 8))
-            ds = max(1, min(ds, (nact + 7) // 8))
+            ds = max(1, min(ds, (nact + 15) // 16))
         s.num_splits, s.dense_splits = ns, ds
         s.part_m, s.part_l, s.part_acc = self.part_m.data_ptr(), self.part_l.data_ptr(), self.part_acc.data_ptr()
         s.dense_m, s.dense_l, s.dense_acc = self.dense_m.data_ptr(), self.dense_l.data_ptr(), self.dense_acc.data_ptr()
         s.cert = self.cert_buf.data_ptr()
         s.any_flags = self.cert_buf.data_ptr() + self.cert_bytes
         s.out = self.out.data_ptr()
+        s.tickets = self.tickets.data_ptr()
         return s
 
     def read_cert(self) -> tuple[dict, list]:
@@ -541,7 +544,7 @@ def compute_adaptive_topk_mask(m_b, S_b, tau_cov: float = DEFAULT_TAU_COV, k_min
     expl = torch.empty(H, nb, dtype=torch.uint8, device=dev)
     sidx = torch.empty(H, hi, dtype=torch.int32, device=dev)
     scum = torch.empty(H, hi, **f32)
-    cert = torch.zeros(H * _lib.CERT_BYTES + 16, dtype=torch.uint8, device=dev)
+    cert = torch.zeros(H * _lib.CERT_BYTES + 4 * (5 + H), dtype=torch.uint8, device=dev)
     w = _lib.CqaWorkspace()
     w.ld = nb
     w.m_b, w.s_b, w.mass_frac = m.data_ptr(), s.data_ptr(), mass.data_ptr()

@@ -31,6 +31,8 @@ extern "C" {
 #define CQA_NGROUPS 8
 #define CQA_MAX_RANKING_K 32
 #define CQA_MAX_SORT_BLOCKS 16384 /* selector limit: quantised blocks per call */
+#define CQA_MAX_SPLITS 256        /* Phase-2 splits per KV head */
+#define CQA_MAX_DENSE_SPLITS 64   /* dense-recompute chunks per head */
 
 typedef enum cqa_status {
     CQA_OK = 0,
@@ -153,8 +155,10 @@ typedef struct cqa_workspace {
     float *dense_l;
     float *dense_acc;            /* [H][dense_splits][128] */
     cqa_head_cert *cert;         /* [H] */
-    int32_t *any_flags;          /* [4]: any rung1, any rung3, any rung4 (violation), any value promotion */
+    int32_t *any_flags;          /* [5 + H]: any rung1, any rung3, any rung4 (violation), any value promotion,
+                                    number of heads flagged for dense recompute, then their ids */
     float *out;                  /* [H][128] float32 */
+    int32_t *tickets;            /* [KV + H] merge tickets: zero them once after allocation; kernels leave them at zero */
 } cqa_workspace;
 
 const char *cqa_version(void);
@@ -226,7 +230,8 @@ int cqa_certify(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace 
 /* Phase 2: mixed INT8/FP16-key, INT4/FP16-value split-K attend over blocks
  * [0, nact) with `last_block_valid` valid tokens in the last block, the dense
  * FP16 recompute of heads whose cert[h].dense is set, and the LSE merge into
- * ws->out.  INT8 blocks reuse ws->token_scores.
+ * ws->out (one launch; the last CTA per KV head merges).  INT8 blocks reuse
+ * ws->token_scores.  ws->num_splits must not exceed nact.
  * Replaces hybrid_mixedv_split_k_cuda (backends/certified_blackwell.py:138-224),
  * selective_attend_multihead_hybrid_{int4v,mixedv,mixedv_split_k}
  * (kernels/selective_attend_triton.py:633-708, 1448-1576),

@@ -54,7 +54,7 @@ def test_static_scratch_attend_matches_caller_scratch_attend():
         ref = _attend(L.cqa_attend, cc, ws, wstruct, q, nq, nact, last_valid)
         # the static variant must not need the caller's partial buffers at all
         no_scratch = _lib.CqaWorkspace.from_buffer_copy(bytes(wstruct))
-        for f in ("part_m", "part_l", "part_acc", "dense_m", "dense_l", "dense_acc"):
+        for f in ("part_m", "part_l", "part_acc", "dense_m", "dense_l", "dense_acc", "tickets"):
             setattr(no_scratch, f, None)
         ws.out.zero_()
         got = _attend(L.cqa_attend_static, cc, ws, no_scratch, q, nq, nact, last_valid)
