@@ -35,43 +35,39 @@ __device__ __forceinline__ void cp_async_wait()
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-// Issue the copies of one warp stage: blocks b0 (lanes 0-15) and b0+1 (lanes 16-31).
-__device__ __forceinline__ void score_issue(const cqa_cache &c, int kv, long b_first, long b_end, char *stage,
+// Issue the copies of one warp stage: blocks b0 (lanes 0-15 consume it) and b0+1 (lanes 16-31).
+// A stage half is 192 chunks of 16 B: 128 of key bytes, 32 of scales, 32 of zero points; with 32 lanes
+// every copy of the twelve is of one kind, known at compile time.  Block numbers are clamped to the last
+// block of the CTA's range, so an odd tail block is simply scored twice (only one result is stored).
+__device__ __forceinline__ void score_issue(const cqa_cache &c, int kv, long b_first, long b_last, char *stage,
                                             int lane)
 {
-    // 6144 bytes = 384 chunks of 16 B; chunk i belongs to half (i / 192).
 #pragma unroll
-    for (int r = 0; r < 12; ++r) {
-        const int i = r * 32 + lane;
-        const int half = i / 192, j = i % 192;
-        const long b = b_first + half;
-        if (b < b_end) {
-            const char *src;
-            if (j < 128)
-                src = reinterpret_cast<const char *>(c.keys_int8) + ((long)kv * c.cap_tokens + b * BS) * D + j * 16;
-            else if (j < 160)
-                src = reinterpret_cast<const char *>(c.keys_scale + ((long)kv * c.max_blocks + b) * D) + (j - 128) * 16;
-            else
-                src = reinterpret_cast<const char *>(c.keys_zero_points + ((long)kv * c.max_blocks + b) * D) + (j - 160) * 16;
-            cp_async16(stage + half * STAGE_HALF + j * 16, src);
-        }
+    for (int half = 0; half < 2; ++half) {
+        const long b = min(b_first + half, b_last);
+        const char *keys = reinterpret_cast<const char *>(c.keys_int8) + ((long)kv * c.cap_tokens + b * BS) * D + lane * 16;
+        const char *sc = reinterpret_cast<const char *>(c.keys_scale + ((long)kv * c.max_blocks + b) * D) + lane * 16;
+        const char *zp = reinterpret_cast<const char *>(c.keys_zero_points + ((long)kv * c.max_blocks + b) * D) + lane * 16;
+        char *dst = stage + half * STAGE_HALF + lane * 16;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) cp_async16(dst + r * 512, keys + r * 512);
+        cp_async16(dst + BLOCK_BYTES, sc);
+        cp_async16(dst + BLOCK_BYTES + 512, zp);
     }
     cp_async_commit();
 }
 
 // 8 signed bytes -> four float pairs, exactly: flip the sign bit (u = k + 128), drop each byte into the
-// mantissa of 2^23 with one logic op, and remove offset and scale with one fused multiply-add per pair.
+// low mantissa byte of 2^23 with one byte permute, and remove the offset with one packed add per pair.
 __device__ __forceinline__ void i8x8_to_f2(uint2 w, float2 (&k)[4])
 {
     const unsigned M = 0x4B000000u;
-    const float2 cs = make_float2(1.0f, 0.00390625f);
-    const float2 off = make_float2(-8388736.0f, -32896.0f);   // -(2^23 + 128), -(2^15 + 128)
+    const float2 off = make_float2(-8388736.0f, -8388736.0f);   // -(2^23 + 128)
     const unsigned x0 = w.x ^ 0x80808080u, x1 = w.y ^ 0x80808080u;
-    const unsigned x0h = x0 >> 16, x1h = x1 >> 16;
-    k[0] = __ffma2_rn(make_float2(__uint_as_float((x0 & 0xFFu) | M), __uint_as_float((x0 & 0xFF00u) | M)), cs, off);
-    k[1] = __ffma2_rn(make_float2(__uint_as_float((x0h & 0xFFu) | M), __uint_as_float((x0h & 0xFF00u) | M)), cs, off);
-    k[2] = __ffma2_rn(make_float2(__uint_as_float((x1 & 0xFFu) | M), __uint_as_float((x1 & 0xFF00u) | M)), cs, off);
-    k[3] = __ffma2_rn(make_float2(__uint_as_float((x1h & 0xFFu) | M), __uint_as_float((x1h & 0xFF00u) | M)), cs, off);
+    k[0] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(x0, M, 0x7440)), __uint_as_float(__byte_perm(x0, M, 0x7441))), off);
+    k[1] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(x0, M, 0x7442)), __uint_as_float(__byte_perm(x0, M, 0x7443))), off);
+    k[2] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(x1, M, 0x7440)), __uint_as_float(__byte_perm(x1, M, 0x7441))), off);
+    k[3] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(x1, M, 0x7442)), __uint_as_float(__byte_perm(x1, M, 0x7443))), off);
 }
 
 // chain8 on packed operands: the .x lanes are the even-channel chain, the .y lanes the odd one.
@@ -97,6 +93,7 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
     const int L = lane & 15, hw = lane >> 4;
     const long b_begin = (long)blockIdx.x * blocks_per_cta;
     const long b_end = min(nq, b_begin + (long)blocks_per_cta);
+    const long b_last = b_end - 1;
     char *wbuf = smem + warp * 2 * STAGE_WARP;
     float *s_q = reinterpret_cast<float *>(smem + SCORE_SMEM);   // [G][128] query rows of this KV group
 
@@ -104,14 +101,14 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
     const long stride = 2 * SCORE_WARPS;
     long b0 = b_begin + 2 * warp;
     int stage = 0;
-    if (b0 < b_end) score_issue(c, kv, b0, b_end, wbuf, lane);
+    if (b0 < b_end) score_issue(c, kv, b0, b_last, wbuf, lane);
     for (int i = threadIdx.x; i < G * D; i += SCORE_WARPS * 32) s_q[i] = load_q(q, q_dtype, (long)kv * G * D + i);
     __syncthreads();
 
     for (; b0 < b_end; b0 += stride) {
         const long bn = b0 + stride;
         if (bn < b_end) {
-            score_issue(c, kv, bn, b_end, wbuf + (stage ^ 1) * STAGE_WARP, lane);
+            score_issue(c, kv, bn, b_last, wbuf + (stage ^ 1) * STAGE_WARP, lane);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -128,13 +125,8 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
             float zq[GH];
             {
                 float sg[8], zz[8];
-                if (live) {
-                    load8<float>(sc + 8 * L, sg);
-                    load8<float>(zp + 8 * L, zz);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) { sg[i] = 0.0f; zz[i] = 0.0f; }
-                }
+                load8<float>(sc + 8 * L, sg);
+                load8<float>(zp + 8 * L, zz);
 #pragma unroll
                 for (int g = 0; g < GH; ++g) {
                     float qv[8];
@@ -148,17 +140,13 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
             // Tokens are visited in pairs (j^L, (j+8)^L): the first step of the 16-lane reduce-scatter
             // (stride 8) is applied at once, so only 8 partial sums per head stay live.
             float acc[GH][8];
+            const char *krow = kb + 8 * L;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int t = j ^ L;
                 float2 klo[4], khi[4];
-                uint2 wlo = make_uint2(0x80808080u, 0x80808080u), whi = wlo;   // bytes that decode to 0
-                if (live) {
-                    wlo = *reinterpret_cast<const uint2 *>(kb + t * D + 8 * L);
-                    whi = *reinterpret_cast<const uint2 *>(kb + (t ^ 8) * D + 8 * L);
-                }
-                i8x8_to_f2(wlo, klo);
-                i8x8_to_f2(whi, khi);
+                i8x8_to_f2(*reinterpret_cast<const uint2 *>(krow + t * D), klo);
+                i8x8_to_f2(*reinterpret_cast<const uint2 *>(krow + (t ^ 8) * D), khi);
 #pragma unroll
                 for (int g = 0; g < GH; ++g) {
                     const float lo = chain8_f2(klo, qs[g]);

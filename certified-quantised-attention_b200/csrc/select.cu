@@ -33,14 +33,26 @@ typedef unsigned long long u64;
 // numbered points; the deltas land in the unused tail of cert[h].fp16_logmass.
 #ifdef CQA_PHASE_CLOCKS
 #define CQA_CLK(i) do { if (threadIdx.x == 0) phase_clk[i] = clock64(); } while (0)
+#define CQA_CLK_FLUSH(lo, hi) do { if (threadIdx.x == 0) for (int i_ = (lo); i_ <= (hi); ++i_) \
+    ct->fp16_logmass[16 + i_] = (float)(phase_clk[i_] - phase_clk[0]); } while (0)
+#define CQA_LM_ROWS 16
+#define CQA_DBG(i) do { if (threadIdx.x == 0) sh.dbg[i] = clock64(); } while (0)
 #else
 #define CQA_CLK(i) do { } while (0)
+#define CQA_DBG(i) do { } while (0)
+#define CQA_CLK_FLUSH(lo, hi) do { } while (0)
+#define CQA_LM_ROWS CQA_MAX_RANKING_K
 #endif
 
 struct SCShared {
     float red_f[SC_WARPS];
     u64 red_u[SC_WARPS * 4];
-    unsigned hist[256];
+    int red_i[2][SC_WARPS];
+    unsigned char rank_part[4][CAND];
+    unsigned short rank_pos[CAND];
+#ifdef CQA_PHASE_CLOCKS
+    long long dbg[8];
+#endif
     float bcast_f[8];
     int bcast_i[8];
     unsigned bcast_u[4];
@@ -133,139 +145,142 @@ __device__ __noinline__ void bitonic_sort_desc(u64 *keys, int n_pad)
     }
 }
 
-// One warp sorts 256 keys (descending) held 8 per lane, element index = lane*8 + r: compare-exchange
-// distances below 8 stay inside a lane, larger ones cross lanes by shuffles.  Fully unrolled (static
-// register indices); called from one place only so the code exists once.
-__device__ __noinline__ void warp_sort256_desc(u64 (&e)[8])
+// Sort the CAND keys of cand[] in place, descending, by rank counting: four threads (in four different
+// warps) share one key and count the keys above it in a quarter of the list each; every warp reads one
+// list entry at a time (a broadcast).  Real keys are distinct and non-zero; zero is padding and ends up
+// behind them.
+__device__ __forceinline__ void rank_sort_desc(u64 *cand, SCShared &sh)
 {
-    const int lane = threadIdx.x & 31;
-#pragma unroll
-    for (int k = 2; k <= 256; k <<= 1) {
-#pragma unroll
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            if (j >= 8) {
-                const int lm = j >> 3;
-                const bool lower = (lane & lm) == 0;
-#pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    const bool desc = (((lane << 3) | r) & k) == 0;
-                    const u64 o = shfl_xor_u64(e[r], lm);
-                    const bool keep_max = (lower == desc);
-                    const bool o_gt = o > e[r];
-                    e[r] = (keep_max == o_gt) ? o : e[r];
-                }
-            } else {
-#pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    if ((r & j) == 0) {
-                        const bool desc = (((lane << 3) | r) & k) == 0;
-                        const u64 a = e[r], b = e[r | j];
-                        const bool sw = desc ? (a < b) : (a > b);
-                        e[r] = sw ? b : a;
-                        e[r | j] = sw ? a : b;
-                    }
-                }
-            }
-        }
+    static_assert(CAND * 4 == SC_THREADS, "one key per four threads");
+    const int tid = threadIdx.x;
+    const int cidx = tid & (CAND - 1), part = tid >> 8;
+    const u64 key = cand[cidx];
+    const u64 *seg = cand + part * (CAND / 4);
+    int above = 0;
+#pragma unroll 8
+    for (int j = 0; j < CAND / 4; ++j) above += seg[j] > key ? 1 : 0;
+    sh.rank_part[part][cidx] = (unsigned char)above;   // at most 64
+    __syncthreads();
+    if (part == 0) {
+        const int pos = (int)sh.rank_part[0][cidx] + sh.rank_part[1][cidx] + sh.rank_part[2][cidx] + sh.rank_part[3][cidx];
+        cand[cidx] = 0ull;
+        sh.rank_pos[cidx] = (unsigned short)pos;
     }
+    __syncthreads();
+    if (part == 0 && key != 0ull) cand[sh.rank_pos[cidx]] = key;
+    __syncthreads();
+}
+
+// Sum of one int per thread over the CTA with a single barrier: per-warp sums go to one of two
+// alternating rows of sh.red_i, so the next call never overwrites a row that is still being read.
+__device__ __forceinline__ int block_sum_int(int v, SCShared &sh, int parity)
+{
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    v = __reduce_add_sync(FULL, v);
+    if (l == 0) sh.red_i[parity][w] = v;
+    __syncthreads();
+    return __reduce_add_sync(FULL, sh.red_i[parity][l]);
 }
 
 // The M = min(CAND, n) largest (value, lower-index-first) entries of vals[0..n), vals >= 0, sorted
 // descending into cand[0..CAND) (padding = 0).  Returns M.
+//
+// The value of the M-th largest entry is found bit by bit (most significant first): a bit is kept when
+// at least M entries are >= the candidate threshold.  Each step is one pass over the values and one
+// barrier, with no shared-memory atomics, and the search stops as soon as a threshold separates exactly
+// M entries.  Entries above the threshold are then compacted and ordered by rank counting.
 __device__ __noinline__ int select_top_sorted(const float *vals, int n, u64 *cand, SCShared &sh)
 {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    CQA_DBG(0);
     __syncthreads();
-    if (tid == 0) { sh.counter = 0; sh.counter2 = 0; }
+    CQA_DBG(1);
+    if (tid == 0) sh.counter = 0;
     for (int i = tid; i < CAND; i += SC_THREADS) cand[i] = 0ull;
-    __syncthreads();
     const int M = n < CAND ? n : CAND;
     if (n <= CAND) {
+        __syncthreads();
         for (int b = tid; b < n; b += SC_THREADS) cand[b] = make_key(vals[b], b);
     } else {
-        unsigned prefix = 0u, pmask = 0u;
-        int need = M;
-        for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            if (tid < 256) sh.hist[tid] = 0u;
-            __syncthreads();
-            for (int b0 = warp * 32; b0 < n; b0 += SC_THREADS) {
-                const int b = b0 + lane;
-                bool ok = false;
-                unsigned digit = 0;
-                if (b < n) {
-                    const unsigned bits = __float_as_uint(vals[b]);
-                    ok = (bits & pmask) == prefix;
-                    digit = (bits >> shift) & 255u;
-                }
-                // one shared-memory atomic per distinct digit in the warp
-                const unsigned act = __ballot_sync(FULL, ok);
-                if (ok) {
-                    const unsigned same = __match_any_sync(act, digit);
-                    if (lane == __ffs(same) - 1) atomicAdd(&sh.hist[digit], (unsigned)__popc(same));
-                }
+        unsigned thr = 0u;
+        int n_ge = n;            // entries >= thr
+        int parity = 0;
+        const int w = tid >> 5;
+        // Two bits per step: three candidate thresholds are counted at once, the per-warp counts travel
+        // as 10-bit fields of one word (a warp holds at most 512 entries).
+#pragma unroll 1
+        for (int bit = 30; bit >= 0 && n_ge != M; bit -= 2) {
+            const bool single = bit == 0;                 // 31 value bits: the last step decides one bit
+            const int lo = single ? 0 : bit - 1;
+            const unsigned t1 = thr | (1u << lo);                              // 01 (or 1)
+            const unsigned t2 = single ? 0xFFFFFFFFu : thr | (2u << lo);       // 10
+            const unsigned t3 = single ? 0xFFFFFFFFu : thr | (3u << lo);       // 11
+            unsigned local = 0;
+            for (int b = tid; b < n; b += SC_THREADS) {
+                const unsigned v = __float_as_uint(vals[b]);
+                local += (v >= t1 ? 1u : 0u) + (v >= t2 ? 1u << 10 : 0u) + (v >= t3 ? 1u << 20 : 0u);
             }
+            local = __reduce_add_sync(FULL, local);
+            if (lane == 0) sh.red_i[parity][w] = (int)local;
             __syncthreads();
-            if (warp == 0) {
-                // lane l owns bins 8l..8l+7; find the highest bin d with count(bins > d) < need <= count(bins >= d)
-                unsigned c[8], tot = 0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { c[i] = sh.hist[lane * 8 + i]; tot += c[i]; }
-                unsigned suffix = tot;   // inclusive suffix sum over lanes >= this one
-#pragma unroll
-                for (int s = 1; s < 32; s <<= 1) {
-                    const unsigned o = __shfl_down_sync(FULL, suffix, s);
-                    if (lane + s < 32) suffix += o;
-                }
-                const unsigned above_lane = suffix - tot;   // elements in the bins of higher lanes
-                if (above_lane < (unsigned)need && suffix >= (unsigned)need) {
-                    unsigned above = above_lane;
-                    int d = 7;
-                    for (; d > 0; --d) {
-                        if (above + c[d] >= (unsigned)need) break;
-                        above += c[d];
-                    }
-                    sh.bcast_u[0] = (unsigned)(lane * 8 + d);
-                    sh.bcast_u[1] = above;
-                }
+            const unsigned p = (unsigned)sh.red_i[parity][lane];
+            parity ^= 1;
+            // cross-warp totals can reach 16384: two 16-bit fields in one reduction, the third alone
+            const unsigned c12 = __reduce_add_sync(FULL, (p & 1023u) | (((p >> 10) & 1023u) << 16));
+            const int c3 = (int)__reduce_add_sync(FULL, p >> 20);
+            const int c1 = (int)(c12 & 0xFFFFu), c2 = (int)(c12 >> 16);
+            if (!single && c3 >= M) { thr = t3; n_ge = c3; }
+            else if (!single && c2 >= M) { thr = t2; n_ge = c2; }
+            else if (c1 >= M) { thr = t1; n_ge = c1; }
+        }
+        // n_ge == M: the entries >= thr are the answer.  Otherwise thr is the value of the M-th largest
+        // entry and several entries equal it: take everything above, then the lowest block ids among the equal.
+        const bool ties = n_ge != M;
+        CQA_DBG(2);
+        __syncthreads();   // cand is zeroed, sh.counter is 0
+        for (int b0 = tid - lane; b0 < n; b0 += SC_THREADS) {
+            const int b = b0 + lane;
+            const unsigned bits = b < n ? __float_as_uint(vals[b]) : 0u;
+            const bool take = b < n && (ties ? bits > thr : bits >= thr);
+            const unsigned who = __ballot_sync(FULL, take);
+            if (who) {
+                int base = 0;
+                if (lane == 0) base = atomicAdd(&sh.counter, __popc(who));
+                base = __shfl_sync(FULL, base, 0);
+                if (take) cand[base + __popc(who & ((1u << lane) - 1u))] = make_key(vals[b], b);
             }
-            __syncthreads();
-            prefix |= sh.bcast_u[0] << shift;
-            pmask |= 255u << shift;
-            need -= (int)sh.bcast_u[1];
-            __syncthreads();
         }
-        const unsigned thr = prefix;   // value bits of the M-th largest entry
-        const int need_eq = need;      // entries equal to it to take (lowest block ids first)
-        int cnt_eq = 0;
-        for (int b = tid; b < n; b += SC_THREADS) {
-            const unsigned bits = __float_as_uint(vals[b]);
-            if (bits > thr) cand[atomicAdd(&sh.counter, 1)] = make_key(vals[b], b);
-            else if (bits == thr) ++cnt_eq;
-        }
-        if (cnt_eq) atomicAdd(&sh.counter2, cnt_eq);
-        __syncthreads();
-        if (sh.counter2 == need_eq) {
-            for (int b = tid; b < n; b += SC_THREADS)
-                if (__float_as_uint(vals[b]) == thr) cand[atomicAdd(&sh.counter, 1)] = make_key(vals[b], b);
-        } else if (tid == 0) {
-            // more equal values than needed (exact ties): take the lowest block ids
-            int taken = 0;
-            const int base = sh.counter;
-            for (int b = 0; b < n && taken < need_eq; ++b)
-                if (__float_as_uint(vals[b]) == thr) { cand[base + taken] = make_key(vals[b], b); ++taken; }
+        CQA_DBG(3);
+        if (ties) {
+            // entries equal to the threshold fill the remaining places in block order: an ordered compaction,
+            // 1024 consecutive blocks per round (per-warp counts, then an exclusive scan over the warps)
+            __syncthreads();
+            int taken = sh.counter;
+            for (int b0 = 0; b0 < n && taken < M; b0 += SC_THREADS) {
+                const int b = b0 + tid;
+                const bool eq = b < n && __float_as_uint(vals[b]) == thr;
+                const unsigned who = __ballot_sync(FULL, eq);
+                if (lane == 0) sh.red_i[parity][w] = __popc(who);
+                __syncthreads();
+                const int cw = sh.red_i[parity][lane];
+                parity ^= 1;
+                int incl = cw;   // inclusive scan of the per-warp counts
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(FULL, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                const int before = __shfl_sync(FULL, incl - cw, w);
+                const int pos = taken + before + __popc(who & ((1u << lane) - 1u));
+                if (eq && pos < M) cand[pos] = make_key(vals[b], b);
+                taken += __shfl_sync(FULL, incl, 31);
+            }
         }
     }
     __syncthreads();
-    if (warp == 0) {
-        u64 e[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) e[r] = cand[lane * 8 + r];
-        warp_sort256_desc(e);
-#pragma unroll
-        for (int r = 0; r < 8; ++r) cand[lane * 8 + r] = e[r];
-    }
-    __syncthreads();
+    CQA_DBG(4);
+    rank_sort_desc(cand, sh);
+    CQA_DBG(5);
     return M;
 }
 
@@ -280,34 +295,34 @@ __device__ __forceinline__ void insert4(u64 (&t)[4], u64 k)
         t[i] = hi;
     }
 }
-// Butterfly merge of per-lane sorted 4-lists: afterwards every lane holds the warp's four largest keys.
-__device__ __noinline__ void warp_merge_top4(u64 (&t)[4])
+// The four largest keys held by a warp, given one descending 4-list per lane (keys distinct, zero is
+// padding): four rounds of a warp-wide maximum over the list heads; the lane that wins pops its list.
+__device__ __forceinline__ void warp_top4(u64 (&t)[4], u64 (&out)[4])
 {
-#pragma unroll 1
-    for (int s = 16; s >= 1; s >>= 1) {
-        u64 o[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) o[i] = shfl_xor_u64(t[i], s);
-        // keep the 4 largest of two descending lists: max(t[i], o[3-i]) is a bitonic sequence; two more stages sort it
-        u64 x[4];
+    for (int r = 0; r < 4; ++r) {
+        u64 best = t[0];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) x[i] = t[i] > o[3 - i] ? t[i] : o[3 - i];
-        u64 a0 = x[0] > x[2] ? x[0] : x[2], a2 = x[0] > x[2] ? x[2] : x[0];
-        u64 a1 = x[1] > x[3] ? x[1] : x[3], a3 = x[1] > x[3] ? x[3] : x[1];
-        t[0] = a0 > a1 ? a0 : a1;
-        t[1] = a0 > a1 ? a1 : a0;
-        t[2] = a2 > a3 ? a2 : a3;
-        t[3] = a2 > a3 ? a3 : a2;
+        for (int s = 16; s >= 1; s >>= 1) {
+            const u64 o = shfl_xor_u64(best, s);
+            best = o > best ? o : best;
+        }
+        out[r] = best;
+        if (t[0] == best) { t[0] = t[1]; t[1] = t[2]; t[2] = t[3]; t[3] = 0ull; }
     }
 }
 
 // Dynamic shared memory: A[n_pad] B[n_pad] C[n_pad] (floats), cand[CAND] (u64), cum[CAND], gsum, leaf, mask[n_pad]
 // (bytes).  The full-sort fallbacks alias their keys over B and C.
+#ifdef CQA_WARM_REPEAT
+#define CQA_BODY_QUAL __device__ __noinline__   // instrumentation: the body runs twice, the second time with warm code
+#else
+#define CQA_BODY_QUAL __device__ __forceinline__
+#endif
 template <typename T2>
-__global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_knobs kn, cqa_workspace ws, const void *q,
-                                                            int q_dtype, long nq, long nact, const float *u, long u_ld,
-                                                            int n_pad, int hi, int base_width, int two_level, int rk,
-                                                            int phases, int role_base)
+CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const cqa_workspace &ws, const void *q,
+                                int q_dtype, long nq, long nact, const float *u, long u_ld, int n_pad, int hi,
+                                int base_width, int two_level, int rk, int phases, int role_base)
 {
     extern __shared__ __align__(16) unsigned char dsm[];
     float *A = reinterpret_cast<float *>(dsm);                 // m_b, later mass*eta
@@ -518,7 +533,7 @@ __global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_kn
         }
     }
     CQA_CLK(5);
-    if (role == 0) return;
+    if (role == 0) { CQA_CLK_FLUSH(1, 5); return; }
     __syncthreads();
 
     // ---- ranking / boundary / score consistency
@@ -528,20 +543,22 @@ __global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_kn
             u64 t4[4] = {0ull, 0ull, 0ull, 0ull};
             for (int b = tid; b < n; b += SC_THREADS)
                 insert4(t4, ((u64)orderable(A[b]) << 32) | (u64)(0xFFFFFFFFu - (unsigned)b));
-            warp_merge_top4(t4);
+            CQA_CLK(15);
+            u64 w4[4];
+            warp_top4(t4, w4);
             if (lane == 0) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) s_top[warp * 4 + i] = t4[i];
+                for (int i = 0; i < 4; ++i) s_top[warp * 4 + i] = w4[i];
             }
             __syncthreads();
             if (warp == 0) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) t4[i] = s_top[lane * 4 + i];
-                warp_merge_top4(t4);
+                warp_top4(t4, w4);
                 if (lane == 0) {
                     for (int r = 0; r < rk; ++r) {
-                        top_idx[r] = key_idx(t4[r]);
-                        top_i8[r] = A[key_idx(t4[r])];
+                        top_idx[r] = key_idx(w4[r]);
+                        top_i8[r] = A[key_idx(w4[r])];
                     }
                 }
             }
@@ -576,6 +593,12 @@ __global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_kn
         }
         __syncthreads();
         CQA_CLK(6);
+        // Boundary bound: max over the blocks outside the top list of (ell_b + delta).  Rounding is monotone,
+        // so it equals (max ell_b) + delta; the maximum is taken by the warps that neither re-score a block
+        // nor compute delta, while those wait for Tier-2 rows.
+        const int ub_first = rk + 1, ub_warps = SC_WARPS - ub_first;
+        const bool overlap = ub_warps >= 8;
+        float ubm = -INFINITY;
         if (warp < rk) {
             float s, lm;
             fp16_block_score_warp<T2>(c, q, q_dtype, h, (long)top_idx[warp], nq * BS, kn.q_scale, s, lm);
@@ -583,83 +606,96 @@ __global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_kn
         } else if (warp == rk) {
             const float d = delta_bound_warp(c, q, q_dtype, h);
             if (lane == 0) s_delta = d;
+        } else if (overlap && kn.ranking_fallback) {
+            for (int b = (warp - ub_first) * 32 + lane; b < n; b += ub_warps * 32) {
+                bool in_top = false;
+                for (int r = 0; r < rk; ++r) in_top |= (top_idx[r] == b);
+                if (!in_top) ubm = fmaxf(ubm, B[b]);
+            }
+        }
+        if (overlap) {
+            ubm = warp_max(ubm);
+            if (lane == 0) sh.red_f[warp] = ubm;
         }
         __syncthreads();
         CQA_CLK(7);
         const float delta = s_delta;
         float ub = -INFINITY;
         if (kn.ranking_fallback) {
-            for (int b = tid; b < n; b += SC_THREADS) {
-                bool in_top = false;
-                for (int r = 0; r < rk; ++r) in_top |= (top_idx[r] == b);
-                if (!in_top) ub = fmaxf(ub, __fadd_rn(B[b], delta));
+            if (overlap) {
+                ubm = warp_max(sh.red_f[lane]);
+            } else {
+                for (int b = tid; b < n; b += SC_THREADS) {
+                    bool in_top = false;
+                    for (int r = 0; r < rk; ++r) in_top |= (top_idx[r] == b);
+                    if (!in_top) ubm = fmaxf(ubm, B[b]);
+                }
+                ubm = block_max(ubm, sh);
             }
-            ub = block_max(ub, sh);
+            ub = __fadd_rn(ubm, delta);
         }
         CQA_CLK(8);
-        if (tid == 0) {
-            int rank16[CQA_MAX_RANKING_K];
-            bool used[CQA_MAX_RANKING_K];
-            for (int i = 0; i < rk; ++i) used[i] = false;
-            for (int p = 0; p < rk; ++p) {
-                int bi = -1;
-                for (int i = 0; i < rk; ++i)
-                    if (!used[i] && (bi < 0 || top_f16[i] > top_f16[bi])) bi = i;
-                used[bi] = true;
-                rank16[p] = bi;
+        if (warp == 1) {
+            // the certificate's per-candidate rows do not depend on the flag logic below
+            ct->top_blocks[lane] = lane < rk ? top_idx[lane] : -1;
+            if (lane < CQA_LM_ROWS) ct->fp16_scores[lane] = lane < rk ? top_f16[lane] : 0.0f;
+            if (lane < CQA_LM_ROWS) ct->fp16_logmass[lane] = lane < rk ? top_lm[lane] : 0.0f;
+        }
+        if (warp == 0) {
+            // lane i owns candidate i (candidates are in INT8 order): its position in the stable
+            // descending FP16 order, and in the descending FP16 log-mass order
+            const bool mine = lane < rk;
+            const float f = mine ? top_f16[lane] : 0.0f;
+            const float lmv = mine ? top_lm[lane] : 0.0f;
+            int pos16 = 0, poslm = 0;
+#pragma unroll 1
+            for (int j = 0; j < rk; ++j) {
+                const float fj = top_f16[j], lj = top_lm[j];
+                pos16 += (fj > f || (fj == f && j < lane)) ? 1 : 0;
+                poslm += (lj > lmv || (lj == lmv && j < lane)) ? 1 : 0;
             }
-            int dis_main = 0, dis_r1 = 0, dis_r3 = 0, boundary = 0, violation = 0;
+            const int r_main = min(kn.ranking_r, rk);
+            const bool rf = kn.ranking_fallback && kn.ranking_r > 0;
+            const bool d = mine && pos16 != lane;
+            const int dis_main = (rf && __any_sync(FULL, d && lane < r_main)) ? 1 : 0;
+            const int dis_r1 = (rf && __any_sync(FULL, d && lane < 1)) ? 1 : 0;
+            const int dis_r3 = (rf && __any_sync(FULL, d && lane < 3)) ? 1 : 0;
+            const unsigned who_r = __ballot_sync(FULL, mine && poslm == r_main - 1);
+            const unsigned who_1 = __ballot_sync(FULL, mine && pos16 == 0);
+            const unsigned who_2 = __ballot_sync(FULL, mine && pos16 == 1);
             float ell_r = -INFINITY;
-            if (kn.ranking_fallback) {
-                const int r_main = min(kn.ranking_r, rk);
-                for (int p = 0; p < rk; ++p) {
-                    const bool d = rank16[p] != p;
-                    if (p < r_main) dis_main |= d;
-                    if (p < 1) dis_r1 |= d;
-                    if (p < 3) dis_r3 |= d;
-                }
-                float tmp[CQA_MAX_RANKING_K];
-                for (int i = 0; i < rk; ++i) tmp[i] = top_lm[i];
-                for (int p = 0; p < r_main; ++p) {
-                    int bi = p;
-                    for (int i = p + 1; i < rk; ++i)
-                        if (tmp[i] > tmp[bi]) bi = i;
-                    const float t = tmp[p]; tmp[p] = tmp[bi]; tmp[bi] = t;
-                }
-                ell_r = r_main > 0 ? tmp[r_main - 1] : -INFINITY;
-                boundary = (r_main > 0 && ub > ell_r) ? 1 : 0;
-                if (kn.ranking_r <= 0) { dis_main = 0; dis_r1 = 0; dis_r3 = 0; }
-            }
+            if (kn.ranking_fallback && r_main > 0) ell_r = __shfl_sync(FULL, lmv, __ffs(who_r) - 1);
+            const float top1 = __shfl_sync(FULL, f, __ffs(who_1) - 1);
+            const float top2 = who_2 ? __shfl_sync(FULL, f, __ffs(who_2) - 1) : top1;
+            const int boundary = (kn.ranking_fallback && r_main > 0 && ub > ell_r) ? 1 : 0;
+            int violation = 0;
             if (kn.score_consistency) {
                 const float thr = __fadd_rn(delta, kn.eps_guard);
-                for (int i = 0; i < rk; ++i)
-                    if (fabsf(__fsub_rn(top_f16[i], top_i8[i])) > thr) violation = 1;
+                violation = __any_sync(FULL, mine && fabsf(__fsub_rn(f, top_i8[lane])) > thr) ? 1 : 0;
             }
-            const int rung3 = (dis_main | boundary) ? 1 : 0;
-            ct->ranking_disagree = dis_main;
-            ct->ranking_disagree_r1 = dis_r1;
-            ct->ranking_disagree_r3 = dis_r3;
-            ct->boundary_triggered = boundary;
-            ct->rung3 = rung3;
-            ct->consistency_violation = violation;
-            ct->delta = delta;
-            ct->boundary_ub = ub;
-            ct->ell_fp16_r = ell_r;
-            ct->fp16_top1 = top_f16[rank16[0]];
-            ct->fp16_top2 = rk > 1 ? top_f16[rank16[1]] : top_f16[rank16[0]];
-            ct->int8_top1 = top_i8[0];
-            for (int i = 0; i < CQA_MAX_RANKING_K; ++i) {
-                ct->top_blocks[i] = i < rk ? top_idx[i] : -1;
-                ct->fp16_scores[i] = i < rk ? top_f16[i] : 0.0f;
-                ct->fp16_logmass[i] = i < rk ? top_lm[i] : 0.0f;
+            if (lane == 0) {
+                const int rung3 = (dis_main | boundary) ? 1 : 0;
+                ct->ranking_disagree = dis_main;
+                ct->ranking_disagree_r1 = dis_r1;
+                ct->ranking_disagree_r3 = dis_r3;
+                ct->boundary_triggered = boundary;
+                ct->rung3 = rung3;
+                ct->consistency_violation = violation;
+                ct->delta = delta;
+                ct->boundary_ub = ub;
+                ct->ell_fp16_r = ell_r;
+                ct->fp16_top1 = top1;
+                ct->fp16_top2 = top2;
+                ct->int8_top1 = top_i8[0];
+                const int dense = (kn.ranking_fallback && kn.rung3_recompute && rung3) ? 1 : 0;
+                ct->dense = dense;
+                if (dense) {
+                    const int slot = atomicAdd(ws.any_flags + 4, 1);
+                    if (slot < (int)gridDim.x) ws.any_flags[5 + slot] = h;
+                }
+                if (rung3) atomicOr(ws.any_flags + 1, 1);
+                if (violation) atomicOr(ws.any_flags + 2, 1);
             }
-            ct->dense = (kn.ranking_fallback && kn.rung3_recompute && rung3) ? 1 : 0;
-            if (ct->dense) {
-                const int slot = atomicAdd(ws.any_flags + 4, 1);
-                ws.any_flags[5 + slot] = h;
-            }
-            if (rung3) atomicOr(ws.any_flags + 1, 1);
-            if (violation) atomicOr(ws.any_flags + 2, 1);
         }
     } else if (role == 1 && tid == 0) {
         ct->ranking_disagree = ct->ranking_disagree_r1 = ct->ranking_disagree_r3 = 0;
@@ -672,7 +708,7 @@ __global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_kn
     }
 
     CQA_CLK(9);
-    if (role == 1) return;
+    if (role == 1) { CQA_CLK_FLUSH(6, 9); CQA_CLK_FLUSH(15, 15); return; }
     // ---- Rung-2 value check
     unsigned char *vm = ws.value_mask + (long)h * ws.ld;
     if (!have_int4) {
@@ -757,11 +793,25 @@ __global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_kn
         ct->e_val = fmaxf(__fsub_rn(e_pre, sh.bcast_f[1]), 0.0f);
         ct->value_promoted_blocks = sh.bcast_i[1];
         if (sh.bcast_i[1] > 0) atomicOr(ws.any_flags + 3, 1);
-#ifdef CQA_PHASE_CLOCKS
-        phase_clk[14] = clock64();
-        for (int i = 1; i < 15; ++i) ct->fp16_logmass[16 + i] = phase_clk[i] ? (float)(phase_clk[i] - phase_clk[0]) : 0.0f;
-#endif
     }
+    CQA_CLK(14);
+    CQA_CLK_FLUSH(10, 14);
+#ifdef CQA_PHASE_CLOCKS
+    if (threadIdx.x == 0) for (int i = 0; i < 6; ++i) ct->fp16_scores[16 + i] = (float)(sh.dbg[i] - phase_clk[0]);
+#endif
+}
+
+template <typename T2>
+__global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_knobs kn, cqa_workspace ws, const void *q,
+                                                            int q_dtype, long nq, long nact, const float *u, long u_ld,
+                                                            int n_pad, int hi, int base_width, int two_level, int rk,
+                                                            int phases, int role_base)
+{
+#ifdef CQA_WARM_REPEAT
+    selcert_body<T2>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
+    __syncthreads();
+#endif
+    selcert_body<T2>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
 }
 
 static int next_pow2(long n)

@@ -140,6 +140,27 @@ def test_layer_step_vs_oracle_large(n_tokens, planted, dtype, seed):
           f"value_fallback_blocks={stats.get('value_fallback_blocks', 0)} out_err={err:.2e}")
 
 
+def test_exact_ties_take_lowest_block_ids():
+    """Every 16-token block repeats the same keys and values, so all mass fractions and all value-error
+    terms tie exactly: the selector, the top-4 list and the value check must break the ties by block id
+    exactly as the oracle does (512 blocks, more than the 256 candidates the selector keeps)."""
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(21, 8192, dtype=dtype, n_planted_blocks=0)
+    k = np.tile(base.k[:, :16], (1, 512, 1)).copy()
+    v = np.tile(base.v[:, :16], (1, 512, 1)).copy()
+    # a second family of blocks so that two distinct tied values exist
+    k[:, 4096:] = np.tile(base.k[:, 16:32], (1, 256, 1))
+    v[:, 4096:] = np.tile(base.v[:, 16:32], (1, 256, 1))
+    cc = hz.make_cuda_cache(k, v, dtype, 64)
+    oc = hz.make_oracle_cache(k, v, dtype, 64)
+    rng = np.random.default_rng(21)
+    u = rng.random((32, oc.num_quantized_blocks), dtype=np.float32)
+    for knobs in (_knobs(), _knobs(v_tolerance=0.0), _knobs(k_max=None, rung1_threshold=-1.0)):
+        R = orc.layer_step(oc, base.q, 4, **_oracle_knobs(knobs, u))
+        out, _ = hz.cuda_step(cc, base.q, dtype, 4, knobs, u)
+        hz.compare_step(cc, R, out, f"ties {knobs['v_tolerance']} {knobs['k_max']}")
+
+
 def test_decode_loop_bit_exact_selections():
     """48 decode steps (3 block completions) at 4K context: every step's
     selections, flags and appended bytes match the oracle."""
