@@ -20,7 +20,9 @@ SYMBOLS = [
     "cqa_version", "cqa_last_error", "cqa_quantize_blocks", "cqa_append_token", "cqa_int4_quantise",
     "cqa_score_blocks", "cqa_select", "cqa_fp16_block_scores", "cqa_delta_bound", "cqa_certify",
     "cqa_attend", "cqa_attend_static", "cqa_layer_step", "cqa_suggest_splits",
+    "cqa_select_certify_local", "cqa_rescore_owned", "cqa_certify_given", "cqa_merge_partials",
 ]
+PARTIAL_STRIDE = 130
 
 vp = C.c_void_p
 
@@ -78,6 +80,7 @@ class CqaWorkspace(C.Structure):
         ("part_m", vp), ("part_l", vp), ("part_acc", vp),
         ("dense_m", vp), ("dense_l", vp), ("dense_acc", vp),
         ("cert", vp), ("any_flags", vp), ("out", vp), ("tickets", vp),
+        ("given_fp16", vp), ("partial_out", vp),
     ]
 
 
@@ -121,6 +124,10 @@ def lib() -> C.CDLL:
     L.cqa_attend_static.argtypes = [pc, pw, vp, i32, i64, i64, i64, i32, f32, vp]
     L.cqa_layer_step.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp, i64, vp]
     L.cqa_suggest_splits.argtypes = [i32, i32, i64, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    L.cqa_select_certify_local.argtypes = [pc, pk, pw, i64, i64, vp, i64, vp]
+    L.cqa_rescore_owned.argtypes = [pc, vp, vp, i32, i64, i64, f32, vp, vp]
+    L.cqa_certify_given.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp]
+    L.cqa_merge_partials.argtypes = [vp, i32, i32, vp, vp]
     for s in SYMBOLS[2:]:
         getattr(L, s).restype = C.c_int
     _lib = L

@@ -31,6 +31,13 @@ int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *
                   const float *u, long u_ld, cudaStream_t st);
 int certify_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
                    long nq, long nact, cudaStream_t st);
+int select_certify_local_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq,
+                                long nact, const float *u, long u_ld, cudaStream_t st);
+int certify_given_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q,
+                         int q_dtype, long nq, long nact, cudaStream_t st);
+int rescore_owned_launch(const cqa_cache *c, const cqa_head_cert *cert, const void *q, int q_dtype, long first_block,
+                         long n_local, float q_scale, float *out, cudaStream_t st);
+int merge_partials_launch(const float *parts, int n_parts, int n_heads, float *out, cudaStream_t st);
 int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
                    long nq, long nact, const float *u, long u_ld, int phases, cudaStream_t st);
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
@@ -96,6 +103,54 @@ extern "C" int cqa_certify(const cqa_cache *c, const cqa_knobs *knobs, const cqa
     if (!ws->value_mask) { set_error("cqa_certify: value_mask missing"); return CQA_ERR_INVALID; }
     if (nact < nq || nact > nq + 1 || nact > ws->ld) { set_error("cqa_certify: bad nact"); return CQA_ERR_INVALID; }
     return certify_launch(c, knobs, ws, q, q_dtype, nq, nact, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_select_certify_local(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, int64_t nq,
+                                        int64_t nact, const float *exploration_u, int64_t u_ld, void *stream)
+{
+    int rc = check_common(c, ws, "cqa_select_certify_local");
+    if (rc) return rc;
+    if (!knobs) { set_error("cqa_select_certify_local: NULL knobs"); return CQA_ERR_INVALID; }
+    rc = check_select_ws(ws, "cqa_select_certify_local");
+    if (rc) return rc;
+    if (!ws->value_mask) { set_error("cqa_select_certify_local: value_mask missing"); return CQA_ERR_INVALID; }
+    if (nact < nq || nact > nq + 1 || nact > ws->ld) {
+        set_error("cqa_select_certify_local: nact=%ld inconsistent with nq=%ld (ld=%ld)", (long)nact, (long)nq, (long)ws->ld);
+        return CQA_ERR_INVALID;
+    }
+    if (!(knobs->tau_cov > 0.0f)) { set_error("cqa_select_certify_local: tau_cov must be positive"); return CQA_ERR_INVALID; }
+    if (exploration_u && u_ld < nq) { set_error("cqa_select_certify_local: exploration_u leading dimension too small"); return CQA_ERR_INVALID; }
+    return select_certify_local_launch(c, knobs, ws, nq, nact, exploration_u, u_ld, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_rescore_owned(const cqa_cache *c, const cqa_head_cert *cert, const void *q, int q_dtype,
+                                 int64_t first_block, int64_t n_local, float q_scale, float *out, void *stream)
+{
+    if (!c || !cert || !q || !out || !c->keys_t2) { set_error("cqa_rescore_owned: NULL pointer"); return CQA_ERR_INVALID; }
+    if (first_block < 0 || n_local < 0 || n_local > c->max_blocks) {
+        set_error("cqa_rescore_owned: block range [%ld, +%ld) does not fit the local cache", (long)first_block, (long)n_local);
+        return CQA_ERR_INVALID;
+    }
+    if (q_dtype < 0 || q_dtype > 2) { set_error("cqa_rescore_owned: unknown q dtype"); return CQA_ERR_INVALID; }
+    return rescore_owned_launch(c, cert, q, q_dtype, first_block, n_local, q_scale, out, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_certify_given(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *q,
+                                 int q_dtype, int64_t nq, int64_t nact, void *stream)
+{
+    int rc = check_common(c, ws, "cqa_certify_given");
+    if (rc) return rc;
+    if (!knobs || !q) { set_error("cqa_certify_given: NULL knobs or q"); return CQA_ERR_INVALID; }
+    rc = check_select_ws(ws, "cqa_certify_given");
+    if (rc) return rc;
+    if (nact < nq || nact > nq + 1 || nact > ws->ld) { set_error("cqa_certify_given: bad nact"); return CQA_ERR_INVALID; }
+    return certify_given_launch(c, knobs, ws, q, q_dtype, nq, nact, (cudaStream_t)stream);
+}
+
+extern "C" int cqa_merge_partials(const float *parts, int n_parts, int n_heads, float *out, void *stream)
+{
+    if (!parts || !out || n_parts <= 0 || n_heads <= 0) { set_error("cqa_merge_partials: bad arguments"); return CQA_ERR_INVALID; }
+    return merge_partials_launch(parts, n_parts, n_heads, out, (cudaStream_t)stream);
 }
 
 extern "C" int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,

@@ -60,6 +60,11 @@ struct AttLayout {
     static constexpr int MERGE_B = (2 * G * CQA_MAX_SPLITS + G + 4 + ATT_WARPS * D) * 4;
     static constexpr int MERGE = MERGE_A > MERGE_B ? MERGE_A : MERGE_B;
     static constexpr int RING_BYTES = RING > MERGE ? RING : MERGE;
+    // per warp: two weight tiles [16 tokens][G] of (w, w) pairs (INT4 part, zero where a head reads Tier-2
+    // values), two tiles of true weights for those heads, and the FP16-key logits of the block being prepared
+    static constexpr int W_TILE = BS * G * 8;
+    static constexpr int PER_WARP = 4 * W_TILE + G * BS * 4;
+    static constexpr int TOTAL = RING_BYTES + ATT_WARPS * PER_WARP;
 };
 
 // Per-lane source pointers of the next block to stage.  A block's stage is 1536 + 64*G bytes = packed codes
@@ -84,17 +89,24 @@ struct AttIssuer {
         sz = szb + row0 * NG * 2 + (lane & 15) * 16;
         sc = reinterpret_cast<const char *>(tok + ((long)kv * nq_ + b0) * G * BS) + lane * 16;
     }
-    // Stage the block `b` (if any) and advance by one warp stride; always commits one group.
+    // Stage the block `b` (if any) and advance by one warp stride; always commits one group.  A block without
+    // INT4 data (the trailing partial block) gets zeros, so the INT4 arithmetic on it is finite.
     __device__ __forceinline__ void issue(char *stage, int lane)
     {
         using LY = AttLayout<G>;
         if (b < b_end) {
-            if (have4) {
+            if (have4 && b < nq) {
                 att_cp16(stage + lane * 16, pk);
                 att_cp16(stage + 512 + lane * 16, pk + 512);
                 att_cp16(stage + LY::SCALES + lane * 16, sz);
+                if (lane < 4 * G) att_cp16(stage + LY::SCORES + lane * 16, sc);
+            } else {
+                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4 *>(stage + lane * 16) = z;
+                *reinterpret_cast<uint4 *>(stage + 512 + lane * 16) = z;
+                *reinterpret_cast<uint4 *>(stage + LY::SCALES + lane * 16) = z;
+                if (b < nq && lane < 4 * G) att_cp16(stage + LY::SCORES + lane * 16, sc);
             }
-            if (b < nq && lane < 4 * G) att_cp16(stage + LY::SCORES + lane * 16, sc);
         }
         att_commit();
         b += ATT_WARPS;
@@ -103,6 +115,31 @@ struct AttIssuer {
         sc += ATT_WARPS * G * BS * 4;
     }
 };
+
+// (a & b) | c in one logic instruction.
+__device__ __forceinline__ unsigned and_or(unsigned a, unsigned b, unsigned c)
+{
+    unsigned d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Eight INT4 codes of one 32-bit word -> four float pairs, dequantised.  (bits | 2^(23-4j)) reads as
+// 2^(23-4j) + code for a nibble at bit 4j of a 16-bit half; one exact packed add removes the offset, one packed
+// fused multiply-add applies scale and zero point.
+__device__ __forceinline__ void int4x8_dequant(unsigned pk, float2 s2, float2 z2, float2 (&v)[4])
+{
+    const float2 o01 = make_float2(-8388608.0f, -524288.0f), o23 = make_float2(-32768.0f, -2048.0f);
+    const unsigned hi = pk >> 16;
+    v[0] = make_float2(__uint_as_float(and_or(pk, 0x000Fu, 0x4B000000u)), __uint_as_float(and_or(pk, 0x00F0u, 0x49000000u)));
+    v[1] = make_float2(__uint_as_float(and_or(pk, 0x0F00u, 0x47000000u)), __uint_as_float(and_or(pk, 0xF000u, 0x45000000u)));
+    v[2] = make_float2(__uint_as_float(and_or(hi, 0x000Fu, 0x4B000000u)), __uint_as_float(and_or(hi, 0x00F0u, 0x49000000u)));
+    v[3] = make_float2(__uint_as_float(and_or(hi, 0x0F00u, 0x47000000u)), __uint_as_float(and_or(hi, 0xF000u, 0x45000000u)));
+    v[0] = __ffma2_rn(__fadd2_rn(v[0], o01), s2, z2);
+    v[1] = __ffma2_rn(__fadd2_rn(v[1], o23), s2, z2);
+    v[2] = __ffma2_rn(__fadd2_rn(v[2], o01), s2, z2);
+    v[3] = __ffma2_rn(__fadd2_rn(v[3], o23), s2, z2);
+}
 
 // Cross-warp merge of (m, l, acc) inside the CTA, then one partial per head to global memory.
 template <int G>
@@ -147,16 +184,27 @@ __device__ __forceinline__ void cta_merge_store(float (&m)[G], float (&l)[G], fl
 
 // Final merge of `ns` split partials of heads [head0, head0+nh) by the last CTA to arrive.
 // All 256 threads take part; `sm` is 16-byte aligned scratch of at least 2*nh*ns + nh + 3 + 8*128 floats.
-// Step 1 brings the (m, l) partials into shared memory in one round of loads, step 2 (one warp per head)
-// computes the scale of every split, step 3 streams the acc rows with the warps of a head striding over the
-// splits (float4 per lane, all loads independent), step 4 adds the per-warp sums and normalises.
+// A thread owns one float4 column of one head and every (256 / (32*nh))-th split.  Its accumulator rows are
+// requested first (up to 20 loads in flight per thread), then the (m, l) partials go through shared memory and
+// one warp per head turns them into per-split scales while those loads are still travelling; the rows are then
+// scaled and summed, the per-thread sums combined through shared memory, normalised and written.
 __device__ __forceinline__ void final_merge(const float *pm, const float *pl, const float *pa, int ns, int head0,
                                             int nh, const cqa_workspace &ws, bool dense_role, float *sm)
 {
+    constexpr int BATCH = 20;
     float *s_m = sm, *s_sc = sm + nh * ns, *s_l = s_sc + nh * ns;
     float *s_part = sm + ((2 * nh * ns + nh + 3) & ~3);  // 16-byte aligned for float4 stores
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    __syncthreads();
+    const int nparts = ATT_WARPS / nh;      // nh is 1, 2, 4 or 8
+    const int g = warp / nparts, part = warp % nparts;
+    const float4 *rows = reinterpret_cast<const float4 *>(pa + (long)(head0 + g) * ns * D) + lane;
+    float4 buf[BATCH];
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {
+        const int sp = part + j * nparts;
+        buf[j] = sp < ns ? __ldcg(rows + (long)sp * (D / 4)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    __syncthreads();   // the scratch may still be in use as merge buffers
     for (int i = tid; i < nh * ns; i += ATT_THREADS) {
         s_m[i] = __ldcg(pm + (long)head0 * ns + i);
         s_sc[i] = __ldcg(pl + (long)head0 * ns + i);
@@ -164,44 +212,64 @@ __device__ __forceinline__ void final_merge(const float *pm, const float *pl, co
     __syncthreads();
     if (warp < nh) {
         float M = -INFINITY;
-        for (int s = lane; s < ns; s += 32) M = fmaxf(M, s_m[warp * ns + s]);
+        for (int sp = lane; sp < ns; sp += 32) M = fmaxf(M, s_m[warp * ns + sp]);
         M = warp_max(M);
         float lsum = 0.0f;
-        for (int s = lane; s < ns; s += 32) {
-            const float mi = s_m[warp * ns + s];
+        for (int sp = lane; sp < ns; sp += 32) {
+            const float mi = s_m[warp * ns + sp];
             const float sc = mi == -INFINITY ? 0.0f : fexp(mi - M);
-            lsum = fmaf(s_sc[warp * ns + s], sc, lsum);
-            s_sc[warp * ns + s] = sc;
+            lsum = fmaf(s_sc[warp * ns + sp], sc, lsum);
+            s_sc[warp * ns + sp] = sc;
         }
         lsum = warp_sum(lsum);
-        if (lane == 0) s_l[warp] = lsum;
+        if (lane == 0) {
+            s_l[warp] = lsum;
+            if (ws.partial_out != nullptr) {
+                const int h = head0 + warp;
+                const bool flagged = ws.cert != nullptr && (ws.cert[h].dense || ws.any_flags[2]);
+                if (flagged == dense_role) {
+                    ws.partial_out[(long)h * CQA_PARTIAL_STRIDE] = M;
+                    ws.partial_out[(long)h * CQA_PARTIAL_STRIDE + 1] = lsum;
+                }
+            }
+        }
     }
     __syncthreads();
-    const int wph = ATT_WARPS / nh;  // warps per head (nh is 1, 2, 4 or 8)
-    {
-        const int g = warp / wph, part = warp % wph;
-        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        const float4 *rows = reinterpret_cast<const float4 *>(pa + (long)(head0 + g) * ns * D) + lane;
-#pragma unroll 8
-        for (int s = part; s < ns; s += wph) {
-            const float4 v = __ldcg(rows + (long)s * (D / 4));
-            const float sc = s_sc[g * ns + s];
-            a.x = fmaf(v.x, sc, a.x);
-            a.y = fmaf(v.y, sc, a.y);
-            a.z = fmaf(v.z, sc, a.z);
-            a.w = fmaf(v.w, sc, a.w);
+    float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {
+        const int sp = part + j * nparts;
+        if (sp < ns) {
+            const float sc = s_sc[g * ns + sp];
+            a.x = fmaf(buf[j].x, sc, a.x);
+            a.y = fmaf(buf[j].y, sc, a.y);
+            a.z = fmaf(buf[j].z, sc, a.z);
+            a.w = fmaf(buf[j].w, sc, a.w);
         }
-        reinterpret_cast<float4 *>(s_part + warp * D)[lane] = a;
     }
+#pragma unroll 4
+    for (int sp = part + BATCH * nparts; sp < ns; sp += nparts) {   // more splits than one batch covers
+        const float4 v = __ldcg(rows + (long)sp * (D / 4));
+        const float sc = s_sc[g * ns + sp];
+        a.x = fmaf(v.x, sc, a.x);
+        a.y = fmaf(v.y, sc, a.y);
+        a.z = fmaf(v.z, sc, a.z);
+        a.w = fmaf(v.w, sc, a.w);
+    }
+    reinterpret_cast<float4 *>(s_part + warp * D)[lane] = a;
     __syncthreads();
     for (int item = tid; item < nh * D; item += ATT_THREADS) {
-        const int g = item / D, ch = item % D, h = head0 + g;
+        const int gg = item / D, ch = item % D, h = head0 + gg;
         const bool flagged = ws.cert != nullptr && (ws.cert[h].dense || ws.any_flags[2]);
         if (flagged != dense_role) continue;
-        float a = 0.0f;
-        for (int p = 0; p < wph; ++p) a += s_part[(g * wph + p) * D + ch];
-        const float l = s_l[g];
-        ws.out[(long)h * D + ch] = a / (l > 0.0f ? l : 1.0f);
+        float acc = 0.0f;
+        for (int p = 0; p < nparts; ++p) acc += s_part[(gg * nparts + p) * D + ch];
+        if (ws.partial_out != nullptr) {
+            ws.partial_out[(long)h * CQA_PARTIAL_STRIDE + 2 + ch] = acc;   // un-normalised: merged across ranks later
+            continue;
+        }
+        const float l = s_l[gg];
+        ws.out[(long)h * D + ch] = acc / (l > 0.0f ? l : 1.0f);
     }
     __syncthreads();
 }
@@ -328,26 +396,28 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
     }
     // ---- shared memory carve-up
     char *ring = dsm;
-    float *s_q = reinterpret_cast<float *>(dsm + LY::RING_BYTES);              // [G][128]
-    float2 *s_w = reinterpret_cast<float2 *>(s_q + G * D);                      // [warps][16][G] (w, w)
-    float *s_sc = reinterpret_cast<float *>(s_w + ATT_WARPS * BS * G);          // [warps][G][16]
-    unsigned char *s_km = reinterpret_cast<unsigned char *>(s_sc + ATT_WARPS * G * BS);  // [bps]
-    unsigned char *s_vm = s_km + blocks_per_split;
-
     const int split = (int)blockIdx.x - pool_x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, L = lane & 15, hw = lane >> 4;
     const long b_begin = (long)split * blocks_per_split;
     const long b_end = min(nact, b_begin + (long)blocks_per_split);
     char *wring = ring + warp * ATT_STAGES * LY::STAGE;
+    char *wpriv = dsm + LY::RING_BYTES + warp * LY::PER_WARP;
+    float2 *w_tiles = reinterpret_cast<float2 *>(wpriv);                       // [2][16][G] INT4-part weights
+    float2 *w16_tiles = reinterpret_cast<float2 *>(wpriv + 2 * LY::W_TILE);    // [2][16][G] true weights (Tier-2 values)
+    float *sc_tile = reinterpret_cast<float *>(wpriv + 4 * LY::W_TILE);        // [G][16] FP16-key logits
 
     // start the pipeline before anything else
     AttIssuer<G> issuer;
     issuer.init(c, ws.token_scores, nq, kv, b_begin + warp, b_end, lane);
 #pragma unroll
     for (int s = 0; s < ATT_STAGES - 1; ++s) issuer.issue(wring + s * LY::STAGE, lane);
-    for (int i = threadIdx.x; i < G * D; i += ATT_THREADS) s_q[i] = load_q(q, q_dtype, (long)kv * G * D + i);
-    for (int i = threadIdx.x; i < blocks_per_split; i += ATT_THREADS) {
-        const long b = b_begin + i;
+
+    // Blocks of this warp: b_begin + warp + 8*it.  Lane j keeps the key / value promotion bits of the warp's
+    // block (it0 + j), one bit per head of the group; they are re-read every 32 blocks.
+    const int n_my = b_begin + warp < b_end ? (int)((b_end - b_begin - warp + ATT_WARPS - 1) / ATT_WARPS) : 0;
+    unsigned my_masks = 0;   // km | vm << 8 of block (it0 + lane)
+    auto load_masks = [&](int it0) {
+        const long b = b_begin + warp + (long)(it0 + lane) * ATT_WARPS;
         unsigned km = 0, vm = 0;
         if (b < b_end) {
 #pragma unroll
@@ -357,10 +427,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
                 vm |= ws.value_mask[o] ? (1u << g) : 0u;
             }
         }
-        s_km[i] = (unsigned char)km;
-        s_vm[i] = (unsigned char)vm;
+        my_masks = km | (vm << 8);
+    };
+    load_masks(0);
+    // Largest Phase-1 block maximum over this warp's quantised blocks, per head: the softmax reference point.
+    const bool have_mb = ws.m_b != nullptr;
+    float m_init = -INFINITY;
+    if (have_mb) {
+        float mx[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) mx[g] = -INFINITY;
+        for (long b = b_begin + warp + (long)lane * ATT_WARPS; b < b_end && b < nq; b += 32 * ATT_WARPS) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) mx[g] = fmaxf(mx[g], ws.m_b[(long)(kv * G + g) * ws.ld + b]);
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float v = warp_max(mx[g]);
+            if (g == lane / (G >= 8 ? 4 : (G == 4 ? 8 : 16))) m_init = v;
+        }
     }
-    __syncthreads();
 
     // Softmax bookkeeping layout: LPH lanes per head, each lane holds TPL tokens of its head `gl`.
     constexpr int LPH = G >= 8 ? 4 : (G == 4 ? 8 : 16);
@@ -368,183 +454,191 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
     const int gl = lane / LPH, sub = lane % LPH;
     const bool gl_valid = gl < G;
 
-    float m[G], l[G];
     float2 acc2[G][4];
-    float m_mine = -INFINITY;   // running max of head gl (same value as m[gl])
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        m[g] = -INFINITY;
-        l[g] = 0.0f;
+    for (int g = 0; g < G; ++g)
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc2[g][k] = make_float2(0.0f, 0.0f);
-    }
+    float m_mine = m_init;      // running max of head gl (uniform over its LPH lanes)
+    float l_mine = 0.0f;        // this lane's share of the running sum of head gl
     const T2 *kt2 = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
     const T2 *vt2 = reinterpret_cast<const T2 *>(c.values_t2) + (long)kv * c.values_t2_rows * D;
-    float2 *w_tile = s_w + warp * BS * G;
-    float *sc_tile = s_sc + warp * G * BS;
-    const unsigned all = (1u << G) - 1u;
+    const bool have4 = c.values_int4_packed != nullptr;
 
-    int it = 0;
-    for (long b = b_begin + warp; b < b_end; b += ATT_WARPS, ++it) {
-        issuer.issue(wring + ((it + ATT_STAGES - 1) % ATT_STAGES) * LY::STAGE, lane);
-        att_wait<ATT_STAGES - 1>();
-        __syncwarp();
-        const char *st = wring + (it % ATT_STAGES) * LY::STAGE;
-        const unsigned km = s_km[b - b_begin], vm = s_vm[b - b_begin];
+    // prepare(it): logits -> weights of block `it` into w_tiles[it & 1]; returns this lane's rescale factor for
+    // head gl (1 when the running max did not move).
+    auto prepare = [&](int it, unsigned masks) -> float {
+        const long b = b_begin + warp + (long)it * ATT_WARPS;
+        const unsigned km = masks & 0xFFu, vm = (masks >> 8) & 0xFFu;
         const int n_valid = (b == nact - 1) ? last_valid : BS;
-        // ---- FP16-key logits for promoted heads
+        const char *st = wring + (it % ATT_STAGES) * LY::STAGE;
         if (km) {
+            // FP16-key logits for promoted heads (rare): Tier-2 rows straight from global memory
             long kslot = c.key_slots ? (long)c.key_slots[b] : b;
             if (kslot < 0) kslot = 0;
 #pragma unroll 1
             for (int g = 0; g < G; ++g) {
                 if (!(km & (1u << g))) continue;
                 float qv[8];
-                load8<float>(s_q + g * D + 8 * L, qv);
+                load_q8(q, q_dtype, (long)(kv * G + g) * D + 8 * L, qv);
+                Raw8<T2> kr[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int t = hw * 8 + i;
-                    float kf[8];
-                    if (t < n_valid) load8<T2>(kt2 + (kslot * BS + t) * D + 8 * L, kf);
-                    else {
+                    kr[i] = t < n_valid ? raw_load8<T2>(kt2 + (kslot * BS + t) * D + 8 * L) : raw_zero8<T2>();
+                }
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) kf[k] = 0.0f;
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    float kf[8];
+                    raw_to_f(kr[i], kf);
                     const float d = hw_sum(chain8(kf, qv));
-                    if (L == i) sc_tile[g * BS + t] = d * q_scale;
+                    if (L == i) sc_tile[g * BS + hw * 8 + i] = d * q_scale;
                 }
             }
             __syncwarp();
         }
-        // ---- softmax bookkeeping: every lane owns TPL tokens of head gl
         const float *st_sc = reinterpret_cast<const float *>(st + LY::SCORES);
         float sv_[TPL];
-        float bm = -INFINITY;
 #pragma unroll
         for (int i = 0; i < TPL; ++i) {
             const int t = sub * TPL + i;
             float x = -INFINITY;
             if (gl_valid && t < n_valid) x = ((km >> gl) & 1u) ? sc_tile[gl * BS + t] : st_sc[gl * BS + t];
             sv_[i] = x;
-            bm = fmaxf(bm, x);
         }
+        // The running max starts at the largest Phase-1 block maximum of this warp's blocks, so it can only move
+        // when FP16-key logits (or a block without Phase-1 scores) are involved.
+        float alpha = 1.0f;
+        if (km || !have_mb) {
+            float bm = -INFINITY;
 #pragma unroll
-        for (int o = LPH / 2; o >= 1; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(FULL, bm, o));
-        const float m_new_mine = fmaxf(m_mine, bm);
-        m_mine = m_new_mine;
+            for (int i = 0; i < TPL; ++i) bm = fmaxf(bm, sv_[i]);
+#pragma unroll
+            for (int o = LPH / 2; o >= 1; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(FULL, bm, o));
+            const float m_up = fmaxf(m_mine, bm);
+            alpha = (m_up == -INFINITY || m_mine == m_up) ? 1.0f : fexp(m_mine - m_up);
+            m_mine = m_up;
+        }
+        const float m_new = m_mine;
+        float2 *wt = w_tiles + (it & 1) * BS * G;
+        const bool v16 = (vm >> gl) & 1u;
         float ls = 0.0f;
 #pragma unroll
         for (int i = 0; i < TPL; ++i) {
-            const float w = sv_[i] == -INFINITY ? 0.0f : fexp(sv_[i] - m_new_mine);
+            const float w = sv_[i] == -INFINITY ? 0.0f : fexp(sv_[i] - m_new);
             ls += w;
-            if (gl_valid) w_tile[(sub * TPL + i) * G + gl] = make_float2(w, w);
+            const float w4 = v16 ? 0.0f : w;
+            if (gl_valid) wt[(sub * TPL + i) * G + gl] = make_float2(w4, w4);
         }
+        if (vm) {
 #pragma unroll
-        for (int o = LPH / 2; o >= 1; o >>= 1) ls += __shfl_xor_sync(FULL, ls, o);
+            for (int i = 0; i < TPL; ++i) {
+                const float w = sv_[i] == -INFINITY ? 0.0f : fexp(sv_[i] - m_new);
+                if (gl_valid) w16_tiles[((it & 1) * BS + sub * TPL + i) * G + gl] = make_float2(w, w);
+            }
+        }
+        l_mine = fmaf(l_mine, alpha, ls);
+        return alpha;
+    };
+
+    float alpha_cur = 1.0f;
+    if (n_my > 0) {
+        att_wait<ATT_STAGES - 2>();
+        __syncwarp();
+        alpha_cur = prepare(0, __shfl_sync(FULL, my_masks, 0));
+    }
+    for (int it = 0; it < n_my; ++it) {
+        const long b = b_begin + warp + (long)it * ATT_WARPS;
+        __syncwarp();   // every lane is done with the slot that is about to be refilled, and with w_tiles[(it+1)&1]
+        issuer.issue(wring + ((it + ATT_STAGES - 1) % ATT_STAGES) * LY::STAGE, lane);
+        att_wait<ATT_STAGES - 2>();   // block it+1 has landed
+        __syncwarp();
+        const unsigned masks_cur = __shfl_sync(FULL, my_masks, it & 31);
+        const unsigned vm = (masks_cur >> 8) & 0xFFu;
+        if ((it & 31) == 31 && it + 1 < n_my) load_masks(it + 1);
+        const unsigned masks_next = __shfl_sync(FULL, my_masks, (it + 1) & 31);
+        // rescale the accumulators if the running max of any head moved when block `it` was prepared
+        if (__any_sync(FULL, alpha_cur != 1.0f)) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float bmg = __shfl_sync(FULL, bm, g * LPH);
-            const float lsg = __shfl_sync(FULL, ls, g * LPH);
-            const float mn = fmaxf(m[g], bmg);
-            const float alpha = (mn == -INFINITY || m[g] == mn) ? 1.0f : fexp(m[g] - mn);
-            m[g] = mn;
-            l[g] = fmaf(l[g], alpha, lsg);
-            if (alpha != 1.0f) {
-                const float2 a2 = make_float2(alpha, alpha);
+            for (int g = 0; g < G; ++g) {
+                const float ag = __shfl_sync(FULL, alpha_cur, g * LPH);
+                const float2 a2 = make_float2(ag, ag);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) acc2[g][k] = __fmul2_rn(acc2[g][k], a2);
             }
         }
-        __syncwarp();
-        // ---- values: this half warp takes tokens t = 2i + hw
-        long vslot = c.value_slots ? (long)c.value_slots[b] : b;
-        if (vslot < 0) vslot = 0;
-        const unsigned *st_pk = reinterpret_cast<const unsigned *>(st + LY::PACKED);
-        const __half *st_s = reinterpret_cast<const __half *>(st + LY::SCALES);
-        const __half *st_z = reinterpret_cast<const __half *>(st + LY::ZEROS);
-        // codes -> floats: (bits | 2^(23-4j)) is 2^(23-4j) + code; one exact add removes the offset
-        const float2 o01 = make_float2(-8388608.0f, -524288.0f), o23 = make_float2(-32768.0f, -2048.0f);
-        if (vm == 0 && n_valid == BS) {
-            // common case: a full block whose values are INT4 for every head of the group
+        const char *st = wring + (it % ATT_STAGES) * LY::STAGE;
+        const float2 *wt = w_tiles + (it & 1) * BS * G;
+        // ---- INT4 values of block `it` (zero weights where a head reads Tier-2 values or the token is padding);
+        // this half warp takes tokens t = 2i + hw
+        if (have4) {
+            const unsigned *st_pk = reinterpret_cast<const unsigned *>(st + LY::PACKED);
+            const __half *st_s = reinterpret_cast<const __half *>(st + LY::SCALES);
+            const __half *st_z = reinterpret_cast<const __half *>(st + LY::ZEROS);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int t = 2 * i + hw;
                 const unsigned pk = st_pk[t * 16 + L];
                 const float sv = __half2float(st_s[t * NG + (L >> 1)]);
                 const float zv = __half2float(st_z[t * NG + (L >> 1)]);
-                const float2 s2 = make_float2(sv, sv), z2 = make_float2(zv, zv);
-                const unsigned lo = pk & 0xFFFFu, hi = pk >> 16;
                 float2 v[4];
-                v[0] = make_float2(__uint_as_float((lo & 0x000Fu) | 0x4B000000u), __uint_as_float((lo & 0x00F0u) | 0x49000000u));
-                v[1] = make_float2(__uint_as_float((lo & 0x0F00u) | 0x47000000u), __uint_as_float((lo & 0xF000u) | 0x45000000u));
-                v[2] = make_float2(__uint_as_float((hi & 0x000Fu) | 0x4B000000u), __uint_as_float((hi & 0x00F0u) | 0x49000000u));
-                v[3] = make_float2(__uint_as_float((hi & 0x0F00u) | 0x47000000u), __uint_as_float((hi & 0xF000u) | 0x45000000u));
-                v[0] = __ffma2_rn(__fadd2_rn(v[0], o01), s2, z2);
-                v[1] = __ffma2_rn(__fadd2_rn(v[1], o23), s2, z2);
-                v[2] = __ffma2_rn(__fadd2_rn(v[2], o01), s2, z2);
-                v[3] = __ffma2_rn(__fadd2_rn(v[3], o23), s2, z2);
+                int4x8_dequant(pk, make_float2(sv, sv), make_float2(zv, zv), v);
+                float2 w2[G];
+                if constexpr (G % 2 == 0) {
+#pragma unroll
+                    for (int g = 0; g < G; g += 2) {
+                        const float4 ww = *reinterpret_cast<const float4 *>(wt + t * G + g);
+                        w2[g] = make_float2(ww.x, ww.y);
+                        w2[g + 1] = make_float2(ww.z, ww.w);
+                    }
+                } else {
+                    w2[0] = wt[t * G];
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc2[g][k] = __ffma2_rn(w2[g], v[k], acc2[g][k]);
+            }
+        }
+        // ---- weights of the next block, in the same straight-line stretch so the two interleave
+        float alpha_next = 1.0f;
+        if (it + 1 < n_my) alpha_next = prepare(it + 1, masks_next);
+        // ---- Tier-2 values for the heads that were promoted (rare)
+        if (vm) {
+            const int n_valid = (b == nact - 1) ? last_valid : BS;
+            long vslot = c.value_slots ? (long)c.value_slots[b] : b;
+            if (vslot < 0) vslot = 0;
+#pragma unroll 2
+            for (int i = 0; i < 8; ++i) {
+                const int t = 2 * i + hw;
+                if (t >= n_valid) continue;
+                float v16[8];
+                load8<T2>(vt2 + (vslot * BS + t) * D + 8 * L, v16);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
-                    const float2 w2 = w_tile[t * G + g];
+                    if (!(vm & (1u << g))) continue;
+                    const float2 w2 = w16_tiles[((it & 1) * BS + t) * G + g];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) acc2[g][k] = __ffma2_rn(w2, v[k], acc2[g][k]);
-                }
-            }
-        } else {
-            if (vm != all) {
-#pragma unroll 2
-                for (int i = 0; i < 8; ++i) {
-                    const int t = 2 * i + hw;
-                    if (t >= n_valid) continue;
-                    const unsigned pk = st_pk[t * 16 + L];
-                    const float sv = __half2float(st_s[t * NG + (L >> 1)]);
-                    const float zv = __half2float(st_z[t * NG + (L >> 1)]);
-                    const float2 s2 = make_float2(sv, sv), z2 = make_float2(zv, zv);
-                    const unsigned lo = pk & 0xFFFFu, hi = pk >> 16;
-                    float2 v[4];
-                    v[0] = make_float2(__uint_as_float((lo & 0x000Fu) | 0x4B000000u), __uint_as_float((lo & 0x00F0u) | 0x49000000u));
-                    v[1] = make_float2(__uint_as_float((lo & 0x0F00u) | 0x47000000u), __uint_as_float((lo & 0xF000u) | 0x45000000u));
-                    v[2] = make_float2(__uint_as_float((hi & 0x000Fu) | 0x4B000000u), __uint_as_float((hi & 0x00F0u) | 0x49000000u));
-                    v[3] = make_float2(__uint_as_float((hi & 0x0F00u) | 0x47000000u), __uint_as_float((hi & 0xF000u) | 0x45000000u));
-                    v[0] = __ffma2_rn(__fadd2_rn(v[0], o01), s2, z2);
-                    v[1] = __ffma2_rn(__fadd2_rn(v[1], o23), s2, z2);
-                    v[2] = __ffma2_rn(__fadd2_rn(v[2], o01), s2, z2);
-                    v[3] = __ffma2_rn(__fadd2_rn(v[3], o23), s2, z2);
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        if (vm & (1u << g)) continue;
-                        const float2 w2 = w_tile[t * G + g];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) acc2[g][k] = __ffma2_rn(w2, v[k], acc2[g][k]);
-                    }
-                }
-            }
-            if (vm) {
-#pragma unroll 2
-                for (int i = 0; i < 8; ++i) {
-                    const int t = 2 * i + hw;
-                    if (t >= n_valid) continue;
-                    float v16[8];
-                    load8<T2>(vt2 + (vslot * BS + t) * D + 8 * L, v16);
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        if (!(vm & (1u << g))) continue;
-                        const float2 w2 = w_tile[t * G + g];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            acc2[g][k] = __ffma2_rn(w2, make_float2(v16[2 * k], v16[2 * k + 1]), acc2[g][k]);
-                    }
+                    for (int k = 0; k < 4; ++k)
+                        acc2[g][k] = __ffma2_rn(w2, make_float2(v16[2 * k], v16[2 * k + 1]), acc2[g][k]);
                 }
             }
         }
-        __syncwarp();
+        alpha_cur = alpha_next;
     }
     att_wait<0>();
+    // per-head (m, l) for the CTA merge: l is summed over the lanes of a head first
+#pragma unroll
+    for (int o = LPH / 2; o >= 1; o >>= 1) l_mine += __shfl_xor_sync(FULL, l_mine, o);
+    float m[G], l[G];
     float acc[G][8];
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int g = 0; g < G; ++g) {
+        m[g] = __shfl_sync(FULL, m_mine, (g * LPH) & 31);
+        l[g] = __shfl_sync(FULL, l_mine, (g * LPH) & 31);
 #pragma unroll
         for (int k = 0; k < 4; ++k) { acc[g][2 * k] = acc2[g][k].x; acc[g][2 * k + 1] = acc2[g][k].y; }
+    }
     __syncthreads();  // the ring is reused as merge buffers
     float *sm_m = reinterpret_cast<float *>(ring);
     float *sm_l = sm_m + ATT_WARPS * G;
@@ -555,13 +649,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
 }
 
 template <int G>
-static size_t attend_smem(int bps)
+static size_t attend_smem()
 {
     using LY = AttLayout<G>;
     size_t dense_bytes = (size_t)(2 * CQA_MAX_DENSE_SPLITS + 8 + 8 * D + 2 * ATT_WARPS + ATT_WARPS * D) * 4;
-    size_t mixed = (size_t)LY::RING_BYTES + (size_t)G * D * 4 + (size_t)ATT_WARPS * BS * G * 8 +
-                   (size_t)ATT_WARPS * G * BS * 4 + 2 * (size_t)bps;
-    mixed = (mixed + 15) & ~(size_t)15;
+    size_t mixed = ((size_t)LY::TOTAL + 15) & ~(size_t)15;
     return mixed > dense_bytes ? mixed : dense_bytes;
 }
 
@@ -574,7 +666,7 @@ static int attend_launch_gt(const cqa_cache *c, const cqa_workspace *ws, const v
     const bool dense = ws->cert && ws->dense_splits > 0 && ws->dense_m && ws->dense_l && ws->dense_acc;
     cqa_workspace w = *ws;
     if (!dense) w.dense_splits = 0;
-    const size_t smem = attend_smem<G>(bps);
+    const size_t smem = attend_smem<G>();
     static size_t attr = 0;
     if (smem > attr) {
         int rc = check_cuda(cudaFuncSetAttribute(attend_kernel<G, T2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -606,7 +698,7 @@ static int attend_launch_t(const cqa_cache *c, const cqa_workspace *ws, const vo
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
                   long num_tokens, int last_valid, float q_scale, cudaStream_t st)
 {
-    if (ws->num_splits <= 0 || !ws->part_m || !ws->part_l || !ws->part_acc || !ws->out || !ws->topk_mask ||
+    if (ws->num_splits <= 0 || !ws->part_m || !ws->part_l || !ws->part_acc || (!ws->out && !ws->partial_out) || !ws->topk_mask ||
         !ws->value_mask || !ws->tickets) {
         set_error("cqa_attend: workspace is missing partial buffers, tickets, masks or the output");
         return CQA_ERR_INVALID;
@@ -633,6 +725,28 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
     }
     set_error("cqa_attend: unknown Tier-2 dtype %d", c->t2_dtype);
     return CQA_ERR_INVALID;
+}
+
+// Merge of per-rank partial rows (max, sum, acc[128]) of every head: one CTA per head, one thread per channel.
+__global__ void __launch_bounds__(D) merge_partials_kernel(const float *parts, int n_parts, int n_heads, float *out)
+{
+    const int h = blockIdx.x, ch = threadIdx.x;
+    float M = -INFINITY;
+    for (int p = 0; p < n_parts; ++p) M = fmaxf(M, parts[((long)p * n_heads + h) * CQA_PARTIAL_STRIDE]);
+    float l = 0.0f, a = 0.0f;
+    for (int p = 0; p < n_parts; ++p) {
+        const float *row = parts + ((long)p * n_heads + h) * CQA_PARTIAL_STRIDE;
+        const float sc = row[0] == -INFINITY ? 0.0f : fexp(row[0] - M);
+        l = fmaf(row[1], sc, l);
+        a = fmaf(row[2 + ch], sc, a);
+    }
+    out[(long)h * D + ch] = a / (l > 0.0f ? l : 1.0f);
+}
+
+int merge_partials_launch(const float *parts, int n_parts, int n_heads, float *out, cudaStream_t st)
+{
+    merge_partials_kernel<<<n_heads, D, 0, st>>>(parts, n_parts, n_heads, out);
+    return check_launch("merge_partials_kernel");
 }
 
 // ---------------------------------------------------------------------------

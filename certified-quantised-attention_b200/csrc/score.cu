@@ -195,6 +195,23 @@ __global__ void __launch_bounds__(32) fp16_block_scores_kernel(cqa_cache c, cons
     }
 }
 
+// Sequence-sharded ranking check: one warp per (top-list slot, head); blocks outside this rank's range give zeros.
+template <typename T2>
+__global__ void __launch_bounds__(32) rescore_owned_kernel(cqa_cache c, const cqa_head_cert *cert, const void *q,
+                                                          int q_dtype, long first_block, long n_local, float q_scale,
+                                                          float *out)
+{
+    const int h = blockIdx.y, i = blockIdx.x;
+    const long b = (long)cert[h].top_blocks[i] - first_block;
+    float s = 0.0f, lm = 0.0f;
+    if (cert[h].top_blocks[i] >= 0 && b >= 0 && b < n_local)
+        fp16_block_score_warp<T2>(c, q, q_dtype, h, b, n_local * BS, q_scale, s, lm);
+    if (threadIdx.x == 0) {
+        out[((long)h * CQA_MAX_RANKING_K + i) * 2] = s;
+        out[((long)h * CQA_MAX_RANKING_K + i) * 2 + 1] = lm;
+    }
+}
+
 __global__ void __launch_bounds__(32) delta_bound_kernel(cqa_cache c, const void *q, int q_dtype, float *delta)
 {
     float d = delta_bound_warp(c, q, q_dtype, blockIdx.x);
@@ -216,6 +233,20 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
     }
     score_blocks_kernel<G><<<grid, SCORE_WARPS * 32, SMEM, st>>>(*c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, bpc);
     return check_launch("score_blocks_kernel");
+}
+
+int rescore_owned_launch(const cqa_cache *c, const cqa_head_cert *cert, const void *q, int q_dtype, long first_block,
+                         long n_local, float q_scale, float *out, cudaStream_t st)
+{
+    const int H = c->kv_heads * c->gqa_group;
+    dim3 grid(CQA_MAX_RANKING_K, (unsigned)H);
+    switch (c->t2_dtype) {
+    case CQA_F32: rescore_owned_kernel<float><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); break;
+    case CQA_F16: rescore_owned_kernel<__half><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); break;
+    case CQA_BF16: rescore_owned_kernel<__nv_bfloat16><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); break;
+    default: set_error("cqa_rescore_owned: unknown Tier-2 dtype"); return CQA_ERR_INVALID;
+    }
+    return check_launch("rescore_owned_kernel");
 }
 
 int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,

@@ -26,6 +26,10 @@ constexpr int SC_THREADS = 1024;
 constexpr int SC_WARPS = 32;
 constexpr int CAND = 256;          // candidates kept by the radix select
 constexpr int PH_SELECT = 1, PH_CERTIFY = 2;
+// Sequence-sharded runs split the ranking check around an exchange: PH_TOP_ONLY stops role 1 once the top
+// list is in the certificate; PH_GIVEN resumes it from that list with FP16 scores computed by the ranks that
+// own the blocks (ws.given_fp16) and runs role 1 alone.
+constexpr int PH_TOP_ONLY = 4, PH_GIVEN = 8;
 
 typedef unsigned long long u64;
 
@@ -539,7 +543,16 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
     // ---- ranking / boundary / score consistency
     const bool need_fp16 = (kn.ranking_fallback || kn.score_consistency) && n > 0;
     if (role == 1 && need_fp16) {
-        if (rk <= 4) {
+        const bool given = (phases & PH_GIVEN) != 0;
+        if (given) {
+            if (tid < rk) {
+                const int b = ct->top_blocks[tid];
+                top_idx[tid] = b;
+                top_i8[tid] = A[b];
+                top_f16[tid] = ws.given_fp16[((long)h * CQA_MAX_RANKING_K + tid) * 2];
+                top_lm[tid] = ws.given_fp16[((long)h * CQA_MAX_RANKING_K + tid) * 2 + 1];
+            }
+        } else if (rk <= 4) {
             u64 t4[4] = {0ull, 0ull, 0ull, 0ull};
             for (int b = tid; b < n; b += SC_THREADS)
                 insert4(t4, ((u64)orderable(A[b]) << 32) | (u64)(0xFFFFFFFFu - (unsigned)b));
@@ -593,6 +606,10 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
         }
         __syncthreads();
         CQA_CLK(6);
+        if (phases & PH_TOP_ONLY) {
+            if (tid < CQA_MAX_RANKING_K) ct->top_blocks[tid] = tid < rk ? top_idx[tid] : -1;
+            return;
+        }
         // Boundary bound: max over the blocks outside the top list of (ell_b + delta).  Rounding is monotone,
         // so it equals (max ell_b) + delta; the maximum is taken by the warps that neither re-score a block
         // nor compute delta, while those wait for Tier-2 rows.
@@ -600,9 +617,11 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
         const bool overlap = ub_warps >= 8;
         float ubm = -INFINITY;
         if (warp < rk) {
-            float s, lm;
-            fp16_block_score_warp<T2>(c, q, q_dtype, h, (long)top_idx[warp], nq * BS, kn.q_scale, s, lm);
-            if (lane == 0) { top_f16[warp] = s; top_lm[warp] = lm; }
+            if (!given) {
+                float s, lm;
+                fp16_block_score_warp<T2>(c, q, q_dtype, h, (long)top_idx[warp], nq * BS, kn.q_scale, s, lm);
+                if (lane == 0) { top_f16[warp] = s; top_lm[warp] = lm; }
+            }
         } else if (warp == rk) {
             const float d = delta_bound_warp(c, q, q_dtype, h);
             if (lane == 0) s_delta = d;
@@ -870,7 +889,8 @@ static int selcert_launch_t(const cqa_cache *c, const cqa_knobs *kn, const cqa_w
     }
     // select only: role 0; certify only: roles 1 and 2; fused: all three
     const int role_base = (phases & PH_SELECT) ? 0 : 1;
-    const int n_roles = phases == (PH_SELECT | PH_CERTIFY) ? 3 : (phases == PH_SELECT ? 1 : 2);
+    int n_roles = (phases & PH_SELECT) ? ((phases & PH_CERTIFY) ? 3 : 1) : 2;
+    if (phases & PH_GIVEN) n_roles = 1;   // role 1 alone
     dim3 grid((unsigned)H, (unsigned)n_roles);
     selcert_kernel<T2><<<grid, SC_THREADS, smem, st>>>(*c, *kn, *ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi,
                                                        base_width, two_level, rk, phases, role_base);
@@ -887,8 +907,13 @@ int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace 
     }
     if (phases & PH_CERTIFY) {
         const bool need_fp16 = kn->ranking_fallback || kn->score_consistency;
-        if (need_fp16 && (!c->keys_t2 || !c->sigma_max || !q)) {
+        const bool local_keys = !(phases & (PH_TOP_ONLY | PH_GIVEN));
+        if (need_fp16 && local_keys && (!c->keys_t2 || !c->sigma_max || !q)) {
             set_error("cqa_certify: ranking / consistency checks need q, Tier-2 keys and sigma_max");
+            return CQA_ERR_INVALID;
+        }
+        if (need_fp16 && (phases & PH_GIVEN) && (!ws->given_fp16 || !c->sigma_max || !q)) {
+            set_error("cqa_certify_given: needs q, sigma_max and the exchanged FP16 scores");
             return CQA_ERR_INVALID;
         }
     }
@@ -905,6 +930,18 @@ int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *
                   const float *u, long u_ld, cudaStream_t st)
 {
     return selcert_launch(c, kn, ws, nullptr, CQA_F32, nq, nact, u, u_ld, PH_SELECT, st);
+}
+
+int select_certify_local_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq,
+                                long nact, const float *u, long u_ld, cudaStream_t st)
+{
+    return selcert_launch(c, kn, ws, nullptr, CQA_F32, nq, nact, u, u_ld, PH_SELECT | PH_CERTIFY | PH_TOP_ONLY, st);
+}
+
+int certify_given_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q,
+                         int q_dtype, long nq, long nact, cudaStream_t st)
+{
+    return selcert_launch(c, kn, ws, q, q_dtype, nq, nact, nullptr, 0, PH_CERTIFY | PH_GIVEN, st);
 }
 
 int certify_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,

@@ -41,9 +41,9 @@ _CERT_F32_FIELDS = [f for f, t in _lib.CqaHeadCert._fields_ if t is C.c_float]
 class _Workspace:
     """Device buffers for one layer's step, kept in cache._certified_workspace."""
 
-    def __init__(self, cache: TieredKeyCacheLayer, H: int, G: int, device: torch.device):
+    def __init__(self, cache: TieredKeyCacheLayer, H: int, G: int, device: torch.device, ld: int | None = None):
         self.H, self.G = H, G
-        ld = int(cache.keys_scale.shape[1])
+        ld = int(cache.keys_scale.shape[1]) if ld is None else int(ld)
         self.ld = ld
         f32 = dict(dtype=torch.float32, device=device)
         u8 = dict(dtype=torch.uint8, device=device)

@@ -159,7 +159,14 @@ typedef struct cqa_workspace {
                                     number of heads flagged for dense recompute, then their ids */
     float *out;                  /* [H][128] float32 */
     int32_t *tickets;            /* [KV + H] merge tickets: zero them once after allocation; kernels leave them at zero */
+    /* Sequence-sharded runs only (NULL otherwise). */
+    const float *given_fp16;     /* [H][CQA_MAX_RANKING_K][2]: FP16 score and log-mass of each top-list block,
+                                    computed by the rank that owns the block (cqa_rescore_owned) and summed over ranks */
+    float *partial_out;          /* [H][CQA_PARTIAL_STRIDE]: when set, cqa_attend writes the un-normalised
+                                    (max, sum, acc[128]) of its own blocks here instead of the output rows */
 } cqa_workspace;
+
+#define CQA_PARTIAL_STRIDE 130
 
 const char *cqa_version(void);
 /* Text of the last error on the calling thread (host memory, valid until the next call). */
@@ -279,6 +286,28 @@ int cqa_attend_static(const cqa_cache *c, const cqa_workspace *ws, const void *q
 int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *q,
                    int q_dtype, int64_t num_tokens, int64_t nq, const float *exploration_u,
                    int64_t u_ld, void *stream);
+
+/* ---- sequence sharding: every rank owns a contiguous range of blocks ----
+ * The reference runs one cache per process; these entry points let P ranks that each
+ * hold the blocks [first_block, first_block + n_local) of one long sequence reproduce
+ * the unsharded certificate bit for bit (same selector on the all-gathered m_b / S_b /
+ * eta arrays) and merge their Phase-2 partials.  No reference counterpart.
+ *
+ * cqa_select_certify_local: selector, value check and the top-list search on global
+ * arrays (ws->m_b, ws->s_b, c->values_int4_errors cover all blocks of all ranks); stops
+ * the ranking check after writing cert[h].top_blocks. */
+int cqa_select_certify_local(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, int64_t nq,
+                             int64_t nact, const float *exploration_u, int64_t u_ld, void *stream);
+/* FP16 re-score of the top-list blocks this rank owns: out[h][i] = (score, log-mass) for
+ * cert[h].top_blocks[i] in [first_block, first_block + n_local), zeros otherwise, so a
+ * sum over ranks gives every rank all scores.  `c` is the rank's local cache. */
+int cqa_rescore_owned(const cqa_cache *c, const cqa_head_cert *cert, const void *q, int q_dtype,
+                      int64_t first_block, int64_t n_local, float q_scale, float *out, void *stream);
+/* Ranking / boundary / consistency flags from cert[h].top_blocks and ws->given_fp16. */
+int cqa_certify_given(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *q,
+                      int q_dtype, int64_t nq, int64_t nact, void *stream);
+/* Log-sum-exp merge of n_parts partial rows per head ([n_parts][H][CQA_PARTIAL_STRIDE]) into out[H][128]. */
+int cqa_merge_partials(const float *parts, int n_parts, int n_heads, float *out, void *stream);
 
 /* Suggested split counts for a context of `nact` blocks on the current device. */
 int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int *num_splits, int *dense_splits);
