@@ -67,6 +67,9 @@ def parse_args():
     ap.add_argument("--kernel-steps", type=int, default=32)
     ap.add_argument("--cpu-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sharded-context", type=int, default=131072,
+                    help="context of the sequence-sharded measurement taken when --gpus > 1 (0 = skip)")
+    ap.add_argument("--sharded-steps", type=int, default=64)
     return ap.parse_args()
 
 
@@ -89,7 +92,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -271,10 +274,12 @@ def run_ours(args, rank, world, device_index):
     sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t_host = time.perf_counter()
     for _ in range(K):
         for l in range(NL):
             layer_step(s_idx, l)
         s_idx += 1
+    host_us = (time.perf_counter() - t_host) * 1e6 / (K * NL)   # CPU time to queue one layer-step
     e1.record()
     barrier()
     clocks = sampler.stop()
@@ -320,8 +325,12 @@ def run_ours(args, rank, world, device_index):
     n_meas = 0
     sel_stats = {"k_star_mean": [], "value_fallback_blocks": [], "rung3": 0, "fp16_key_bytes": 0,
                  "fp16_value_bytes": 0}
+    # A 512 MB fill runs ahead of every staged layer-step: it evicts L2 and keeps the GPU busy while the host
+    # queues the four launches, so the events bracket kernel time and not launch latency.
+    flush = torch.empty(128 * 1024 * 1024, dtype=torch.float32, device=dev)
     for _ in range(args.kernel_steps):
         for l in range(NL):
+            flush.fill_(1.0)
             layer_step(s_idx, l, collect=False, timings=phase)
             c = caches[l]
             ws = c._certified_workspace["cqa_ws"]
@@ -356,11 +365,15 @@ def run_ours(args, rank, world, device_index):
     achieved = dom_bytes / (kern_us[dominant] * 1e-6) / 1e9
     chain_bytes = bytes_acc["total"] / n_meas
     chain_gbs = chain_bytes / (us_per_layer * 1e-6) / 1e9
+    # DRAM bytes per launch of the two streaming kernels at this workload, from one ncu capture each
+    # (dram__bytes_read.sum + dram__bytes_write.sum; profiles/ncu_decode_step_ctx32k.md)
+    ncu_traffic = {"phase1_int8_scoring": 50.39e6 + 0.20e6, "phase2_fused_attend": 35.96e6 + 0.07e6}
     roof = {
         "bound": "hbm", "kernel": {"phase1_int8_scoring": "score_blocks_kernel",
                                    "phase2_fused_attend": "attend_kernel"}[dominant],
         "achieved": round(achieved, 1), "peak": peak_gbs, "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
-        "peak_source": peak_src, "traffic": None,
+        "peak_source": peak_src,
+        "traffic": int(ncu_traffic[dominant]) if args.context == 32768 else None,
         "algorithmic_bytes_per_launch": int(dom_bytes), "kernel_us": round(kern_us[dominant], 2),
         "chain": {"algorithmic_bytes_per_layer_step": int(chain_bytes), "us_per_layer_step": round(us_per_layer, 2),
                   "achieved_gbs": round(chain_gbs, 1), "frac": round(chain_gbs / peak_gbs, 4),
@@ -382,6 +395,7 @@ def run_ours(args, rank, world, device_index):
         "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": h2d * NL, "d2h_bytes_per_step": d2h * NL,
                 "tokens_per_s_32layer_equiv": round(1e6 / (32.0 * e2e_us), 2)},
         "gpu_launches": KERNELS_PER_LAYER_STEP * NL * K,
+        "host_us_per_layer_step": round(host_us, 2),
         "clocks": clocks,
         "roofline": roof,
         "selection": {"k_star_mean": round(float(np.mean(sel_stats["k_star_mean"])), 2),
@@ -389,6 +403,84 @@ def run_ours(args, rank, world, device_index):
                       "rung3_heads_total": sel_stats["rung3"], "layer_steps_measured": n_meas},
     }
     return result, bases
+
+
+def run_sharded(args, rank, world, device_index):
+    """Config 4: one layer, 128K context with 10 needle blocks (cosine 0.95 at depths 0.0 .. 0.9), sharded by
+    block range over the ranks.  Rank 0 also times the same sequence unsharded on its own GPU."""
+    import torch
+    import torch.distributed as dist
+
+    from cqa_b200 import synth
+    from dotcache.kernels import certified_attention as ca
+    from dotcache.kernels.sharded_certified_attention import ShardedCertifiedLayer, ShardPlan
+    from dotcache.kernels.tiered_kv_cache import TieredKeyCacheLayer
+
+    dev = torch.device("cuda", device_index)
+    n, K, W = args.sharded_context, args.sharded_steps, max(3, args.warmup)
+    base = synth.make_layer_inputs(args.seed + 77, n, dtype="bfloat16", n_planted_blocks=10, planted_cos=0.95,
+                                   planted_depths=[i / 10.0 for i in range(10)])
+    steps = [synth.decode_step_inputs(base, s, dtype="bfloat16") for s in range(W + K)]
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).to(dev)
+    qs = [to(q) for q, _, _ in steps]
+    ks = [to(k.reshape(8, 1, 128)) for _, k, _ in steps]
+    vs = [to(v.reshape(8, 1, 128)) for _, _, v in steps]
+    knobs = dict(PAPER_KNOBS)
+    knobs["exploration_rate"] = 0.0   # the draw must be identical on every rank; off keeps the comparison simple
+    plan = ShardPlan(world, rank, n, W + K + 16)
+    lo, hi = plan.prefill_token_range()
+    cache = TieredKeyCacheLayer.from_fp16_cache_int4v(to(base.k[:, lo:hi]), to(base.v[:, lo:hi]),
+                                                      max_new_tokens=(W + K + 16) if rank == plan.last else 0,
+                                                      defer_int4_append_quantization=True)
+    layer = ShardedCertifiedLayer(plan, cache, 4)
+
+    def timed(fn):
+        for s in range(W):
+            fn(s)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(W, W + K):
+            fn(s)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / K
+
+    def sharded_step(s):
+        layer.append_token(ks[s], vs[s])
+        layer.step(qs[s], None, **knobs)
+
+    us = timed(sharded_step)
+    t = torch.tensor([us], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t.item())
+    single = None
+    if rank == 0:
+        full = TieredKeyCacheLayer.from_fp16_cache_int4v(to(base.k), to(base.v), max_new_tokens=W + K + 16,
+                                                         defer_int4_append_quantization=True)
+        q_scale = 1.0 / math.sqrt(128.0)
+        for s in range(W):
+            full.append_token(ks[s], vs[s])
+            ca.certified_attention_layer(full, qs[s], 4, q_scale, False, **knobs)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(W, W + K):
+            full.append_token(ks[s], vs[s])
+            ca.certified_attention_layer(full, qs[s], 4, q_scale, False, **knobs)
+        e1.record()
+        torch.cuda.synchronize()
+        single = e0.elapsed_time(e1) * 1e3 / K
+    dist.barrier()
+    if rank != 0:
+        return None
+    per_rank_bytes = 2304.0 * n / world
+    return {"workload": f"one layer, context {n}, 10 needle blocks (cosine 0.95), block ranges over {world} ranks, "
+                        "NCCL all-gather / all-reduce exchanges", "ranks": world, "steps": K,
+            "us_per_layer_step": round(us, 2), "single_gpu_us_per_layer_step": round(single, 2),
+            "speedup_vs_single_gpu": round(single / us, 3),
+            "hbm_floor_us_per_rank": round(per_rank_bytes / 6540.2e3, 2)}
 
 
 def main():
@@ -437,6 +529,13 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     result, bases = run_ours(args, rank, world, local)
+    if world > 1 and args.sharded_context > 0:
+        del bases
+        torch.cuda.empty_cache()
+        sharded = run_sharded(args, rank, world, local)
+        if rank == 0:
+            result["sharded"] = sharded
+        bases = [None]
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             us = cpu_baseline(args, bases[0], args.cpu_steps, max_new)

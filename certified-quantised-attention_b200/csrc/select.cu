@@ -53,6 +53,8 @@ struct SCShared {
     u64 red_u[SC_WARPS * 4];
     int red_i[2][SC_WARPS];
     unsigned char rank_part[4][CAND];
+    float vs_f[2][8];
+    int vs_i[2][8];
     unsigned short rank_pos[CAND];
 #ifdef CQA_PHASE_CLOCKS
     long long dbg[8];
@@ -184,6 +186,39 @@ __device__ __forceinline__ int block_sum_int(int v, SCShared &sh, int parity)
     if (l == 0) sh.red_i[parity][w] = v;
     __syncthreads();
     return __reduce_add_sync(FULL, sh.red_i[parity][l]);
+}
+
+// Named barrier for the first VS_THREADS threads of the CTA (the rest do not take part).
+constexpr int VS_THREADS = 256, VS_WARPS = VS_THREADS / 32;
+__device__ __forceinline__ void vs_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(VS_THREADS) : "memory"); }
+
+// "Column sum" of the entries of vals[0..n) that `pred(bits, index)` admits, and their number; called by
+// threads 0..VS_THREADS-1 only, result in every one of them.  Fixed order: thread t adds its entries
+// t, t+256, t+512, ... in ascending order; the 32 columns of a warp are combined by the butterfly
+// 16,8,4,2,1; the 8 warp sums by the butterfly 4,2,1.  Adding an admitted entry never lowers the result
+// (every step is a monotone rounding), which is what the threshold search below relies on.
+template <typename Pred>
+__device__ __forceinline__ float column_sum(const float *vals, int n, Pred pred, SCShared &sh, int &parity, int &count)
+{
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    float s = 0.0f;
+    int c = 0;
+    for (int b = tid; b < n; b += VS_THREADS) {
+        const float v = vals[b];
+        if (pred(__float_as_uint(v), b)) { s = __fadd_rn(s, v); ++c; }
+    }
+    s = warp_sum(s);
+    c = __reduce_add_sync(FULL, c);
+    if (lane == 0) { sh.vs_f[parity][w] = s; sh.vs_i[parity][w] = c; }
+    vs_barrier();
+    float x = lane < VS_WARPS ? sh.vs_f[parity][lane] : 0.0f;
+    int y = lane < VS_WARPS ? sh.vs_i[parity][lane] : 0;
+    parity ^= 1;
+    x = __fadd_rn(x, __shfl_xor_sync(FULL, x, 4));
+    x = __fadd_rn(x, __shfl_xor_sync(FULL, x, 2));
+    x = __fadd_rn(x, __shfl_xor_sync(FULL, x, 1));
+    count = __reduce_add_sync(FULL, y);
+    return __shfl_sync(FULL, x, 0);
 }
 
 // The M = min(CAND, n) largest (value, lower-index-first) entries of vals[0..n), vals >= 0, sorted
@@ -741,67 +776,82 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
         mask[b] = 0;
     }
     CQA_CLK(10);
-    const float e_pre = block_canonical_sum(A, n, gsum, leaf, sh);
-    CQA_CLK(11);
-    const float excess = fmaxf(__fsub_rn(e_pre, kn.v_tolerance), 0.0f);
-    if (tid == 0) { sh.bcast_f[1] = 0.0f; sh.bcast_i[1] = 0; sh.bcast_i[2] = 1; }
-    if (kn.value_mode_tight) {
-        if (excess > 0.0f) {
-            // greedy promotion over the descending order: the 256 largest contributors first
-            const int M = select_top_sorted(A, n, cand, sh);
-            CQA_CLK(12);
-            if (tid == 0) {
-                float run = 0.0f, promoted = 0.0f;
-                int n_prom = 0, done = 0;
-                for (int j = 0; j < M; ++j) {
-                    const float v = key_val(cand[j]);
-                    run = j == 0 ? v : __fadd_rn(run, v);
-                    if (!(__fsub_rn(run, v) < excess)) { done = 1; break; }
-                    mask[key_idx(cand[j])] = 1;
-                    promoted = run;
-                    ++n_prom;
+    __syncthreads();
+    // Greedy promotion, largest contribution first (ties: lower block id first): block b is promoted while the
+    // column sum of the contributions ranked before it is below the excess.  That sum never decreases along the
+    // ranking, so the promoted blocks are exactly those with contribution bits >= t0, where t0 is the largest
+    // threshold whose admitted set still sums to at least the excess; t0 is found bit by bit by the first 256
+    // threads (no sort, no serial walk).  Exact ties at t0 are resolved the same way over the block id.
+    if (tid == 0) { sh.bcast_f[1] = 0.0f; sh.bcast_f[2] = 0.0f; sh.bcast_i[1] = 0; sh.bcast_u[0] = 0xFFFFFFFFu; sh.bcast_i[3] = 0; }
+    if (tid < VS_THREADS) {
+        int parity = 0, cnt = 0;
+        const float e_pre_v = column_sum(A, n, [](unsigned, int) { return true; }, sh, parity, cnt);
+        const float excess = fmaxf(__fsub_rn(e_pre_v, kn.v_tolerance), 0.0f);
+        float promoted = 0.0f;
+        int n_prom = 0;
+        unsigned t0 = 0xFFFFFFFFu;   // nothing admitted
+        int id_bound = 0;
+        if (kn.value_mode_tight) {
+            if (excess > 0.0f) {
+                t0 = 0u;
+                int cnt_lo = cnt, cnt_hi = 0;     // entries >= t0, entries >= the upper end of the open range
+                float f_lo = e_pre_v;
+#pragma unroll 1
+                for (int bit = 30; bit >= 0 && cnt_lo - cnt_hi > 1; --bit) {
+                    const unsigned trial = t0 | (1u << bit);
+                    int c = 0;
+                    const float f = column_sum(A, n, [trial](unsigned bits, int) { return bits >= trial; }, sh, parity, c);
+                    if (f >= excess) { t0 = trial; cnt_lo = c; f_lo = f; } else { cnt_hi = c; }
                 }
-                if (M == n) done = 1;
-                sh.bcast_f[1] = promoted;
-                sh.bcast_i[1] = n_prom;
-                sh.bcast_i[2] = done;
-            }
-            __syncthreads();
-            if (!sh.bcast_i[2]) {
-                // 256 contributors were not enough: sort everything and walk the whole order
-                u64 *keys = reinterpret_cast<u64 *>(B);
-                for (int b = tid; b < n_pad; b += SC_THREADS) keys[b] = b < n ? make_key(A[b], b) : 0ull;
-                __syncthreads();
-                bitonic_sort_desc(keys, n_pad);
-                if (tid == 0) {
-                    float run = 0.0f, promoted = 0.0f;
-                    int n_prom = 0;
-                    for (int j = 0; j < n; ++j) {
-                        const float v = key_val(keys[j]);
-                        run = j == 0 ? v : __fadd_rn(run, v);
-                        if (!(__fsub_rn(run, v) < excess)) break;
-                        mask[key_idx(keys[j])] = 1;
-                        promoted = run;
-                        ++n_prom;
+                promoted = f_lo;
+                n_prom = cnt_lo;
+                id_bound = n;                     // every entry equal to t0 is admitted ...
+                if (cnt_lo - cnt_hi > 1) {
+                    // ... unless several entries equal t0: admit them in block order while the sum stays below
+                    int i0 = 0;
+#pragma unroll 1
+                    for (int bit = 14; bit >= 0; --bit) {
+                        const int trial = i0 | (1 << bit);
+                        if (trial > n) continue;
+                        int c = 0;
+                        const unsigned tt = t0;
+                        const float g = column_sum(A, n, [tt, trial](unsigned bits, int b) { return bits > tt || (bits == tt && b < trial); }, sh, parity, c);
+                        if (g < excess) i0 = trial;
                     }
-                    sh.bcast_f[1] = promoted;
-                    sh.bcast_i[1] = n_prom;
+                    id_bound = i0 + 1;
+                    const unsigned tt = t0;
+                    const int ib = id_bound;
+                    promoted = column_sum(A, n, [tt, ib](unsigned bits, int b) { return bits > tt || (bits == tt && b < ib); }, sh, parity, n_prom);
                 }
             }
+        } else {
+            const float vt = kn.v_tolerance;
+            promoted = column_sum(A, n, [eta, vt](unsigned, int b) { return eta[b] > vt; }, sh, parity, n_prom);
         }
-    } else {
-        __syncthreads();
-        int cnt = 0;
+        if (tid == 0) {
+            sh.bcast_f[1] = promoted;
+            sh.bcast_f[2] = e_pre_v;
+            sh.bcast_i[1] = n_prom;
+            sh.bcast_u[0] = t0;
+            sh.bcast_i[3] = id_bound;
+        }
+    }
+    __syncthreads();
+    CQA_CLK(12);
+    const float e_pre = sh.bcast_f[2];
+    {
+        const unsigned t0 = sh.bcast_u[0];
+        const int id_bound = sh.bcast_i[3];
         for (int b = tid; b < n; b += SC_THREADS) {
-            const bool unsafe = eta[b] > kn.v_tolerance;
-            mask[b] = unsafe ? 1 : 0;
-            if (!unsafe) A[b] = 0.0f; else ++cnt;
+            bool up;
+            if (kn.value_mode_tight) {
+                const unsigned bits = __float_as_uint(A[b]);
+                up = t0 != 0xFFFFFFFFu && (bits > t0 || (bits == t0 && b < id_bound));
+            } else {
+                up = eta[b] > kn.v_tolerance;
+            }
+            mask[b] = up ? 1 : 0;
         }
-        if (tid == 0) sh.counter = 0;
-        __syncthreads();
-        if (cnt) atomicAdd(&sh.counter, cnt);
-        const float promoted = block_canonical_sum(A, n, gsum, leaf, sh);
-        if (tid == 0) { sh.bcast_f[1] = promoted; sh.bcast_i[1] = sh.counter; }
     }
     __syncthreads();
     CQA_CLK(13);

@@ -58,6 +58,7 @@ def lib():
         _lib.cqa_o_log.restype = C.c_float
         _lib.cqa_o_log.argtypes = [C.c_float]
         _lib.cqa_o_canonical_sum.restype = C.c_float
+        _lib.cqa_o_column_sum.restype = C.c_float
     return _lib
 
 
@@ -82,6 +83,13 @@ def log32(x):
 def canonical_sum(x) -> np.float32:
     x = _c(x, np.float32)
     return f32(lib().cqa_o_canonical_sum(_p(x), C.c_long(x.size)))
+
+
+def column_sum(x, include=None) -> np.float32:
+    """Sum of x[include] in the fixed column order of the Rung-2 value check (256 columns, butterflies)."""
+    x = _c(x, np.float32)
+    inc = None if include is None else _c(include, np.uint8)
+    return f32(lib().cqa_o_column_sum(_p(x), _p(inc), C.c_long(x.size)))
 
 
 def leaf_sums(x) -> np.ndarray:
@@ -453,26 +461,39 @@ def value_check(frac, eta, gqa_group, v_tolerance, mode="tight"):
     H, nq = frac.shape
     kv_idx = np.minimum(np.arange(H) // gqa_group, eta.shape[0] - 1)
     e = (frac * eta[kv_idx][:, :nq]).astype(np.float32)
-    e_pre = np.array([canonical_sum(e[h]) for h in range(H)], dtype=np.float32)
+    e_pre = np.array([column_sum(e[h]) for h in range(H)], dtype=np.float32)
     unsafe = np.zeros((H, nq), dtype=bool)
     promoted = np.zeros((H,), dtype=np.float32)
     vt = f32(v_tolerance)
     if mode == "tight":
+        # Greedy promotion over the descending order (ties: lower block id first): the entry at position j is
+        # promoted while the column sum of the entries before it is below the excess.  The column sum of a prefix
+        # never decreases with its length, so the promoted entries are a prefix and its length can be bisected.
         for h in range(H):
             excess = max(e_pre[h] - vt, f32(0.0))
+            if not excess > 0:
+                continue
             order = np.argsort(-e[h], kind="stable")
-            sv = e[h][order]
-            cum = seq_cumsum(sv)
-            cb = (cum - sv).astype(np.float32)
-            prom = (excess > 0) & (cb < excess)
-            unsafe[h, order[prom]] = True
-            # sum of promoted contributions in sorted order, sequential
-            pv = sv[prom]
-            promoted[h] = seq_cumsum(pv)[-1] if pv.size else f32(0.0)
+            inc = np.zeros(nq, dtype=np.uint8)
+
+            def before(j):
+                inc[:] = 0
+                inc[order[:j]] = 1
+                return column_sum(e[h], inc)
+
+            lo, hi = 0, nq - 1          # position lo is promoted (nothing before it); find the last promoted one
+            while lo < hi:
+                mid = (lo + hi + 1) // 2
+                if before(mid) < excess:
+                    lo = mid
+                else:
+                    hi = mid - 1
+            unsafe[h, order[: lo + 1]] = True
+            promoted[h] = before(lo + 1)
     else:
         unsafe = eta[kv_idx][:, :nq] > vt
         for h in range(H):
-            promoted[h] = canonical_sum(e[h] * unsafe[h].astype(np.float32))
+            promoted[h] = column_sum(e[h], unsafe[h])
     e_val = np.maximum(e_pre - promoted, f32(0.0)).astype(np.float32)
     return dict(e=e, e_pre=e_pre, unsafe=unsafe, promoted=promoted, e_val=e_val)
 
