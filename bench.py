@@ -485,6 +485,17 @@ def run_sharded(args, rank, world, device_index):
 
 def main():
     args = parse_args()
+    # Libraries (NCCL prints its version on start-up) write to file descriptor 1; the one JSON line the caller
+    # parses goes to the original stdout, everything else to stderr.
+    out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    try:
+        return _main(args, out)
+    finally:
+        out.flush()
+
+
+def _main(args, out):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -515,13 +526,13 @@ def main():
                     "times the CPU oracle port of its algorithm",
             "wall_s": round(time.perf_counter() - t0, 1),
         }
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=out, flush=True)
         return 0
 
     import torch
 
     if not torch.cuda.is_available():
-        print(json.dumps({"error": "no CUDA device: bench.py --impl ours needs a B200; there is no CPU fallback"}))
+        print(json.dumps({"error": "no CUDA device: bench.py --impl ours needs a B200; there is no CPU fallback"}), file=out)
         return 1
     if world > 1:
         import torch.distributed as dist
@@ -544,7 +555,7 @@ def main():
                 "value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
                 "sample": f"{args.cpu_steps} decode steps of one layer at context {args.context} (median), "
                           f"OpenMP over {cores} host threads, after 1 warm-up step"}
-        print(json.dumps(result), flush=True)
+        print(json.dumps(result), file=out, flush=True)
     if world > 1:
         import torch.distributed as dist
 

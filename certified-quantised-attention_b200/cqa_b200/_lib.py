@@ -81,6 +81,7 @@ class CqaWorkspace(C.Structure):
         ("dense_m", vp), ("dense_l", vp), ("dense_acc", vp),
         ("cert", vp), ("any_flags", vp), ("out", vp), ("tickets", vp),
         ("given_fp16", vp), ("partial_out", vp),
+        ("rng_seed", C.c_uint64), ("rng_offset", C.c_uint64),
     ]
 
 
@@ -159,6 +160,35 @@ def ptr(t) -> int | None:
 
 
 def current_stream(device) -> int:
+    """Raw cudaStream_t of torch's current stream on `device` (no Stream object is built)."""
     import torch
 
-    return torch.cuda.current_stream(device).cuda_stream
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(idx)
+
+
+class on_device:
+    """`with on_device(dev):` makes `dev` the current CUDA device, and is free when it already is."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = device.index
+        self.prev = -1
+
+    def __enter__(self):
+        import torch
+
+        if self.idx is not None:
+            cur = torch.cuda.current_device()
+            if cur != self.idx:
+                self.prev = cur
+                torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            import torch
+
+            torch.cuda.set_device(self.prev)
+        return False

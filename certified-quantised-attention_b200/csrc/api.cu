@@ -26,7 +26,7 @@ int check_cuda(cudaError_t e, const char *what)
 int check_launch(const char *what) { return check_cuda(cudaGetLastError(), what); }
 
 int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
-                        float *s_b, long ld, float *tok, cudaStream_t st);
+                        float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words);
 int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq, long nact,
                   const float *u, long u_ld, cudaStream_t st);
 int certify_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
@@ -189,13 +189,15 @@ extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const 
     const int last_valid = nact == nq ? BS : (int)(num_tokens - nq * BS);
     cudaStream_t st = (cudaStream_t)stream;
     if (!ws->token_scores) { set_error("cqa_layer_step: token_scores missing"); return CQA_ERR_INVALID; }
-    rc = score_blocks_launch(c, q, q_dtype, nq, knobs->q_scale, ws->m_b, ws->s_b, ws->ld, ws->token_scores, st);
+    const int n_flag_words = 5 + c->kv_heads * c->gqa_group;
+    rc = score_blocks_launch(c, q, q_dtype, nq, knobs->q_scale, ws->m_b, ws->s_b, ws->ld, ws->token_scores, st,
+                             ws->any_flags, n_flag_words);
     if (rc) return rc;
     if (!(knobs->tau_cov > 0.0f)) { set_error("cqa_layer_step: tau_cov must be positive"); return CQA_ERR_INVALID; }
     if (!ws->value_mask) { set_error("cqa_layer_step: value_mask missing"); return CQA_ERR_INVALID; }
     if (nact > ws->ld) { set_error("cqa_layer_step: workspace ld too small"); return CQA_ERR_INVALID; }
     if (exploration_u && u_ld < nq) { set_error("cqa_layer_step: exploration_u leading dimension too small"); return CQA_ERR_INVALID; }
-    rc = selcert_launch(c, knobs, ws, q, q_dtype, nq, nact, exploration_u, u_ld, 3, st);   // select + certify, one launch
+    rc = selcert_launch(c, knobs, ws, q, q_dtype, nq, nact, exploration_u, u_ld, 3 | 16, st);   // select + certify in one launch; flags cleared by the score kernel
     if (rc) return rc;
     return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, knobs->q_scale, st);
 }

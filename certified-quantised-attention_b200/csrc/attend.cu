@@ -608,12 +608,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
             const int n_valid = (b == nact - 1) ? last_valid : BS;
             long vslot = c.value_slots ? (long)c.value_slots[b] : b;
             if (vslot < 0) vslot = 0;
-#pragma unroll 2
+            // all eight rows of this half warp are requested before the first is used
+            Raw8<T2> vr[8];
+#pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int t = 2 * i + hw;
-                if (t >= n_valid) continue;
+                vr[i] = t < n_valid ? raw_load8<T2>(vt2 + (vslot * BS + t) * D + 8 * L) : raw_zero8<T2>();
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int t = 2 * i + hw;
                 float v16[8];
-                load8<T2>(vt2 + (vslot * BS + t) * D + 8 * L, v16);
+                raw_to_f(vr[i], v16);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     if (!(vm & (1u << g))) continue;

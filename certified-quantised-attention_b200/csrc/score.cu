@@ -84,11 +84,15 @@ template <int G>
 __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_cache c, const void *q, int q_dtype,
                                                                           long nq, float q_scale, float *m_b,
                                                                           float *s_b, long ld, float *tok,
-                                                                          int blocks_per_cta)
+                                                                          int blocks_per_cta, int32_t *zero_words,
+                                                                          int n_zero_words)
 {
     extern __shared__ __align__(16) char smem[];
     constexpr int GH = G >= 4 ? 4 : G;  // heads per register pass
     const int kv = blockIdx.y;
+    // the fused layer step lets this kernel clear the certifier's flag words (one memset launch fewer)
+    if (zero_words != nullptr && blockIdx.x == 0 && blockIdx.y == 0)
+        for (int i = threadIdx.x; i < n_zero_words; i += SCORE_WARPS * 32) zero_words[i] = 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int L = lane & 15, hw = lane >> 4;
     const long b_begin = (long)blockIdx.x * blocks_per_cta;
@@ -220,7 +224,8 @@ __global__ void __launch_bounds__(32) delta_bound_kernel(cqa_cache c, const void
 
 template <int G>
 static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
-                          float *s_b, long ld, float *tok, dim3 grid, int bpc, cudaStream_t st)
+                          float *s_b, long ld, float *tok, dim3 grid, int bpc, int32_t *zero_words, int n_zero_words,
+                          cudaStream_t st)
 {
     constexpr int SMEM = SCORE_SMEM + G * D * 4;
     static bool attr_set = false;
@@ -231,7 +236,8 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
         if (rc) return rc;
         attr_set = true;
     }
-    score_blocks_kernel<G><<<grid, SCORE_WARPS * 32, SMEM, st>>>(*c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, bpc);
+    score_blocks_kernel<G><<<grid, SCORE_WARPS * 32, SMEM, st>>>(*c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, bpc,
+                                                                 zero_words, n_zero_words);
     return check_launch("score_blocks_kernel");
 }
 
@@ -250,7 +256,7 @@ int rescore_owned_launch(const cqa_cache *c, const cqa_head_cert *cert, const vo
 }
 
 int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
-                        float *s_b, long ld, float *tok, cudaStream_t st)
+                        float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words)
 {
     static int sm_count = 0;
     if (sm_count == 0) {
@@ -266,10 +272,10 @@ int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq,
     if (bpc < 2) bpc = 2;
     dim3 grid((unsigned)((nq + bpc - 1) / bpc), (unsigned)c->kv_heads);
     switch (c->gqa_group) {
-    case 1: return score_launch_g<1>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, st);
-    case 2: return score_launch_g<2>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, st);
-    case 4: return score_launch_g<4>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, st);
-    case 8: return score_launch_g<8>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, st);
+    case 1: return score_launch_g<1>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, st);
+    case 2: return score_launch_g<2>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, st);
+    case 4: return score_launch_g<4>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, st);
+    case 8: return score_launch_g<8>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, st);
     }
     set_error("score_blocks: unsupported gqa_group %d", c->gqa_group);
     return CQA_ERR_UNSUPPORTED;
@@ -293,7 +299,7 @@ extern "C" int cqa_score_blocks(const cqa_cache *c, const void *q, int q_dtype, 
         return CQA_ERR_INVALID;
     }
     if (q_dtype < 0 || q_dtype > 2) { set_error("cqa_score_blocks: unknown q dtype"); return CQA_ERR_INVALID; }
-    return score_blocks_launch(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, token_scores, (cudaStream_t)stream);
+    return score_blocks_launch(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, token_scores, (cudaStream_t)stream, nullptr, 0);
 }
 
 extern "C" int cqa_fp16_block_scores(const cqa_cache *c, const void *q, int q_dtype, const int32_t *idx, int K,

@@ -30,6 +30,7 @@ constexpr int PH_SELECT = 1, PH_CERTIFY = 2;
 // list is in the certificate; PH_GIVEN resumes it from that list with FP16 scores computed by the ranks that
 // own the blocks (ws.given_fp16) and runs role 1 alone.
 constexpr int PH_TOP_ONLY = 4, PH_GIVEN = 8;
+constexpr int PH_FLAGS_CLEARED = 16;   // the caller already zeroed ws.any_flags on this stream
 
 typedef unsigned long long u64;
 
@@ -47,6 +48,24 @@ typedef unsigned long long u64;
 #define CQA_CLK_FLUSH(lo, hi) do { } while (0)
 #define CQA_LM_ROWS CQA_MAX_RANKING_K
 #endif
+
+// One uniform in [0, 1) per (block, head, call): Philox4x32-10 on the counter (block, head, offset) under `seed`.
+__device__ __forceinline__ float philox_uniform(unsigned long long seed, unsigned long long offset, unsigned head,
+                                                unsigned block)
+{
+    unsigned c0 = block, c1 = head, c2 = (unsigned)offset, c3 = (unsigned)(offset >> 32);
+    unsigned k0 = (unsigned)seed, k1 = (unsigned)(seed >> 32);
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const unsigned hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const unsigned hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        const unsigned n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return (float)(c0 >> 8) * 5.9604644775390625e-08f;   // 2^-24
+}
 
 struct SCShared {
     float red_f[SC_WARPS];
@@ -400,7 +419,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
 
     // ---- one round of global loads, all issued up front: m_b, S_b; the exploration draw (role 0);
     // eta_b and, when only certifying, the mass fractions (role 2)
-    const bool explore_on = kn.exploration_rate > 0.0f && u != nullptr;
+    const bool explore_on = kn.exploration_rate > 0.0f;
     const float *eta = have_int4 ? c.values_int4_errors + (long)kv * c.max_blocks : nullptr;
     float mg = -INFINITY;
     for (int b = tid; b < n_pad; b += SC_THREADS) {
@@ -408,7 +427,11 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             const float m = mb[b];
             const float s = fmaxf(sb[b], 1e-30f);
             unsigned char ebit = 0;
-            if (role == 0 && explore_on) ebit = u[(long)h * u_ld + b] < kn.exploration_rate ? 2 : 0;
+            if (role == 0 && explore_on) {
+                const float uv = u != nullptr ? u[(long)h * u_ld + b]
+                                              : philox_uniform(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)b);
+                ebit = uv < kn.exploration_rate ? 2 : 0;
+            }
             if (role == 2) {
                 if (!fused) C[b] = mf[b];
                 A[b] = eta ? eta[b] : 0.0f;      // role 2 never needs m_b
@@ -932,7 +955,7 @@ static int selcert_launch_t(const cqa_cache *c, const cqa_knobs *kn, const cqa_w
         if (rc) return rc;
         attr = smem;
     }
-    if (phases & PH_SELECT) {
+    if ((phases & PH_SELECT) && !(phases & PH_FLAGS_CLEARED)) {
         int rc = check_cuda(cudaMemsetAsync(ws->any_flags, 0, (5 + H) * sizeof(int32_t), st),
                             "cudaMemsetAsync(any_flags)");
         if (rc) return rc;

@@ -75,7 +75,11 @@ class _Workspace:
         self.out = torch.empty(H, 128, **f32)
         self.tickets = torch.zeros(cache.kv_heads + H, dtype=torch.int32, device=device)
         self.cert_host = None
+        self._u_flat = None
+        self.rng_seed = None
+        self.rng_calls = 0
         self.struct = _lib.CqaWorkspace()
+        self._struct_stale = True
 
     def ensure_sel_width(self, width: int, device):
         if self.sel_width < width:
@@ -83,30 +87,48 @@ class _Workspace:
             self.sorted_idx = torch.zeros(self.H, width, dtype=torch.int32, device=device)
             self.sorted_cumsum = torch.zeros(self.H, width, dtype=torch.float32, device=device)
 
+    def uniform_buffer(self, nq: int, device) -> torch.Tensor:
+        """A reused [H, nq] float32 view for the exploration draw."""
+        if self._u_flat is None or self._u_flat.numel() < self.H * self.ld:
+            self._u_flat = torch.empty(self.H * self.ld, dtype=torch.float32, device=device)
+        return self._u_flat[: self.H * nq].view(self.H, nq)
+
     def fill_struct(self, nact: int | None = None) -> _lib.CqaWorkspace:
+        """The cqa_workspace struct over these buffers.  Pointers are written once (again after a buffer is
+        replaced); per call only the split counts follow `nact`."""
         s = self.struct
-        s.ld = self.ld
-        s.m_b, s.s_b = self.m_b.data_ptr(), self.s_b.data_ptr()
-        s.token_scores = self.token_scores.data_ptr()
-        s.mass_frac = self.mass_frac.data_ptr()
-        s.topk_mask, s.value_mask = self.topk_mask.data_ptr(), self.value_mask.data_ptr()
-        s.explore_mask = self.explore_mask.data_ptr()
-        s.sorted_idx = _lib.ptr(self.sorted_idx)
-        s.sorted_cumsum = _lib.ptr(self.sorted_cumsum)
-        s.sel_width = self.sel_width
+        if self._struct_stale:
+            s.ld = self.ld
+            s.m_b, s.s_b = self.m_b.data_ptr(), self.s_b.data_ptr()
+            s.token_scores = self.token_scores.data_ptr()
+            s.mass_frac = self.mass_frac.data_ptr()
+            s.topk_mask, s.value_mask = self.topk_mask.data_ptr(), self.value_mask.data_ptr()
+            s.explore_mask = self.explore_mask.data_ptr()
+            s.sorted_idx = _lib.ptr(self.sorted_idx)
+            s.sorted_cumsum = _lib.ptr(self.sorted_cumsum)
+            s.sel_width = self.sel_width
+            s.part_m, s.part_l, s.part_acc = self.part_m.data_ptr(), self.part_l.data_ptr(), self.part_acc.data_ptr()
+            s.dense_m, s.dense_l, s.dense_acc = self.dense_m.data_ptr(), self.dense_l.data_ptr(), self.dense_acc.data_ptr()
+            s.cert = self.cert_buf.data_ptr()
+            s.any_flags = self.cert_buf.data_ptr() + self.cert_bytes
+            s.out = self.out.data_ptr()
+            s.tickets = self.tickets.data_ptr()
+            self._struct_stale = False
         ns, ds = self.num_splits, self.dense_splits
         if nact is not None:
             # never more splits than eight-block groups of work
             ns = max(1, min(ns, (nact + 7) // 8))
             ds = max(1, min(ds, (nact + 15) // 16))
         s.num_splits, s.dense_splits = ns, ds
-        s.part_m, s.part_l, s.part_acc = self.part_m.data_ptr(), self.part_l.data_ptr(), self.part_acc.data_ptr()
-        s.dense_m, s.dense_l, s.dense_acc = self.dense_m.data_ptr(), self.dense_l.data_ptr(), self.dense_acc.data_ptr()
-        s.cert = self.cert_buf.data_ptr()
-        s.any_flags = self.cert_buf.data_ptr() + self.cert_bytes
-        s.out = self.out.data_ptr()
-        s.tickets = self.tickets.data_ptr()
         return s
+
+    def __setattr__(self, name, value):
+        # replacing a buffer (tests and the sharded layer do) makes the cached pointers stale
+        if name in ("m_b", "s_b", "token_scores", "mass_frac", "topk_mask", "value_mask", "explore_mask",
+                    "sorted_idx", "sorted_cumsum", "part_m", "part_l", "part_acc", "dense_m", "dense_l", "dense_acc",
+                    "cert_buf", "out", "tickets", "sel_width"):
+            object.__setattr__(self, "_struct_stale", True)
+        object.__setattr__(self, name, value)
 
     def read_cert(self) -> tuple[dict, list]:
         """Copy the certificate structs and flags to the host (synchronises)."""
@@ -132,10 +154,23 @@ def _workspace(cache: TieredKeyCacheLayer, H: int, G: int, device) -> _Workspace
     return ws
 
 
+_KNOBS_CACHE: dict = {}
+
+
 def _make_knobs(*, q_scale, tau_cov, k_min, k_max, rung1_threshold, rung1_multiplier, eps_guard,
                 exploration_rate, v_tolerance, ranking_r, top_k_fp16_keys, ranking_fallback,
                 ranking_fallback_mode, score_consistency_check, value_error_mode,
                 force_trailing_value_fp16) -> _lib.CqaKnobs:
+    """The cqa_knobs struct for these settings (structs are read-only to the library, so one per distinct
+    setting is kept and reused)."""
+    key = (q_scale, tau_cov, k_min, k_max, rung1_threshold, rung1_multiplier, eps_guard, exploration_rate,
+           v_tolerance, ranking_r, top_k_fp16_keys, ranking_fallback, ranking_fallback_mode,
+           score_consistency_check, value_error_mode, force_trailing_value_fp16)
+    cached = _KNOBS_CACHE.get(key)
+    if cached is not None:
+        return cached
+    if len(_KNOBS_CACHE) > 256:
+        _KNOBS_CACHE.clear()
     k = _lib.CqaKnobs()
     k.q_scale = float(q_scale)
     k.tau_cov = float(tau_cov)
@@ -153,6 +188,7 @@ def _make_knobs(*, q_scale, tau_cov, k_min, k_max, rung1_threshold, rung1_multip
     k.score_consistency = int(bool(score_consistency_check))
     k.value_mode_tight = int(value_error_mode == "tight")
     k.force_trailing_value_fp16 = int(bool(force_trailing_value_fp16))
+    _KNOBS_CACHE[key] = k
     return k
 
 
@@ -221,7 +257,10 @@ def certified_attention_layer(
     reused workspace tensor; consume it before the next call on this cache.
 
     `exploration_uniforms` ([H, nq] floats in [0,1)) is an addition: when given
-    it replaces the `torch.rand` draw so a run can be replayed exactly.
+    it replaces the random draw so a run can be replayed exactly.  With an
+    `exploration_generator` the draw is the reference's `torch.rand` from that
+    generator; with neither, the selector kernel draws (Philox keyed by
+    `torch.initial_seed()` and a per-cache call counter).
     """
     if not q_all.is_cuda:
         raise RuntimeError("certified_attention_layer needs CUDA tensors; there is no CPU fallback")
@@ -273,7 +312,7 @@ def certified_attention_layer(
         if nq == 0:
             raise NotImplementedError("baseline attend needs at least one complete block")
         wstruct = ws.fill_struct(nact)
-        with torch.cuda.device(device), _PhaseTimer(phase_timings, "phase2_fused_attend", pending):
+        with _lib.on_device(device), _PhaseTimer(phase_timings, "phase2_fused_attend", pending):
             ws.topk_mask[:, :nact].zero_()
             ws.value_mask[:, :nact].zero_()
             if trailing:
@@ -308,14 +347,23 @@ def certified_attention_layer(
     if exploration_rate > 0.0:
         if exploration_uniforms is not None:
             u_keep = exploration_uniforms.to(device=device, dtype=torch.float32).contiguous()
+        elif exploration_generator is not None:
+            # the reference's draw from the caller's generator (one uniform per (head, complete block))
+            u_keep = torch.rand((H, nq), generator=exploration_generator, out=ws.uniform_buffer(nq, device))
+        if u_keep is not None:
+            if tuple(u_keep.shape) != (H, nq):
+                raise ValueError(f"exploration uniforms must have shape {(H, nq)}, got {tuple(u_keep.shape)}")
+            u_ptr, u_ld = u_keep.data_ptr(), nq
         else:
-            # same draw as the reference: one uniform per (head, complete block)
-            u_keep = torch.rand((H, nq), device=device, generator=exploration_generator)
-        if tuple(u_keep.shape) != (H, nq):
-            raise ValueError(f"exploration uniforms must have shape {(H, nq)}, got {tuple(u_keep.shape)}")
-        u_ptr, u_ld = u_keep.data_ptr(), nq
+            # no generator given: the selector draws in-kernel (Philox keyed by torch's seed and a call counter;
+            # same distribution as torch.rand, one launch fewer)
+            if ws.rng_seed is None:
+                ws.rng_seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
+            wstruct.rng_seed = ws.rng_seed
+            wstruct.rng_offset = ws.rng_calls
+            ws.rng_calls += 1
 
-    with torch.cuda.device(device):
+    with _lib.on_device(device):
         if phase_timings is None:
             _lib.check(L.cqa_layer_step(C.byref(desc), C.byref(knobs), C.byref(wstruct), q.data_ptr(), qd,
                                         cache.num_tokens, nq, u_ptr, u_ld, stream), "cqa_layer_step")

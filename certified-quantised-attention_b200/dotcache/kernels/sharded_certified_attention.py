@@ -110,7 +110,7 @@ def exchange_rows(n_heads: int, kv_heads: int) -> int:
 
 
 def scatter_exchange_a(plan: ShardPlan, recv: torch.Tensor, glob: torch.Tensor, sigma: torch.Tensor,
-                       nq_global: int, n_heads: int, kv_heads: int) -> None:
+                       nq_global: int, n_heads: int, kv_heads: int, with_sigma: bool = True) -> None:
     """recv [P][rows][chunk] (rank-major) -> glob [2H+KV][ld] (block-major rows) and sigma [KV*128]."""
     rows = 2 * n_heads + kv_heads
     P, R = plan.world, plan.stride
@@ -119,7 +119,8 @@ def scatter_exchange_a(plan: ShardPlan, recv: torch.Tensor, glob: torch.Tensor, 
     n_last = plan.local_blocks(nq_global, plan.last)
     lo = plan.first_block(plan.last)
     glob[:, lo: lo + n_last].copy_(recv[P - 1, :rows, :n_last])
-    torch.amax(recv[:, rows, : sigma.numel()], dim=0, out=sigma)
+    if with_sigma:
+        torch.amax(recv[:, rows, : sigma.numel()], dim=0, out=sigma)
 
 
 class DistComm:
@@ -165,7 +166,9 @@ class ShardedCertifiedLayer:
         self.ws.m_b = self.glob[:H]
         self.ws.s_b = self.glob[H: 2 * H]
         self.eta = self.glob[2 * H:]
-        self.generator = None
+        self.rng_seed, self.rng_calls = 0, 0     # exploration draw: identical on every rank
+        self._meta_nq = -1
+        self._wg, self._wl = _lib.CqaWorkspace(), _lib.CqaWorkspace()   # private copies: fields are overridden
 
     # -------------------------------------------------------------- bookkeeping
     @property
@@ -206,16 +209,20 @@ class ShardedCertifiedLayer:
         ws = self.ws
         desc_l = cache._desc(G)
 
-        with torch.cuda.device(self.device):
+        with _lib.on_device(self.device):
             # 1. Phase 1 straight into the send buffer (rows 0..H-1 m_b, H..2H-1 S_b)
             _lib.check(L.cqa_score_blocks(C.byref(desc_l), q.data_ptr(), qd, n_loc, float(q_scale),
                                           self.send.data_ptr(), self.send[H].data_ptr(), plan.chunk,
                                           ws.token_scores.data_ptr(), stream), "cqa_score_blocks")
-            self.send[2 * H: 2 * H + KV, :n_loc].copy_(cache.values_int4_errors[:, :n_loc])
-            self.send[2 * H + KV, : KV * 128].copy_(cache.keys_scale_max.reshape(-1))
+            # eta_b and the scale maxima only change when a block completes
+            fresh_meta = self._meta_nq != nq_g
+            if fresh_meta:
+                self.send[2 * H: 2 * H + KV, :n_loc].copy_(cache.values_int4_errors[:, :n_loc])
+                self.send[2 * H + KV, : KV * 128].copy_(cache.keys_scale_max.reshape(-1))
             # 2. Exchange A and the global selector
             self.comm.all_gather(self.recv, self.send)
-            scatter_exchange_a(plan, self.recv, self.glob, self.sigma, nq_g, H, KV)
+            scatter_exchange_a(plan, self.recv, self.glob, self.sigma, nq_g, H, KV, with_sigma=fresh_meta)
+            self._meta_nq = nq_g
             knobs = _make_knobs(
                 q_scale=q_scale, tau_cov=tau_cov, k_min=k_min, k_max=k_max, rung1_threshold=rung1_threshold,
                 rung1_multiplier=rung1_multiplier, eps_guard=eps_guard, exploration_rate=exploration_rate,
@@ -225,10 +232,11 @@ class ShardedCertifiedLayer:
                 force_trailing_value_fp16=True,
             )
             ws.ensure_sel_width(_selection_width(k_max, rung1_threshold, rung1_multiplier, nq_g), self.device)
-            wg = ws.fill_struct(nact_g)
+            wg = self._wg
+            C.memmove(C.byref(wg), C.byref(ws.fill_struct(nact_g)), C.sizeof(wg))
             wg.given_fp16 = self.given.data_ptr()
             wg.partial_out = None
-            desc_g = cache._desc(G)
+            desc_g = cache._desc_copy(G)
             desc_g.max_blocks = plan.ld
             desc_g.values_int4_errors = self.eta.data_ptr()
             desc_g.sigma_max = self.sigma.data_ptr()
@@ -236,12 +244,12 @@ class ShardedCertifiedLayer:
             if exploration_rate > 0.0:
                 if exploration_uniforms is not None:
                     u_keep = exploration_uniforms.to(device=self.device, dtype=torch.float32).contiguous()
+                    u_ptr, u_ld = u_keep.data_ptr(), nq_g
                 else:
-                    if self.generator is None:
-                        raise ValueError("exploration needs `exploration_uniforms` or a generator seeded "
-                                         "identically on every rank (ShardedCertifiedLayer.generator)")
-                    u_keep = torch.rand((H, nq_g), device=self.device, generator=self.generator)
-                u_ptr, u_ld = u_keep.data_ptr(), nq_g
+                    # in-kernel draw: same seed and call counter on every rank, hence the same exploration set
+                    wg.rng_seed = self.rng_seed
+                    wg.rng_offset = self.rng_calls
+                    self.rng_calls += 1
             _lib.check(L.cqa_select_certify_local(C.byref(desc_g), C.byref(knobs), C.byref(wg), nq_g, nact_g,
                                                   u_ptr, u_ld, stream), "cqa_select_certify_local")
             # 3. owners re-score the top list; Exchange B; flags
@@ -255,7 +263,8 @@ class ShardedCertifiedLayer:
                                            nact_g, stream), "cqa_certify_given")
             # 4. Phase 2 over the local blocks, global masks viewed from this rank's first block
             nact_l = n_loc + (1 if (is_last and nact_g > nq_g) else 0)
-            wl = ws.fill_struct(nact_l)
+            wl = self._wl
+            C.memmove(C.byref(wl), C.byref(ws.fill_struct(nact_l)), C.sizeof(wl))
             wl.m_b = self.glob.data_ptr() + 4 * first
             wl.s_b = self.glob[H].data_ptr() + 4 * first
             wl.topk_mask = ws.topk_mask.data_ptr() + first

@@ -85,14 +85,20 @@ class TieredKeyCacheLayer:
     keys_scale_max: torch.Tensor | None = None
     gqa_group_hint: int = 1
     _certified_workspace: dict = field(default_factory=dict, repr=False)
+    _desc_cache: dict = field(default_factory=dict, repr=False)
 
     # ------------------------------------------------------------------ C ABI view
 
     def _desc(self, gqa_group: int | None = None) -> _lib.CqaCache:
-        """The cqa_cache struct over this layer's tensors."""
+        """The cqa_cache struct over this layer's tensors.  Built once per GQA group and reused: the tensors
+        are allocated at construction and never replaced (call `_invalidate_desc` after swapping one)."""
+        g = int(gqa_group if gqa_group is not None else self.gqa_group_hint)
+        cached = self._desc_cache.get(g)
+        if cached is not None:
+            return cached
         d = _lib.CqaCache()
         d.kv_heads = self.kv_heads
-        d.gqa_group = int(gqa_group if gqa_group is not None else self.gqa_group_hint)
+        d.gqa_group = g
         t2 = self.keys_fp16_gpu
         d.t2_dtype = _lib.dtype_code(t2.dtype) if t2 is not None else _lib.CQA_F16
         d.cap_tokens = int(self.keys_int8.shape[1])
@@ -116,7 +122,18 @@ class TieredKeyCacheLayer:
         d.values_t2_rows = int(vt2.shape[1]) if vt2 is not None else 0
         d.key_slots = None      # identity: full mirrors
         d.value_slots = None
+        self._desc_cache[g] = d
         return d
+
+    def _desc_copy(self, gqa_group: int | None = None) -> _lib.CqaCache:
+        """A private copy of the descriptor, for callers that override fields."""
+        src = self._desc(gqa_group)
+        d = _lib.CqaCache()
+        C.memmove(C.byref(d), C.byref(src), C.sizeof(d))
+        return d
+
+    def _invalidate_desc(self) -> None:
+        self._desc_cache.clear()
 
     # ------------------------------------------------------------------ construction
 
@@ -256,17 +273,20 @@ class TieredKeyCacheLayer:
         v = value_fp16.reshape(self.kv_heads, self.d_v)
         if v.dtype != k.dtype:
             v = v.to(k.dtype)
-        k = k.contiguous()
-        v = v.contiguous()
+        if not k.is_contiguous():
+            k = k.contiguous()
+        if not v.is_contiguous():
+            v = v.contiguous()
         defer = bool(
             self.defer_int4_append_quantization
             and self.values_fp16_gpu is not None
             and (self.fp16_value_cache_capacity is None or self.static_resident_value_cache)
         )
-        with torch.cuda.device(k.device):
+        dev = k.device
+        with _lib.on_device(dev):
             rc = _lib.lib().cqa_append_token(
                 C.byref(self._desc()), k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype), pos,
-                1 if defer else 0, _lib.current_stream(k.device))
+                1 if defer else 0, _lib.current_stream(dev))
         _lib.check(rc, "cqa_append_token")
         self.num_tokens = pos + 1
         self.num_blocks = (self.num_tokens + BLOCK - 1) // BLOCK

@@ -164,6 +164,12 @@ typedef struct cqa_workspace {
                                     computed by the rank that owns the block (cqa_rescore_owned) and summed over ranks */
     float *partial_out;          /* [H][CQA_PARTIAL_STRIDE]: when set, cqa_attend writes the un-normalised
                                     (max, sum, acc[128]) of its own blocks here instead of the output rows */
+    /* Exploration draw when no uniforms are passed (exploration_u == NULL, exploration_rate > 0): one
+     * Philox4x32-10 value per (head, block), keyed by rng_seed, counter (block, head, rng_offset).  Callers
+     * advance rng_offset by one per call.  Same distribution as the reference's torch.rand draw, not the
+     * same stream. */
+    uint64_t rng_seed;
+    uint64_t rng_offset;
 } cqa_workspace;
 
 #define CQA_PARTIAL_STRIDE 130

@@ -161,6 +161,34 @@ def test_exact_ties_take_lowest_block_ids():
         hz.compare_step(cc, R, out, f"ties {knobs['v_tolerance']} {knobs['k_max']}")
 
 
+def test_in_kernel_exploration_draw():
+    """Without uniforms or a generator the selector draws its own: the rate is respected, the draw is a function
+    of torch's seed and the per-cache call counter only, and explored blocks are never blocks the selector chose."""
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(13, 16384, dtype=dtype, n_planted_blocks=32)
+    knobs = _knobs(exploration_rate=0.05)
+    masks = []
+    for rep in range(2):
+        torch.manual_seed(1234)
+        cc = hz.make_cuda_cache(base.k, base.v, dtype, 16)
+        per_call = []
+        for call in range(2):
+            hz.cuda_step(cc, base.q, dtype, 4, knobs, None)
+            ws = cc._certified_workspace["cqa_ws"]
+            nq = cc.num_quantized_blocks
+            ex = ws.explore_mask[:, :nq].cpu().numpy().astype(bool)
+            tk = ws.topk_mask[:, :nq].cpu().numpy().astype(bool)
+            cert, _ = ws.read_cert()
+            assert (ex <= tk).all(), "explored blocks must be in the key mask"
+            assert np.array_equal(ex.sum(axis=1), cert["exploration_blocks"])
+            per_call.append(ex)
+        masks.append(per_call)
+        frac = per_call[0].mean()
+        assert 0.035 < frac < 0.065, f"exploration fraction {frac}"
+        assert not np.array_equal(per_call[0], per_call[1]), "the call counter must change the draw"
+    assert np.array_equal(masks[0][0], masks[1][0]) and np.array_equal(masks[0][1], masks[1][1])
+
+
 def test_decode_loop_bit_exact_selections():
     """48 decode steps (3 block completions) at 4K context: every step's
     selections, flags and appended bytes match the oracle."""
