@@ -21,6 +21,7 @@ SYMBOLS = [
     "cqa_score_blocks", "cqa_select", "cqa_fp16_block_scores", "cqa_delta_bound", "cqa_certify",
     "cqa_attend", "cqa_attend_static", "cqa_layer_step", "cqa_suggest_splits",
     "cqa_select_certify_local", "cqa_rescore_owned", "cqa_certify_given", "cqa_merge_partials",
+    "cqa_decode_step_host",
 ]
 PARTIAL_STRIDE = 130
 
@@ -129,6 +130,7 @@ def lib() -> C.CDLL:
     L.cqa_rescore_owned.argtypes = [pc, vp, vp, i32, i64, i64, f32, vp, vp]
     L.cqa_certify_given.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp]
     L.cqa_merge_partials.argtypes = [vp, i32, i32, vp, vp]
+    L.cqa_decode_step_host.argtypes = [pc, pk, pw, vp, vp, i32, i64, i32, vp, vp]
     for s in SYMBOLS[2:]:
         getattr(L, s).restype = C.c_int
     _lib = L

@@ -105,6 +105,34 @@ extern "C" int cqa_certify(const cqa_cache *c, const cqa_knobs *knobs, const cqa
     return certify_launch(c, knobs, ws, q, q_dtype, nq, nact, (cudaStream_t)stream);
 }
 
+extern "C" int cqa_decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws,
+                                    const void *qkv_host, void *qkv_dev, int dtype, int64_t pos, int defer_int4,
+                                    float *out_host, void *stream)
+{
+    if (!c || !knobs || !ws || !qkv_host || !qkv_dev || !out_host) {
+        set_error("cqa_decode_step_host: NULL pointer");
+        return CQA_ERR_INVALID;
+    }
+    if (dtype < 0 || dtype > 2) { set_error("cqa_decode_step_host: unknown dtype"); return CQA_ERR_INVALID; }
+    if (!ws->out) { set_error("cqa_decode_step_host: workspace has no output rows"); return CQA_ERR_INVALID; }
+    const size_t esz = dtype == CQA_F32 ? 4 : 2;
+    const size_t H = (size_t)c->kv_heads * c->gqa_group, KV = (size_t)c->kv_heads;
+    const size_t n_in = (H + 2 * KV) * D;
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = check_cuda(cudaMemcpyAsync(qkv_dev, qkv_host, n_in * esz, cudaMemcpyHostToDevice, st), "copy of step inputs");
+    if (rc) return rc;
+    char *dev = static_cast<char *>(qkv_dev);
+    const void *q = dev, *k_new = dev + H * D * esz, *v_new = dev + (H + KV) * D * esz;
+    rc = cqa_append_token(c, k_new, v_new, dtype, pos, defer_int4, stream);
+    if (rc) return rc;
+    const int64_t num_tokens = pos + 1;
+    rc = cqa_layer_step(c, knobs, ws, q, dtype, num_tokens, num_tokens / BS, nullptr, 0, stream);
+    if (rc) return rc;
+    rc = check_cuda(cudaMemcpyAsync(out_host, ws->out, H * D * sizeof(float), cudaMemcpyDeviceToHost, st), "copy of the output");
+    if (rc) return rc;
+    return check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+}
+
 extern "C" int cqa_select_certify_local(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, int64_t nq,
                                         int64_t nact, const float *exploration_u, int64_t u_ld, void *stream)
 {

@@ -76,6 +76,7 @@ class _Workspace:
         self.tickets = torch.zeros(cache.kv_heads + H, dtype=torch.int32, device=device)
         self.cert_host = None
         self._u_flat = None
+        self._step_in = None
         self.rng_seed = None
         self.rng_calls = 0
         self.struct = _lib.CqaWorkspace()
@@ -86,6 +87,14 @@ class _Workspace:
             self.sel_width = width
             self.sorted_idx = torch.zeros(self.H, width, dtype=torch.int32, device=device)
             self.sorted_cumsum = torch.zeros(self.H, width, dtype=torch.float32, device=device)
+
+    def step_input_buffer(self, n: int, dtype, device) -> torch.Tensor:
+        """Device scratch for the packed (q, k_new, v_new) of cqa_decode_step_host."""
+        buf = self._step_in
+        if buf is None or buf.numel() != n or buf.dtype != dtype:
+            buf = torch.empty(n, dtype=dtype, device=device)
+            self._step_in = buf
+        return buf
 
     def uniform_buffer(self, nq: int, device) -> torch.Tensor:
         """A reused [H, nq] float32 view for the exploration draw."""
@@ -223,6 +232,78 @@ class _PhaseTimer:
 
 
 # ----------------------------------------------------------------------------- main entry
+
+def certified_decode_step_host(
+    cache: TieredKeyCacheLayer,
+    qkv_host: torch.Tensor,
+    gqa_group: int,
+    out_host: torch.Tensor,
+    q_scale: float | None = None,
+    *,
+    v_tolerance: float,
+    top_k_fp16_keys: int = 4,
+    ranking_fallback: bool = True,
+    ranking_r: int = 1,
+    ranking_fallback_mode: str = "full",
+    tau_cov: float = 0.995,
+    k_min: int = DEFAULT_K_MIN,
+    k_max: int | None = DEFAULT_K_MAX,
+    rung1_threshold: float = DEFAULT_RUNG1_THRESHOLD,
+    rung1_multiplier: float = DEFAULT_RUNG1_MULTIPLIER,
+    score_consistency_check: bool = False,
+    eps_guard: float = 0.01,
+    exploration_rate: float = 0.0,
+    value_error_mode: str = "tight",
+) -> torch.Tensor:
+    """`cache.append_token(k, v)` followed by `certified_attention_layer(cache, q, ...)` for a caller whose step
+    inputs live in host memory, as ONE library call (cqa_decode_step_host): `qkv_host` is a pinned 1-D tensor
+    [q (H*128) | k_new (KV*128) | v_new (KV*128)] in the cache's model dtype, `out_host` a pinned float32 [H, 128]
+    tensor that holds the attention output when the call returns.  An addition (no reference counterpart): it
+    removes the interpreter from between the copies and the launches; results equal the two-call sequence."""
+    H = cache.kv_heads * int(gqa_group)
+    n_in = (H + 2 * cache.kv_heads) * cache.head_dim
+    if qkv_host.is_cuda or out_host.is_cuda:
+        raise ValueError("certified_decode_step_host takes host tensors (pinned for asynchronous copies)")
+    if qkv_host.numel() != n_in or not qkv_host.is_contiguous():
+        raise ValueError(f"qkv_host must be a contiguous tensor of {n_in} elements")
+    if out_host.dtype != torch.float32 or out_host.numel() != H * cache.head_dim or not out_host.is_contiguous():
+        raise ValueError(f"out_host must be a contiguous float32 tensor of {H * cache.head_dim} elements")
+    pos = cache.num_tokens
+    if pos >= cache.keys_int8.shape[1]:
+        raise ValueError(f"cache capacity {cache.keys_int8.shape[1]} exhausted")
+    if (pos + 1) // cache.block_size <= 0:
+        raise NotImplementedError("the certified path needs at least one complete block")
+    device = cache.keys_int8.device
+    if q_scale is None:
+        q_scale = 1.0 / (cache.head_dim ** 0.5)
+    G = int(gqa_group)
+    ws = _workspace(cache, H, G, device)
+    nq = (pos + 1) // cache.block_size
+    knobs = _make_knobs(
+        q_scale=q_scale, tau_cov=tau_cov, k_min=k_min, k_max=k_max, rung1_threshold=rung1_threshold,
+        rung1_multiplier=rung1_multiplier, eps_guard=eps_guard, exploration_rate=exploration_rate,
+        v_tolerance=v_tolerance, ranking_r=ranking_r, top_k_fp16_keys=top_k_fp16_keys,
+        ranking_fallback=ranking_fallback, ranking_fallback_mode=ranking_fallback_mode,
+        score_consistency_check=score_consistency_check, value_error_mode=value_error_mode,
+        force_trailing_value_fp16=True,
+    )
+    ws.ensure_sel_width(_selection_width(k_max, rung1_threshold, rung1_multiplier, nq), device)
+    wstruct = ws.fill_struct((pos + 1 + cache.block_size - 1) // cache.block_size)
+    if exploration_rate > 0.0:
+        if ws.rng_seed is None:
+            ws.rng_seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
+        wstruct.rng_seed = ws.rng_seed
+        wstruct.rng_offset = ws.rng_calls
+        ws.rng_calls += 1
+    stage = ws.step_input_buffer(n_in, qkv_host.dtype, device)
+    with _lib.on_device(device):
+        _lib.check(_lib.lib().cqa_decode_step_host(
+            C.byref(cache._desc(G)), C.byref(knobs), C.byref(wstruct), qkv_host.data_ptr(), stage.data_ptr(),
+            _lib.dtype_code(qkv_host.dtype), pos, 1 if cache._defers_int4() else 0, out_host.data_ptr(),
+            _lib.current_stream(device)), "cqa_decode_step_host")
+    cache._advance_after_append(pos)
+    return out_host
+
 
 def certified_attention_layer(
     cache: TieredKeyCacheLayer,

@@ -288,6 +288,16 @@ class TieredKeyCacheLayer:
                 C.byref(self._desc()), k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype), pos,
                 1 if defer else 0, _lib.current_stream(dev))
         _lib.check(rc, "cqa_append_token")
+        self._advance_after_append(pos)
+
+    def _defers_int4(self) -> bool:
+        return bool(
+            self.defer_int4_append_quantization
+            and self.values_fp16_gpu is not None
+            and (self.fp16_value_cache_capacity is None or self.static_resident_value_cache)
+        )
+
+    def _advance_after_append(self, pos: int) -> None:
         self.num_tokens = pos + 1
         self.num_blocks = (self.num_tokens + BLOCK - 1) // BLOCK
         if pos % BLOCK == BLOCK - 1:

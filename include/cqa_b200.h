@@ -293,6 +293,17 @@ int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspa
                    int q_dtype, int64_t num_tokens, int64_t nq, const float *exploration_u,
                    int64_t u_ld, void *stream);
 
+/* One decode step of one layer from HOST buffers: copies the packed step inputs
+ * [q (H*128) | k_new (KV*128) | v_new (KV*128)] (elements of `dtype`) from `qkv_host`
+ * to the device scratch `qkv_dev` (same size), appends the token at position `pos`
+ * (cqa_append_token), runs cqa_layer_step on the pos+1 tokens, copies the H*128 float32
+ * output rows to `out_host` and waits for the stream.  Pinned host buffers make the two
+ * copies asynchronous DMA transfers.  An addition with no reference counterpart: it is
+ * cqa_append_token + cqa_layer_step for a caller that holds its activations on the host,
+ * in one call (no interpreter between the launches). */
+int cqa_decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *qkv_host,
+                         void *qkv_dev, int dtype, int64_t pos, int defer_int4, float *out_host, void *stream);
+
 /* ---- sequence sharding: every rank owns a contiguous range of blocks ----
  * The reference runs one cache per process; these entry points let P ranks that each
  * hold the blocks [first_block, first_block + n_local) of one long sequence reproduce

@@ -161,6 +161,36 @@ def test_exact_ties_take_lowest_block_ids():
         hz.compare_step(cc, R, out, f"ties {knobs['v_tolerance']} {knobs['k_max']}")
 
 
+def test_decode_step_from_host_buffers_equals_two_calls():
+    """cqa_decode_step_host (pinned host inputs, one library call) gives the bytes and rows of
+    append_token + certified_attention_layer."""
+    from dotcache.kernels import certified_attention as ca
+
+    dtype = "bfloat16"
+    base = synth.make_layer_inputs(17, 4096 + 9, dtype=dtype, n_planted_blocks=8)
+    aligned = 4096
+    knobs = _knobs(exploration_rate=0.0)
+    ca_a = hz.make_cuda_cache(base.k[:, :aligned], base.v[:, :aligned], dtype, 64)
+    ca_b = hz.make_cuda_cache(base.k[:, :aligned], base.v[:, :aligned], dtype, 64)
+    for t in range(aligned, 4096 + 9):
+        for c in (ca_a, ca_b):
+            c.append_token(hz.to_dev(base.k[:, t:t + 1], dtype), hz.to_dev(base.v[:, t:t + 1], dtype))
+    qkv = torch.empty((32 + 16) * 128, dtype=torch.bfloat16).pin_memory()
+    out_host = torch.empty(32, 128, dtype=torch.float32).pin_memory()
+    for step in range(20):
+        q, kn, vn = synth.decode_step_inputs(base, step, dtype=dtype)
+        ca_a.append_token(hz.to_dev(kn, dtype), hz.to_dev(vn, dtype))
+        ref, _ = hz.cuda_step(ca_a, q, dtype, 4, knobs, None, collect_stats=False)
+        qkv[: 32 * 128] = torch.from_numpy(q).to(torch.bfloat16).reshape(-1)
+        qkv[32 * 128: 40 * 128] = torch.from_numpy(kn).to(torch.bfloat16).reshape(-1)
+        qkv[40 * 128:] = torch.from_numpy(vn).to(torch.bfloat16).reshape(-1)
+        ca.certified_decode_step_host(ca_b, qkv, 4, out_host, **knobs)
+        assert ca_b.num_tokens == ca_a.num_tokens and ca_b.num_quantized_blocks == ca_a.num_quantized_blocks
+        assert np.array_equal(out_host.numpy(), ref), f"step {step}"
+    for name in ("keys_int8", "values_int4_packed", "keys_scale", "values_int4_errors"):
+        assert torch.equal(getattr(ca_a, name), getattr(ca_b, name)), name
+
+
 def test_in_kernel_exploration_draw():
     """Without uniforms or a generator the selector draws its own: the rate is respected, the draw is a function
     of torch's seed and the per-cache call counter only, and explored blocks are never blocks the selector chose."""
