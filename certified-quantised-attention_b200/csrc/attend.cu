@@ -380,6 +380,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
     const int kv = blockIdx.y;
     const int ns = ws.num_splits;
     const int pool_x = ws.dense_splits > 0 ? DENSE_POOL_X : 0;
+    grid_dependency_wait();
     if ((int)blockIdx.x < pool_x) {
         // Dense-recompute pool: units are (flagged head, chunk); unflagged steps leave at once.
         const int H = c.kv_heads * G;
@@ -672,7 +673,10 @@ static int attend_launch_gt(const cqa_cache *c, const cqa_workspace *ws, const v
     const bool dense = ws->cert && ws->dense_splits > 0 && ws->dense_m && ws->dense_l && ws->dense_acc;
     cqa_workspace w = *ws;
     if (!dense) w.dense_splits = 0;
-    const size_t smem = attend_smem<G>();
+    size_t smem = attend_smem<G>();
+#ifdef CQA_DEBUG_SMEM_PAD
+    smem += CQA_DEBUG_SMEM_PAD;
+#endif
     static size_t attr = 0;
     if (smem > attr) {
         int rc = check_cuda(cudaFuncSetAttribute(attend_kernel<G, T2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -682,9 +686,9 @@ static int attend_launch_gt(const cqa_cache *c, const cqa_workspace *ws, const v
         attr = smem;
     }
     dim3 grid((unsigned)(ns + (dense ? DENSE_POOL_X : 0)), (unsigned)c->kv_heads);
-    attend_kernel<G, T2><<<grid, ATT_THREADS, smem, st>>>(*c, w, q, q_dtype, nq, nact, num_tokens, last_valid,
-                                                         q_scale, bps);
-    return check_launch("attend_kernel");
+    return check_cuda(launch_chained(attend_kernel<G, T2>, grid, dim3(ATT_THREADS), smem, st, true, *c, w, q, q_dtype, nq,
+                                     nact, num_tokens, last_valid, q_scale, bps),
+                      "attend_kernel");
 }
 
 template <typename T2>

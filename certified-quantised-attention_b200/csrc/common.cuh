@@ -260,6 +260,35 @@ __device__ __forceinline__ void i8x8_to_f(uint2 w, float (&out)[8])
     for (int i = 0; i < 8; ++i) out[i] = (float)b[i];
 }
 
+// ------------------------------------------------- programmatic dependent launch
+
+// Kernels of the fused decode chain are launched with programmatic stream serialisation: the next kernel's CTAs
+// may be scheduled while the previous kernel drains, and wait here until that kernel has completed and its writes
+// are visible.  Without the launch attribute the wait returns at once.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Launch with (or without) the programmatic-serialisation attribute.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                         bool chained, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = chained ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ----------------------------------------------------------------- errors
 
 void set_error(const char *fmt, ...);

@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(128) append_token_kernel(cqa_cache c, const vo
     const long blk = pos / BS;
     const int pib = (int)(pos % BS);
     const long bidx = (long)kv * c.max_blocks + blk;
+    grid_dependency_wait();
 
     long krow = pos, vrow = pos;
     if (c.key_slots) { int s = c.key_slots[blk]; krow = s < 0 ? -1 : (long)s * BS + pib; }
@@ -399,12 +400,12 @@ extern "C" int cqa_append_token(const cqa_cache *c, const void *k_new, const voi
     if (src_dtype < 0 || src_dtype > 2) { set_error("cqa_append_token: unknown dtype"); return CQA_ERR_INVALID; }
     cudaStream_t st = (cudaStream_t)stream;
     switch (c->t2_dtype) {
-    case CQA_F32: append_token_kernel<float><<<c->kv_heads, 128, 0, st>>>(*c, k_new, v_new, src_dtype, pos, defer_int4); break;
-    case CQA_F16: append_token_kernel<__half><<<c->kv_heads, 128, 0, st>>>(*c, k_new, v_new, src_dtype, pos, defer_int4); break;
-    case CQA_BF16: append_token_kernel<__nv_bfloat16><<<c->kv_heads, 128, 0, st>>>(*c, k_new, v_new, src_dtype, pos, defer_int4); break;
+    case CQA_F32: rc = check_cuda(launch_chained(append_token_kernel<float>, dim3(c->kv_heads), dim3(128), 0, st, true, *c, k_new, v_new, src_dtype, pos, defer_int4), "append_token_kernel"); break;
+    case CQA_F16: rc = check_cuda(launch_chained(append_token_kernel<__half>, dim3(c->kv_heads), dim3(128), 0, st, true, *c, k_new, v_new, src_dtype, pos, defer_int4), "append_token_kernel"); break;
+    case CQA_BF16: rc = check_cuda(launch_chained(append_token_kernel<__nv_bfloat16>, dim3(c->kv_heads), dim3(128), 0, st, true, *c, k_new, v_new, src_dtype, pos, defer_int4), "append_token_kernel"); break;
     default: set_error("cqa_append_token: unknown Tier-2 dtype %d", c->t2_dtype); return CQA_ERR_INVALID;
     }
-    return check_launch("append_token_kernel");
+    return rc;
 }
 
 extern "C" int cqa_int4_quantise(const void *x, int src_dtype, int64_t T, uint8_t *packed, uint16_t *scales,

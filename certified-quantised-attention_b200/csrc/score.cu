@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
     extern __shared__ __align__(16) char smem[];
     constexpr int GH = G >= 4 ? 4 : G;  // heads per register pass
     const int kv = blockIdx.y;
+    grid_dependency_wait();
     // the fused layer step lets this kernel clear the certifier's flag words (one memset launch fewer)
     if (zero_words != nullptr && blockIdx.x == 0 && blockIdx.y == 0)
         for (int i = threadIdx.x; i < n_zero_words; i += SCORE_WARPS * 32) zero_words[i] = 0;
@@ -227,7 +228,11 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
                           float *s_b, long ld, float *tok, dim3 grid, int bpc, int32_t *zero_words, int n_zero_words,
                           cudaStream_t st)
 {
+#ifdef CQA_DEBUG_SMEM_PAD
+    constexpr int SMEM = SCORE_SMEM + G * D * 4 + CQA_DEBUG_SMEM_PAD;
+#else
     constexpr int SMEM = SCORE_SMEM + G * D * 4;
+#endif
     static bool attr_set = false;
     if (!attr_set) {
         int rc = check_cuda(cudaFuncSetAttribute(score_blocks_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -236,9 +241,9 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
         if (rc) return rc;
         attr_set = true;
     }
-    score_blocks_kernel<G><<<grid, SCORE_WARPS * 32, SMEM, st>>>(*c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, bpc,
-                                                                 zero_words, n_zero_words);
-    return check_launch("score_blocks_kernel");
+    return check_cuda(launch_chained(score_blocks_kernel<G>, grid, dim3(SCORE_WARPS * 32), SMEM, st, true, *c, q, q_dtype,
+                                     nq, q_scale, m_b, s_b, ld, tok, bpc, zero_words, n_zero_words),
+                      "score_blocks_kernel");
 }
 
 int rescore_owned_launch(const cqa_cache *c, const cqa_head_cert *cert, const void *q, int q_dtype, long first_block,

@@ -899,6 +899,7 @@ __global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_kn
                                                             int n_pad, int hi, int base_width, int two_level, int rk,
                                                             int phases, int role_base)
 {
+    grid_dependency_wait();
 #ifdef CQA_WARM_REPEAT
     selcert_body<T2>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
     __syncthreads();
@@ -965,9 +966,11 @@ static int selcert_launch_t(const cqa_cache *c, const cqa_knobs *kn, const cqa_w
     int n_roles = (phases & PH_SELECT) ? ((phases & PH_CERTIFY) ? 3 : 1) : 2;
     if (phases & PH_GIVEN) n_roles = 1;   // role 1 alone
     dim3 grid((unsigned)H, (unsigned)n_roles);
-    selcert_kernel<T2><<<grid, SC_THREADS, smem, st>>>(*c, *kn, *ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi,
-                                                       base_width, two_level, rk, phases, role_base);
-    return check_launch("selcert_kernel");
+    // chained to the score kernel only in the fused step (a memset precedes the launch otherwise)
+    const bool chained = (phases & PH_FLAGS_CLEARED) != 0;
+    return check_cuda(launch_chained(selcert_kernel<T2>, grid, dim3(SC_THREADS), smem, st, chained, *c, *kn, *ws, q, q_dtype,
+                                     nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base),
+                      "selcert_kernel");
 }
 
 int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
