@@ -41,7 +41,7 @@ int merge_partials_launch(const float *parts, int n_parts, int n_heads, float *o
 int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
                    long nq, long nact, const float *u, long u_ld, int phases, cudaStream_t st);
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
-                  long num_tokens, int last_valid, float q_scale, cudaStream_t st);
+                  long num_tokens, int last_valid, float q_scale, cudaStream_t st, bool chained);
 
 int attend_static_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
                          long num_tokens, int last_valid, float q_scale, cudaStream_t st);
@@ -187,7 +187,7 @@ extern "C" int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const voi
     int rc = check_common(c, ws, "cqa_attend");
     if (rc) return rc;
     if (!q) { set_error("cqa_attend: NULL q"); return CQA_ERR_INVALID; }
-    return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_block_valid, q_scale, (cudaStream_t)stream);
+    return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_block_valid, q_scale, (cudaStream_t)stream, false);
 }
 
 extern "C" int cqa_attend_static(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,
@@ -227,7 +227,7 @@ extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const 
     if (exploration_u && u_ld < nq) { set_error("cqa_layer_step: exploration_u leading dimension too small"); return CQA_ERR_INVALID; }
     rc = selcert_launch(c, knobs, ws, q, q_dtype, nq, nact, exploration_u, u_ld, 3 | 16, st);   // select + certify in one launch; flags cleared by the score kernel
     if (rc) return rc;
-    return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, knobs->q_scale, st);
+    return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, knobs->q_scale, st, true);
 }
 
 extern "C" int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int *num_splits, int *dense_splits)

@@ -380,8 +380,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
     const int kv = blockIdx.y;
     const int ns = ws.num_splits;
     const int pool_x = ws.dense_splits > 0 ? DENSE_POOL_X : 0;
-    grid_dependency_wait();
     if ((int)blockIdx.x < pool_x) {
+        grid_dependency_wait();   // the list of flagged heads comes from the selector
         // Dense-recompute pool: units are (flagged head, chunk); unflagged steps leave at once.
         const int H = c.kv_heads * G;
         const bool all = ws.any_flags[2] != 0;
@@ -416,6 +416,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
     // Blocks of this warp: b_begin + warp + 8*it.  Lane j keeps the key / value promotion bits of the warp's
     // block (it0 + j), one bit per head of the group; they are re-read every 32 blocks.
     const int n_my = b_begin + warp < b_end ? (int)((b_end - b_begin - warp + ATT_WARPS - 1) / ATT_WARPS) : 0;
+    // Everything above reads what the append and score kernels wrote (they completed before the selector, the
+    // previous kernel of the chain, began); the masks and flags below are the selector's, so wait for it here.
+    // CTAs that were scheduled while the selector was still running have their first blocks in flight by now.
+    grid_dependency_wait();
     unsigned my_masks = 0;   // km | vm << 8 of block (it0 + lane)
     auto load_masks = [&](int it0) {
         const long b = b_begin + warp + (long)(it0 + lane) * ATT_WARPS;
@@ -666,7 +670,7 @@ static size_t attend_smem()
 
 template <int G, typename T2>
 static int attend_launch_gt(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq,
-                            long nact, long num_tokens, int last_valid, float q_scale, cudaStream_t st)
+                            long nact, long num_tokens, int last_valid, float q_scale, cudaStream_t st, bool chained)
 {
     const int ns = ws->num_splits;
     const int bps = (int)((nact + ns - 1) / ns);
@@ -686,27 +690,29 @@ static int attend_launch_gt(const cqa_cache *c, const cqa_workspace *ws, const v
         attr = smem;
     }
     dim3 grid((unsigned)(ns + (dense ? DENSE_POOL_X : 0)), (unsigned)c->kv_heads);
-    return check_cuda(launch_chained(attend_kernel<G, T2>, grid, dim3(ATT_THREADS), smem, st, true, *c, w, q, q_dtype, nq,
+    return check_cuda(launch_chained(attend_kernel<G, T2>, grid, dim3(ATT_THREADS), smem, st, chained, *c, w, q, q_dtype, nq,
                                      nact, num_tokens, last_valid, q_scale, bps),
                       "attend_kernel");
 }
 
 template <typename T2>
 static int attend_launch_t(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq,
-                           long nact, long num_tokens, int last_valid, float q_scale, cudaStream_t st)
+                           long nact, long num_tokens, int last_valid, float q_scale, cudaStream_t st, bool chained)
 {
     switch (c->gqa_group) {
-    case 1: return attend_launch_gt<1, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
-    case 2: return attend_launch_gt<2, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
-    case 4: return attend_launch_gt<4, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
-    case 8: return attend_launch_gt<8, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
+    case 1: return attend_launch_gt<1, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
+    case 2: return attend_launch_gt<2, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
+    case 4: return attend_launch_gt<4, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
+    case 8: return attend_launch_gt<8, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
     }
     set_error("cqa_attend: unsupported gqa_group %d", c->gqa_group);
     return CQA_ERR_UNSUPPORTED;
 }
 
+// `chained`: the previous kernel on the stream is the selector of the same fused step, so the kernel may be
+// scheduled early and stage its first blocks (written two kernels back) before waiting for the selector.
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
-                  long num_tokens, int last_valid, float q_scale, cudaStream_t st)
+                  long num_tokens, int last_valid, float q_scale, cudaStream_t st, bool chained)
 {
     if (ws->num_splits <= 0 || !ws->part_m || !ws->part_l || !ws->part_acc || (!ws->out && !ws->partial_out) || !ws->topk_mask ||
         !ws->value_mask || !ws->tickets) {
@@ -729,9 +735,9 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
         return CQA_ERR_INVALID;
     }
     switch (c->t2_dtype) {
-    case CQA_F32: return attend_launch_t<float>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
-    case CQA_F16: return attend_launch_t<__half>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
-    case CQA_BF16: return attend_launch_t<__nv_bfloat16>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
+    case CQA_F32: return attend_launch_t<float>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
+    case CQA_F16: return attend_launch_t<__half>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
+    case CQA_BF16: return attend_launch_t<__nv_bfloat16>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
     }
     set_error("cqa_attend: unknown Tier-2 dtype %d", c->t2_dtype);
     return CQA_ERR_INVALID;
@@ -822,7 +828,7 @@ int attend_static_launch(const cqa_cache *c, const cqa_workspace *ws, const void
     // The merge tickets are the only part of the shared array that must start at zero.
     rc = check_cuda(cudaMemsetAsync(w.tickets, 0, STATIC_TICKETS * sizeof(int32_t), st), "cudaMemsetAsync(tickets)");
     if (rc) return rc;
-    return attend_launch(c, &w, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st);
+    return attend_launch(c, &w, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, false);
 }
 
 }  // namespace cqa
