@@ -366,7 +366,7 @@ def run_ours(args, rank, world, device_index):
     chain_gbs = chain_bytes / (us_per_layer * 1e-6) / 1e9
     # DRAM bytes per launch of the two streaming kernels at this workload, from one ncu capture each
     # (dram__bytes_read.sum + dram__bytes_write.sum; profiles/ncu_decode_step_ctx32k.md)
-    ncu_traffic = {"phase1_int8_scoring": 50.39e6 + 0.20e6, "phase2_fused_attend": 35.96e6 + 0.07e6}
+    ncu_traffic = {"phase1_int8_scoring": 50.39e6 + 0.23e6, "phase2_fused_attend": 36.12e6 + 0.11e6}
     roof = {
         "bound": "hbm", "kernel": {"phase1_int8_scoring": "score_blocks_kernel",
                                    "phase2_fused_attend": "attend_kernel"}[dominant],
