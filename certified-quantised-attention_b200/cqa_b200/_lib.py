@@ -21,7 +21,7 @@ SYMBOLS = [
     "cqa_score_blocks", "cqa_select", "cqa_fp16_block_scores", "cqa_delta_bound", "cqa_certify",
     "cqa_attend", "cqa_attend_static", "cqa_layer_step", "cqa_suggest_splits",
     "cqa_select_certify_local", "cqa_rescore_owned", "cqa_certify_given", "cqa_merge_partials",
-    "cqa_decode_step_host",
+    "cqa_decode_step_host", "cqa_hot_tier_update",
 ]
 PARTIAL_STRIDE = 130
 
@@ -38,6 +38,7 @@ class CqaCache(C.Structure):
         ("values_int4_error_counts", vp), ("values_norm_max", vp),
         ("keys_t2", vp), ("keys_t2_rows", C.c_int64), ("values_t2", vp), ("values_t2_rows", C.c_int64),
         ("key_slots", vp), ("value_slots", vp),
+        ("keys_t2_backing", vp), ("values_t2_backing", vp), ("t2_backing_rows", C.c_int64),
     ]
 
 
@@ -86,6 +87,15 @@ class CqaWorkspace(C.Structure):
     ]
 
 
+class CqaHotTier(C.Structure):
+    _fields_ = [
+        ("key_capacity_blocks", C.c_int32), ("value_capacity_blocks", C.c_int32),
+        ("max_fill_blocks", C.c_int32), ("reserved", C.c_int32),
+        ("key_slots", vp), ("value_slots", vp), ("key_owner", vp), ("value_owner", vp),
+        ("key_stamp", vp), ("value_stamp", vp), ("work", vp), ("counters", vp),
+    ]
+
+
 CERT_BYTES = C.sizeof(CqaHeadCert)
 
 _lib = None
@@ -131,6 +141,7 @@ def lib() -> C.CDLL:
     L.cqa_certify_given.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp]
     L.cqa_merge_partials.argtypes = [vp, i32, i32, vp, vp]
     L.cqa_decode_step_host.argtypes = [pc, pk, pw, vp, vp, i32, i64, i32, vp, vp]
+    L.cqa_hot_tier_update.argtypes = [pc, pw, C.POINTER(CqaHotTier), i64, vp]
     for s in SYMBOLS[2:]:
         getattr(L, s).restype = C.c_int
     _lib = L

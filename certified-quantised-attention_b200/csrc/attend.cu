@@ -307,23 +307,20 @@ __device__ void dense_unit(const cqa_cache &c, const cqa_workspace &ws, const vo
     const long b_end = min(nblk, b_begin + bps);
     float qv[8];
     load_q8(q, q_dtype, (long)h * D + 8 * L, qv);
-    const T2 *kt2 = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
-    const T2 *vt2 = reinterpret_cast<const T2 *>(c.values_t2) + (long)kv * c.values_t2_rows * D;
     float m[1] = {-INFINITY}, l[1] = {0.0f}, acc[1][8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[0][i] = 0.0f;
     for (long b = b_begin + warp; b < b_end; b += ATT_WARPS) {
-        long kslot = c.key_slots ? (long)c.key_slots[b] : b;
-        long vslot = c.value_slots ? (long)c.value_slots[b] : b;
-        if (kslot < 0 || vslot < 0) continue;
+        const T2 *kblk = t2_key_block<T2>(c, kv, b), *vblk = t2_value_block<T2>(c, kv, b);
+        if (kblk == nullptr || vblk == nullptr) continue;
         // all key and value rows of this half warp's 8 tokens are requested before anything is consumed
         Raw8<T2> kr[8], vr[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const long t = b * BS + hw * 8 + i;
             if (t < num_tokens) {
-                kr[i] = raw_load8<T2>(kt2 + (kslot * BS + hw * 8 + i) * D + 8 * L);
-                vr[i] = raw_load8<T2>(vt2 + (vslot * BS + hw * 8 + i) * D + 8 * L);
+                kr[i] = raw_load8<T2>(kblk + (hw * 8 + i) * D + 8 * L);
+                vr[i] = raw_load8<T2>(vblk + (hw * 8 + i) * D + 8 * L);
             } else {
                 kr[i] = raw_zero8<T2>();
                 vr[i] = raw_zero8<T2>();
@@ -466,8 +463,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
         for (int k = 0; k < 4; ++k) acc2[g][k] = make_float2(0.0f, 0.0f);
     float m_mine = m_init;      // running max of head gl (uniform over its LPH lanes)
     float l_mine = 0.0f;        // this lane's share of the running sum of head gl
-    const T2 *kt2 = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
-    const T2 *vt2 = reinterpret_cast<const T2 *>(c.values_t2) + (long)kv * c.values_t2_rows * D;
     const bool have4 = c.values_int4_packed != nullptr;
 
     // prepare(it): logits -> weights of block `it` into w_tiles[it & 1]; returns this lane's rescale factor for
@@ -479,8 +474,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
         const char *st = wring + (it % ATT_STAGES) * LY::STAGE;
         if (km) {
             // FP16-key logits for promoted heads (rare): Tier-2 rows straight from global memory
-            long kslot = c.key_slots ? (long)c.key_slots[b] : b;
-            if (kslot < 0) kslot = 0;
+            const T2 *kblk = t2_key_block<T2>(c, kv, b);
 #pragma unroll 1
             for (int g = 0; g < G; ++g) {
                 if (!(km & (1u << g))) continue;
@@ -490,7 +484,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int t = hw * 8 + i;
-                    kr[i] = t < n_valid ? raw_load8<T2>(kt2 + (kslot * BS + t) * D + 8 * L) : raw_zero8<T2>();
+                    kr[i] = (t < n_valid && kblk != nullptr) ? raw_load8<T2>(kblk + t * D + 8 * L) : raw_zero8<T2>();
                 }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -611,14 +605,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
         // ---- Tier-2 values for the heads that were promoted (rare)
         if (vm) {
             const int n_valid = (b == nact - 1) ? last_valid : BS;
-            long vslot = c.value_slots ? (long)c.value_slots[b] : b;
-            if (vslot < 0) vslot = 0;
+            const T2 *vblk = t2_value_block<T2>(c, kv, b);
             // all eight rows of this half warp are requested before the first is used
             Raw8<T2> vr[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int t = 2 * i + hw;
-                vr[i] = t < n_valid ? raw_load8<T2>(vt2 + (vslot * BS + t) * D + 8 * L) : raw_zero8<T2>();
+                vr[i] = (t < n_valid && vblk != nullptr) ? raw_load8<T2>(vblk + t * D + 8 * L) : raw_zero8<T2>();
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {

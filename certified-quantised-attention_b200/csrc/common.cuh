@@ -260,6 +260,31 @@ __device__ __forceinline__ void i8x8_to_f(uint2 w, float (&out)[8])
     for (int i = 0; i < 8; ++i) out[i] = (float)b[i];
 }
 
+// ------------------------------------------------------------- Tier-2 block rows
+
+// First row (token 0) of block `b` of KV head `kv` in Tier 2: the hot slot when the block is resident (or when there
+// is no slot table: identity), else the backing array; nullptr when neither holds it.
+template <typename T2>
+__device__ __forceinline__ const T2 *t2_block(const void *hot, long hot_rows, const int32_t *slots, const void *backing,
+                                              long backing_rows, int kv, long b)
+{
+    if (slots == nullptr)
+        return hot ? reinterpret_cast<const T2 *>(hot) + ((long)kv * hot_rows + b * BS) * D : nullptr;
+    const int s = slots[b];
+    if (s >= 0) return reinterpret_cast<const T2 *>(hot) + ((long)kv * hot_rows + (long)s * BS) * D;
+    return backing ? reinterpret_cast<const T2 *>(backing) + ((long)kv * backing_rows + b * BS) * D : nullptr;
+}
+template <typename T2>
+__device__ __forceinline__ const T2 *t2_key_block(const cqa_cache &c, int kv, long b)
+{
+    return t2_block<T2>(c.keys_t2, c.keys_t2_rows, c.key_slots, c.keys_t2_backing, c.t2_backing_rows, kv, b);
+}
+template <typename T2>
+__device__ __forceinline__ const T2 *t2_value_block(const cqa_cache &c, int kv, long b)
+{
+    return t2_block<T2>(c.values_t2, c.values_t2_rows, c.value_slots, c.values_t2_backing, c.t2_backing_rows, kv, b);
+}
+
 // ------------------------------------------------- programmatic dependent launch
 
 // Kernels of the fused decode chain are launched with programmatic stream serialisation: the next kernel's CTAs

@@ -173,11 +173,14 @@ __global__ void __launch_bounds__(128) quantize_blocks_kernel(cqa_cache c, const
     const T *ks = k_src + ((long)kv * src_rows + lb * BS) * D;
     const T *vs = v_src + ((long)kv * src_rows + lb * BS) * D;
     if (copy_t2) {
-        T *kd = reinterpret_cast<T *>(c.keys_t2) + ((long)kv * c.keys_t2_rows + blk * BS) * D;
-        T *vd = reinterpret_cast<T *>(c.values_t2) + ((long)kv * c.values_t2_rows + blk * BS) * D;
+        // full mirror: the Tier-2 arrays themselves; bounded hot tier: the backing arrays (the scratch starts empty)
+        T *kd = c.key_slots ? (c.keys_t2_backing ? reinterpret_cast<T *>(c.keys_t2_backing) + ((long)kv * c.t2_backing_rows + blk * BS) * D : nullptr)
+                            : (c.keys_t2 ? reinterpret_cast<T *>(c.keys_t2) + ((long)kv * c.keys_t2_rows + blk * BS) * D : nullptr);
+        T *vd = c.value_slots ? (c.values_t2_backing ? reinterpret_cast<T *>(c.values_t2_backing) + ((long)kv * c.t2_backing_rows + blk * BS) * D : nullptr)
+                              : (c.values_t2 ? reinterpret_cast<T *>(c.values_t2) + ((long)kv * c.values_t2_rows + blk * BS) * D : nullptr);
         for (int i = threadIdx.x; i < BS * D; i += 128) {
-            if (c.keys_t2) kd[i] = ks[i];
-            if (c.values_t2) vd[i] = vs[i];
+            if (kd) kd[i] = ks[i];
+            if (vd) vd[i] = vs[i];
         }
     }
     quantize_one_block<T>(c, kv, blk, ks, vs, true, c.values_int4_packed != nullptr, false, true, sm);
@@ -217,6 +220,11 @@ __global__ void __launch_bounds__(128) append_token_kernel(cqa_cache c, const vo
     T2 *vt2 = reinterpret_cast<T2 *>(c.values_t2);
     if (kt2 && krow >= 0) kt2[((long)kv * c.keys_t2_rows + krow) * D + tid] = kq;
     if (vt2 && vrow >= 0) vt2[((long)kv * c.values_t2_rows + vrow) * D + tid] = vq;
+    // bounded hot tier: the backing arrays always receive the row (the hot copy above only if the block is resident)
+    if (c.key_slots && c.keys_t2_backing)
+        reinterpret_cast<T2 *>(c.keys_t2_backing)[((long)kv * c.t2_backing_rows + pos) * D + tid] = kq;
+    if (c.value_slots && c.values_t2_backing)
+        reinterpret_cast<T2 *>(c.values_t2_backing)[((long)kv * c.t2_backing_rows + pos) * D + tid] = vq;
     s_v[tid] = Cvt<T2>::to_f(vq);
     __syncthreads();
 
@@ -264,12 +272,10 @@ __global__ void __launch_bounds__(128) append_token_kernel(cqa_cache c, const vo
         // The block just filled: quantise it from the Tier-2 rows (this CTA wrote the last one).
         __threadfence_block();
         __syncthreads();
-        long kb = blk, vb = blk;
-        if (c.key_slots) kb = c.key_slots[blk];
-        if (c.value_slots) vb = c.value_slots[blk];
-        if (kt2 && vt2 && kb >= 0 && vb >= 0) {
-            const T2 *ks = kt2 + ((long)kv * c.keys_t2_rows + kb * BS) * D;
-            const T2 *vs = vt2 + ((long)kv * c.values_t2_rows + vb * BS) * D;
+        __threadfence();   // the rows may have gone to the backing arrays only
+        const T2 *ks = t2_key_block<T2>(c, kv, blk);
+        const T2 *vs = t2_value_block<T2>(c, kv, blk);
+        if (ks && vs) {
             quantize_one_block<T2>(c, kv, blk, ks, vs, true,
                                    c.values_int4_packed != nullptr && defer_int4 != 0, true, false, sm);
         }
@@ -344,7 +350,9 @@ static int launch_quantize(const cqa_cache *c, const void *k, const void *v, lon
 {
     const T *ks = reinterpret_cast<const T *>(k), *vs = reinterpret_cast<const T *>(v);
     int copy = 1;
-    if (k == c->keys_t2 && v == c->values_t2 && src_rows == c->keys_t2_rows && first == 0) copy = 0;
+    if (!c->key_slots && !c->value_slots && k == c->keys_t2 && v == c->values_t2 && src_rows == c->keys_t2_rows &&
+        first == 0)
+        copy = 0;
     const long max_x = 1L << 30;
     for (long off = 0; off < n; off += max_x) {
         long cnt = n - off < max_x ? n - off : max_x;

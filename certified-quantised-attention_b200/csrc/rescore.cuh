@@ -9,7 +9,7 @@ namespace cqa {
 
 // One warp scores one (head, block): 16 token logits from Tier-2 keys, then
 // m = max, logmass = m + log(max(sum exp(logit - m), 1e-30)).  Tokens with
-// block*16+t >= n_scoring_tokens, slot < 0 or slot row out of range are -inf.
+// block*16+t >= n_scoring_tokens, or of a block held by neither tier, are -inf.
 template <typename T2>
 __device__ __forceinline__ void fp16_block_score_warp(const cqa_cache &c, const void *q, int q_dtype, int h,
                                                       long bid, long n_scoring_tokens, float q_scale,
@@ -18,26 +18,22 @@ __device__ __forceinline__ void fp16_block_score_warp(const cqa_cache &c, const 
     const int lane = threadIdx.x & 31, L = lane & 15, hw = lane >> 4;
     const int kv = h / c.gqa_group;
     const bool valid_block = bid >= 0 && bid * BS < n_scoring_tokens;
-    long slot = -1;
-    if (valid_block) slot = c.key_slots ? (long)c.key_slots[bid] : bid;
+    const T2 *base = valid_block ? t2_key_block<T2>(c, kv, bid) : nullptr;   // hot slot or backing array
     float qv[8];
     load_q8(q, q_dtype, (long)h * D + 8 * L, qv);
-    const T2 *base = reinterpret_cast<const T2 *>(c.keys_t2) + (long)kv * c.keys_t2_rows * D;
     float lg[8];  // this half warp's tokens hw*8 .. hw*8+7 (all lanes hold all 8)
     // issue the eight row loads together, then reduce (small code: this runs once per launch)
     Raw8<T2> raw[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int t = hw * 8 + i;
-        const long ti = slot * BS + t;
-        const bool valid = valid_block && (bid * BS + t) < n_scoring_tokens && slot >= 0 && ti < c.keys_t2_rows;
-        raw[i] = valid ? raw_load8<T2>(base + ti * D + 8 * L) : raw_zero8<T2>();
+        const bool valid = base != nullptr && (bid * BS + t) < n_scoring_tokens;
+        raw[i] = valid ? raw_load8<T2>(base + t * D + 8 * L) : raw_zero8<T2>();
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int t = hw * 8 + i;
-        const long ti = slot * BS + t;
-        const bool valid = valid_block && (bid * BS + t) < n_scoring_tokens && slot >= 0 && ti < c.keys_t2_rows;
+        const bool valid = base != nullptr && (bid * BS + t) < n_scoring_tokens;
         float kf[8];
         raw_to_f(raw[i], kf);
         float d = hw_sum(chain8(kf, qv));

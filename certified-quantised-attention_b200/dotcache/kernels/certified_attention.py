@@ -301,6 +301,9 @@ def certified_decode_step_host(
             C.byref(cache._desc(G)), C.byref(knobs), C.byref(wstruct), qkv_host.data_ptr(), stage.data_ptr(),
             _lib.dtype_code(qkv_host.dtype), pos, 1 if cache._defers_int4() else 0, out_host.data_ptr(),
             _lib.current_stream(device)), "cqa_decode_step_host")
+        if cache.bounded_hot_tier:
+            cache._hot_tier_update(cache._desc(G), wstruct, (pos + 1 + cache.block_size - 1) // cache.block_size,
+                                   _lib.current_stream(device))
     cache._advance_after_append(pos)
     return out_host
 
@@ -463,6 +466,9 @@ def certified_attention_layer(
             with _PhaseTimer(phase_timings, "phase2_fused_attend", pending):
                 _lib.check(L.cqa_attend(C.byref(desc), C.byref(wstruct), q.data_ptr(), qd, nq, nact,
                                         cache.num_tokens, last_valid, float(q_scale), stream), "cqa_attend")
+        if cache.bounded_hot_tier:
+            # queue the residency update (mark the blocks this step used, page the missed ones in)
+            cache._hot_tier_update(desc, wstruct, nact, stream)
     _flush_timers(phase_timings, pending)
     output = ws.out
     if not collect_stats:

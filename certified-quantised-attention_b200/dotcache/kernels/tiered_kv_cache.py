@@ -86,6 +86,7 @@ class TieredKeyCacheLayer:
     gqa_group_hint: int = 1
     _certified_workspace: dict = field(default_factory=dict, repr=False)
     _desc_cache: dict = field(default_factory=dict, repr=False)
+    _hot: dict | None = field(default=None, repr=False)     # bounded hot tier: tables, counters, struct
 
     # ------------------------------------------------------------------ C ABI view
 
@@ -122,6 +123,13 @@ class TieredKeyCacheLayer:
         d.values_t2_rows = int(vt2.shape[1]) if vt2 is not None else 0
         d.key_slots = None      # identity: full mirrors
         d.value_slots = None
+        if self._hot is not None:
+            # bounded hot tier: the *_gpu arrays are slot scratch, the pinned *_cpu arrays back them
+            d.key_slots = self._hot["key_slots"].data_ptr()
+            d.value_slots = self._hot["value_slots"].data_ptr()
+            d.keys_t2_backing = self.keys_fp16_cpu.data_ptr()
+            d.values_t2_backing = self.values_fp16_cpu.data_ptr()
+            d.t2_backing_rows = int(self.keys_fp16_cpu.shape[1])
         self._desc_cache[g] = d
         return d
 
@@ -139,7 +147,8 @@ class TieredKeyCacheLayer:
 
     @classmethod
     def _allocate(cls, keys: torch.Tensor, values: torch.Tensor, block_size: int, max_pagein_blocks: int,
-                  max_new_tokens: int, int4: bool, group_size: int) -> "TieredKeyCacheLayer":
+                  max_new_tokens: int, int4: bool, group_size: int,
+                  hot_blocks: tuple[int, int] | None = None) -> "TieredKeyCacheLayer":
         _require_cuda(keys, "keys")
         _require_cuda(values, "values")
         if block_size != BLOCK:
@@ -172,10 +181,34 @@ class TieredKeyCacheLayer:
             num_quantized_blocks=nb,
             _pagein_buffer=torch.empty(max_pagein_blocks * BLOCK, hd, dtype=kvd, device=dev),
             values_norm_max_per_block=z(kv, maxblk, dtype=torch.float32, device=dev),
-            keys_fp16_gpu=z(kv, cap, hd, dtype=kvd, device=dev),
+            keys_fp16_gpu=z(kv, cap if hot_blocks is None else hot_blocks[0] * BLOCK, hd, dtype=kvd, device=dev),
             keys_scale_max=z(kv, hd, dtype=torch.float32, device=dev),
         )
-        vbuf = z(kv, cap, dv, dtype=kvd, device=dev)
+        vbuf = z(kv, cap if hot_blocks is None else hot_blocks[1] * BLOCK, dv, dtype=kvd, device=dev)
+        if hot_blocks is not None:
+            # Bounded hot tier: the complete Tier 2 lives in pinned host memory (device-addressable); the
+            # *_gpu arrays above are slot scratch; residency tables and counters live on the device.
+            kcap, vcap = hot_blocks
+            self.keys_fp16_cpu = torch.zeros(kv, cap, hd, dtype=kvd).pin_memory()
+            self.values_fp16_cpu = torch.zeros(kv, cap, dv, dtype=kvd).pin_memory()
+            i32 = dict(dtype=torch.int32, device=dev)
+            hot = {
+                "key_slots": torch.full((maxblk,), -1, **i32), "value_slots": torch.full((maxblk,), -1, **i32),
+                "key_owner": torch.full((kcap,), -1, **i32), "value_owner": torch.full((vcap,), -1, **i32),
+                "key_stamp": torch.full((kcap,), -1, **i32), "value_stamp": torch.full((vcap,), -1, **i32),
+                "work": torch.zeros(2 * (2 + 3 * maxblk), **i32),
+                "counters": torch.zeros(12, dtype=torch.int64, device=dev),
+            }
+            st = _lib.CqaHotTier()
+            st.key_capacity_blocks, st.value_capacity_blocks = kcap, vcap
+            st.max_fill_blocks = max(1, int(max_pagein_blocks))
+            for name in ("key_slots", "value_slots", "key_owner", "value_owner", "key_stamp", "value_stamp", "work",
+                         "counters"):
+                setattr(st, name, hot[name].data_ptr())
+            hot["struct"] = st
+            self._hot = hot
+            self.fp16_key_cache_capacity = kcap
+            self.fp16_value_cache_capacity = vcap
         if int4:
             self.values_int4_packed = z(kv, cap, dv // 2, dtype=torch.uint8, device=dev)
             self.values_int4_scales = z(kv, cap, dv // 16, dtype=torch.float16, device=dev)
@@ -204,15 +237,11 @@ class TieredKeyCacheLayer:
 
     @staticmethod
     def _check_capacity(cap, max_blocks: int, what: str):
+        """None = full HBM mirror; a capacity covering the reserved context = static-resident (same layout);
+        anything smaller = bounded hot tier (INT4-value caches only)."""
         if cap is None:
             return None
-        cap = max(int(cap), 0)
-        if cap < max_blocks:
-            raise NotImplementedError(
-                f"{what}={cap} is smaller than the reserved {max_blocks} blocks: the bounded hot tier "
-                "(LRU scratch with page-in) is not built yet; pass None (full HBM mirror) or a capacity "
-                "that covers the reserved context (static-resident)")
-        return cap
+        return max(int(cap), 0)
 
     @classmethod
     def from_fp16_cache(cls, keys_fp16: torch.Tensor, values_fp16: torch.Tensor, block_size: int = 16,
@@ -222,6 +251,10 @@ class TieredKeyCacheLayer:
         self = cls._allocate(keys_fp16, values_fp16, block_size, max_pagein_blocks, max_new_tokens,
                              int4=False, group_size=16)
         cap = cls._check_capacity(fp16_key_cache_capacity, self.keys_scale.shape[1], "fp16_key_cache_capacity")
+        if cap is not None and cap < self.keys_scale.shape[1]:
+            raise NotImplementedError(
+                "a bounded FP16-key scratch is built for the INT4-value cache (from_fp16_cache_int4v) only; "
+                "pass None or a capacity that covers the reserved context")
         self._quantize_prefill(keys_fp16, values_fp16)
         if cap is not None:
             self.fp16_key_cache_capacity = cap
@@ -236,11 +269,25 @@ class TieredKeyCacheLayer:
                               fp16_value_cache_capacity: int | None = None,
                               defer_int4_append_quantization: bool = False) -> "TieredKeyCacheLayer":
         """INT8 keys + INT4 g16 values (reference: tiered_kv_cache.py:289-405)."""
-        self = cls._allocate(keys_fp16, values_fp16, block_size, max_pagein_blocks, max_new_tokens,
-                             int4=True, group_size=group_size)
-        maxblk = self.keys_scale.shape[1]
+        nb0 = keys_fp16.shape[1] // BLOCK
+        maxblk = nb0 + (max_new_tokens + BLOCK - 1) // BLOCK
         kcap = cls._check_capacity(fp16_key_cache_capacity, maxblk, "fp16_key_cache_capacity")
         vcap = cls._check_capacity(fp16_value_cache_capacity, maxblk, "fp16_value_cache_capacity")
+        bounded = (kcap is not None and kcap < maxblk) or (vcap is not None and vcap < maxblk)
+        hot_blocks = None
+        if bounded:
+            if (kcap is not None and kcap < 1) or (vcap is not None and vcap < 1):
+                raise ValueError("hot-tier capacities must be at least one block")
+            hot_blocks = (min(kcap, maxblk) if kcap is not None else maxblk,
+                          min(vcap, maxblk) if vcap is not None else maxblk)
+        self = cls._allocate(keys_fp16, values_fp16, block_size, max_pagein_blocks, max_new_tokens,
+                             int4=True, group_size=group_size, hot_blocks=hot_blocks)
+        if bounded:
+            self.defer_int4_append_quantization = bool(defer_int4_append_quantization)
+            self._quantize_prefill(keys_fp16, values_fp16)
+            self._fp16_key_resident = OrderedDict()
+            self._fp16_value_resident = OrderedDict()
+            return self
         self.defer_int4_append_quantization = bool(defer_int4_append_quantization)
         self._quantize_prefill(keys_fp16, values_fp16)
         if kcap is not None:
@@ -289,6 +336,32 @@ class TieredKeyCacheLayer:
                 1 if defer else 0, _lib.current_stream(dev))
         _lib.check(rc, "cqa_append_token")
         self._advance_after_append(pos)
+
+    # ------------------------------------------------------------------ bounded hot tier
+
+    @property
+    def bounded_hot_tier(self) -> bool:
+        return self._hot is not None
+
+    def _hot_tier_update(self, desc, ws_struct, nact: int, stream: int) -> None:
+        """Queue the residency update for the step whose masks are in `ws_struct` (no host wait)."""
+        rc = _lib.lib().cqa_hot_tier_update(C.byref(desc), C.byref(ws_struct), C.byref(self._hot["struct"]), nact,
+                                            stream)
+        _lib.check(rc, "cqa_hot_tier_update")
+
+    def hot_tier_counters(self) -> dict:
+        """Residency telemetry since construction (synchronises): hits, misses, page-ins and evictions per tier,
+        and the bytes the page-ins moved from the backing arrays."""
+        if self._hot is None:
+            return {}
+        c = self._hot["counters"].cpu().tolist()
+        blk = BLOCK * self.head_dim * self.keys_fp16_gpu.element_size() * self.kv_heads
+        out = {"steps": c[0]}
+        for name, o in (("key", 3), ("value", 7)):
+            out[f"{name}_hits"], out[f"{name}_misses"] = c[o], c[o + 1]
+            out[f"{name}_pageins"], out[f"{name}_evictions"] = c[o + 2], c[o + 3]
+            out[f"{name}_pagein_bytes"] = c[o + 2] * blk
+        return out
 
     def _defers_int4(self) -> bool:
         return bool(

@@ -74,6 +74,13 @@ typedef struct cqa_cache {
     int64_t values_t2_rows;
     const int32_t *key_slots;        /* block -> 16-row slot in keys_t2; NULL = identity */
     const int32_t *value_slots;      /* block -> slot in values_t2; NULL = identity */
+    /* Bounded hot tier: when a slot table is given, keys_t2 / values_t2 are scratch arrays of a few thousand
+     * blocks and the complete Tier-2 lives in the backing arrays ([KV][t2_backing_rows][128] of t2_dtype, row =
+     * token index), typically pinned host memory mapped into the device address space.  Blocks with slot -1 are read
+     * from the backing array directly; cqa_hot_tier_update pages them in afterwards. */
+    void *keys_t2_backing;
+    void *values_t2_backing;
+    int64_t t2_backing_rows;
 } cqa_cache;
 
 /* Certification knobs (the keyword arguments of certified_attention_layer,
@@ -325,6 +332,31 @@ int cqa_certify_given(const cqa_cache *c, const cqa_knobs *knobs, const cqa_work
                       int q_dtype, int64_t nq, int64_t nact, void *stream);
 /* Log-sum-exp merge of n_parts partial rows per head ([n_parts][H][CQA_PARTIAL_STRIDE]) into out[H][128]. */
 int cqa_merge_partials(const float *parts, int n_parts, int n_heads, float *out, void *stream);
+
+/* ---- bounded hot tier (reference: ensure_fp16_{keys,values}_resident, _page_in_fp16_blocks,
+ * _prepare_bounded_fp16_key_scratch - tiered_kv_cache.py:986-1537; backends/cuda_pagein.*) ----
+ * The reference keeps an LRU on the host, reads the selection back, copies the missing blocks host-to-device and
+ * only then attends.  Here the step never waits: kernels read a non-resident block straight from the backing
+ * array, and cqa_hot_tier_update, queued after the step, marks the blocks the step used (FP16-key mask, FP16-value
+ * mask), takes slots that were not used in this step in clock order, and copies the missed blocks into them, so
+ * the next steps find them in HBM.  All bookkeeping is on the device. */
+typedef struct cqa_hot_tier {
+    int32_t key_capacity_blocks;   /* slots in keys_t2 */
+    int32_t value_capacity_blocks; /* slots in values_t2 */
+    int32_t max_fill_blocks;       /* page-in budget per call and tier (blocks) */
+    int32_t reserved;
+    int32_t *key_slots;          /* [max_blocks], the table cqa_cache.key_slots points at */
+    int32_t *value_slots;
+    int32_t *key_owner;          /* [capacity] block held by a slot, -1 = free */
+    int32_t *value_owner;
+    int32_t *key_stamp;          /* [capacity] step in which the slot was last used */
+    int32_t *value_stamp;
+    int32_t *work;               /* [2][2 + 3 * max_blocks] per tier: miss count, fill count, missed blocks, (block, slot) pairs */
+    int64_t *counters;           /* [12]: step, clock hands (keys, values), then per tier: hits, misses, page-ins, evictions; 1 spare */
+} cqa_hot_tier;
+
+int cqa_hot_tier_update(const cqa_cache *c, const cqa_workspace *ws, const cqa_hot_tier *ht, int64_t nact,
+                        void *stream);
 
 /* Suggested split counts for a context of `nact` blocks on the current device. */
 int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int *num_splits, int *dense_splits);

@@ -161,6 +161,69 @@ def test_exact_ties_take_lowest_block_ids():
         hz.compare_step(cc, R, out, f"ties {knobs['v_tolerance']} {knobs['k_max']}")
 
 
+@pytest.mark.parametrize("kcap,vcap,planted", [(48, 48, 16), (8, 300, 0), (2000, 24, 8)])
+def test_bounded_hot_tier_equals_full_mirror(kcap, vcap, planted):
+    """Tier 2 in pinned host memory with a small device scratch: non-resident blocks are read from the backing
+    arrays, used blocks are paged in after the step, slots are recycled.  Outputs, certificates and cache bytes
+    equal the full-mirror run bit for bit; the scratch always mirrors the backing rows of the blocks it holds."""
+    from dotcache.kernels.tiered_kv_cache import TieredKeyCacheLayer
+
+    dtype = "bfloat16"
+    n = 4096 + 7
+    base = synth.make_layer_inputs(19, n, dtype=dtype, n_planted_blocks=planted)
+    aligned = 4096
+    knobs = _knobs(exploration_rate=0.02)
+    full = hz.make_cuda_cache(base.k[:, :aligned], base.v[:, :aligned], dtype, 96, defer=False)
+    kd, vd = hz.to_dev(base.k[:, :aligned], dtype), hz.to_dev(base.v[:, :aligned], dtype)
+    hot = TieredKeyCacheLayer.from_fp16_cache_int4v(kd, vd, max_new_tokens=96, max_pagein_blocks=32,
+                                                    fp16_key_cache_capacity=kcap, fp16_value_cache_capacity=vcap)
+    assert hot.bounded_hot_tier and hot.keys_fp16_cpu.is_pinned()
+    assert hot.keys_fp16_gpu.shape[1] == min(kcap, 262) * 16 and hot.values_fp16_gpu.shape[1] == min(vcap, 262) * 16
+    for t in range(aligned, n):
+        for c in (full, hot):
+            c.append_token(hz.to_dev(base.k[:, t:t + 1], dtype), hz.to_dev(base.v[:, t:t + 1], dtype))
+    rng = np.random.default_rng(19)
+    for step in range(40):
+        q, kn, vn = synth.decode_step_inputs(base, step, dtype=dtype)
+        for c in (full, hot):
+            c.append_token(hz.to_dev(kn, dtype), hz.to_dev(vn, dtype))
+        u = rng.random((32, full.num_quantized_blocks), dtype=np.float32)
+        o_full, _ = hz.cuda_step(full, q, dtype, 4, knobs, u, collect_stats=False)
+        o_hot, _ = hz.cuda_step(hot, q, dtype, 4, knobs, u, collect_stats=False)
+        assert np.array_equal(o_full, o_hot), f"step {step}"
+        cf, ff = full._certified_workspace["cqa_ws"].read_cert()
+        ch, fh = hot._certified_workspace["cqa_ws"].read_cert()
+        assert ff[:5] == fh[:5]
+        for key in cf:
+            assert np.array_equal(np.asarray(cf[key]).view(np.uint8), np.asarray(ch[key]).view(np.uint8)), key
+    for name in ("keys_int8", "keys_scale", "values_int4_packed", "values_int4_scales", "values_int4_errors"):
+        assert torch.equal(getattr(full, name), getattr(hot, name)), name
+    nt = full.num_tokens
+    assert torch.equal(full.keys_fp16_gpu[:, :nt].cpu(), hot.keys_fp16_cpu[:, :nt])
+    assert torch.equal(full.values_fp16_gpu[:, :nt].cpu(), hot.values_fp16_cpu[:, :nt])
+    torch.cuda.synchronize()
+    for tier, slots, owner, gpu, cpu_t in (("key", "key_slots", "key_owner", hot.keys_fp16_gpu, hot.keys_fp16_cpu),
+                                           ("value", "value_slots", "value_owner", hot.values_fp16_gpu,
+                                            hot.values_fp16_cpu)):
+        sl = hot._hot[slots].cpu().numpy()
+        ow = hot._hot[owner].cpu().numpy()
+        res = np.nonzero(sl >= 0)[0]
+        assert len(res) > 0
+        for b in res:
+            assert ow[sl[b]] == b, f"{tier}: owner table disagrees for block {b}"
+            lo = b * 16
+            hi = min(lo + 16, nt)
+            assert torch.equal(gpu[:, sl[b] * 16: sl[b] * 16 + (hi - lo)].cpu(), cpu_t[:, lo:hi]), f"{tier} block {b}"
+        assert len(set(sl[res].tolist())) == len(res), f"{tier}: two blocks share a slot"
+    ctr = hot.hot_tier_counters()
+    assert ctr["steps"] == 40 and ctr["key_misses"] > 0 and ctr["key_pageins"] > 0 and ctr["value_pageins"] >= 0
+    assert ctr["key_hits"] > 0, ctr
+    # a slot used in the current step is never recycled, so a scratch smaller than one step's working set
+    # fills once and then serves hits; misses beyond it are read from the backing arrays every step
+    assert ctr["key_pageins"] - ctr["key_evictions"] <= min(kcap, 262)
+    assert ctr["value_pageins"] - ctr["value_evictions"] <= min(vcap, 262)
+
+
 def test_decode_step_from_host_buffers_equals_two_calls():
     """cqa_decode_step_host (pinned host inputs, one library call) gives the bytes and rows of
     append_token + certified_attention_layer."""
