@@ -264,33 +264,43 @@ __device__ __noinline__ int select_top_sorted(const float *vals, int n, u64 *can
         int n_ge = n;            // entries >= thr
         int parity = 0;
         const int w = tid >> 5;
-        // Two bits per step: three candidate thresholds are counted at once, the per-warp counts travel
-        // as 10-bit fields of one word (a warp holds at most 512 entries).
+        // Two bits per step: three candidate thresholds are counted at once.  Only the first 256 threads search
+        // (named barrier): a step is a short dependent chain, and with all 32 warps the issue slots of their
+        // bookkeeping cost more than the shorter element loops save.
+        if (tid < VS_THREADS) {
 #pragma unroll 1
-        for (int bit = 30; bit >= 0 && n_ge != M; bit -= 2) {
-            const bool single = bit == 0;                 // 31 value bits: the last step decides one bit
-            const int lo = single ? 0 : bit - 1;
-            const unsigned t1 = thr | (1u << lo);                              // 01 (or 1)
-            const unsigned t2 = single ? 0xFFFFFFFFu : thr | (2u << lo);       // 10
-            const unsigned t3 = single ? 0xFFFFFFFFu : thr | (3u << lo);       // 11
-            unsigned local = 0;
-            for (int b = tid; b < n; b += SC_THREADS) {
-                const unsigned v = __float_as_uint(vals[b]);
-                local += (v >= t1 ? 1u : 0u) + (v >= t2 ? 1u << 10 : 0u) + (v >= t3 ? 1u << 20 : 0u);
+            for (int bit = 30; bit >= 0 && n_ge != M; bit -= 2) {
+                const bool single = bit == 0;                 // 31 value bits: the last step decides one bit
+                const int lo = single ? 0 : bit - 1;
+                const unsigned t1 = thr | (1u << lo);                              // 01 (or 1)
+                const unsigned t2 = single ? 0xFFFFFFFFu : thr | (2u << lo);       // 10
+                const unsigned t3 = single ? 0xFFFFFFFFu : thr | (3u << lo);       // 11
+                unsigned l12 = 0, l3 = 0;                     // a thread holds at most 64 entries
+                for (int b = tid; b < n; b += VS_THREADS) {
+                    const unsigned v = __float_as_uint(vals[b]);
+                    l12 += (v >= t1 ? 1u : 0u) + (v >= t2 ? 1u << 16 : 0u);
+                    l3 += v >= t3 ? 1u : 0u;
+                }
+                l12 = __reduce_add_sync(FULL, l12);
+                l3 = __reduce_add_sync(FULL, l3);
+                if (lane == 0) { sh.vs_i[parity][w] = (int)l12; sh.red_i[parity][w] = (int)l3; }
+                vs_barrier();
+                const unsigned p12 = lane < VS_WARPS ? (unsigned)sh.vs_i[parity][lane] : 0u;
+                const unsigned p3 = lane < VS_WARPS ? (unsigned)sh.red_i[parity][lane] : 0u;
+                parity ^= 1;
+                const unsigned c12 = __reduce_add_sync(FULL, p12);   // totals stay below 2^15 per field
+                const int c3 = (int)__reduce_add_sync(FULL, p3);
+                const int c1 = (int)(c12 & 0xFFFFu), c2 = (int)(c12 >> 16);
+                if (!single && c3 >= M) { thr = t3; n_ge = c3; }
+                else if (!single && c2 >= M) { thr = t2; n_ge = c2; }
+                else if (c1 >= M) { thr = t1; n_ge = c1; }
             }
-            local = __reduce_add_sync(FULL, local);
-            if (lane == 0) sh.red_i[parity][w] = (int)local;
-            __syncthreads();
-            const unsigned p = (unsigned)sh.red_i[parity][lane];
-            parity ^= 1;
-            // cross-warp totals can reach 16384: two 16-bit fields in one reduction, the third alone
-            const unsigned c12 = __reduce_add_sync(FULL, (p & 1023u) | (((p >> 10) & 1023u) << 16));
-            const int c3 = (int)__reduce_add_sync(FULL, p >> 20);
-            const int c1 = (int)(c12 & 0xFFFFu), c2 = (int)(c12 >> 16);
-            if (!single && c3 >= M) { thr = t3; n_ge = c3; }
-            else if (!single && c2 >= M) { thr = t2; n_ge = c2; }
-            else if (c1 >= M) { thr = t1; n_ge = c1; }
+            if (tid == 0) { sh.bcast_u[1] = thr; sh.bcast_i[4] = n_ge; }
         }
+        __syncthreads();
+        thr = sh.bcast_u[1];
+        n_ge = sh.bcast_i[4];
+        parity = 0;
         // n_ge == M: the entries >= thr are the answer.  Otherwise thr is the value of the M-th largest
         // entry and several entries equal it: take everything above, then the lowest block ids among the equal.
         const bool ties = n_ge != M;
