@@ -84,6 +84,8 @@ class CqaWorkspace(C.Structure):
         ("cert", vp), ("any_flags", vp), ("out", vp), ("tickets", vp),
         ("given_fp16", vp), ("partial_out", vp),
         ("rng_seed", C.c_uint64), ("rng_offset", C.c_uint64),
+        ("shard_stride", C.c_int64), ("shard_chunk", C.c_int64), ("shard_rank_stride", C.c_int64),
+        ("shard_ranks", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 

@@ -434,6 +434,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
     load_masks(0);
     // Largest Phase-1 block maximum over this warp's quantised blocks, per head: the softmax reference point.
     const bool have_mb = ws.m_b != nullptr;
+    const long mb_ld = ws.shard_chunk > 0 ? ws.shard_chunk : ws.ld;   // a rank's own rows of the exchange buffer
     float m_init = -INFINITY;
     if (have_mb) {
         float mx[G];
@@ -441,7 +442,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
         for (int g = 0; g < G; ++g) mx[g] = -INFINITY;
         for (long b = b_begin + warp + (long)lane * ATT_WARPS; b < b_end && b < nq; b += 32 * ATT_WARPS) {
 #pragma unroll
-            for (int g = 0; g < G; ++g) mx[g] = fmaxf(mx[g], ws.m_b[(long)(kv * G + g) * ws.ld + b]);
+            for (int g = 0; g < G; ++g) mx[g] = fmaxf(mx[g], ws.m_b[(long)(kv * G + g) * mb_ld + b]);
         }
 #pragma unroll
         for (int g = 0; g < G; ++g) {

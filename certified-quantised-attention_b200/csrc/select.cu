@@ -410,8 +410,18 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv = h / c.gqa_group;
     const int n = (int)nq;
-    const float *mb = ws.m_b + (long)h * ws.ld;
-    const float *sb = ws.s_b + (long)h * ws.ld;
+    // Plain layout: row h of an [H][ld] array.  Sharded layout: row h of rank r's slot in the all-gather buffer,
+    // [rank][row][chunk]; `gcol` maps a global block to its offset from the row start of rank 0.
+    const bool sharded_in = ws.shard_stride > 0;
+    const long row_ld = sharded_in ? ws.shard_chunk : ws.ld;
+    const float *mb = ws.m_b + (long)h * row_ld;
+    const float *sb = ws.s_b + (long)h * row_ld;
+    auto gcol = [&](int b) -> long {
+        if (!sharded_in) return b;
+        long r = b / ws.shard_stride;
+        if (r > ws.shard_ranks - 1) r = ws.shard_ranks - 1;
+        return r * ws.shard_rank_stride + (b - r * ws.shard_stride);
+    };
     float *mf = ws.mass_frac + (long)h * ws.ld;
     cqa_head_cert *ct = ws.cert + h;
     // Three independent roles per head run as separate CTAs (grid.y): 0 = selector, 1 = ranking /
@@ -430,12 +440,13 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
     // ---- one round of global loads, all issued up front: m_b, S_b; the exploration draw (role 0);
     // eta_b and, when only certifying, the mass fractions (role 2)
     const bool explore_on = kn.exploration_rate > 0.0f;
-    const float *eta = have_int4 ? c.values_int4_errors + (long)kv * c.max_blocks : nullptr;
+    const float *eta = have_int4 ? c.values_int4_errors + (long)kv * (sharded_in ? ws.shard_chunk : c.max_blocks) : nullptr;
     float mg = -INFINITY;
     for (int b = tid; b < n_pad; b += SC_THREADS) {
         if (b < n) {
-            const float m = mb[b];
-            const float s = fmaxf(sb[b], 1e-30f);
+            const long gb = gcol(b);
+            const float m = mb[gb];
+            const float s = fmaxf(sb[gb], 1e-30f);
             unsigned char ebit = 0;
             if (role == 0 && explore_on) {
                 const float uv = u != nullptr ? u[(long)h * u_ld + b]
@@ -444,7 +455,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             }
             if (role == 2) {
                 if (!fused) C[b] = mf[b];
-                A[b] = eta ? eta[b] : 0.0f;      // role 2 never needs m_b
+                A[b] = eta ? eta[gb] : 0.0f;     // role 2 never needs m_b
             } else {
                 A[b] = m;
             }
@@ -599,7 +610,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
         if (!narrow) {
             // the full sort overwrote ell and the fractions: rebuild them (each thread re-reads what it wrote)
             for (int b = tid; b < n; b += SC_THREADS) {
-                B[b] = __fadd_rn(clog(fmaxf(sb[b], 1e-30f)), A[b]);
+                B[b] = __fadd_rn(clog(fmaxf(sb[gcol(b)], 1e-30f)), A[b]);
                 C[b] = mf[b];
             }
         }
@@ -859,7 +870,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             }
         } else {
             const float vt = kn.v_tolerance;
-            promoted = column_sum(A, n, [eta, vt](unsigned, int b) { return eta[b] > vt; }, sh, parity, n_prom);
+            promoted = column_sum(A, n, [eta, vt, &gcol](unsigned, int b) { return eta[gcol(b)] > vt; }, sh, parity, n_prom);
         }
         if (tid == 0) {
             sh.bcast_f[1] = promoted;
@@ -881,7 +892,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
                 const unsigned bits = __float_as_uint(A[b]);
                 up = t0 != 0xFFFFFFFFu && (bits > t0 || (bits == t0 && b < id_bound));
             } else {
-                up = eta[b] > kn.v_tolerance;
+                up = eta[gcol(b)] > kn.v_tolerance;
             }
             mask[b] = up ? 1 : 0;
         }

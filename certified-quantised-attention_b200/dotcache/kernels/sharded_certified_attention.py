@@ -109,18 +109,11 @@ def exchange_rows(n_heads: int, kv_heads: int) -> int:
     return 2 * n_heads + kv_heads + 1
 
 
-def scatter_exchange_a(plan: ShardPlan, recv: torch.Tensor, glob: torch.Tensor, sigma: torch.Tensor,
-                       nq_global: int, n_heads: int, kv_heads: int, with_sigma: bool = True) -> None:
-    """recv [P][rows][chunk] (rank-major) -> glob [2H+KV][ld] (block-major rows) and sigma [KV*128]."""
-    rows = 2 * n_heads + kv_heads
-    P, R = plan.world, plan.stride
-    if P > 1:
-        glob[:, : (P - 1) * R].view(rows, P - 1, R).copy_(recv[: P - 1, :rows, :R].permute(1, 0, 2))
-    n_last = plan.local_blocks(nq_global, plan.last)
-    lo = plan.first_block(plan.last)
-    glob[:, lo: lo + n_last].copy_(recv[P - 1, :rows, :n_last])
-    if with_sigma:
-        torch.amax(recv[:, rows, : sigma.numel()], dim=0, out=sigma)
+def global_column(plan: ShardPlan, rows: int, b: int) -> int:
+    """Offset of global block `b` from the start of a row of rank 0 in the all-gather buffer
+    [rank][row][chunk] (the selector kernel computes the same)."""
+    r = min(b // plan.stride, plan.world - 1) if plan.world > 1 else 0
+    return r * rows * plan.chunk + (b - r * plan.stride)
 
 
 class DistComm:
@@ -155,17 +148,20 @@ class ShardedCertifiedLayer:
         rows = exchange_rows(H, KV)
         self.send = torch.zeros(rows, plan.chunk, **f32)
         self.recv = torch.zeros(plan.world, rows, plan.chunk, **f32)
-        self.glob = torch.zeros(2 * H + KV, plan.ld, **f32)      # m_b | S_b | eta, global block index
         self.sigma = torch.zeros(KV * 128, **f32)
         self.given = torch.zeros(H, _lib.MAX_RANKING_K, 2, **f32)
         self.partial = torch.zeros(H, _lib.PARTIAL_STRIDE, **f32)
         self.partials = torch.zeros(plan.world, H, _lib.PARTIAL_STRIDE, **f32)
-        # masks, certificate and scratch: a workspace sized for the global block count, whose Phase-1
-        # arrays are replaced by views of `glob`
+        # masks, certificate and scratch: a workspace sized for the global block count; the selector reads
+        # m_b / S_b / eta straight from the all-gather buffer, Phase 2 reads this rank's rows of the send buffer
         self.ws = _Workspace(local_cache, H, self.G, dev, ld=plan.ld)
-        self.ws.m_b = self.glob[:H]
-        self.ws.s_b = self.glob[H: 2 * H]
-        self.eta = self.glob[2 * H:]
+        self._rows = rows
+        esz = 4
+        self._p_send = self.send.data_ptr()
+        self._p_send_sb = self._p_send + H * plan.chunk * esz
+        self._p_recv = self.recv.data_ptr()
+        self._p_recv_sb = self._p_recv + H * plan.chunk * esz
+        self._p_recv_eta = self._p_recv + 2 * H * plan.chunk * esz
         self.rng_seed, self.rng_calls = 0, 0     # exploration draw: identical on every rank
         self._meta_nq = -1
         self._wg, self._wl = _lib.CqaWorkspace(), _lib.CqaWorkspace()   # private copies: fields are overridden
@@ -212,7 +208,7 @@ class ShardedCertifiedLayer:
         with _lib.on_device(self.device):
             # 1. Phase 1 straight into the send buffer (rows 0..H-1 m_b, H..2H-1 S_b)
             _lib.check(L.cqa_score_blocks(C.byref(desc_l), q.data_ptr(), qd, n_loc, float(q_scale),
-                                          self.send.data_ptr(), self.send[H].data_ptr(), plan.chunk,
+                                          self._p_send, self._p_send_sb, plan.chunk,
                                           ws.token_scores.data_ptr(), stream), "cqa_score_blocks")
             # eta_b and the scale maxima only change when a block completes
             fresh_meta = self._meta_nq != nq_g
@@ -221,7 +217,8 @@ class ShardedCertifiedLayer:
                 self.send[2 * H + KV, : KV * 128].copy_(cache.keys_scale_max.reshape(-1))
             # 2. Exchange A and the global selector
             self.comm.all_gather(self.recv, self.send)
-            scatter_exchange_a(plan, self.recv, self.glob, self.sigma, nq_g, H, KV, with_sigma=fresh_meta)
+            if fresh_meta:
+                torch.amax(self.recv[:, self._rows - 1, : KV * 128], dim=0, out=self.sigma)
             self._meta_nq = nq_g
             knobs = _make_knobs(
                 q_scale=q_scale, tau_cov=tau_cov, k_min=k_min, k_max=k_max, rung1_threshold=rung1_threshold,
@@ -236,9 +233,12 @@ class ShardedCertifiedLayer:
             C.memmove(C.byref(wg), C.byref(ws.fill_struct(nact_g)), C.sizeof(wg))
             wg.given_fp16 = self.given.data_ptr()
             wg.partial_out = None
+            wg.m_b, wg.s_b = self._p_recv, self._p_recv_sb
+            wg.shard_stride, wg.shard_chunk = plan.stride, plan.chunk
+            wg.shard_rank_stride, wg.shard_ranks = self._rows * plan.chunk, plan.world
             desc_g = cache._desc_copy(G)
             desc_g.max_blocks = plan.ld
-            desc_g.values_int4_errors = self.eta.data_ptr()
+            desc_g.values_int4_errors = self._p_recv_eta
             desc_g.sigma_max = self.sigma.data_ptr()
             u_ptr, u_ld, u_keep = None, 0, None
             if exploration_rate > 0.0:
@@ -265,8 +265,8 @@ class ShardedCertifiedLayer:
             nact_l = n_loc + (1 if (is_last and nact_g > nq_g) else 0)
             wl = self._wl
             C.memmove(C.byref(wl), C.byref(ws.fill_struct(nact_l)), C.sizeof(wl))
-            wl.m_b = self.glob.data_ptr() + 4 * first
-            wl.s_b = self.glob[H].data_ptr() + 4 * first
+            wl.m_b, wl.s_b = self._p_send, self._p_send_sb
+            wl.shard_stride, wl.shard_chunk, wl.shard_rank_stride, wl.shard_ranks = 0, plan.chunk, 0, 0
             wl.topk_mask = ws.topk_mask.data_ptr() + first
             wl.value_mask = ws.value_mask.data_ptr() + first
             wl.explore_mask = ws.explore_mask.data_ptr() + first

@@ -177,6 +177,15 @@ typedef struct cqa_workspace {
      * same stream. */
     uint64_t rng_seed;
     uint64_t rng_offset;
+    /* Sequence-sharded selector input straight from the all-gather buffer (0 = plain [row][ld] arrays):
+     * m_b, s_b and cqa_cache.values_int4_errors then point at the rows of rank 0 inside a buffer laid out
+     * [rank][row][shard_chunk] with shard_rank_stride floats per rank; global block b lives in rank
+     * r = min(b / shard_stride, shard_ranks - 1), column b - r * shard_stride. */
+    int64_t shard_stride;
+    int64_t shard_chunk;
+    int64_t shard_rank_stride;
+    int32_t shard_ranks;
+    int32_t reserved2;
 } cqa_workspace;
 
 #define CQA_PARTIAL_STRIDE 130

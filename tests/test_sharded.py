@@ -15,7 +15,7 @@ import torch.multiprocessing as mp
 
 import golden_cases as gc
 from cqa_b200 import synth
-from dotcache.kernels.sharded_certified_attention import DistComm, ShardPlan, exchange_rows, scatter_exchange_a
+from dotcache.kernels.sharded_certified_attention import DistComm, ShardPlan, exchange_rows, global_column
 
 H, KV, G = 32, 8, 4
 
@@ -60,11 +60,13 @@ def _gloo_rank(rank, world, port, n_tok, new, ret):
         send[rows - 1, : KV * 128] = torch.arange(KV * 128, dtype=torch.float32) * (1 + (rank == 1))
         recv = torch.zeros(world, rows, plan.chunk)
         DistComm().all_gather(recv, send)
-        glob = torch.full((rows - 1, plan.ld), -1.0)
-        sigma = torch.zeros(KV * 128)
-        scatter_exchange_a(plan, recv, glob, sigma, nq, H, KV)
-        want = torch.arange(rows - 1, dtype=torch.float32)[:, None] * 1e4 + torch.arange(nq, dtype=torch.float32)[None, :]
-        ok = bool(torch.equal(glob[:, :nq], want)) and bool((glob[:, nq:] == -1).all())
+        # every global block is found, in every row, at the offset the selector kernel uses
+        flat = recv.view(-1)
+        ok = True
+        for row in (0, H, 2 * H + KV - 1):
+            for b in (0, 1, plan.stride - 1, plan.stride, nq // 2, nq - 1):
+                ok = ok and float(flat[row * plan.chunk + global_column(plan, rows, b)]) == row * 1e4 + b
+        sigma = recv[:, rows - 1, : KV * 128].amax(dim=0)
         ok = ok and bool(torch.equal(sigma, torch.arange(KV * 128, dtype=torch.float32) * (2 if world > 1 else 1)))
         t = torch.tensor([1.0 if ok else 0.0])
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
