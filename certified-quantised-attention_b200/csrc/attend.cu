@@ -671,10 +671,7 @@ static int attend_launch_gt(const cqa_cache *c, const cqa_workspace *ws, const v
     const bool dense = ws->cert && ws->dense_splits > 0 && ws->dense_m && ws->dense_l && ws->dense_acc;
     cqa_workspace w = *ws;
     if (!dense) w.dense_splits = 0;
-    size_t smem = attend_smem<G>();
-#ifdef CQA_DEBUG_SMEM_PAD
-    smem += CQA_DEBUG_SMEM_PAD;
-#endif
+    const size_t smem = attend_smem<G>();
     static size_t attr = 0;
     if (smem > attr) {
         int rc = check_cuda(cudaFuncSetAttribute(attend_kernel<G, T2>, cudaFuncAttributeMaxDynamicSharedMemorySize,

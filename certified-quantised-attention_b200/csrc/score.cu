@@ -228,11 +228,7 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
                           float *s_b, long ld, float *tok, dim3 grid, int bpc, int32_t *zero_words, int n_zero_words,
                           cudaStream_t st)
 {
-#ifdef CQA_DEBUG_SMEM_PAD
-    constexpr int SMEM = SCORE_SMEM + G * D * 4 + CQA_DEBUG_SMEM_PAD;
-#else
     constexpr int SMEM = SCORE_SMEM + G * D * 4;
-#endif
     static bool attr_set = false;
     if (!attr_set) {
         int rc = check_cuda(cudaFuncSetAttribute(score_blocks_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
