@@ -442,28 +442,49 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
     const bool explore_on = kn.exploration_rate > 0.0f;
     const float *eta = have_int4 ? c.values_int4_errors + (long)kv * (sharded_in ? ws.shard_chunk : c.max_blocks) : nullptr;
     float mg = -INFINITY;
-    for (int b = tid; b < n_pad; b += SC_THREADS) {
-        if (b < n) {
-            const long gb = gcol(b);
-            const float m = mb[gb];
-            const float s = fmaxf(sb[gb], 1e-30f);
-            unsigned char ebit = 0;
-            if (role == 0 && explore_on) {
-                const float uv = u != nullptr ? u[(long)h * u_ld + b]
-                                              : philox_uniform(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)b);
-                ebit = uv < kn.exploration_rate ? 2 : 0;
+    // four blocks per thread and round: all global loads of a round are issued before any is used
+    for (int b0 = tid; b0 < n_pad; b0 += 4 * SC_THREADS) {
+        float m4[4], s4[4], x4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int b = b0 + k * SC_THREADS;
+            m4[k] = 0.0f; s4[k] = 1.0f; x4[k] = 0.0f;
+            if (b < n) {
+                const long gb = gcol(b);
+                m4[k] = mb[gb];
+                s4[k] = sb[gb];
+                if (role == 0) {
+                    if (explore_on && u != nullptr) x4[k] = u[(long)h * u_ld + b];
+                } else if (role == 2) {
+                    x4[k] = eta ? eta[gb] : 0.0f;
+                }
             }
-            if (role == 2) {
-                if (!fused) C[b] = mf[b];
-                A[b] = eta ? eta[gb] : 0.0f;     // role 2 never needs m_b
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int b = b0 + k * SC_THREADS;
+            if (b >= n_pad) continue;
+            if (b < n) {
+                const float m = m4[k];
+                const float s = fmaxf(s4[k], 1e-30f);
+                unsigned char ebit = 0;
+                if (role == 0 && explore_on) {
+                    const float uv = u != nullptr ? x4[k]
+                                                  : philox_uniform(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)b);
+                    ebit = uv < kn.exploration_rate ? 2 : 0;
+                }
+                if (role == 2) {
+                    if (!fused) C[b] = mf[b];
+                    A[b] = x4[k];                     // eta_b: role 2 never needs m_b
+                } else {
+                    A[b] = m;
+                }
+                B[b] = __fadd_rn(clog(s), m);
+                mask[b] = ebit;                       // bit 1: exploration candidate, bit 0: selected (set later)
+                mg = fmaxf(mg, m);
             } else {
-                A[b] = m;
+                mask[b] = 0;
             }
-            B[b] = __fadd_rn(clog(s), m);
-            mask[b] = ebit;                       // bit 1: exploration candidate, bit 0: selected (set later)
-            mg = fmaxf(mg, m);
-        } else {
-            mask[b] = 0;
         }
     }
     CQA_CLK(1);
