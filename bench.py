@@ -70,6 +70,8 @@ def parse_args():
     ap.add_argument("--sharded-context", type=int, default=131072,
                     help="context of the sequence-sharded measurement taken when --gpus > 1 (0 = skip)")
     ap.add_argument("--sharded-steps", type=int, default=64)
+    ap.add_argument("--sharded-peer", type=int, default=1,
+                    help="also time the sharded step with peer-memory exchanges (0 = collectives only)")
     return ap.parse_args()
 
 
@@ -454,6 +456,21 @@ def run_sharded(args, rank, world, device_index):
     t = torch.tensor([us], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     us = float(t.item())
+    # the same sequence again with peer-memory exchanges (pushes over NVLink, bounded waits on local flags)
+    us_peer, peer_status = None, None
+    if args.sharded_peer:
+        del layer, cache
+        torch.cuda.empty_cache()
+        cache = TieredKeyCacheLayer.from_fp16_cache_int4v(to(base.k[:, lo:hi]), to(base.v[:, lo:hi]),
+                                                          max_new_tokens=(W + K + 16) if rank == plan.last else 0,
+                                                          defer_int4_append_quantization=True)
+        layer = ShardedCertifiedLayer(plan, cache, 4, exchange="peer")
+        us_peer = timed(sharded_step)
+        peer_status = layer.peer_status()
+        t = torch.tensor([us_peer, float(peer_status)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us_peer, peer_status = float(t[0].item()), int(t[1].item())
+        layer.close()
     single = None
     if rank == 0:
         full = TieredKeyCacheLayer.from_fp16_cache_int4v(to(base.k), to(base.v), max_new_tokens=W + K + 16,
@@ -479,6 +496,9 @@ def run_sharded(args, rank, world, device_index):
                         "NCCL all-gather / all-reduce exchanges", "ranks": world, "steps": K,
             "us_per_layer_step": round(us, 2), "single_gpu_us_per_layer_step": round(single, 2),
             "speedup_vs_single_gpu": round(single / us, 3),
+            "peer_exchange_us_per_layer_step": None if us_peer is None else round(us_peer, 2),
+            "peer_exchange_speedup_vs_single_gpu": None if us_peer is None else round(single / us_peer, 3),
+            "peer_exchange_wait_status": peer_status,
             "hbm_floor_us_per_rank": round(per_rank_bytes / 6540.2e3, 2)}
 
 

@@ -17,7 +17,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 INCLUDE = HERE.parent / "include"
 LIB = HERE / "cqa_b200" / "libcqa_b200.so"
-SOURCES = ["api.cu", "quantize.cu", "score.cu", "select.cu", "attend.cu", "hot_tier.cu"]
+SOURCES = ["api.cu", "quantize.cu", "score.cu", "select.cu", "attend.cu", "hot_tier.cu", "peer.cu"]
 
 
 def nvcc_path() -> str:

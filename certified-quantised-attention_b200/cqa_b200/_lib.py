@@ -22,6 +22,8 @@ SYMBOLS = [
     "cqa_attend", "cqa_attend_static", "cqa_layer_step", "cqa_suggest_splits",
     "cqa_select_certify_local", "cqa_rescore_owned", "cqa_certify_given", "cqa_merge_partials",
     "cqa_decode_step_host", "cqa_hot_tier_update",
+    "cqa_peer_buffer_bytes", "cqa_peer_alloc", "cqa_peer_free", "cqa_peer_export", "cqa_peer_import", "cqa_peer_close",
+    "cqa_sharded_layer_step", "cqa_peer_status",
 ]
 PARTIAL_STRIDE = 130
 
@@ -85,7 +87,19 @@ class CqaWorkspace(C.Structure):
         ("given_fp16", vp), ("partial_out", vp),
         ("rng_seed", C.c_uint64), ("rng_offset", C.c_uint64),
         ("shard_stride", C.c_int64), ("shard_chunk", C.c_int64), ("shard_rank_stride", C.c_int64),
-        ("shard_ranks", C.c_int32), ("reserved2", C.c_int32),
+        ("shard_ranks", C.c_int32), ("given_ranks", C.c_int32), ("given_rank_stride", C.c_int64),
+        ("wait_flags", vp), ("wait_n", C.c_int32), ("wait_skip", C.c_int32), ("wait_value", C.c_int32),
+        ("reserved2", C.c_int32), ("wait_status", vp),
+    ]
+
+
+MAX_PEERS = 8
+
+
+class CqaPeers(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("rows", C.c_int32), ("n_heads", C.c_int32),
+        ("chunk", C.c_int64), ("base", vp * MAX_PEERS),
     ]
 
 
@@ -144,8 +158,18 @@ def lib() -> C.CDLL:
     L.cqa_merge_partials.argtypes = [vp, i32, i32, vp, vp]
     L.cqa_decode_step_host.argtypes = [pc, pk, pw, vp, vp, i32, i64, i32, vp, vp]
     L.cqa_hot_tier_update.argtypes = [pc, pw, C.POINTER(CqaHotTier), i64, vp]
+    L.cqa_peer_buffer_bytes.argtypes = [i32, i32, i32, i64]
+    L.cqa_peer_alloc.argtypes = [i64, C.POINTER(vp)]
+    L.cqa_peer_free.argtypes = [vp]
+    L.cqa_peer_export.argtypes = [vp, C.c_char_p]
+    L.cqa_peer_import.argtypes = [C.c_char_p, C.POINTER(vp)]
+    L.cqa_peer_close.argtypes = [vp]
+    L.cqa_peer_status.argtypes = [C.POINTER(CqaPeers), C.POINTER(C.c_int32), i32]
+    L.cqa_sharded_layer_step.argtypes = [pc, pc, pk, pw, pw, C.POINTER(CqaPeers), vp, i32, i64, i64, i64, i64, i64, i64,
+                                         i32, i64, i32, vp, vp]
     for s in SYMBOLS[2:]:
         getattr(L, s).restype = C.c_int
+    L.cqa_peer_buffer_bytes.restype = C.c_int64
     _lib = L
     return L
 

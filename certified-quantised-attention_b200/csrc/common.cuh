@@ -314,6 +314,40 @@ static inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, di
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ----------------------------------------------------------------- peer exchange flags
+
+__device__ __forceinline__ int ld_acquire_sys(const int32_t *p)
+{
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int32_t *p, int v)
+{
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Called by every thread of a CTA before it reads exchanged data: thread 0 waits until flags[i] >= value for every
+// i < n except `skip` (bounded: about half a second), then the CTA synchronises.  A timeout is recorded in *status.
+constexpr int PEER_WAIT_SPINS = 2000000;
+__device__ __forceinline__ void peer_wait(const int32_t *flags, int n, int skip, int value, int32_t *status)
+{
+    if (flags != nullptr && threadIdx.x == 0) {
+        for (int i = 0; i < n; ++i) {
+            if (i == skip) continue;
+            int spins = 0;
+            while (ld_acquire_sys(flags + i) < value) {
+                if (++spins > PEER_WAIT_SPINS) {
+                    if (status) atomicExch(status, 100 + i);
+                    break;
+                }
+                __nanosleep(200);
+            }
+        }
+    }
+    __syncthreads();
+}
+
 // ----------------------------------------------------------------- errors
 
 void set_error(const char *fmt, ...);

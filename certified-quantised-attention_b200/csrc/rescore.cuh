@@ -59,7 +59,9 @@ __device__ __forceinline__ void fp16_block_score_warp(const cqa_cache &c, const 
 }
 
 // Delta[h] = dot(|q_h|, sigma_max[kv]) / (2 sqrt(128))
-__device__ __forceinline__ float delta_bound_warp(const cqa_cache &c, const void *q, int q_dtype, int h)
+// `ranks` > 1: sigma_max is one row per rank, `rank_stride` floats apart (sequence sharding); the maximum is taken.
+__device__ __forceinline__ float delta_bound_warp(const cqa_cache &c, const void *q, int q_dtype, int h, int ranks = 1,
+                                                  long rank_stride = 0)
 {
     const int L = threadIdx.x & 15;
     const int kv = h / c.gqa_group;
@@ -68,7 +70,9 @@ __device__ __forceinline__ float delta_bound_warp(const cqa_cache &c, const void
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         qa[i] = fabsf(qa[i]);
-        sg[i] = c.sigma_max[kv * D + 8 * L + i];
+        float sv = c.sigma_max[kv * D + 8 * L + i];
+        for (int r = 1; r < ranks; ++r) sv = fmaxf(sv, c.sigma_max[r * rank_stride + kv * D + 8 * L + i]);
+        sg[i] = sv;
     }
     const float denom = 22.627416997969522f;  // 2*sqrt(128) rounded to binary32
     return __fdiv_rn(hw_sum(chain8(qa, sg)), denom);

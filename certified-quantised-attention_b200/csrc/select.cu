@@ -649,8 +649,16 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
                 const int b = ct->top_blocks[tid];
                 top_idx[tid] = b;
                 top_i8[tid] = A[b];
-                top_f16[tid] = ws.given_fp16[((long)h * CQA_MAX_RANKING_K + tid) * 2];
-                top_lm[tid] = ws.given_fp16[((long)h * CQA_MAX_RANKING_K + tid) * 2 + 1];
+                // one array per rank when the re-scores were pushed (only a block's owner wrote non-zero values)
+                float gs = 0.0f, gl = 0.0f;
+                const int gr = ws.given_ranks > 1 ? ws.given_ranks : 1;
+                for (int r = 0; r < gr; ++r) {
+                    const float *g = ws.given_fp16 + r * ws.given_rank_stride + ((long)h * CQA_MAX_RANKING_K + tid) * 2;
+                    gs = __fadd_rn(gs, g[0]);
+                    gl = __fadd_rn(gl, g[1]);
+                }
+                top_f16[tid] = gs;
+                top_lm[tid] = gl;
             }
         } else if (rk <= 4) {
             u64 t4[4] = {0ull, 0ull, 0ull, 0ull};
@@ -723,7 +731,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
                 if (lane == 0) { top_f16[warp] = s; top_lm[warp] = lm; }
             }
         } else if (warp == rk) {
-            const float d = delta_bound_warp(c, q, q_dtype, h);
+            const float d = delta_bound_warp(c, q, q_dtype, h, sharded_in ? ws.shard_ranks : 1, ws.shard_rank_stride);
             if (lane == 0) s_delta = d;
         } else if (overlap && kn.ranking_fallback) {
             for (int b = (warp - ub_first) * 32 + lane; b < n; b += ub_warps * 32) {
@@ -942,6 +950,7 @@ __global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_kn
                                                             int phases, int role_base)
 {
     grid_dependency_wait();
+    peer_wait(ws.wait_flags, ws.wait_n, ws.wait_skip, ws.wait_value, ws.wait_status);
 #ifdef CQA_WARM_REPEAT
     selcert_body<T2>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
     __syncthreads();

@@ -95,8 +95,8 @@ class ShardPlan:
 
     @property
     def chunk(self) -> int:
-        """Columns of one rank's slot in the exchange buffers."""
-        return max(self.stride, self.last_capacity, self.sigma_cols)
+        """Columns of one rank's slot in the exchange buffers (a multiple of four: rows stay 16-byte aligned)."""
+        return (max(self.stride, self.last_capacity, self.sigma_cols) + 3) // 4 * 4
 
     @property
     def ld(self) -> int:
@@ -133,8 +133,16 @@ class ShardedCertifiedLayer:
     """One layer of one sequence, sharded over the ranks of a process group.  `comm` is a DistComm (or
     anything with the same two methods)."""
 
-    def __init__(self, plan: ShardPlan, local_cache: TieredKeyCacheLayer, gqa_group: int, comm=None):
+    def __init__(self, plan: ShardPlan, local_cache: TieredKeyCacheLayer, gqa_group: int, comm=None,
+                 exchange: str = "collective"):
+        """`exchange`: "collective" = torch.distributed all-gather / all-reduce through `comm`; "peer" = every rank
+        pushes its slices into the other ranks' buffers over NVLink and kernels wait on local flags
+        (cqa_sharded_layer_step; one node, one process per GPU, at most 8 ranks; the default process group is used
+        once, at construction, to exchange the memory handles)."""
+        if exchange not in ("collective", "peer"):
+            raise ValueError("exchange must be 'collective' or 'peer'")
         self.plan, self.cache, self.G = plan, local_cache, int(gqa_group)
+        self.exchange = exchange
         self.comm = comm if comm is not None else DistComm()
         dev = local_cache.keys_int8.device
         self.device = dev
@@ -148,7 +156,6 @@ class ShardedCertifiedLayer:
         rows = exchange_rows(H, KV)
         self.send = torch.zeros(rows, plan.chunk, **f32)
         self.recv = torch.zeros(plan.world, rows, plan.chunk, **f32)
-        self.sigma = torch.zeros(KV * 128, **f32)
         self.given = torch.zeros(H, _lib.MAX_RANKING_K, 2, **f32)
         self.partial = torch.zeros(H, _lib.PARTIAL_STRIDE, **f32)
         self.partials = torch.zeros(plan.world, H, _lib.PARTIAL_STRIDE, **f32)
@@ -162,9 +169,65 @@ class ShardedCertifiedLayer:
         self._p_recv = self.recv.data_ptr()
         self._p_recv_sb = self._p_recv + H * plan.chunk * esz
         self._p_recv_eta = self._p_recv + 2 * H * plan.chunk * esz
+        self._p_recv_sigma = self._p_recv + (2 * H + KV) * plan.chunk * esz
         self.rng_seed, self.rng_calls = 0, 0     # exploration draw: identical on every rank
         self._meta_nq = -1
         self._wg, self._wl = _lib.CqaWorkspace(), _lib.CqaWorkspace()   # private copies: fields are overridden
+        self._peers = None
+        self._step = 0
+        if exchange == "peer":
+            self._open_peers()
+
+    # -------------------------------------------------------------- peer buffers
+    def _open_peers(self) -> None:
+        plan, L = self.plan, _lib.lib()
+        if plan.world < 2 or plan.world > _lib.MAX_PEERS:
+            raise ValueError(f"peer exchange needs 2..{_lib.MAX_PEERS} ranks")
+        with _lib.on_device(self.device):
+            nbytes = L.cqa_peer_buffer_bytes(plan.world, self.H, self.KV, plan.chunk)
+            own = C.c_void_p()
+            _lib.check(L.cqa_peer_alloc(nbytes, C.byref(own)), "cqa_peer_alloc")
+            handle = C.create_string_buffer(64)
+            _lib.check(L.cqa_peer_export(own, handle), "cqa_peer_export")
+            handles = [None] * plan.world
+            dist.all_gather_object(handles, bytes(handle.raw))
+            st = _lib.CqaPeers()
+            st.world, st.rank, st.rows, st.n_heads, st.chunk = plan.world, plan.rank, self._rows, self.H, plan.chunk
+            self._imported = []
+            for r in range(plan.world):
+                if r == plan.rank:
+                    st.base[r] = own.value
+                else:
+                    p = C.c_void_p()
+                    _lib.check(L.cqa_peer_import(handles[r], C.byref(p)), "cqa_peer_import")
+                    st.base[r] = p.value
+                    self._imported.append(p)
+            self._peers, self._own_buffer, self._peer_bytes = st, own, nbytes
+            dist.barrier()
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's (call on every rank, after the last step)."""
+        if self._peers is None:
+            return
+        L = _lib.lib()
+        torch.cuda.synchronize(self.device)
+        dist.barrier()
+        with _lib.on_device(self.device):
+            for p in self._imported:
+                L.cqa_peer_close(p)
+            dist.barrier()
+            L.cqa_peer_free(self._own_buffer)
+        self._peers = None
+
+    def peer_status(self, reset: bool = False) -> int:
+        """0 unless a bounded wait of the steps so far timed out (synchronises with the device)."""
+        if self._peers is None:
+            return 0
+        out = C.c_int32(0)
+        with _lib.on_device(self.device):
+            _lib.check(_lib.lib().cqa_peer_status(C.byref(self._peers), C.byref(out), 1 if reset else 0),
+                       "cqa_peer_status")
+        return int(out.value)
 
     # -------------------------------------------------------------- bookkeeping
     @property
@@ -182,6 +245,46 @@ class ShardedCertifiedLayer:
         self.num_tokens += 1
 
     # -------------------------------------------------------------------- step
+    def _step_peer(self, q, qd, q_scale, nq_g, nact_g, n_loc, first, is_last, collect_stats, exploration_uniforms,
+                   knob_args):
+        """The whole step as one library call (cqa_sharded_layer_step): eight launches, no collective library."""
+        if exploration_uniforms is not None:
+            raise NotImplementedError("the peer exchange draws exploration in-kernel; explicit uniforms are only "
+                                      "supported with exchange='collective'")
+        plan, cache, ws, G = self.plan, self.cache, self.ws, self.G
+        L = _lib.lib()
+        knobs = _make_knobs(q_scale=q_scale, force_trailing_value_fp16=True, **knob_args)
+        ws.ensure_sel_width(_selection_width(knob_args["k_max"], knob_args["rung1_threshold"],
+                                             knob_args["rung1_multiplier"], nq_g), self.device)
+        wg = self._wg
+        C.memmove(C.byref(wg), C.byref(ws.fill_struct(nact_g)), C.sizeof(wg))
+        wg.shard_stride = plan.stride
+        wg.rng_seed, wg.rng_offset = self.rng_seed, self.rng_calls
+        if knob_args["exploration_rate"] > 0.0:
+            self.rng_calls += 1
+        nact_l = n_loc + (1 if (is_last and nact_g > nq_g) else 0)
+        wl = self._wl
+        C.memmove(C.byref(wl), C.byref(ws.fill_struct(nact_l)), C.sizeof(wl))
+        wl.topk_mask = ws.topk_mask.data_ptr() + first
+        wl.value_mask = ws.value_mask.data_ptr() + first
+        wl.explore_mask = ws.explore_mask.data_ptr() + first
+        desc_g = cache._desc_copy(G)
+        desc_g.max_blocks = plan.ld
+        last_valid = BLOCK if nact_l == n_loc else cache.num_tokens - n_loc * BLOCK
+        self._step += 1
+        push_meta = 1 if self._meta_nq != nq_g else 0
+        self._meta_nq = nq_g
+        with _lib.on_device(self.device):
+            _lib.check(L.cqa_sharded_layer_step(
+                C.byref(cache._desc(G)), C.byref(desc_g), C.byref(knobs), C.byref(wg), C.byref(wl),
+                C.byref(self._peers), q.data_ptr(), qd, nq_g, nact_g, n_loc, nact_l, first, cache.num_tokens,
+                last_valid, self._step, push_meta, ws.out.data_ptr(), _lib.current_stream(self.device)),
+                "cqa_sharded_layer_step")
+        if not collect_stats:
+            return ws.out, {}
+        cert, flags = ws.read_cert()
+        return ws.out, {"cert": cert, "flags": flags, "peer_status": self.peer_status()}
+
     def step(self, q_all: torch.Tensor, q_scale: float | None = None, *, v_tolerance: float,
              top_k_fp16_keys: int = 4, ranking_fallback: bool = True, ranking_r: int = 1,
              ranking_fallback_mode: str = "full", tau_cov: float = 0.995, k_min: int = 2, k_max: int | None = 128,
@@ -204,6 +307,16 @@ class ShardedCertifiedLayer:
             raise RuntimeError("local cache and global token count disagree")
         ws = self.ws
         desc_l = cache._desc(G)
+        if self.exchange == "peer":
+            return self._step_peer(q, qd, q_scale, nq_g, nact_g, n_loc, first, is_last, collect_stats,
+                                   exploration_uniforms, dict(
+                                       tau_cov=tau_cov, k_min=k_min, k_max=k_max, rung1_threshold=rung1_threshold,
+                                       rung1_multiplier=rung1_multiplier, eps_guard=eps_guard,
+                                       exploration_rate=exploration_rate, v_tolerance=v_tolerance, ranking_r=ranking_r,
+                                       top_k_fp16_keys=top_k_fp16_keys, ranking_fallback=ranking_fallback,
+                                       ranking_fallback_mode=ranking_fallback_mode,
+                                       score_consistency_check=score_consistency_check,
+                                       value_error_mode=value_error_mode))
 
         with _lib.on_device(self.device):
             # 1. Phase 1 straight into the send buffer (rows 0..H-1 m_b, H..2H-1 S_b)
@@ -217,8 +330,6 @@ class ShardedCertifiedLayer:
                 self.send[2 * H + KV, : KV * 128].copy_(cache.keys_scale_max.reshape(-1))
             # 2. Exchange A and the global selector
             self.comm.all_gather(self.recv, self.send)
-            if fresh_meta:
-                torch.amax(self.recv[:, self._rows - 1, : KV * 128], dim=0, out=self.sigma)
             self._meta_nq = nq_g
             knobs = _make_knobs(
                 q_scale=q_scale, tau_cov=tau_cov, k_min=k_min, k_max=k_max, rung1_threshold=rung1_threshold,
@@ -239,7 +350,7 @@ class ShardedCertifiedLayer:
             desc_g = cache._desc_copy(G)
             desc_g.max_blocks = plan.ld
             desc_g.values_int4_errors = self._p_recv_eta
-            desc_g.sigma_max = self.sigma.data_ptr()
+            desc_g.sigma_max = self._p_recv_sigma      # one row per rank: the kernel takes the maximum
             u_ptr, u_ld, u_keep = None, 0, None
             if exploration_rate > 0.0:
                 if exploration_uniforms is not None:

@@ -185,7 +185,20 @@ typedef struct cqa_workspace {
     int64_t shard_chunk;
     int64_t shard_rank_stride;
     int32_t shard_ranks;
+    int32_t given_ranks;         /* > 1: given_fp16 holds one [H][32][2] array per rank, given_rank_stride floats
+                                    apart; the kernel adds them (only the owner of a block contributes non-zero) */
+    int64_t given_rank_stride;
+    /* With shard_ranks > 0, cqa_cache.sigma_max points at rank 0's row of per-channel scale maxima inside the
+     * exchange buffer and the kernel takes the maximum over the ranks' rows (shard_rank_stride apart). */
+    /* Peer exchange (cqa_sharded_layer_step): before reading exchanged data the kernel waits, with a bounded
+     * spin, until wait_flags[i] >= wait_value for every i < wait_n except i == wait_skip; on a timeout it sets
+     * *wait_status to a non-zero code and carries on (the step's result is then invalid, the GPU stays usable). */
+    const int32_t *wait_flags;
+    int32_t wait_n;
+    int32_t wait_skip;
+    int32_t wait_value;
     int32_t reserved2;
+    int32_t *wait_status;
 } cqa_workspace;
 
 #define CQA_PARTIAL_STRIDE 130
@@ -341,6 +354,50 @@ int cqa_certify_given(const cqa_cache *c, const cqa_knobs *knobs, const cqa_work
                       int q_dtype, int64_t nq, int64_t nact, void *stream);
 /* Log-sum-exp merge of n_parts partial rows per head ([n_parts][H][CQA_PARTIAL_STRIDE]) into out[H][128]. */
 int cqa_merge_partials(const float *parts, int n_parts, int n_heads, float *out, void *stream);
+
+/* ---- peer-memory exchange for the sharded step (one node, up to 8 GPUs) ----
+ * Every rank allocates one buffer (cqa_peer_alloc), exports it (cqa_peer_export), the 64-byte handles are exchanged by
+ * the host (e.g. torch.distributed all_gather_object) and opened (cqa_peer_import).  Ranks then PUSH their slices into
+ * every peer's buffer with plain stores followed by a system-scope release of a per-(exchange, source) flag word;
+ * consumers wait on their LOCAL flag words.  No rank ever loads from a peer, no collective library is involved, and
+ * every wait is bounded.  Layout of a rank's buffer (floats unless noted), both parities of a step back to back:
+ *   xa [2][world][rows][chunk]    Exchange A: m_b rows, S_b rows, eta rows, one row of scale maxima
+ *   xb [2][world][H][32][2]       Exchange B: FP16 re-scores of the top list
+ *   xc [2][world][H][130]         Exchange C: un-normalised Phase-2 partials
+ *   flags int32 [3][world], status int32 [4], tickets int32 [3][world]
+ */
+#define CQA_MAX_PEERS 8
+typedef struct cqa_peers {
+    int32_t world, rank;
+    int32_t rows;                /* 2H + KV + 1 */
+    int32_t n_heads;
+    int64_t chunk;               /* columns per row of xa */
+    void *base[CQA_MAX_PEERS];   /* every rank's buffer as seen from this process (base[rank] = own) */
+} cqa_peers;
+
+int64_t cqa_peer_buffer_bytes(int world, int n_heads, int kv_heads, int64_t chunk);
+int cqa_peer_alloc(int64_t bytes, void **ptr);
+int cqa_peer_free(void *ptr);
+int cqa_peer_export(void *ptr, unsigned char handle[64]);
+int cqa_peer_import(const unsigned char handle[64], void **ptr);
+int cqa_peer_close(void *ptr);
+/* Wait status of this rank's buffer (0 = no bounded wait has timed out; 100 + i = the flag of source rank i did
+ * not arrive in time).  Synchronises with the device; `reset` clears it. */
+int cqa_peer_status(const cqa_peers *peers, int32_t *status_out, int reset);
+
+/* One sharded layer step with peer-memory exchanges: local Phase 1, push A, global selector (waits for A),
+ * owner re-scores pushed to every rank (B), flags (waits for B), local Phase 2, push C, merge (waits for C).
+ * `local` is the rank's cache; `global_view` the same descriptor with max_blocks = the global leading dimension
+ * (its values_int4_errors and sigma_max are replaced by pointers into the exchange buffer); `wg` is the workspace
+ * for the global selector (masks, certificate), `wl` the one for the local Phase 2 (mask pointers offset to the
+ * rank's first block).  `step` counts calls from 1 and must be the same on every rank; `push_meta` != 0 when a
+ * block completed since the previous call (eta rows and scale maxima are re-sent).  *status is set non-zero if a
+ * wait timed out.  No reference counterpart. */
+int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *global_view, const cqa_knobs *knobs,
+                           const cqa_workspace *wg, const cqa_workspace *wl, const cqa_peers *peers, const void *q,
+                           int q_dtype, int64_t nq_global, int64_t nact_global, int64_t n_local, int64_t nact_local,
+                           int64_t first_block, int64_t num_tokens_local, int last_valid, int64_t step, int push_meta,
+                           float *out, void *stream);
 
 /* ---- bounded hot tier (reference: ensure_fp16_{keys,values}_resident, _page_in_fp16_blocks,
  * _prepare_bounded_fp16_key_scratch - tiered_kv_cache.py:986-1537; backends/cuda_pagein.*) ----

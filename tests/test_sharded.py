@@ -226,7 +226,7 @@ def test_sharded_step_matches_unsharded(world, knobs):
 
 # ----------------------------------------------------------------------------- CUDA, real ranks over NCCL
 
-def _nccl_rank(rank, world, port, ret):
+def _nccl_rank(rank, world, port, ret, exchange="collective"):
     import sys
     from pathlib import Path
 
@@ -251,18 +251,24 @@ def _nccl_rank(rank, world, port, ret):
         lo, hi = plan.prefill_token_range()
         with torch.cuda.device(rank):
             cache = hz.make_cuda_cache(base.k[:, lo:hi], base.v[:, lo:hi], dtype, 64 if rank == plan.last else 0)
-            layer = ShardedCertifiedLayer(plan, cache, G)
+            layer = ShardedCertifiedLayer(plan, cache, G, exchange=exchange)
             rng = np.random.default_rng(33)
             outs, ks = [], []
             for s in range(4):
                 q, knew, vnew = synth.decode_step_inputs(base, s, dtype=dtype)
                 layer.append_token(hz.to_dev(knew, dtype).cuda(rank), hz.to_dev(vnew, dtype).cuda(rank))
                 u = rng.random((H, layer.nq), dtype=np.float32)
-                out, st = layer.step(hz.to_dev(q, dtype).cuda(rank), None, exploration_uniforms=torch.from_numpy(u),
-                                     collect_stats=True, **kn)
+                if exchange == "peer":
+                    kn["exploration_rate"] = 0.0
+                    out, st = layer.step(hz.to_dev(q, dtype).cuda(rank), None, collect_stats=True, **kn)
+                    assert st["peer_status"] == 0, f"rank {rank}: a bounded wait timed out ({st['peer_status']})"
+                else:
+                    out, st = layer.step(hz.to_dev(q, dtype).cuda(rank), None,
+                                         exploration_uniforms=torch.from_numpy(u), collect_stats=True, **kn)
                 torch.cuda.synchronize()
                 outs.append(out.cpu().numpy().copy())
                 ks.append(st["cert"]["k_star"].copy())
+            layer.close()
         if rank == 0:
             ret.put((outs, ks))
     finally:
@@ -270,7 +276,8 @@ def _nccl_rank(rank, world, port, ret):
 
 
 @pytest.mark.gpu
-def test_sharded_step_over_nccl():
+@pytest.mark.parametrize("exchange", ["collective", "peer"])
+def test_sharded_step_over_nccl(exchange):
     """Two (or four) real ranks over NCCL against the one-GPU run.  Skipped on a one-GPU box."""
     import cuda_harness as hz
 
@@ -281,7 +288,7 @@ def test_sharded_step_over_nccl():
     ctx = mp.get_context("spawn")
     ret = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, ret, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     outs, ks = ret.get()
@@ -296,7 +303,10 @@ def test_sharded_step_over_nccl():
         q, knew, vnew = synth.decode_step_inputs(base, s, dtype=dtype)
         cc.append_token(hz.to_dev(knew, dtype), hz.to_dev(vnew, dtype))
         u = rng.random((H, cc.num_quantized_blocks), dtype=np.float32)
-        out, stats = hz.cuda_step(cc, q, dtype, G, dict(gc.PAPER_KNOBS), u)
+        knobs = dict(gc.PAPER_KNOBS)
+        if exchange == "peer":
+            knobs["exploration_rate"] = 0.0
+        out, stats = hz.cuda_step(cc, q, dtype, G, knobs, u)
         cert, _ = cc._certified_workspace["cqa_ws"].read_cert()
         assert np.array_equal(cert["k_star"], ks[s])
         err = np.abs(out - outs[s]).max() / max(np.abs(out).max(), 1e-6)
