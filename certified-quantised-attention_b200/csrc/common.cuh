@@ -330,13 +330,14 @@ __device__ __forceinline__ void st_release_sys(int32_t *p, int v)
 // Called by every thread of a CTA before it reads exchanged data: thread 0 waits until flags[i] >= value for every
 // i < n except `skip` (bounded: about half a second), then the CTA synchronises.  A timeout is recorded in *status.
 constexpr int PEER_WAIT_SPINS = 2000000;
-__device__ __forceinline__ void peer_wait(const int32_t *flags, int n, int skip, int value, int32_t *status)
+__device__ __forceinline__ void peer_wait(const int32_t *flags, int n, int skip, int value, int32_t *status,
+                                          long stride = 1)
 {
     if (flags != nullptr && threadIdx.x == 0) {
         for (int i = 0; i < n; ++i) {
             if (i == skip) continue;
             int spins = 0;
-            while (ld_acquire_sys(flags + i) < value) {
+            while (ld_acquire_sys(flags + i * stride) < value) {
                 if (++spins > PEER_WAIT_SPINS) {
                     if (status) atomicExch(status, 100 + i);
                     break;

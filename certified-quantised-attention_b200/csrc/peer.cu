@@ -8,7 +8,10 @@
 // Buffer layout (all ranks identical; two parities so that step s+1 never overwrites what a slower rank still reads
 // from step s):
 //   xa [2][world][rows][chunk] f32 | xb [2][world][H][32][2] f32 | xc [2][world][H][130] f32 |
-//   flags [3][world] i32 | status [4] i32 | tickets [3][world] i32
+//   flags [3][world] i32 | flags_b [world][H] i32 | status [4] i32 | tickets [3][world] i32
+#include <cstdio>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "rescore.cuh"
 
@@ -23,7 +26,7 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
 
 struct PeerLayout {
     long xa_parity, xb_parity, xc_parity;      // floats per parity
-    long xa, xb, xc, flags, status, tickets;   // offsets in 4-byte words
+    long xa, xb, xc, flags, flags_b, status, tickets;   // offsets in 4-byte words
     long words;
     int world, rows, H;
     long chunk;
@@ -40,7 +43,8 @@ __host__ __device__ inline PeerLayout peer_layout(int world, int H, int rows, lo
     L.xb = L.xa + 2 * L.xa_parity;
     L.xc = L.xb + 2 * L.xb_parity;
     L.flags = L.xc + 2 * L.xc_parity;
-    L.status = L.flags + 3 * world;
+    L.flags_b = L.flags + 3 * world;          // [source rank][head]: Exchange B is per head
+    L.status = L.flags_b + (long)world * H;
     L.tickets = L.status + 4;
     L.words = L.tickets + 3 * world;
     return L;
@@ -53,7 +57,7 @@ struct PeerArgs {
 
 // Copy `n_rows` rows (row r has cols(r) floats, at src + r*src_ld) into every peer's buffer at dst_off + r*dst_ld,
 // then release flag word `flag_word` (value `step`) on that peer.  Grid (world, PUSH_CTAS): blockIdx.x = peer.
-constexpr int PUSH_CTAS = 8, PUSH_THREADS = 256;
+constexpr int PUSH_CTAS = 16, PUSH_THREADS = 256;
 __device__ __forceinline__ void push_row(const float *src, float *dst, long cols)
 {
     if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
@@ -83,49 +87,16 @@ __global__ void __launch_bounds__(PUSH_THREADS) peer_push_kernel(PeerArgs pa, co
         if (dst_off_alt >= 0 && r >= alt_first_row)
             push_row(src + (long)r * src_ld, pa.base[peer] + dst_off_alt + (long)r * dst_ld, cols);
     }
-    // last CTA for this peer: everything above is visible system-wide before the flag is
-    __threadfence_system();
+    // One thread per CTA fences after the CTA barrier (the barrier orders the other threads' stores before it); the
+    // last CTA for this peer then releases the flag, so everything above is visible there before the flag is.
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         int32_t *tick = reinterpret_cast<int32_t *>(pa.base[pa.rank]) + ticket_word + peer;
         const int t = atomicAdd(tick, 1);
         if (t == PUSH_CTAS - 1) {
             *tick = 0;
-            __threadfence_system();
             st_release_sys(reinterpret_cast<int32_t *>(pa.base[peer]) + flag_word, step);
-        }
-    }
-}
-
-// Exchange B: one warp per (top-list slot, head) re-scores the block if this rank owns it and writes (score, log-mass)
-// or zeros into every rank's xb slot of this rank; the last warp releases the flags.
-template <typename T2>
-__global__ void __launch_bounds__(32) rescore_push_kernel(cqa_cache c, const cqa_head_cert *cert, const void *q,
-                                                         int q_dtype, long first_block, long n_local, float q_scale,
-                                                         PeerArgs pa, long xb_off, long flag_word, long ticket_word,
-                                                         int step)
-{
-    const int h = blockIdx.y, i = blockIdx.x;
-    const long b = (long)cert[h].top_blocks[i] - first_block;
-    float s = 0.0f, lm = 0.0f;
-    if (cert[h].top_blocks[i] >= 0 && b >= 0 && b < n_local)
-        fp16_block_score_warp<T2>(c, q, q_dtype, h, b, n_local * BS, q_scale, s, lm);
-    const long o = xb_off + ((long)h * CQA_MAX_RANKING_K + i) * 2;
-    if (threadIdx.x < pa.world) {
-        float *d = pa.base[threadIdx.x] + o;
-        d[0] = s;
-        d[1] = lm;
-    }
-    __threadfence_system();
-    __syncwarp();
-    if (threadIdx.x == 0) {
-        int32_t *tick = reinterpret_cast<int32_t *>(pa.base[pa.rank]) + ticket_word;
-        const int t = atomicAdd(tick, 1);
-        if (t == (int)(gridDim.x * gridDim.y) - 1) {
-            *tick = 0;
-            __threadfence_system();
-            for (int p = 0; p < pa.world; ++p)
-                if (p != pa.rank) st_release_sys(reinterpret_cast<int32_t *>(pa.base[p]) + flag_word, step);
         }
     }
 }
@@ -206,6 +177,48 @@ extern "C" int cqa_peer_status(const cqa_peers *peers, int32_t *status_out, int 
     return rc;
 }
 
+// Optional stage timing (environment variable CQA_SHARDED_TIMING=1): CUDA events between the stages of the step,
+// averaged and printed to stderr every 32 steps.  Off by default; when on, every step ends with a stream wait.
+namespace {
+struct StageTimer {
+    bool on = false;
+    cudaEvent_t ev[10];
+    double acc[9] = {0};
+    int n = 0, k = 0;
+    StageTimer()
+    {
+        const char *e = getenv("CQA_SHARDED_TIMING");
+        on = e && e[0] == '1';
+    }
+    void mark(cudaStream_t st)
+    {
+        if (!on) return;
+        if (n == 0 && k == 0)
+            for (auto &x : ev) cudaEventCreate(&x);
+        cudaEventRecord(ev[k++], st);
+    }
+    void finish(cudaStream_t st, int rank)
+    {
+        if (!on) return;
+        cudaStreamSynchronize(st);
+        for (int i = 0; i + 1 < k; ++i) {
+            float ms = 0;
+            cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+            acc[i] += ms * 1e3;
+        }
+        const int stages = k - 1;
+        k = 0;
+        if (++n % 32 == 0) {
+            fprintf(stderr, "[cqa sharded rank %d] us per stage:", rank);
+            static const char *names[] = {"score", "pushA", "select+certify", "attend", "pushC", "merge"};
+            for (int i = 0; i < stages; ++i) { fprintf(stderr, " %s %.1f", names[i], acc[i] / 32); acc[i] = 0; }
+            fprintf(stderr, "\n");
+        }
+    }
+};
+StageTimer g_timer;
+}  // namespace
+
 extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *global_view, const cqa_knobs *knobs,
                                       const cqa_workspace *wg, const cqa_workspace *wl, const cqa_peers *peers,
                                       const void *q, int q_dtype, int64_t nq_global, int64_t nact_global,
@@ -243,6 +256,7 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     float *xc_par = own + L.xc + par * L.xc_parity;
     float *xc_own = xc_par + (long)R * H * CQA_PARTIAL_STRIDE;
 
+    g_timer.mark(st);
     // 1. Phase 1 on the local blocks, straight into this rank's slot of xa
     int rc = score_blocks_launch(local, q, q_dtype, n_local, knobs->q_scale, xa_own, xa_own + (long)H * peers->chunk,
                                  peers->chunk, wl->token_scores, st, nullptr, 0);
@@ -257,6 +271,7 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
                                         cudaMemcpyDeviceToDevice, st), "copy of scale maxima");
         if (rc) return rc;
     }
+    g_timer.mark(st);
     // 2. push A: the 2H score rows every step; eta rows and scale maxima only when they changed.  The other parity's
     // meta rows are refreshed too, so both parities always hold the latest.
     {
@@ -274,7 +289,10 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
             if (rc) return rc;
         }
     }
-    // 3. the global selector, value check and top list on the exchanged arrays (waits for every rank's A)
+    g_timer.mark(st);
+    // 3. the global selector and certificate on the exchanged arrays, one launch: it waits for every rank's A; the
+    // ranking-check CTA of each head re-scores the top-list blocks this rank owns, pushes them to every rank, waits
+    // for the other ranks' rows (Exchange B, per head) and raises the flags
     cqa_workspace g = *wg;
     g.m_b = xa_par;
     g.s_b = xa_par + (long)H * peers->chunk;
@@ -287,32 +305,24 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     g.wait_value = (int)step;
     g.wait_status = own_i + L.status;
     g.partial_out = nullptr;
+    g.given_fp16 = own + L.xb + par * L.xb_parity;
+    g.given_ranks = W;
+    g.given_rank_stride = (long)H * CQA_MAX_RANKING_K * 2;
+    for (int p = 0; p < CQA_MAX_PEERS; ++p) {
+        g.peer_xb[p] = p < W ? pa.base[p] + xb_off : nullptr;
+        g.peer_flags_b[p] = p < W ? reinterpret_cast<int32_t *>(pa.base[p]) + L.flags_b : nullptr;
+    }
+    g.peer_first_block = first_block;
+    g.peer_n_local = n_local;
+    g.peer_world = W;
+    g.peer_rank = R;
+    g.peer_step = (int)step;
     cqa_cache gv = *global_view;
     gv.values_int4_errors = xa_par + 2L * H * peers->chunk;
     gv.sigma_max = xa_par + (2L * H + KV) * peers->chunk;
-    rc = selcert_launch(&gv, knobs, &g, nullptr, CQA_F32, nq_global, nact_global, nullptr, 0, 1 | 2 | 4, st);
+    rc = selcert_launch(&gv, knobs, &g, q, q_dtype, nq_global, nact_global, nullptr, 0, 1 | 2 | 64, st);
     if (rc) return rc;
-    // 4. owners re-score the top list and push the results to every rank (B)
-    const bool need_fp16 = knobs->ranking_fallback || knobs->score_consistency;
-    if (need_fp16) {
-        dim3 grid(CQA_MAX_RANKING_K, (unsigned)H);
-        const long fw = L.flags + 1 * W + R, tw = L.tickets + 1 * W;
-        switch (local->t2_dtype) {
-        case CQA_F32: rescore_push_kernel<float><<<grid, 32, 0, st>>>(*local, g.cert, q, q_dtype, first_block, n_local, knobs->q_scale, pa, xb_off, fw, tw, (int)step); break;
-        case CQA_F16: rescore_push_kernel<__half><<<grid, 32, 0, st>>>(*local, g.cert, q, q_dtype, first_block, n_local, knobs->q_scale, pa, xb_off, fw, tw, (int)step); break;
-        case CQA_BF16: rescore_push_kernel<__nv_bfloat16><<<grid, 32, 0, st>>>(*local, g.cert, q, q_dtype, first_block, n_local, knobs->q_scale, pa, xb_off, fw, tw, (int)step); break;
-        default: set_error("cqa_sharded_layer_step: unknown Tier-2 dtype"); return CQA_ERR_INVALID;
-        }
-        g.wait_flags = own_i + L.flags + 1 * W;
-        g.given_fp16 = own + L.xb + par * L.xb_parity;
-        g.given_ranks = W;
-        g.given_rank_stride = (long)H * CQA_MAX_RANKING_K * 2;
-    } else {
-        g.wait_flags = nullptr;
-    }
-    // 5. ranking / boundary / consistency flags (waits for every rank's B)
-    rc = selcert_launch(&gv, knobs, &g, q, q_dtype, nq_global, nact_global, nullptr, 0, 2 | 8, st);
-    if (rc) return rc;
+    g_timer.mark(st);
     // 6. Phase 2 over the local blocks; un-normalised partial rows go to this rank's slot of xc
     cqa_workspace l = *wl;
     l.m_b = xa_own;
@@ -323,6 +333,7 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     l.wait_flags = nullptr;
     rc = attend_launch(local, &l, q, q_dtype, n_local, nact_local, num_tokens_local, last_valid, knobs->q_scale, st, false);
     if (rc) return rc;
+    g_timer.mark(st);
     // 7. push C and merge (waits for every rank's C)
     {
         dim3 grid(W, PUSH_CTAS);
@@ -331,6 +342,9 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
                                                         H, H, row, row, row, L.flags + 2 * W + R, L.tickets + 2 * W,
                                                         (int)step, -1L, 0);
     }
+    g_timer.mark(st);
     merge_wait_kernel<<<H, D, 0, st>>>(xc_par, W, H, out, own_i + L.flags + 2 * W, R, (int)step, own_i + L.status);
+    g_timer.mark(st);
+    g_timer.finish(st, R);
     return check_launch("sharded step kernels");
 }

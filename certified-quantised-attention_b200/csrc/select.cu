@@ -31,6 +31,7 @@ constexpr int PH_SELECT = 1, PH_CERTIFY = 2;
 // own the blocks (ws.given_fp16) and runs role 1 alone.
 constexpr int PH_TOP_ONLY = 4, PH_GIVEN = 8;
 constexpr int PH_FLAGS_CLEARED = 16;   // the caller already zeroed ws.any_flags on this stream
+constexpr int PH_PEER_B = 64;          // role 1 exchanges the FP16 re-scores with the other ranks itself (ws.peer_*)
 
 typedef unsigned long long u64;
 
@@ -724,8 +725,20 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
         const int ub_first = rk + 1, ub_warps = SC_WARPS - ub_first;
         const bool overlap = ub_warps >= 8;
         float ubm = -INFINITY;
+        const bool peer_b = (phases & PH_PEER_B) != 0;
         if (warp < rk) {
-            if (!given) {
+            if (peer_b) {
+                // re-score the block if this rank owns it (local block ids), zeros otherwise; every rank gets the row
+                const long bl = (long)top_idx[warp] - ws.peer_first_block;
+                float s = 0.0f, lm = 0.0f;
+                if (bl >= 0 && bl < ws.peer_n_local)
+                    fp16_block_score_warp<T2>(c, q, q_dtype, h, bl, ws.peer_n_local * BS, kn.q_scale, s, lm);
+                if (lane < ws.peer_world) {
+                    float *d = ws.peer_xb[lane] + ((long)h * CQA_MAX_RANKING_K + warp) * 2;
+                    d[0] = s;
+                    d[1] = lm;
+                }
+            } else if (!given) {
                 float s, lm;
                 fp16_block_score_warp<T2>(c, q, q_dtype, h, (long)top_idx[warp], nq * BS, kn.q_scale, s, lm);
                 if (lane == 0) { top_f16[warp] = s; top_lm[warp] = lm; }
@@ -745,6 +758,28 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             if (lane == 0) sh.red_f[warp] = ubm;
         }
         __syncthreads();
+        if (peer_b) {
+            // publish this rank's rows of head h, then wait (bounded) for the other ranks' rows and add them up
+            if (tid == 0) {
+                __threadfence_system();
+                for (int p = 0; p < ws.peer_world; ++p)
+                    if (p != ws.peer_rank)
+                        st_release_sys(ws.peer_flags_b[p] + (long)ws.peer_rank * gridDim.x + h, ws.peer_step);
+            }
+            peer_wait(ws.peer_flags_b[ws.peer_rank] + h, ws.peer_world, ws.peer_rank, ws.peer_step, ws.wait_status,
+                      (long)gridDim.x);
+            if (tid < rk) {
+                float gs = 0.0f, gl = 0.0f;
+                for (int r = 0; r < ws.peer_world; ++r) {
+                    const float *g = ws.given_fp16 + r * ws.given_rank_stride + ((long)h * CQA_MAX_RANKING_K + tid) * 2;
+                    gs = __fadd_rn(gs, __ldcg(g));
+                    gl = __fadd_rn(gl, __ldcg(g + 1));
+                }
+                top_f16[tid] = gs;
+                top_lm[tid] = gl;
+            }
+            __syncthreads();
+        }
         CQA_CLK(7);
         const float delta = s_delta;
         float ub = -INFINITY;
@@ -1035,6 +1070,10 @@ int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace 
     if (phases & PH_CERTIFY) {
         const bool need_fp16 = kn->ranking_fallback || kn->score_consistency;
         const bool local_keys = !(phases & (PH_TOP_ONLY | PH_GIVEN));
+        if ((phases & PH_PEER_B) && (ws->peer_world < 2 || ws->peer_world > 8 || !ws->given_fp16 || ws->peer_step < 1)) {
+            set_error("selector: incomplete peer description for the in-kernel exchange");
+            return CQA_ERR_INVALID;
+        }
         if (need_fp16 && local_keys && (!c->keys_t2 || !c->sigma_max || !q)) {
             set_error("cqa_certify: ranking / consistency checks need q, Tier-2 keys and sigma_max");
             return CQA_ERR_INVALID;

@@ -199,6 +199,18 @@ typedef struct cqa_workspace {
     int32_t wait_value;
     int32_t reserved2;
     int32_t *wait_status;
+    /* Exchange B inside the selector (cqa_sharded_layer_step): the ranking-check CTA of a head re-scores the
+     * top-list blocks this rank owns ([peer_first_block, +peer_n_local), local block ids), writes (score, log-mass)
+     * into every rank's buffer at peer_xb[r], releases peer_flags_b[r][peer_rank * H + head] = peer_step, waits
+     * (bounded) for the other ranks' flags in its own buffer and carries on to the flags.  peer_world = 0: off. */
+    float *peer_xb[8];
+    int32_t *peer_flags_b[8];
+    int64_t peer_first_block;
+    int64_t peer_n_local;
+    int32_t peer_world;
+    int32_t peer_rank;
+    int32_t peer_step;
+    int32_t reserved3;
 } cqa_workspace;
 
 #define CQA_PARTIAL_STRIDE 130
@@ -364,7 +376,7 @@ int cqa_merge_partials(const float *parts, int n_parts, int n_heads, float *out,
  *   xa [2][world][rows][chunk]    Exchange A: m_b rows, S_b rows, eta rows, one row of scale maxima
  *   xb [2][world][H][32][2]       Exchange B: FP16 re-scores of the top list
  *   xc [2][world][H][130]         Exchange C: un-normalised Phase-2 partials
- *   flags int32 [3][world], status int32 [4], tickets int32 [3][world]
+ *   flags int32 [3][world], flags_b int32 [world][H], status int32 [4], tickets int32 [3][world]
  */
 #define CQA_MAX_PEERS 8
 typedef struct cqa_peers {
@@ -386,7 +398,7 @@ int cqa_peer_close(void *ptr);
 int cqa_peer_status(const cqa_peers *peers, int32_t *status_out, int reset);
 
 /* One sharded layer step with peer-memory exchanges: local Phase 1, push A, global selector (waits for A),
- * owner re-scores pushed to every rank (B), flags (waits for B), local Phase 2, push C, merge (waits for C).
+ * owner re-scores pushed to every rank and awaited inside the same kernel (B), local Phase 2, push C, merge (waits for C).
  * `local` is the rank's cache; `global_view` the same descriptor with max_blocks = the global leading dimension
  * (its values_int4_errors and sigma_max are replaced by pointers into the exchange buffer); `wg` is the workspace
  * for the global selector (masks, certificate), `wl` the one for the local Phase 2 (mask pointers offset to the
