@@ -26,7 +26,8 @@ int check_cuda(cudaError_t e, const char *what)
 int check_launch(const char *what) { return check_cuda(cudaGetLastError(), what); }
 
 int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
-                        float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words);
+                        float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words,
+                        const ScorePush *push);
 int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq, long nact,
                   const float *u, long u_ld, cudaStream_t st);
 int certify_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
@@ -219,7 +220,7 @@ extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const 
     if (!ws->token_scores) { set_error("cqa_layer_step: token_scores missing"); return CQA_ERR_INVALID; }
     const int n_flag_words = 5 + c->kv_heads * c->gqa_group;
     rc = score_blocks_launch(c, q, q_dtype, nq, knobs->q_scale, ws->m_b, ws->s_b, ws->ld, ws->token_scores, st,
-                             ws->any_flags, n_flag_words);
+                             ws->any_flags, n_flag_words, nullptr);
     if (rc) return rc;
     if (!(knobs->tau_cov > 0.0f)) { set_error("cqa_layer_step: tau_cov must be positive"); return CQA_ERR_INVALID; }
     if (!ws->value_mask) { set_error("cqa_layer_step: value_mask missing"); return CQA_ERR_INVALID; }

@@ -327,6 +327,16 @@ __device__ __forceinline__ void st_release_sys(int32_t *p, int v)
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Exchange A from inside the score kernel: every (head, block) result is also stored into the other ranks' buffers,
+// and the last CTA to finish releases the flags.  world == 0: off.
+struct ScorePush {
+    float *mb[8];        // each rank's rows for this rank's m_b (same leading dimension as the local rows)
+    float *sb[8];
+    int32_t *flag[8];    // flag word to release on each rank
+    int32_t *ticket;     // local counter
+    int world, rank, step;
+};
+
 // Called by every thread of a CTA before it reads exchanged data: thread 0 waits until flags[i] >= value for every
 // i < n except `skip` (bounded: about half a second), then the CTA synchronises.  A timeout is recorded in *status.
 constexpr int PEER_WAIT_SPINS = 2000000;

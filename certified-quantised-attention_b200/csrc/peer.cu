@@ -18,7 +18,8 @@
 namespace cqa {
 
 int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
-                        float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words);
+                        float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words,
+                        const ScorePush *push);
 int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
                    long nq, long nact, const float *u, long u_ld, int phases, cudaStream_t st);
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
@@ -96,6 +97,7 @@ __global__ void __launch_bounds__(PUSH_THREADS) peer_push_kernel(PeerArgs pa, co
         const int t = atomicAdd(tick, 1);
         if (t == PUSH_CTAS - 1) {
             *tick = 0;
+            __threadfence_system();   // acquire side of the ticket chain: the other CTAs' fenced stores come first
             st_release_sys(reinterpret_cast<int32_t *>(pa.base[peer]) + flag_word, step);
         }
     }
@@ -257,12 +259,28 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     float *xc_own = xc_par + (long)R * H * CQA_PARTIAL_STRIDE;
 
     g_timer.mark(st);
-    // 1. Phase 1 on the local blocks, straight into this rank's slot of xa
+    // 1. Phase 1 on the local blocks, straight into this rank's slot of xa.  On ordinary steps the kernel also stores
+    // every result into the other ranks' buffers and its last CTA releases the Exchange-A flags; when eta rows and
+    // scale maxima changed (a block completed) the rows go out together through the push kernel instead.
+    ScorePush sp = {};
+    if (!push_meta) {
+        const long row0 = L.xa + par * L.xa_parity + (long)R * slot;
+        for (int p = 0; p < W; ++p) {
+            sp.mb[p] = pa.base[p] + row0;
+            sp.sb[p] = pa.base[p] + row0 + (long)H * peers->chunk;
+            sp.flag[p] = reinterpret_cast<int32_t *>(pa.base[p]) + L.flags + 0 * W + R;
+        }
+        sp.ticket = own_i + L.tickets + 0 * W + R;
+        sp.world = W;
+        sp.rank = R;
+        sp.step = (int)step;
+    }
     int rc = score_blocks_launch(local, q, q_dtype, n_local, knobs->q_scale, xa_own, xa_own + (long)H * peers->chunk,
-                                 peers->chunk, wl->token_scores, st, nullptr, 0);
+                                 peers->chunk, wl->token_scores, st, nullptr, 0, push_meta ? nullptr : &sp);
     if (rc) return rc;
+    g_timer.mark(st);
     if (push_meta) {
-        // eta rows and the row of scale maxima follow the 2H score rows
+        // eta rows and the row of scale maxima follow the 2H score rows; both parities get them
         rc = check_cuda(cudaMemcpy2DAsync(xa_own + 2L * H * peers->chunk, peers->chunk * 4, local->values_int4_errors,
                                           local->max_blocks * 4, (size_t)n_local * 4, KV, cudaMemcpyDeviceToDevice, st),
                         "copy of eta rows");
@@ -270,24 +288,15 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
         rc = check_cuda(cudaMemcpyAsync(xa_own + (2L * H + KV) * peers->chunk, local->sigma_max, (size_t)KV * D * 4,
                                         cudaMemcpyDeviceToDevice, st), "copy of scale maxima");
         if (rc) return rc;
-    }
-    g_timer.mark(st);
-    // 2. push A: the 2H score rows every step; eta rows and scale maxima only when they changed.  The other parity's
-    // meta rows are refreshed too, so both parities always hold the latest.
-    {
-        const int n_rows = push_meta ? peers->rows : 2 * H;
         dim3 grid(W, PUSH_CTAS);
         peer_push_kernel<<<grid, PUSH_THREADS, 0, st>>>(pa, xa_own, peers->chunk, L.xa + par * L.xa_parity + (long)R * slot,
-                                                        peers->chunk, n_rows, 2 * H, n_local, n_local, (long)KV * D,
+                                                        peers->chunk, peers->rows, 2 * H, n_local, n_local, (long)KV * D,
                                                         L.flags + 0 * W + R, L.tickets + 0 * W, (int)step,
-                                                        push_meta ? L.xa + (par ^ 1) * L.xa_parity + (long)R * slot : -1L,
-                                                        2 * H);
-        if (push_meta) {
-            float *other = own + L.xa + (par ^ 1) * L.xa_parity + (long)R * slot + 2L * H * peers->chunk;
-            rc = check_cuda(cudaMemcpyAsync(other, xa_own + 2L * H * peers->chunk, (size_t)(KV + 1) * peers->chunk * 4,
-                                            cudaMemcpyDeviceToDevice, st), "copy of meta rows to the other parity");
-            if (rc) return rc;
-        }
+                                                        L.xa + (par ^ 1) * L.xa_parity + (long)R * slot, 2 * H);
+        float *other = own + L.xa + (par ^ 1) * L.xa_parity + (long)R * slot + 2L * H * peers->chunk;
+        rc = check_cuda(cudaMemcpyAsync(other, xa_own + 2L * H * peers->chunk, (size_t)(KV + 1) * peers->chunk * 4,
+                                        cudaMemcpyDeviceToDevice, st), "copy of meta rows to the other parity");
+        if (rc) return rc;
     }
     g_timer.mark(st);
     // 3. the global selector and certificate on the exchanged arrays, one launch: it waits for every rank's A; the

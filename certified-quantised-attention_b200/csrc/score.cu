@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
                                                                           long nq, float q_scale, float *m_b,
                                                                           float *s_b, long ld, float *tok,
                                                                           int blocks_per_cta, int32_t *zero_words,
-                                                                          int n_zero_words)
+                                                                          int n_zero_words, ScorePush push)
 {
     extern __shared__ __align__(16) char smem[];
     constexpr int GH = G >= 4 ? 4 : G;  // heads per register pass
@@ -177,12 +177,31 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
                         const long o = (long)(kv * G + gg) * ld + b;
                         m_b[o] = mx;
                         s_b[o] = ssum;
+                        for (int p = 0; p < push.world; ++p) {
+                            if (p == push.rank) continue;
+                            push.mb[p][o] = mx;
+                            push.sb[p][o] = ssum;
+                        }
                     }
                 }
             }
         }
         __syncwarp();
         stage ^= 1;
+    }
+    if (push.world > 0) {
+        // the last CTA of the grid tells every rank that this rank's rows have landed
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            const int t = atomicAdd(push.ticket, 1);
+            if (t == (int)(gridDim.x * gridDim.y) - 1) {
+                *push.ticket = 0;
+                __threadfence_system();   // acquire side of the ticket chain: the other CTAs' fenced stores come first
+                for (int p = 0; p < push.world; ++p)
+                    if (p != push.rank) st_release_sys(push.flag[p], push.step);
+            }
+        }
     }
 }
 
@@ -226,7 +245,7 @@ __global__ void __launch_bounds__(32) delta_bound_kernel(cqa_cache c, const void
 template <int G>
 static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
                           float *s_b, long ld, float *tok, dim3 grid, int bpc, int32_t *zero_words, int n_zero_words,
-                          cudaStream_t st)
+                          const ScorePush &push, cudaStream_t st)
 {
     constexpr int SMEM = SCORE_SMEM + G * D * 4;
     static bool attr_set = false;
@@ -238,7 +257,7 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
         attr_set = true;
     }
     return check_cuda(launch_chained(score_blocks_kernel<G>, grid, dim3(SCORE_WARPS * 32), SMEM, st, true, *c, q, q_dtype,
-                                     nq, q_scale, m_b, s_b, ld, tok, bpc, zero_words, n_zero_words),
+                                     nq, q_scale, m_b, s_b, ld, tok, bpc, zero_words, n_zero_words, push),
                       "score_blocks_kernel");
 }
 
@@ -257,8 +276,11 @@ int rescore_owned_launch(const cqa_cache *c, const cqa_head_cert *cert, const vo
 }
 
 int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
-                        float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words)
+                        float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words,
+                        const ScorePush *push_in)
 {
+    ScorePush push = {};
+    if (push_in) push = *push_in;
     static int sm_count = 0;
     if (sm_count == 0) {
         int dev = 0;
@@ -273,10 +295,10 @@ int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq,
     if (bpc < 2) bpc = 2;
     dim3 grid((unsigned)((nq + bpc - 1) / bpc), (unsigned)c->kv_heads);
     switch (c->gqa_group) {
-    case 1: return score_launch_g<1>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, st);
-    case 2: return score_launch_g<2>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, st);
-    case 4: return score_launch_g<4>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, st);
-    case 8: return score_launch_g<8>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, st);
+    case 1: return score_launch_g<1>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, push, st);
+    case 2: return score_launch_g<2>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, push, st);
+    case 4: return score_launch_g<4>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, push, st);
+    case 8: return score_launch_g<8>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, grid, (int)bpc, zero_words, n_zero_words, push, st);
     }
     set_error("score_blocks: unsupported gqa_group %d", c->gqa_group);
     return CQA_ERR_UNSUPPORTED;
@@ -300,7 +322,8 @@ extern "C" int cqa_score_blocks(const cqa_cache *c, const void *q, int q_dtype, 
         return CQA_ERR_INVALID;
     }
     if (q_dtype < 0 || q_dtype > 2) { set_error("cqa_score_blocks: unknown q dtype"); return CQA_ERR_INVALID; }
-    return score_blocks_launch(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, token_scores, (cudaStream_t)stream, nullptr, 0);
+    return score_blocks_launch(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, token_scores, (cudaStream_t)stream, nullptr, 0,
+                               nullptr);
 }
 
 extern "C" int cqa_fp16_block_scores(const cqa_cache *c, const void *q, int q_dtype, const int32_t *idx, int K,
