@@ -189,9 +189,10 @@ __device__ __forceinline__ void cta_merge_store(float (&m)[G], float (&l)[G], fl
 // one warp per head turns them into per-split scales while those loads are still travelling; the rows are then
 // scaled and summed, the per-thread sums combined through shared memory, normalised and written.
 __device__ __forceinline__ void final_merge(const float *pm, const float *pl, const float *pa, int ns, int head0,
-                                            int nh, const cqa_workspace &ws, bool dense_role, float *sm)
+                                            int nh, const cqa_workspace &ws, bool dense_role, float *sm, int n_heads_total)
 {
     constexpr int BATCH = 20;
+    const bool push_c = ws.partial_out != nullptr && ws.peer_world > 0 && ws.peer_partial[0] != nullptr;
     float *s_m = sm, *s_sc = sm + nh * ns, *s_l = s_sc + nh * ns;
     float *s_part = sm + ((2 * nh * ns + nh + 3) & ~3);  // 16-byte aligned for float4 stores
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -228,8 +229,15 @@ __device__ __forceinline__ void final_merge(const float *pm, const float *pl, co
                 const int h = head0 + warp;
                 const bool flagged = ws.cert != nullptr && (ws.cert[h].dense || ws.any_flags[2]);
                 if (flagged == dense_role) {
-                    ws.partial_out[(long)h * CQA_PARTIAL_STRIDE] = M;
-                    ws.partial_out[(long)h * CQA_PARTIAL_STRIDE + 1] = lsum;
+                    if (push_c) {
+                        for (int p = 0; p < ws.peer_world; ++p) {
+                            ws.peer_partial[p][(long)h * CQA_PARTIAL_STRIDE] = M;
+                            ws.peer_partial[p][(long)h * CQA_PARTIAL_STRIDE + 1] = lsum;
+                        }
+                    } else {
+                        ws.partial_out[(long)h * CQA_PARTIAL_STRIDE] = M;
+                        ws.partial_out[(long)h * CQA_PARTIAL_STRIDE + 1] = lsum;
+                    }
                 }
             }
         }
@@ -265,13 +273,32 @@ __device__ __forceinline__ void final_merge(const float *pm, const float *pl, co
         float acc = 0.0f;
         for (int p = 0; p < nparts; ++p) acc += s_part[(gg * nparts + p) * D + ch];
         if (ws.partial_out != nullptr) {
-            ws.partial_out[(long)h * CQA_PARTIAL_STRIDE + 2 + ch] = acc;   // un-normalised: merged across ranks later
+            // un-normalised: merged across ranks later
+            if (push_c) {
+                for (int p = 0; p < ws.peer_world; ++p) ws.peer_partial[p][(long)h * CQA_PARTIAL_STRIDE + 2 + ch] = acc;
+            } else {
+                ws.partial_out[(long)h * CQA_PARTIAL_STRIDE + 2 + ch] = acc;
+            }
             continue;
         }
         const float l = s_l[gg];
         ws.out[(long)h * D + ch] = acc / (l > 0.0f ? l : 1.0f);
     }
     __syncthreads();
+    if (push_c && tid == 0) {
+        // Exchange C: one arrival per KV head (regular merges) plus one per densely recomputed head; the last one
+        // tells every rank that this rank's partial rows have landed
+        __threadfence_system();
+        int expected = (int)gridDim.y;
+        if (ws.dense_splits > 0 && ws.cert != nullptr) expected += ws.any_flags[2] ? n_heads_total : ws.any_flags[4];
+        const int t = atomicAdd(ws.peer_ticket_c, 1);
+        if (t == expected - 1) {
+            *ws.peer_ticket_c = 0;
+            __threadfence_system();
+            for (int p = 0; p < ws.peer_world; ++p)
+                if (p != ws.peer_rank) st_release_sys(ws.peer_flag_c[p], ws.peer_step);
+        }
+    }
 }
 
 // Returns true in every thread of the CTA that took the last ticket.
@@ -361,7 +388,8 @@ __device__ void dense_unit(const cqa_cache &c, const cqa_workspace &ws, const vo
     __syncthreads();
     cta_merge_store<1>(m, l, acc, sm_m, sm_l, sm_acc, ws.dense_m, ws.dense_l, ws.dense_acc, h, chunk, ds);
     if (take_ticket(ws.tickets + c.kv_heads + h, ds, s_flag))
-        final_merge(ws.dense_m, ws.dense_l, ws.dense_acc, ds, h, 1, ws, true, reinterpret_cast<float *>(smem_raw));
+        final_merge(ws.dense_m, ws.dense_l, ws.dense_acc, ds, h, 1, ws, true, reinterpret_cast<float *>(smem_raw),
+                    c.kv_heads * c.gqa_group);
 }
 
 constexpr int DENSE_POOL_X = 8;  // dense-recompute CTAs per KV row of the grid
@@ -650,7 +678,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa
     float *sm_acc = sm_l + ATT_WARPS * G;
     cta_merge_store<G>(m, l, acc, sm_m, sm_l, sm_acc, ws.part_m, ws.part_l, ws.part_acc, kv * G, split, ns);
     if (take_ticket(ws.tickets + kv, ns, &s_flag))
-        final_merge(ws.part_m, ws.part_l, ws.part_acc, ns, kv * G, G, ws, false, reinterpret_cast<float *>(ring));
+        final_merge(ws.part_m, ws.part_l, ws.part_acc, ns, kv * G, G, ws, false, reinterpret_cast<float *>(ring),
+                    c.kv_heads * G);
 }
 
 template <int G>

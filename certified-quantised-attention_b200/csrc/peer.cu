@@ -212,7 +212,7 @@ struct StageTimer {
         k = 0;
         if (++n % 32 == 0) {
             fprintf(stderr, "[cqa sharded rank %d] us per stage:", rank);
-            static const char *names[] = {"score", "pushA", "select+certify", "attend", "pushC", "merge"};
+            static const char *names[] = {"score", "pushA", "select+certify", "attend", "-", "merge"};
             for (int i = 0; i < stages; ++i) { fprintf(stderr, " %s %.1f", names[i], acc[i] / 32); acc[i] = 0; }
             fprintf(stderr, "\n");
         }
@@ -340,17 +340,20 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     l.shard_chunk = peers->chunk;
     l.partial_out = xc_own;
     l.wait_flags = nullptr;
+    // Exchange C is written by Phase 2 itself: its final merges store the partial rows into every rank's buffer and
+    // the last of them releases the flags
+    const long xc_slot = L.xc + par * L.xc_parity + (long)R * H * CQA_PARTIAL_STRIDE;
+    for (int p = 0; p < CQA_MAX_PEERS; ++p) {
+        l.peer_partial[p] = p < W ? pa.base[p] + xc_slot : nullptr;
+        l.peer_flag_c[p] = p < W ? reinterpret_cast<int32_t *>(pa.base[p]) + L.flags + 2 * W + R : nullptr;
+    }
+    l.peer_ticket_c = own_i + L.tickets + 2 * W + R;
+    l.peer_world = W;
+    l.peer_rank = R;
+    l.peer_step = (int)step;
     rc = attend_launch(local, &l, q, q_dtype, n_local, nact_local, num_tokens_local, last_valid, knobs->q_scale, st, false);
     if (rc) return rc;
     g_timer.mark(st);
-    // 7. push C and merge (waits for every rank's C)
-    {
-        dim3 grid(W, PUSH_CTAS);
-        const long row = CQA_PARTIAL_STRIDE;
-        peer_push_kernel<<<grid, PUSH_THREADS, 0, st>>>(pa, xc_own, row, L.xc + par * L.xc_parity + (long)R * H * row, row,
-                                                        H, H, row, row, row, L.flags + 2 * W + R, L.tickets + 2 * W,
-                                                        (int)step, -1L, 0);
-    }
     g_timer.mark(st);
     merge_wait_kernel<<<H, D, 0, st>>>(xc_par, W, H, out, own_i + L.flags + 2 * W, R, (int)step, own_i + L.status);
     g_timer.mark(st);

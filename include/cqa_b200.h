@@ -205,6 +205,12 @@ typedef struct cqa_workspace {
      * (bounded) for the other ranks' flags in its own buffer and carries on to the flags.  peer_world = 0: off. */
     float *peer_xb[8];
     int32_t *peer_flags_b[8];
+    /* Exchange C from inside cqa_attend: with peer_partial[r] set (r < peer_world), the un-normalised partial rows
+     * are written into every rank's buffer (peer_partial[peer_rank] is this rank's own slot and replaces
+     * partial_out), and the last merge of the launch releases *peer_flag_c[r] = peer_step on the other ranks. */
+    float *peer_partial[8];
+    int32_t *peer_flag_c[8];
+    int32_t *peer_ticket_c;
     int64_t peer_first_block;
     int64_t peer_n_local;
     int32_t peer_world;
