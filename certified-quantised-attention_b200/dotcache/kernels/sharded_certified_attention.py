@@ -24,9 +24,12 @@ range of 16-token blocks.  One layer step:
   5. Exchange C (all-gather) and the log-sum-exp merge (cqa_merge_partials).
 
 New tokens go to the last rank (it owns the tail of the sequence).
-The exchanges are plain torch.distributed collectives (NCCL on GPUs); the
-packing helpers below are device-agnostic so the host logic can be exercised
-with the gloo backend on CPU tensors.
+Two transports carry the exchanges: torch.distributed collectives (NCCL on
+GPUs; the default, `exchange="collective"`), or pushes into the other ranks'
+buffers over NVLink with bounded waits on local flags, all inside one library
+call per step (`exchange="peer"`, cqa_sharded_layer_step).  The plan and index
+helpers below are device-agnostic so the host logic can be exercised with the
+gloo backend on CPU tensors.
 """
 from __future__ import annotations
 
