@@ -276,7 +276,7 @@ def run_case(name: str, spec: dict, ref_mods) -> dict:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (read only)")
     ap.add_argument("--cases", default="small_fp32,small_vtol0,planted_bf16_append,planted_fp16_g2")
     ap.add_argument("--out", default=str(HERE))
     args = ap.parse_args()
