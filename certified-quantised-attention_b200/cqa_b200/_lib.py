@@ -21,7 +21,7 @@ SYMBOLS = [
     "cqa_score_blocks", "cqa_select", "cqa_fp16_block_scores", "cqa_delta_bound", "cqa_certify",
     "cqa_attend", "cqa_attend_static", "cqa_layer_step", "cqa_suggest_splits",
     "cqa_select_certify_local", "cqa_rescore_owned", "cqa_certify_given", "cqa_merge_partials",
-    "cqa_decode_step_host", "cqa_hot_tier_update",
+    "cqa_decode_step_host", "cqa_decode_step_host_async", "cqa_decode_token_host", "cqa_hot_tier_update",
     "cqa_peer_buffer_bytes", "cqa_peer_alloc", "cqa_peer_free", "cqa_peer_export", "cqa_peer_import", "cqa_peer_close",
     "cqa_sharded_layer_step", "cqa_peer_status",
 ]
@@ -115,6 +115,13 @@ class CqaHotTier(C.Structure):
     ]
 
 
+class CqaLayerCall(C.Structure):
+    _fields_ = [
+        ("cache", vp), ("ws", vp), ("qkv_host", vp), ("out_host", vp),
+        ("pos", C.c_int64), ("defer_int4", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 CERT_BYTES = C.sizeof(CqaHeadCert)
 
 _lib = None
@@ -160,6 +167,8 @@ def lib() -> C.CDLL:
     L.cqa_certify_given.argtypes = [pc, pk, pw, vp, i32, i64, i64, vp]
     L.cqa_merge_partials.argtypes = [vp, i32, i32, vp, vp]
     L.cqa_decode_step_host.argtypes = [pc, pk, pw, vp, vp, i32, i64, i32, vp, vp]
+    L.cqa_decode_step_host_async.argtypes = [pc, pk, pw, vp, vp, i32, i64, i32, vp, vp]
+    L.cqa_decode_token_host.argtypes = [C.POINTER(CqaLayerCall), i32, pk, vp, i32, vp]
     L.cqa_hot_tier_update.argtypes = [pc, pw, C.POINTER(CqaHotTier), i64, vp]
     L.cqa_peer_buffer_bytes.argtypes = [i32, i32, i32, i64]
     L.cqa_peer_alloc.argtypes = [i64, C.POINTER(vp)]

@@ -106,9 +106,9 @@ extern "C" int cqa_certify(const cqa_cache *c, const cqa_knobs *knobs, const cqa
     return certify_launch(c, knobs, ws, q, q_dtype, nq, nact, (cudaStream_t)stream);
 }
 
-extern "C" int cqa_decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws,
-                                    const void *qkv_host, void *qkv_dev, int dtype, int64_t pos, int defer_int4,
-                                    float *out_host, void *stream)
+static int decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *qkv_host,
+                            void *qkv_dev, int dtype, int64_t pos, int defer_int4, float *out_host, void *stream,
+                            bool wait)
 {
     if (!c || !knobs || !ws || !qkv_host || !qkv_dev || !out_host) {
         set_error("cqa_decode_step_host: NULL pointer");
@@ -130,7 +130,81 @@ extern "C" int cqa_decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, 
     rc = cqa_layer_step(c, knobs, ws, q, dtype, num_tokens, num_tokens / BS, nullptr, 0, stream);
     if (rc) return rc;
     rc = check_cuda(cudaMemcpyAsync(out_host, ws->out, H * D * sizeof(float), cudaMemcpyDeviceToHost, st), "copy of the output");
-    if (rc) return rc;
+    if (rc || !wait) return rc;
+    return check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+}
+
+extern "C" int cqa_decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws,
+                                    const void *qkv_host, void *qkv_dev, int dtype, int64_t pos, int defer_int4,
+                                    float *out_host, void *stream)
+{
+    return decode_step_host(c, knobs, ws, qkv_host, qkv_dev, dtype, pos, defer_int4, out_host, stream, true);
+}
+
+extern "C" int cqa_decode_step_host_async(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws,
+                                          const void *qkv_host, void *qkv_dev, int dtype, int64_t pos, int defer_int4,
+                                          float *out_host, void *stream)
+{
+    return decode_step_host(c, knobs, ws, qkv_host, qkv_dev, dtype, pos, defer_int4, out_host, stream, false);
+}
+
+extern "C" int cqa_decode_token_host(const cqa_layer_call *layers, int n_layers, const cqa_knobs *knobs, void *qkv_dev,
+                                     int dtype, void *stream)
+{
+    if (!layers || n_layers <= 0 || !knobs || !qkv_dev) {
+        set_error("cqa_decode_token_host: no layers, knobs or staging buffer");
+        return CQA_ERR_INVALID;
+    }
+    if (dtype < 0 || dtype > 2) { set_error("cqa_decode_token_host: unknown dtype"); return CQA_ERR_INVALID; }
+    for (int l = 0; l < n_layers; ++l) {
+        const cqa_layer_call &c = layers[l];
+        if (!c.cache || !c.ws || !c.qkv_host || !c.out_host || !c.ws->out) {
+            set_error("cqa_decode_token_host: layer %d has a NULL pointer", l);
+            return CQA_ERR_INVALID;
+        }
+        if (c.cache->kv_heads != layers[0].cache->kv_heads || c.cache->gqa_group != layers[0].cache->gqa_group) {
+            set_error("cqa_decode_token_host: layer %d has another head geometry than layer 0", l);
+            return CQA_ERR_INVALID;
+        }
+    }
+    const size_t esz = dtype == CQA_F32 ? 4 : 2;
+    const size_t H = (size_t)layers[0].cache->kv_heads * layers[0].cache->gqa_group, KV = (size_t)layers[0].cache->kv_heads;
+    const size_t row = (H + 2 * KV) * D * esz;
+    cudaStream_t st = (cudaStream_t)stream;
+    char *dev = static_cast<char *>(qkv_dev);
+    // every layer's inputs first (host rows that follow one another go in one transfer), so that no transfer
+    // sits between two layers' kernels
+    for (int l = 0; l < n_layers;) {
+        int r = l + 1;
+        while (r < n_layers &&
+               static_cast<const char *>(layers[r].qkv_host) == static_cast<const char *>(layers[l].qkv_host) + (size_t)(r - l) * row)
+            ++r;
+        const int rc = check_cuda(cudaMemcpyAsync(dev + (size_t)l * row, layers[l].qkv_host, (size_t)(r - l) * row,
+                                                  cudaMemcpyHostToDevice, st), "copy of step inputs");
+        if (rc) return rc;
+        l = r;
+    }
+    for (int l = 0; l < n_layers; ++l) {
+        const cqa_layer_call &c = layers[l];
+        // Phase 2 writes its rows straight into the caller's pinned buffer when the driver maps it for the device
+        cqa_workspace w = *c.ws;
+        void *mapped = nullptr;
+        if (cudaHostGetDevicePointer(&mapped, c.out_host, 0) == cudaSuccess && mapped != nullptr)
+            w.out = static_cast<float *>(mapped);
+        else
+            (void)cudaGetLastError();
+        const char *in = dev + (size_t)l * row;
+        int rc = cqa_append_token(c.cache, in + H * D * esz, in + (H + KV) * D * esz, dtype, c.pos, c.defer_int4, stream);
+        if (rc) return rc;
+        const int64_t num_tokens = c.pos + 1;
+        rc = cqa_layer_step(c.cache, knobs, &w, in, dtype, num_tokens, num_tokens / BS, nullptr, 0, stream);
+        if (rc) return rc;
+        if (w.out == c.ws->out) {
+            rc = check_cuda(cudaMemcpyAsync(c.out_host, c.ws->out, H * D * sizeof(float), cudaMemcpyDeviceToHost, st),
+                            "copy of the output");
+            if (rc) return rc;
+        }
+    }
     return check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
 }
 

@@ -254,12 +254,15 @@ def certified_decode_step_host(
     eps_guard: float = 0.01,
     exploration_rate: float = 0.0,
     value_error_mode: str = "tight",
+    wait: bool = True,
 ) -> torch.Tensor:
     """`cache.append_token(k, v)` followed by `certified_attention_layer(cache, q, ...)` for a caller whose step
     inputs live in host memory, as ONE library call (cqa_decode_step_host): `qkv_host` is a pinned 1-D tensor
     [q (H*128) | k_new (KV*128) | v_new (KV*128)] in the cache's model dtype, `out_host` a pinned float32 [H, 128]
     tensor that holds the attention output when the call returns.  An addition (no reference counterpart): it
-    removes the interpreter from between the copies and the launches; results equal the two-call sequence."""
+    removes the interpreter from between the copies and the launches; results equal the two-call sequence.
+    With `wait=False` the work is only queued on the current stream (cqa_decode_step_host_async): a decoder calls
+    it once per layer, each with its own `qkv_host` and `out_host`, and synchronises the stream once per token."""
     H = cache.kv_heads * int(gqa_group)
     n_in = (H + 2 * cache.kv_heads) * cache.head_dim
     if qkv_host.is_cuda or out_host.is_cuda:
@@ -297,7 +300,8 @@ def certified_decode_step_host(
         ws.rng_calls += 1
     stage = ws.step_input_buffer(n_in, qkv_host.dtype, device)
     with _lib.on_device(device):
-        _lib.check(_lib.lib().cqa_decode_step_host(
+        entry = _lib.lib().cqa_decode_step_host if wait else _lib.lib().cqa_decode_step_host_async
+        _lib.check(entry(
             C.byref(cache._desc(G)), C.byref(knobs), C.byref(wstruct), qkv_host.data_ptr(), stage.data_ptr(),
             _lib.dtype_code(qkv_host.dtype), pos, 1 if cache._defers_int4() else 0, out_host.data_ptr(),
             _lib.current_stream(device)), "cqa_decode_step_host")
@@ -305,6 +309,117 @@ def certified_decode_step_host(
             cache._hot_tier_update(cache._desc(G), wstruct, (pos + 1 + cache.block_size - 1) // cache.block_size,
                                    _lib.current_stream(device))
     cache._advance_after_append(pos)
+    return out_host
+
+
+def certified_decode_token_host(
+    caches,
+    qkv_host: torch.Tensor,
+    gqa_group: int,
+    out_host: torch.Tensor,
+    q_scale: float | None = None,
+    *,
+    v_tolerance: float,
+    top_k_fp16_keys: int = 4,
+    ranking_fallback: bool = True,
+    ranking_r: int = 1,
+    ranking_fallback_mode: str = "full",
+    tau_cov: float = 0.995,
+    k_min: int = DEFAULT_K_MIN,
+    k_max: int | None = DEFAULT_K_MAX,
+    rung1_threshold: float = DEFAULT_RUNG1_THRESHOLD,
+    rung1_multiplier: float = DEFAULT_RUNG1_MULTIPLIER,
+    score_consistency_check: bool = False,
+    eps_guard: float = 0.01,
+    exploration_rate: float = 0.0,
+    value_error_mode: str = "tight",
+) -> torch.Tensor:
+    """`certified_decode_step_host` for every layer of a model in ONE library call (cqa_decode_token_host):
+    `caches` is the list of the layers' caches, `qkv_host` a pinned [L, (H + 2 KV) * 128] tensor, `out_host` a
+    pinned float32 [L, H, 128] tensor that holds every layer's attention rows when the call returns.  The loop over
+    the layers runs inside the library, all inputs are copied before the first kernel, Phase 2 writes into `out_host`
+    directly when it is pinned, and the stream is waited for once.  Row l equals what
+    `certified_decode_step_host(caches[l], qkv_host[l], ...)` returns.  An addition (no reference counterpart)."""
+    n_layers = len(caches)
+    if n_layers == 0:
+        raise ValueError("certified_decode_token_host needs at least one layer cache")
+    first = caches[0]
+    G = int(gqa_group)
+    H = first.kv_heads * G
+    n_in = (H + 2 * first.kv_heads) * first.head_dim
+    if qkv_host.is_cuda or out_host.is_cuda:
+        raise ValueError("certified_decode_token_host takes host tensors (pinned for asynchronous copies)")
+    if qkv_host.numel() != n_layers * n_in or not qkv_host.is_contiguous():
+        raise ValueError(f"qkv_host must be a contiguous [{n_layers}, {n_in}] tensor")
+    if (out_host.dtype != torch.float32 or out_host.numel() != n_layers * H * first.head_dim
+            or not out_host.is_contiguous()):
+        raise ValueError(f"out_host must be a contiguous float32 [{n_layers}, {H}, {first.head_dim}] tensor")
+    device = first.keys_int8.device
+    if q_scale is None:
+        q_scale = 1.0 / (first.head_dim ** 0.5)
+    knobs = _make_knobs(
+        q_scale=q_scale, tau_cov=tau_cov, k_min=k_min, k_max=k_max, rung1_threshold=rung1_threshold,
+        rung1_multiplier=rung1_multiplier, eps_guard=eps_guard, exploration_rate=exploration_rate,
+        v_tolerance=v_tolerance, ranking_r=ranking_r, top_k_fp16_keys=top_k_fp16_keys,
+        ranking_fallback=ranking_fallback, ranking_fallback_mode=ranking_fallback_mode,
+        score_consistency_check=score_consistency_check, value_error_mode=value_error_mode,
+        force_trailing_value_fp16=True,
+    )
+    # the array of per-layer call records is kept on the first cache and rebuilt when the set of layers changes
+    key = (tuple(id(c) for c in caches), G)
+    plan = getattr(first, "_decode_token_plan", None)
+    if plan is not None and any(c._certified_workspace.get("cqa_ws") is not w for c, w in zip(caches, plan[2])):
+        plan = None   # a layer's workspace was replaced since the records were built
+    if plan is None or plan[0] != key:
+        calls = (_lib.CqaLayerCall * n_layers)()
+        spaces = []
+        for l, cache in enumerate(caches):
+            if (cache.kv_heads, cache.head_dim, cache.keys_int8.device) != (first.kv_heads, first.head_dim, device):
+                raise ValueError("all layer caches must share geometry and device")
+            ws = _workspace(cache, H, G, device)
+            spaces.append(ws)
+            calls[l].cache = C.addressof(cache._desc(G))
+            calls[l].ws = C.addressof(ws.struct)
+        plan = (key, calls, spaces, torch.empty(n_layers * n_in, dtype=qkv_host.dtype, device=device))
+        first._decode_token_plan = plan
+    _, calls, spaces, stage = plan
+    if stage.dtype != qkv_host.dtype:
+        raise ValueError("qkv_host changed dtype between calls")
+    block = first.block_size
+    esz = qkv_host.element_size()
+    qkv_base, out_base = qkv_host.data_ptr(), out_host.data_ptr()
+    for l, cache in enumerate(caches):
+        pos = cache.num_tokens
+        if pos >= cache.keys_int8.shape[1]:
+            raise ValueError(f"cache capacity {cache.keys_int8.shape[1]} exhausted")
+        nq = (pos + 1) // block
+        if nq <= 0:
+            raise NotImplementedError("the certified path needs at least one complete block")
+        ws = spaces[l]
+        ws.ensure_sel_width(_selection_width(k_max, rung1_threshold, rung1_multiplier, nq), device)
+        wstruct = ws.fill_struct((pos + block) // block)
+        if exploration_rate > 0.0:
+            if ws.rng_seed is None:
+                ws.rng_seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
+            wstruct.rng_seed = ws.rng_seed
+            wstruct.rng_offset = ws.rng_calls
+            ws.rng_calls += 1
+        call = calls[l]
+        call.cache = C.addressof(cache._desc(G))
+        call.qkv_host = qkv_base + l * n_in * esz
+        call.out_host = out_base + l * H * first.head_dim * 4
+        call.pos = pos
+        call.defer_int4 = 1 if cache._defers_int4() else 0
+    stream = _lib.current_stream(device)
+    with _lib.on_device(device):
+        _lib.check(_lib.lib().cqa_decode_token_host(calls, n_layers, C.byref(knobs), stage.data_ptr(),
+                                                    _lib.dtype_code(qkv_host.dtype), stream), "cqa_decode_token_host")
+        for l, cache in enumerate(caches):
+            if cache.bounded_hot_tier:
+                ws = spaces[l]
+                cache._hot_tier_update(cache._desc(G), ws.struct, (calls[l].pos + block) // block, stream)
+    for l, cache in enumerate(caches):
+        cache._advance_after_append(calls[l].pos)
     return out_host
 
 

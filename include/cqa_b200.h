@@ -351,6 +351,35 @@ int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspa
 int cqa_decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *qkv_host,
                          void *qkv_dev, int dtype, int64_t pos, int defer_int4, float *out_host, void *stream);
 
+/* The same work queued on `stream` without the final wait: a decoder calls it once per
+ * layer and waits on the stream once per token, so the copies and launches of layer l+1
+ * are queued while layer l runs.  qkv_host and out_host must stay untouched until the
+ * caller has waited on the stream; qkv_dev and the workspace may be shared by the layers
+ * (stream order protects them). */
+int cqa_decode_step_host_async(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws,
+                               const void *qkv_host, void *qkv_dev, int dtype, int64_t pos, int defer_int4,
+                               float *out_host, void *stream);
+
+/* One decode token of a whole model from host buffers: the inputs of all n_layers entries are
+ * copied to the device first (qkv_dev holds n_layers rows of (H + 2 KV) * 128 elements), then
+ * each layer's append and layer step are queued in order, then ONE wait on the stream.  When
+ * out_host is pinned memory that the device can address, Phase 2 writes the rows into it
+ * directly (ws->out of that layer is then left untouched); otherwise they are copied.  No
+ * transfer sits between two layers' kernels, and the loop over the layers runs inside the
+ * library.  knobs and dtype are shared by the layers; all caches share the head geometry. */
+typedef struct cqa_layer_call {
+    const cqa_cache *cache;
+    const cqa_workspace *ws;
+    const void *qkv_host; /* [q | k_new | v_new] of this layer, pinned host memory */
+    float *out_host;      /* [H, 128] float32, pinned host memory */
+    int64_t pos;          /* tokens already in this layer's cache */
+    int32_t defer_int4;
+    int32_t reserved;
+} cqa_layer_call;
+
+int cqa_decode_token_host(const cqa_layer_call *layers, int n_layers, const cqa_knobs *knobs, void *qkv_dev, int dtype,
+                          void *stream);
+
 /* ---- sequence sharding: every rank owns a contiguous range of blocks ----
  * The reference runs one cache per process; these entry points let P ranks that each
  * hold the blocks [first_block, first_block + n_local) of one long sequence reproduce

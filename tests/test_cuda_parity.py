@@ -254,6 +254,46 @@ def test_decode_step_from_host_buffers_equals_two_calls():
         assert torch.equal(getattr(ca_a, name), getattr(ca_b, name)), name
 
 
+def test_decode_step_async_layers_one_wait_per_token():
+    """cqa_decode_step_host_async queued for three layer caches and waited for once, and cqa_decode_token_host
+    (the loop over the layers inside the library), give each layer the rows of the waiting entry point (stream
+    order alone protects the shared staging and the copies)."""
+    from dotcache.kernels import certified_attention as ca
+
+    dtype = "bfloat16"
+    knobs = _knobs(exploration_rate=0.0)
+    bases = [synth.make_layer_inputs(31 + l, 4096, dtype=dtype, n_planted_blocks=8) for l in range(3)]
+    sync_caches = [hz.make_cuda_cache(b.k, b.v, dtype, 64) for b in bases]
+    async_caches = [hz.make_cuda_cache(b.k, b.v, dtype, 64) for b in bases]
+    token_caches = [hz.make_cuda_cache(b.k, b.v, dtype, 64) for b in bases]
+    n_in = (32 + 16) * 128
+    qkv = torch.empty(3, n_in, dtype=torch.bfloat16).pin_memory()
+    out_sync = torch.empty(3, 32, 128, dtype=torch.float32).pin_memory()
+    out_async = torch.empty(3, 32, 128, dtype=torch.float32).pin_memory()
+    out_token = torch.empty(3, 32, 128, dtype=torch.float32).pin_memory()
+    for step in range(18):
+        for l, b in enumerate(bases):
+            q, kn, vn = synth.decode_step_inputs(b, step, dtype=dtype)
+            qkv[l, : 32 * 128] = torch.from_numpy(q).to(torch.bfloat16).reshape(-1)
+            qkv[l, 32 * 128: 40 * 128] = torch.from_numpy(kn).to(torch.bfloat16).reshape(-1)
+            qkv[l, 40 * 128:] = torch.from_numpy(vn).to(torch.bfloat16).reshape(-1)
+        out_async.fill_(float("nan"))
+        for l in range(3):
+            ca.certified_decode_step_host(async_caches[l], qkv[l], 4, out_async[l], wait=False, **knobs)
+        torch.cuda.current_stream().synchronize()
+        for l in range(3):
+            ca.certified_decode_step_host(sync_caches[l], qkv[l], 4, out_sync[l], **knobs)
+        assert np.array_equal(out_async.numpy(), out_sync.numpy()), f"step {step}"
+        # the same token through the one-call-per-token entry point
+        out_token.fill_(float("nan"))
+        ca.certified_decode_token_host(token_caches, qkv, 4, out_token, **knobs)
+        assert np.array_equal(out_token.numpy(), out_sync.numpy()), f"token call, step {step}"
+    for a, b, c in zip(async_caches, sync_caches, token_caches):
+        assert a.num_tokens == b.num_tokens == c.num_tokens
+        assert torch.equal(a.keys_int8, b.keys_int8) and torch.equal(c.keys_int8, b.keys_int8)
+        assert torch.equal(c.values_int4_packed, b.values_int4_packed)
+
+
 def test_in_kernel_exploration_draw():
     """Without uniforms or a generator the selector draws its own: the rate is respected, the draw is a function
     of torch's seed and the per-cache call counter only, and explored blocks are never blocks the selector chose."""
