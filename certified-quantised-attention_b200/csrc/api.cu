@@ -127,9 +127,17 @@ static int decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, const cq
     rc = cqa_append_token(c, k_new, v_new, dtype, pos, defer_int4, stream);
     if (rc) return rc;
     const int64_t num_tokens = pos + 1;
-    rc = cqa_layer_step(c, knobs, ws, q, dtype, num_tokens, num_tokens / BS, nullptr, 0, stream);
+    // Phase 2 writes its rows straight into the caller's buffer when it is pinned memory the device can address
+    cqa_workspace w = *ws;
+    void *mapped = nullptr;
+    if (cudaHostGetDevicePointer(&mapped, out_host, 0) == cudaSuccess && mapped != nullptr)
+        w.out = static_cast<float *>(mapped);
+    else
+        (void)cudaGetLastError();
+    rc = cqa_layer_step(c, knobs, &w, q, dtype, num_tokens, num_tokens / BS, nullptr, 0, stream);
     if (rc) return rc;
-    rc = check_cuda(cudaMemcpyAsync(out_host, ws->out, H * D * sizeof(float), cudaMemcpyDeviceToHost, st), "copy of the output");
+    if (w.out == ws->out)
+        rc = check_cuda(cudaMemcpyAsync(out_host, ws->out, H * D * sizeof(float), cudaMemcpyDeviceToHost, st), "copy of the output");
     if (rc || !wait) return rc;
     return check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
 }

@@ -343,9 +343,10 @@ int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspa
 /* One decode step of one layer from HOST buffers: copies the packed step inputs
  * [q (H*128) | k_new (KV*128) | v_new (KV*128)] (elements of `dtype`) from `qkv_host`
  * to the device scratch `qkv_dev` (same size), appends the token at position `pos`
- * (cqa_append_token), runs cqa_layer_step on the pos+1 tokens, copies the H*128 float32
- * output rows to `out_host` and waits for the stream.  Pinned host buffers make the two
- * copies asynchronous DMA transfers.  An addition with no reference counterpart: it is
+ * (cqa_append_token), runs cqa_layer_step on the pos+1 tokens with the H*128 float32
+ * output rows going to `out_host`, and waits for the stream.  A pinned `qkv_host` makes the
+ * input copy an asynchronous DMA transfer; a pinned `out_host` is written by Phase 2
+ * directly (ws->out is then left untouched), any other is filled by a copy from ws->out.  An addition with no reference counterpart: it is
  * cqa_append_token + cqa_layer_step for a caller that holds its activations on the host,
  * in one call (no interpreter between the launches). */
 int cqa_decode_step_host(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, const void *qkv_host,
