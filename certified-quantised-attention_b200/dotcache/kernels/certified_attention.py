@@ -386,19 +386,31 @@ def certified_decode_token_host(
     if stage.dtype != qkv_host.dtype:
         raise ValueError("qkv_host changed dtype between calls")
     block = first.block_size
-    esz = qkv_host.element_size()
+    in_bytes = n_in * qkv_host.element_size()
+    out_bytes = H * first.head_dim * 4
     qkv_base, out_base = qkv_host.data_ptr(), out_host.data_ptr()
+    explore = exploration_rate > 0.0
+    last_pos, width = -1, 0
+    positions = []
     for l, cache in enumerate(caches):
         pos = cache.num_tokens
-        if pos >= cache.keys_int8.shape[1]:
+        if pos != last_pos:   # layers of one model normally hold the same number of tokens
+            if pos >= cache.keys_int8.shape[1]:
+                raise ValueError(f"cache capacity {cache.keys_int8.shape[1]} exhausted")
+            nq = (pos + 1) // block
+            if nq <= 0:
+                raise NotImplementedError("the certified path needs at least one complete block")
+            width = _selection_width(k_max, rung1_threshold, rung1_multiplier, nq)
+            nblocks = (pos + block) // block
+            last_pos = pos
+        elif pos >= cache.keys_int8.shape[1]:
             raise ValueError(f"cache capacity {cache.keys_int8.shape[1]} exhausted")
-        nq = (pos + 1) // block
-        if nq <= 0:
-            raise NotImplementedError("the certified path needs at least one complete block")
+        positions.append(pos)
         ws = spaces[l]
-        ws.ensure_sel_width(_selection_width(k_max, rung1_threshold, rung1_multiplier, nq), device)
-        wstruct = ws.fill_struct((pos + block) // block)
-        if exploration_rate > 0.0:
+        if ws.sel_width < width:
+            ws.ensure_sel_width(width, device)
+        wstruct = ws.fill_struct(nblocks)
+        if explore:
             if ws.rng_seed is None:
                 ws.rng_seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
             wstruct.rng_seed = ws.rng_seed
@@ -406,8 +418,8 @@ def certified_decode_token_host(
             ws.rng_calls += 1
         call = calls[l]
         call.cache = C.addressof(cache._desc(G))
-        call.qkv_host = qkv_base + l * n_in * esz
-        call.out_host = out_base + l * H * first.head_dim * 4
+        call.qkv_host = qkv_base + l * in_bytes
+        call.out_host = out_base + l * out_bytes
         call.pos = pos
         call.defer_int4 = 1 if cache._defers_int4() else 0
     stream = _lib.current_stream(device)
@@ -416,10 +428,9 @@ def certified_decode_token_host(
                                                     _lib.dtype_code(qkv_host.dtype), stream), "cqa_decode_token_host")
         for l, cache in enumerate(caches):
             if cache.bounded_hot_tier:
-                ws = spaces[l]
-                cache._hot_tier_update(cache._desc(G), ws.struct, (calls[l].pos + block) // block, stream)
+                cache._hot_tier_update(cache._desc(G), spaces[l].struct, (positions[l] + block) // block, stream)
     for l, cache in enumerate(caches):
-        cache._advance_after_append(calls[l].pos)
+        cache._advance_after_append(positions[l])
     return out_host
 
 
