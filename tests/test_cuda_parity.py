@@ -140,6 +140,42 @@ def test_layer_step_vs_oracle_large(n_tokens, planted, dtype, seed):
           f"value_fallback_blocks={stats.get('value_fallback_blocks', 0)} out_err={err:.2e}")
 
 
+def test_full_size_128k_needles_vs_oracle():
+    """The long-context retrieval shape at full size: 131072 tokens, ten needle blocks (cosine 0.95) at depths
+    0.0 .. 0.9 among N(0,1) distractors.  Scores, selections and certificates bit-exact against the oracle, output
+    within 1e-3; and the size-independent properties of the step: every head's mass fractions sum to one, the
+    sorted cumulative mass is non-decreasing, and every needle block outranks every distractor block in the mass
+    ranking of the query head it was planted for."""
+    dtype = "bfloat16"
+    n_tokens = 131072
+    depths = [i / 10.0 for i in range(10)]
+    base = synth.make_layer_inputs(77, n_tokens, dtype=dtype, n_planted_blocks=10, planted_cos=0.95,
+                                   planted_depths=depths)
+    cc = hz.make_cuda_cache(base.k, base.v, dtype, 64)
+    oc = hz.make_oracle_cache(base.k, base.v, dtype, 64)
+    hz.compare_caches(cc, oc, "128K prefill")
+    knobs = _knobs(exploration_rate=0.0)
+    R = orc.layer_step(oc, base.q, 4, **_oracle_knobs(knobs, None))
+    out, stats = hz.cuda_step(cc, base.q, dtype, 4, knobs, None)
+    err = hz.compare_step(cc, R, out, "128K needles")
+    assert err < 1e-3
+    ws = cc._certified_workspace["cqa_ws"]
+    nq = cc.num_quantized_blocks
+    frac = ws.mass_frac[:, :nq].double().cpu().numpy()
+    assert np.allclose(frac.sum(axis=1), 1.0, atol=1e-4)
+    cum = ws.sorted_cumsum.cpu().numpy()
+    assert (np.diff(cum, axis=1) >= 0).all()
+    planted = np.asarray(base.planted_blocks)
+    assert len(planted) == 10
+    others = np.ones(nq, dtype=bool)
+    others[planted] = False
+    for i, blk in enumerate(planted):
+        for kv in range(8):
+            h = int(base.planted_heads[i, kv])
+            assert frac[h, blk] > frac[h, others].max(), f"needle block {blk} does not outrank the distractors of head {h}"
+    print(f"128K needles: k*={stats['k_star_mean']:.1f} out_err={err:.2e}")
+
+
 def test_exact_ties_take_lowest_block_ids():
     """Every 16-token block repeats the same keys and values, so all mass fractions and all value-error
     terms tie exactly: the selector, the top-4 list and the value check must break the ties by block id
