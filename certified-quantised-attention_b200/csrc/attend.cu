@@ -701,14 +701,9 @@ static int attend_launch_gt(const cqa_cache *c, const cqa_workspace *ws, const v
     cqa_workspace w = *ws;
     if (!dense) w.dense_splits = 0;
     const size_t smem = attend_smem<G>();
-    static size_t attr = 0;
-    if (smem > attr) {
-        int rc = check_cuda(cudaFuncSetAttribute(attend_kernel<G, T2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)smem),
-                            "cudaFuncSetAttribute(attend_kernel)");
-        if (rc) return rc;
-        attr = smem;
-    }
+    static size_t granted[SMEM_ATTR_DEVICES] = {};
+    const int rc_attr = check_cuda(ensure_dynamic_smem(attend_kernel<G, T2>, smem, granted), "cudaFuncSetAttribute(attend_kernel)");
+    if (rc_attr) return rc_attr;
     dim3 grid((unsigned)(ns + (dense ? DENSE_POOL_X : 0)), (unsigned)c->kv_heads);
     return check_cuda(launch_chained(attend_kernel<G, T2>, grid, dim3(ATT_THREADS), smem, st, chained, *c, w, q, q_dtype, nq,
                                      nact, num_tokens, last_valid, q_scale, bps),

@@ -296,6 +296,23 @@ __device__ __forceinline__ void grid_dependency_wait()
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// Opt a kernel in to `bytes` of dynamic shared memory on the current device.  The attribute belongs to the
+// (function, device) pair, so the largest size already granted is remembered per device ordinal; `granted` is one
+// array per kernel instantiation (a function-local static of the caller).
+constexpr int SMEM_ATTR_DEVICES = 64;
+template <typename K>
+static inline cudaError_t ensure_dynamic_smem(K kernel, size_t bytes, size_t (&granted)[SMEM_ATTR_DEVICES])
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const bool tracked = dev >= 0 && dev < SMEM_ATTR_DEVICES;
+    if (tracked && bytes <= granted[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && tracked) granted[dev] = bytes;
+    return e;
+}
+
 // Launch with (or without) the programmatic-serialisation attribute.
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,

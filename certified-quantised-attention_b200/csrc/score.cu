@@ -248,14 +248,10 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
                           const ScorePush &push, cudaStream_t st)
 {
     constexpr int SMEM = SCORE_SMEM + G * D * 4;
-    static bool attr_set = false;
-    if (!attr_set) {
-        int rc = check_cuda(cudaFuncSetAttribute(score_blocks_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 SMEM),
-                            "cudaFuncSetAttribute(score_blocks_kernel)");
-        if (rc) return rc;
-        attr_set = true;
-    }
+    static size_t granted[SMEM_ATTR_DEVICES] = {};
+    const int rc_attr = check_cuda(ensure_dynamic_smem(score_blocks_kernel<G>, (size_t)SMEM, granted),
+                                   "cudaFuncSetAttribute(score_blocks_kernel)");
+    if (rc_attr) return rc_attr;
     return check_cuda(launch_chained(score_blocks_kernel<G>, grid, dim3(SCORE_WARPS * 32), SMEM, st, true, *c, q, q_dtype,
                                      nq, q_scale, m_b, s_b, ld, tok, bpc, zero_words, n_zero_words, push),
                       "score_blocks_kernel");

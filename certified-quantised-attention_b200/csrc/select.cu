@@ -1034,14 +1034,9 @@ static int selcert_launch_t(const cqa_cache *c, const cqa_knobs *kn, const cqa_w
     }
     const int n_pad = next_pow2(nq);
     const size_t smem = selcert_smem(n_pad);
-    static size_t attr = 0;
-    if (smem > attr) {
-        int rc = check_cuda(cudaFuncSetAttribute(selcert_kernel<T2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)smem),
-                            "cudaFuncSetAttribute(selcert_kernel)");
-        if (rc) return rc;
-        attr = smem;
-    }
+    static size_t granted[SMEM_ATTR_DEVICES] = {};
+    const int rc_attr = check_cuda(ensure_dynamic_smem(selcert_kernel<T2>, smem, granted), "cudaFuncSetAttribute(selcert_kernel)");
+    if (rc_attr) return rc_attr;
     if ((phases & PH_SELECT) && !(phases & PH_FLAGS_CLEARED)) {
         int rc = check_cuda(cudaMemsetAsync(ws->any_flags, 0, (5 + H) * sizeof(int32_t), st),
                             "cudaMemsetAsync(any_flags)");
