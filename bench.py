@@ -366,6 +366,51 @@ def run_ours(args, rank, world, device_index):
             sel_stats["fp16_value_bytes"] += b["fp16_value_bytes"]
             n_meas += 1
         s_idx += 1
+    # ---- the two streaming kernels again, each launched back to back over the NL layer caches (NL x its bytes is
+    # larger than L2 at the default sizes) between ONE pair of events: the average launch duration without the
+    # event and ramp overhead that an isolated launch carries.  Every workspace still holds its last step's masks.
+    from cqa_b200 import _lib as cl
+    import ctypes as C
+    L = cl.lib()
+    stream = cl.current_stream(dev)
+    last_q = [q_dev[s_idx - 1, l] for l in range(NL)]
+    rec = []
+    for l in range(NL):
+        c = caches[l]
+        ws = c._certified_workspace["cqa_ws"]
+        nq, nact = c.num_quantized_blocks, c.active_blocks
+        lv = 16 if nact == nq else c.num_tokens - nq * 16
+        rec.append((c._desc(4), ws, ws.fill_struct(nact), nq, nact, c.num_tokens, lv))
+
+    def launch_score(l):
+        d, ws, w, nq, nact, ntok, lv = rec[l]
+        cl.check(L.cqa_score_blocks(C.byref(d), last_q[l].data_ptr(), cl.dtype_code(last_q[l].dtype), nq, float(q_scale),
+                                    ws.m_b.data_ptr(), ws.s_b.data_ptr(), ws.ld, ws.token_scores.data_ptr(), stream),
+                 "cqa_score_blocks")
+
+    def launch_attend(l):
+        d, ws, w, nq, nact, ntok, lv = rec[l]
+        cl.check(L.cqa_attend(C.byref(d), C.byref(w), last_q[l].data_ptr(), cl.dtype_code(last_q[l].dtype), nq, nact,
+                              ntok, lv, float(q_scale), stream), "cqa_attend")
+
+    def back_to_back(fn, rounds):
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        with cl.on_device(dev):
+            for l in range(NL):
+                fn(l)                       # warm-up of this entry point
+            flush.fill_(1.0)                # evicts L2; the launches below are queued while it runs
+            ea.record()
+            for _ in range(rounds):
+                for l in range(NL):
+                    fn(l)
+            eb.record()
+        torch.cuda.synchronize()
+        return ea.elapsed_time(eb) * 1e3 / (rounds * NL)
+
+    b2b_rounds = max(1, min(8, args.kernel_steps * 2))
+    b2b_us = {"phase1_int8_scoring": back_to_back(launch_score, b2b_rounds),
+              "phase2_fused_attend": back_to_back(launch_attend, b2b_rounds)}
     peaks = {}
     try:
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -375,11 +420,11 @@ def run_ours(args, rank, world, device_index):
     peak_src = "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
     kern_us = {k[:-3]: v / n_meas for k, v in phase.items()}
     stage_of = {"phase1_int8_scoring": "score", "phase2_fused_attend": "attend"}
-    dominant = max(stage_of, key=lambda k: kern_us.get(k, 0.0))
+    dominant = max(stage_of, key=lambda k: b2b_us.get(k, 0.0))
     dom_bytes = bytes_acc[stage_of[dominant]] / n_meas
     if dominant == "phase2_fused_attend":
         dom_bytes += bytes_acc["dense"] / n_meas
-    achieved = dom_bytes / (kern_us[dominant] * 1e-6) / 1e9
+    achieved = dom_bytes / (b2b_us[dominant] * 1e-6) / 1e9
     chain_bytes = bytes_acc["total"] / n_meas
     chain_gbs = chain_bytes / (us_per_layer * 1e-6) / 1e9
     # DRAM bytes per launch of the two streaming kernels at this workload, from one ncu capture each
@@ -391,7 +436,10 @@ def run_ours(args, rank, world, device_index):
         "achieved": round(achieved, 1), "peak": peak_gbs, "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
         "peak_source": peak_src,
         "traffic": int(ncu_traffic[dominant]) if args.context == 32768 else None,
-        "algorithmic_bytes_per_launch": int(dom_bytes), "kernel_us": round(kern_us[dominant], 2),
+        "algorithmic_bytes_per_launch": int(dom_bytes), "kernel_us": round(b2b_us[dominant], 2),
+        "kernel_us_how": "average over %d back-to-back launches on %d layer caches, one event pair" % (b2b_rounds * NL, NL),
+        "kernel_us_isolated": round(kern_us[dominant], 2),
+        "back_to_back_us": {k: round(v, 2) for k, v in b2b_us.items()},
         "chain": {"algorithmic_bytes_per_layer_step": int(chain_bytes), "us_per_layer_step": round(us_per_layer, 2),
                   "achieved_gbs": round(chain_gbs, 1), "frac": round(chain_gbs / peak_gbs, 4),
                   "frac_of_nominal_8000": round(chain_gbs / 8000.0, 4),
