@@ -323,7 +323,7 @@ extern "C" int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
     // Phase 2: two resident CTAs per SM, at least 8 blocks (one per warp) per split.
-    long target = ((long)sms * 2) / kv_heads;
+    long target = ((long)sms * CQA_ATT_MIN_CTAS) / kv_heads;
     if (target < 1) target = 1;
     long by_work = (nact + 7) / 8;
     long ns = target < by_work ? target : by_work;

@@ -31,7 +31,10 @@ namespace cqa {
 
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
-constexpr int ATT_STAGES = 4;
+#ifndef CQA_ATT_STAGES
+#define CQA_ATT_STAGES 4
+#endif
+constexpr int ATT_STAGES = CQA_ATT_STAGES;
 
 __device__ __forceinline__ float fexp(float x) { return __expf(x); }
 
@@ -395,7 +398,7 @@ __device__ void dense_unit(const cqa_cache &c, const cqa_workspace &ws, const vo
 constexpr int DENSE_POOL_X = 8;  // dense-recompute CTAs per KV row of the grid
 
 template <int G, typename T2>
-__global__ void __launch_bounds__(ATT_THREADS, 2) attend_kernel(cqa_cache c, cqa_workspace ws, const void *q,
+__global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_kernel(cqa_cache c, cqa_workspace ws, const void *q,
                                                                int q_dtype, long nq, long nact, long num_tokens,
                                                                int last_valid, float q_scale, int blocks_per_split)
 {

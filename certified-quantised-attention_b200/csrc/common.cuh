@@ -299,6 +299,9 @@ __device__ __forceinline__ void grid_dependency_wait()
 // Opt a kernel in to `bytes` of dynamic shared memory on the current device.  The attribute belongs to the
 // (function, device) pair, so the largest size already granted is remembered per device ordinal; `granted` is one
 // array per kernel instantiation (a function-local static of the caller).
+#ifndef CQA_ATT_MIN_CTAS
+#define CQA_ATT_MIN_CTAS 2   // resident Phase-2 CTAs per SM that the kernel is built for and the split heuristic assumes
+#endif
 constexpr int SMEM_ATTR_DEVICES = 64;
 template <typename K>
 static inline cudaError_t ensure_dynamic_smem(K kernel, size_t bytes, size_t (&granted)[SMEM_ATTR_DEVICES])
