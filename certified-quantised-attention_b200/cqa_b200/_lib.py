@@ -89,7 +89,7 @@ class CqaWorkspace(C.Structure):
         ("shard_stride", C.c_int64), ("shard_chunk", C.c_int64), ("shard_rank_stride", C.c_int64),
         ("shard_ranks", C.c_int32), ("given_ranks", C.c_int32), ("given_rank_stride", C.c_int64),
         ("wait_flags", vp), ("wait_n", C.c_int32), ("wait_skip", C.c_int32), ("wait_value", C.c_int32),
-        ("reserved2", C.c_int32), ("wait_status", vp),
+        ("wait_spins", C.c_int32), ("wait_status", vp),
         ("peer_xb", vp * 8), ("peer_flags_b", vp * 8), ("peer_partial", vp * 8), ("peer_flag_c", vp * 8),
         ("peer_ticket_c", vp), ("peer_first_block", C.c_int64), ("peer_n_local", C.c_int64),
         ("peer_world", C.c_int32), ("peer_rank", C.c_int32), ("peer_step", C.c_int32), ("reserved3", C.c_int32),

@@ -287,6 +287,7 @@ extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const 
                               int q_dtype, int64_t num_tokens, int64_t nq, const float *exploration_u,
                               int64_t u_ld, void *stream)
 {
+    // every argument check comes before the first launch: a bad call must not write anything on the device
     int rc = check_common(c, ws, "cqa_layer_step");
     if (rc) return rc;
     if (!knobs || !q) { set_error("cqa_layer_step: NULL knobs or q"); return CQA_ERR_INVALID; }
@@ -296,18 +297,24 @@ extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const 
         set_error("cqa_layer_step: num_tokens=%ld does not match %ld quantised blocks", (long)num_tokens, (long)nq);
         return CQA_ERR_INVALID;
     }
+    rc = check_score_args(c, q_dtype, nq, ws->ld, "cqa_layer_step");
+    if (rc) return rc;
     const long nact = (num_tokens + BS - 1) / BS;
     const int last_valid = nact == nq ? BS : (int)(num_tokens - nq * BS);
     cudaStream_t st = (cudaStream_t)stream;
     if (!ws->token_scores) { set_error("cqa_layer_step: token_scores missing"); return CQA_ERR_INVALID; }
+    if (!(knobs->tau_cov > 0.0f)) { set_error("cqa_layer_step: tau_cov must be positive"); return CQA_ERR_INVALID; }
+    if (!ws->value_mask) { set_error("cqa_layer_step: value_mask missing"); return CQA_ERR_INVALID; }
+    if (nact > ws->ld || nact > c->max_blocks) { set_error("cqa_layer_step: workspace ld or cache max_blocks too small"); return CQA_ERR_INVALID; }
+    if (exploration_u && u_ld < nq) { set_error("cqa_layer_step: exploration_u leading dimension too small"); return CQA_ERR_INVALID; }
+    rc = selcert_check(c, knobs, ws, q, nq, 3 | 16);
+    if (rc) return rc;
+    rc = attend_check(c, ws, nq, nact, last_valid);
+    if (rc) return rc;
     const int n_flag_words = 5 + c->kv_heads * c->gqa_group;
     rc = score_blocks_launch(c, q, q_dtype, nq, knobs->q_scale, ws->m_b, ws->s_b, ws->ld, ws->token_scores, st,
                              ws->any_flags, n_flag_words, nullptr);
     if (rc) return rc;
-    if (!(knobs->tau_cov > 0.0f)) { set_error("cqa_layer_step: tau_cov must be positive"); return CQA_ERR_INVALID; }
-    if (!ws->value_mask) { set_error("cqa_layer_step: value_mask missing"); return CQA_ERR_INVALID; }
-    if (nact > ws->ld) { set_error("cqa_layer_step: workspace ld too small"); return CQA_ERR_INVALID; }
-    if (exploration_u && u_ld < nq) { set_error("cqa_layer_step: exploration_u leading dimension too small"); return CQA_ERR_INVALID; }
     rc = selcert_launch(c, knobs, ws, q, q_dtype, nq, nact, exploration_u, u_ld, 3 | 16, st);   // select + certify in one launch; flags cleared by the score kernel
     if (rc) return rc;
     return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, knobs->q_scale, st, true);

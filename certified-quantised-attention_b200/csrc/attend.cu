@@ -727,10 +727,8 @@ static int attend_launch_t(const cqa_cache *c, const cqa_workspace *ws, const vo
     return CQA_ERR_UNSUPPORTED;
 }
 
-// `chained`: the previous kernel on the stream is the selector of the same fused step, so the kernel may be
-// scheduled early and stage its first blocks (written two kernels back) before waiting for the selector.
-int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
-                  long num_tokens, int last_valid, float q_scale, cudaStream_t st, bool chained)
+// Argument checks of Phase 2 (also called by the fused step before its first launch).
+int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact, int last_valid)
 {
     if (ws->num_splits <= 0 || !ws->part_m || !ws->part_l || !ws->part_acc || (!ws->out && !ws->partial_out) || !ws->topk_mask ||
         !ws->value_mask || !ws->tickets) {
@@ -738,8 +736,9 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
         return CQA_ERR_INVALID;
     }
     if (nq > 0 && !ws->token_scores) { set_error("cqa_attend: token_scores missing"); return CQA_ERR_INVALID; }
-    if (nact <= 0 || nact > ws->ld || nact > c->max_blocks) {
-        set_error("cqa_attend: nact=%ld out of range (ld=%ld)", nact, (long)ws->ld);
+    if (nq < 0 || nact <= 0 || nact < nq || nact > ws->ld || nact > c->max_blocks) {
+        set_error("cqa_attend: nact=%ld out of range (nq=%ld, ld=%ld, max_blocks=%ld)", nact, nq, (long)ws->ld,
+                  (long)c->max_blocks);
         return CQA_ERR_INVALID;
     }
     if (ws->num_splits > CQA_MAX_SPLITS || ws->dense_splits > CQA_MAX_DENSE_SPLITS) {
@@ -752,13 +751,31 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
         set_error("cqa_attend: Tier-2 key/value arrays are required (promoted and trailing blocks read them)");
         return CQA_ERR_INVALID;
     }
+    // A certificate can flag heads for the dense recompute; their rows are then written by the dense pool only.
+    // Without the dense scratch nothing would write them, so that combination is refused instead of leaving
+    // stale rows in the output.
+    if (ws->cert != nullptr && (ws->dense_splits <= 0 || !ws->dense_m || !ws->dense_l || !ws->dense_acc)) {
+        set_error("cqa_attend: a certificate is attached (ws->cert) but the dense-recompute scratch "
+                  "(dense_splits, dense_m, dense_l, dense_acc) is missing; pass it, or detach the certificate");
+        return CQA_ERR_INVALID;
+    }
+    if (ws->cert != nullptr && !ws->any_flags) { set_error("cqa_attend: certificate without flag words"); return CQA_ERR_INVALID; }
+    if (c->t2_dtype < 0 || c->t2_dtype > 2) { set_error("cqa_attend: unknown Tier-2 dtype %d", c->t2_dtype); return CQA_ERR_INVALID; }
+    return CQA_OK;
+}
+
+// `chained`: the previous kernel on the stream is the selector of the same fused step, so the kernel may be
+// scheduled early and stage its first blocks (written two kernels back) before waiting for the selector.
+int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
+                  long num_tokens, int last_valid, float q_scale, cudaStream_t st, bool chained)
+{
+    const int rc = attend_check(c, ws, nq, nact, last_valid);
+    if (rc) return rc;
     switch (c->t2_dtype) {
     case CQA_F32: return attend_launch_t<float>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
     case CQA_F16: return attend_launch_t<__half>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
-    case CQA_BF16: return attend_launch_t<__nv_bfloat16>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
+    default: return attend_launch_t<__nv_bfloat16>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
     }
-    set_error("cqa_attend: unknown Tier-2 dtype %d", c->t2_dtype);
-    return CQA_ERR_INVALID;
 }
 
 // Merge of per-rank partial rows (max, sum, acc[128]) of every head: one CTA per head, one thread per channel.

@@ -357,18 +357,21 @@ struct ScorePush {
     int world, rank, step;
 };
 
-// Called by every thread of a CTA before it reads exchanged data: thread 0 waits until flags[i] >= value for every
-// i < n except `skip` (bounded: about half a second), then the CTA synchronises.  A timeout is recorded in *status.
+// Called by every thread of a CTA before it reads exchanged data: thread 0 waits until flags[i * stride] >= value
+// for every i < n except `skip`, then the CTA synchronises.  Every wait is bounded: after `spins` polls (0 = the
+// default, about half a second) of one flag the thread records 100 + i in *status and moves on, so the kernel
+// always returns and the context stays usable; the step's result is then invalid and the host reads the status.
 constexpr int PEER_WAIT_SPINS = 2000000;
 __device__ __forceinline__ void peer_wait(const int32_t *flags, int n, int skip, int value, int32_t *status,
-                                          long stride = 1)
+                                          long stride = 1, int spins_limit = 0)
 {
     if (flags != nullptr && threadIdx.x == 0) {
+        const int limit = spins_limit > 0 ? spins_limit : PEER_WAIT_SPINS;
         for (int i = 0; i < n; ++i) {
             if (i == skip) continue;
             int spins = 0;
             while (ld_acquire_sys(flags + i * stride) < value) {
-                if (++spins > PEER_WAIT_SPINS) {
+                if (++spins > limit) {
                     if (status) atomicExch(status, 100 + i);
                     break;
                 }
@@ -384,5 +387,11 @@ __device__ __forceinline__ void peer_wait(const int32_t *flags, int n, int skip,
 void set_error(const char *fmt, ...);
 int check_cuda(cudaError_t e, const char *what);
 int check_launch(const char *what);
+
+// Argument checks of the three kernels of a layer step, callable on their own so that a fused entry point can
+// validate the whole chain before its first launch.
+int check_score_args(const cqa_cache *c, int q_dtype, long nq, long ld, const char *who);
+int selcert_check(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, long nq, int phases);
+int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact, int last_valid);
 
 }  // namespace cqa

@@ -9,8 +9,7 @@
 // from step s):
 //   xa [2][world][rows][chunk] f32 | xb [2][world][H][32][2] f32 | xc [2][world][H][130] f32 |
 //   flags [3][world] i32 | flags_b [world][H] i32 | status [4] i32 | tickets [3][world] i32
-#include <cstdio>
-#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "rescore.cuh"
@@ -105,9 +104,10 @@ __global__ void __launch_bounds__(PUSH_THREADS) peer_push_kernel(PeerArgs pa, co
 
 // Exchange C consumer: wait for every rank's partial rows, then the log-sum-exp merge (one CTA per head).
 __global__ void __launch_bounds__(D) merge_wait_kernel(const float *parts, int n_parts, int n_heads, float *out,
-                                                      const int32_t *flags, int skip, int value, int32_t *status)
+                                                      const int32_t *flags, int skip, int value, int32_t *status,
+                                                      int spins)
 {
-    peer_wait(flags, n_parts, skip, value, status);
+    peer_wait(flags, n_parts, skip, value, status, 1, spins);
     const int h = blockIdx.x, ch = threadIdx.x;
     float M = -INFINITY;
     for (int p = 0; p < n_parts; ++p) M = fmaxf(M, __ldcg(parts + ((long)p * n_heads + h) * CQA_PARTIAL_STRIDE));
@@ -179,48 +179,6 @@ extern "C" int cqa_peer_status(const cqa_peers *peers, int32_t *status_out, int 
     return rc;
 }
 
-// Optional stage timing (environment variable CQA_SHARDED_TIMING=1): CUDA events between the stages of the step,
-// averaged and printed to stderr every 32 steps.  Off by default; when on, every step ends with a stream wait.
-namespace {
-struct StageTimer {
-    bool on = false;
-    cudaEvent_t ev[10];
-    double acc[9] = {0};
-    int n = 0, k = 0;
-    StageTimer()
-    {
-        const char *e = getenv("CQA_SHARDED_TIMING");
-        on = e && e[0] == '1';
-    }
-    void mark(cudaStream_t st)
-    {
-        if (!on) return;
-        if (n == 0 && k == 0)
-            for (auto &x : ev) cudaEventCreate(&x);
-        cudaEventRecord(ev[k++], st);
-    }
-    void finish(cudaStream_t st, int rank)
-    {
-        if (!on) return;
-        cudaStreamSynchronize(st);
-        for (int i = 0; i + 1 < k; ++i) {
-            float ms = 0;
-            cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
-            acc[i] += ms * 1e3;
-        }
-        const int stages = k - 1;
-        k = 0;
-        if (++n % 32 == 0) {
-            fprintf(stderr, "[cqa sharded rank %d] us per stage:", rank);
-            static const char *names[] = {"score", "pushA", "select+certify", "attend", "-", "merge"};
-            for (int i = 0; i < stages; ++i) { fprintf(stderr, " %s %.1f", names[i], acc[i] / 32); acc[i] = 0; }
-            fprintf(stderr, "\n");
-        }
-    }
-};
-StageTimer g_timer;
-}  // namespace
-
 extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *global_view, const cqa_knobs *knobs,
                                       const cqa_workspace *wg, const cqa_workspace *wl, const cqa_peers *peers,
                                       const void *q, int q_dtype, int64_t nq_global, int64_t nact_global,
@@ -242,6 +200,41 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     }
     for (int p = 0; p < W; ++p)
         if (!peers->base[p]) { set_error("cqa_sharded_layer_step: peer %d is not mapped", p); return CQA_ERR_INVALID; }
+    // every range check of the three kernels comes before the first launch or copy
+    if (n_local <= 0 || nact_local < n_local || nact_local > n_local + 1 || nq_global < n_local ||
+        nact_global < nq_global || nact_global > nq_global + 1 || first_block < 0 || first_block + n_local > nq_global) {
+        set_error("cqa_sharded_layer_step: inconsistent block counts (local %ld/%ld, global %ld/%ld, first %ld)",
+                  (long)n_local, (long)nact_local, (long)nq_global, (long)nact_global, (long)first_block);
+        return CQA_ERR_INVALID;
+    }
+    int rc = check_score_args(local, q_dtype, n_local, peers->chunk, "cqa_sharded_layer_step");
+    if (rc) return rc;
+    if (!wl->token_scores || !wg->cert || !wg->any_flags || !wg->mass_frac || !wg->topk_mask || !wg->explore_mask ||
+        !wg->value_mask || !wg->sorted_idx || !wg->sorted_cumsum) {
+        set_error("cqa_sharded_layer_step: workspace is missing selector buffers or token scores");
+        return CQA_ERR_INVALID;
+    }
+    if (nact_global > wg->ld || nact_global > global_view->max_blocks) {
+        set_error("cqa_sharded_layer_step: %ld global blocks exceed the global leading dimension", (long)nact_global);
+        return CQA_ERR_INVALID;
+    }
+    if (push_meta && (!local->values_int4_errors || !local->sigma_max)) {
+        set_error("cqa_sharded_layer_step: eta rows or scale maxima missing");
+        return CQA_ERR_INVALID;
+    }
+    {
+        cqa_workspace probe = *wg;
+        probe.shard_stride = probe.shard_stride > 0 ? probe.shard_stride : 1;   // the exchange layout replaces ld
+        probe.given_fp16 = static_cast<const float *>(peers->base[R]);
+        probe.peer_world = W;
+        probe.peer_step = (int)step;
+        rc = selcert_check(global_view, knobs, &probe, q, nq_global, 1 | 2 | 64);
+        if (rc) return rc;
+        cqa_workspace lp = *wl;
+        lp.partial_out = static_cast<float *>(peers->base[R]);
+        rc = attend_check(local, &lp, n_local, nact_local, last_valid);
+        if (rc) return rc;
+    }
     cudaStream_t st = (cudaStream_t)stream;
     const PeerLayout L = peer_layout(W, H, peers->rows, peers->chunk);
     const int par = (int)(step & 1);
@@ -258,7 +251,6 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     float *xc_par = own + L.xc + par * L.xc_parity;
     float *xc_own = xc_par + (long)R * H * CQA_PARTIAL_STRIDE;
 
-    g_timer.mark(st);
     // 1. Phase 1 on the local blocks, straight into this rank's slot of xa.  On ordinary steps the kernel also stores
     // every result into the other ranks' buffers and its last CTA releases the Exchange-A flags; when eta rows and
     // scale maxima changed (a block completed) the rows go out together through the push kernel instead.
@@ -275,10 +267,9 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
         sp.rank = R;
         sp.step = (int)step;
     }
-    int rc = score_blocks_launch(local, q, q_dtype, n_local, knobs->q_scale, xa_own, xa_own + (long)H * peers->chunk,
+    rc = score_blocks_launch(local, q, q_dtype, n_local, knobs->q_scale, xa_own, xa_own + (long)H * peers->chunk,
                                  peers->chunk, wl->token_scores, st, nullptr, 0, push_meta ? nullptr : &sp);
     if (rc) return rc;
-    g_timer.mark(st);
     if (push_meta) {
         // eta rows and the row of scale maxima follow the 2H score rows; both parities get them
         rc = check_cuda(cudaMemcpy2DAsync(xa_own + 2L * H * peers->chunk, peers->chunk * 4, local->values_int4_errors,
@@ -298,7 +289,6 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
                                         cudaMemcpyDeviceToDevice, st), "copy of meta rows to the other parity");
         if (rc) return rc;
     }
-    g_timer.mark(st);
     // 3. the global selector and certificate on the exchanged arrays, one launch: it waits for every rank's A; the
     // ranking-check CTA of each head re-scores the top-list blocks this rank owns, pushes them to every rank, waits
     // for the other ranks' rows (Exchange B, per head) and raises the flags
@@ -331,7 +321,6 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     gv.sigma_max = xa_par + (2L * H + KV) * peers->chunk;
     rc = selcert_launch(&gv, knobs, &g, q, q_dtype, nq_global, nact_global, nullptr, 0, 1 | 2 | 64, st);
     if (rc) return rc;
-    g_timer.mark(st);
     // 6. Phase 2 over the local blocks; un-normalised partial rows go to this rank's slot of xc
     cqa_workspace l = *wl;
     l.m_b = xa_own;
@@ -353,10 +342,7 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     l.peer_step = (int)step;
     rc = attend_launch(local, &l, q, q_dtype, n_local, nact_local, num_tokens_local, last_valid, knobs->q_scale, st, false);
     if (rc) return rc;
-    g_timer.mark(st);
-    g_timer.mark(st);
-    merge_wait_kernel<<<H, D, 0, st>>>(xc_par, W, H, out, own_i + L.flags + 2 * W, R, (int)step, own_i + L.status);
-    g_timer.mark(st);
-    g_timer.finish(st, R);
+    merge_wait_kernel<<<H, D, 0, st>>>(xc_par, W, H, out, own_i + L.flags + 2 * W, R, (int)step, own_i + L.status,
+                                       wg->wait_spins);
     return check_launch("sharded step kernels");
 }

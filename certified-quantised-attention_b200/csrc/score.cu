@@ -304,20 +304,36 @@ int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq,
 
 using namespace cqa;
 
+// Range checks shared by every entry point that launches the score kernel (they all run before the launch).
+int cqa::check_score_args(const cqa_cache *c, int q_dtype, long nq, long ld, const char *who)
+{
+    if (!c->keys_int8 || !c->keys_scale || !c->keys_zero_points) {
+        set_error("%s: INT8 key arrays missing", who);
+        return CQA_ERR_INVALID;
+    }
+    if (nq < 0 || nq > c->max_blocks || nq * BS > c->cap_tokens || ld < nq) {
+        set_error("%s: nq=%ld out of range (max_blocks=%ld, cap_tokens=%ld, ld=%ld)", who, nq, (long)c->max_blocks,
+                  (long)c->cap_tokens, ld);
+        return CQA_ERR_INVALID;
+    }
+    if (q_dtype < 0 || q_dtype > 2) { set_error("%s: unknown q dtype %d", who, q_dtype); return CQA_ERR_INVALID; }
+    if (c->gqa_group != 1 && c->gqa_group != 2 && c->gqa_group != 4 && c->gqa_group != 8) {
+        set_error("%s: unsupported gqa_group %d", who, c->gqa_group);
+        return CQA_ERR_UNSUPPORTED;
+    }
+    return CQA_OK;
+}
+
 extern "C" int cqa_score_blocks(const cqa_cache *c, const void *q, int q_dtype, int64_t nq, float q_scale,
                                 float *m_b, float *s_b, int64_t ld, float *token_scores, void *stream)
 {
-    if (!c || !q || !m_b || !s_b || !c->keys_int8 || !c->keys_scale || !c->keys_zero_points) {
+    if (!c || !q || !m_b || !s_b) {
         set_error("cqa_score_blocks: NULL pointer");
         return CQA_ERR_INVALID;
     }
+    const int rc = check_score_args(c, q_dtype, nq, ld, "cqa_score_blocks");
+    if (rc) return rc;
     if (nq == 0) return CQA_OK;
-    if (nq < 0 || nq > c->max_blocks || nq * BS > c->cap_tokens || ld < nq) {
-        set_error("cqa_score_blocks: nq=%ld out of range (max_blocks=%ld, ld=%ld)", (long)nq, (long)c->max_blocks,
-                  (long)ld);
-        return CQA_ERR_INVALID;
-    }
-    if (q_dtype < 0 || q_dtype > 2) { set_error("cqa_score_blocks: unknown q dtype"); return CQA_ERR_INVALID; }
     return score_blocks_launch(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, token_scores, (cudaStream_t)stream, nullptr, 0,
                                nullptr);
 }

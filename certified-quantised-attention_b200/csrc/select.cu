@@ -1,22 +1,27 @@
-// Selector and certifier: one CTA of 1024 threads per query head, everything
-// after one round of global loads runs out of shared memory.
+// Selector and certifier: one CTA of 1024 threads per (query head, role).
 //
-//   select : block log-masses and mass fractions (canonical sum), the 256
-//            heaviest blocks in descending order (ties -> lower block id) by a
-//            4-pass radix select plus a one-warp register bitonic sort,
-//            sequential cumulative mass, K* with the Rung-1 expansion,
-//            exploration draw, FP16-key mask.
-//   certify: top-4 blocks by m_b (per-thread lists merged by shuffles), FP16
-//            re-score by four warps, Delta, ranking / boundary /
-//            score-consistency flags, Rung-2 value check (radix select of the
-//            largest mass*eta contributors, sequential greedy prefix; a full
-//            block-wide bitonic sort only if 256 contributors are not enough).
+// A thread owns the blocks b = tid, tid + 1024, ... (at most 16 at the limit of
+// 16384 blocks) and keeps their values in registers, so the searches below are
+// passes over registers with one CTA barrier each; shared memory holds a copy
+// for the few steps that index by block id.
+//
+//   role 0 (select) : block log-masses and mass fractions (canonical sum), the
+//            256 heaviest blocks (ties -> lower block id) by a threshold search
+//            on the float bit patterns, two bits per step, ordered by rank
+//            counting; sequential cumulative mass; K* with the Rung-1
+//            expansion; exploration draw; FP16-key mask.
+//   role 1 (ranking): top-4 blocks by m_b (per-thread lists merged by
+//            shuffles), FP16 re-score by four warps while the other warps take
+//            the boundary maximum, Delta, ranking / boundary /
+//            score-consistency flags, work list of the dense recompute.
+//   role 2 (values) : Rung-2 value check: the promoted blocks are those whose
+//            contribution mass*eta is at or above a threshold found by a search
+//            over "column sums" (two bits per step), no sort and no serial walk.
 //
 // cqa_select, cqa_certify and the fused cqa_layer_step all launch the same
-// kernel with a phase mask.  Sums over blocks use the canonical order (32
-// consecutive values by a warp butterfly, 8 such sums by a butterfly = one
-// 256-block leaf, leaves added left to right); prefix sums over the sorted
-// order are sequential.
+// kernel with a phase mask.  Sums over blocks use the canonical orders
+// documented at the functions; prefix sums over the sorted order are
+// sequential.
 #include "common.cuh"
 #include "rescore.cuh"
 
@@ -24,7 +29,7 @@ namespace cqa {
 
 constexpr int SC_THREADS = 1024;
 constexpr int SC_WARPS = 32;
-constexpr int CAND = 256;          // candidates kept by the radix select
+constexpr int CAND = 256;          // candidates kept by the top search
 constexpr int PH_SELECT = 1, PH_CERTIFY = 2;
 // Sequence-sharded runs split the ranking check around an exchange: PH_TOP_ONLY stops role 1 once the top
 // list is in the certificate; PH_GIVEN resumes it from that list with FP16 scores computed by the ranks that
@@ -35,26 +40,10 @@ constexpr int PH_PEER_B = 64;          // role 1 exchanges the FP16 re-scores wi
 
 typedef unsigned long long u64;
 
-// Optional phase clocks (compile with -DCQA_PHASE_CLOCKS): thread 0 of every CTA stores the cycle count at
-// numbered points; the deltas land in the unused tail of cert[h].fp16_logmass.
-#ifdef CQA_PHASE_CLOCKS
-#define CQA_CLK(i) do { if (threadIdx.x == 0) phase_clk[i] = clock64(); } while (0)
-#define CQA_CLK_FLUSH(lo, hi) do { if (threadIdx.x == 0) for (int i_ = (lo); i_ <= (hi); ++i_) \
-    ct->fp16_logmass[16 + i_] = (float)(phase_clk[i_] - phase_clk[0]); } while (0)
-#define CQA_LM_ROWS 16
-#define CQA_DBG(i) do { if (threadIdx.x == 0) sh.dbg[i] = clock64(); } while (0)
-#else
-#define CQA_CLK(i) do { } while (0)
-#define CQA_DBG(i) do { } while (0)
-#define CQA_CLK_FLUSH(lo, hi) do { } while (0)
-#define CQA_LM_ROWS CQA_MAX_RANKING_K
-#endif
-
-// One uniform in [0, 1) per (block, head, call): Philox4x32-10 on the counter (block, head, offset) under `seed`.
-__device__ __forceinline__ float philox_uniform(unsigned long long seed, unsigned long long offset, unsigned head,
-                                                unsigned block)
+// Philox4x32-10 on the counter (c0, head, offset) under `seed`: four 32-bit words.
+__device__ __forceinline__ uint4 philox4(unsigned long long seed, unsigned long long offset, unsigned head, unsigned c0)
 {
-    unsigned c0 = block, c1 = head, c2 = (unsigned)offset, c3 = (unsigned)(offset >> 32);
+    unsigned c1 = head, c2 = (unsigned)offset, c3 = (unsigned)(offset >> 32);
     unsigned k0 = (unsigned)seed, k1 = (unsigned)(seed >> 32);
 #pragma unroll
     for (int r = 0; r < 10; ++r) {
@@ -65,20 +54,19 @@ __device__ __forceinline__ float philox_uniform(unsigned long long seed, unsigne
         k0 += 0x9E3779B9u;
         k1 += 0xBB67AE85u;
     }
-    return (float)(c0 >> 8) * 5.9604644775390625e-08f;   // 2^-24
+    return make_uint4(c0, c1, c2, c3);
 }
+// One uniform in [0, 1) per (block, head, call).  Blocks b, b + 1024, b + 2048, b + 3072 (the four a thread owns
+// in a row) share one Philox call: counter word (b mod 1024) + 1024 * (b div 4096), output word (b div 1024) mod 4.
+__device__ __forceinline__ float uniform_of_word(unsigned w) { return (float)(w >> 8) * 5.9604644775390625e-08f; }
 
 struct SCShared {
-    float red_f[SC_WARPS];
-    u64 red_u[SC_WARPS * 4];
+    float red_f[2][SC_WARPS];
+    float red_f3[2][3][SC_WARPS];
+    unsigned red_u[2][2][SC_WARPS];
     int red_i[2][SC_WARPS];
     unsigned char rank_part[4][CAND];
-    float vs_f[2][8];
-    int vs_i[2][8];
     unsigned short rank_pos[CAND];
-#ifdef CQA_PHASE_CLOCKS
-    long long dbg[8];
-#endif
     float bcast_f[8];
     int bcast_i[8];
     unsigned bcast_u[4];
@@ -106,31 +94,34 @@ __device__ __forceinline__ u64 shfl_xor_u64(u64 v, int m)
     return ((u64)hi << 32) | lo;
 }
 
-__device__ __forceinline__ float block_max(float v, SCShared &sh)
+// Maximum of one value per thread over the CTA, in every thread; one barrier (rows alternate with `parity`).
+__device__ __forceinline__ float cta_max(float v, SCShared &sh, int &parity)
 {
     v = warp_max(v);
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) sh.red_f[parity][w] = v;
     __syncthreads();
-    if (l == 0) sh.red_f[w] = v;
-    __syncthreads();
-    return warp_max(sh.red_f[l]);
+    const float r = warp_max(sh.red_f[parity][l]);
+    parity ^= 1;
+    return r;
 }
 
-// Canonical sum of vals[0..n) in shared memory; returns the total to every thread.
-// gsum needs ceil(n/32) floats, leaf ceil(n/256).
-__device__ __noinline__ float block_canonical_sum(const float *vals, int n, float *gsum, float *leaf, SCShared &sh)
+// Canonical sum of the n values held one per (thread, k) as v[k] <-> index k * 1024 + tid (entries at or beyond n
+// must be +0): 32 consecutive values by a warp butterfly (16..1), 8 such sums by a butterfly (4,2,1) = one leaf of
+// 256 values, leaves added left to right.  Result in every thread.  gsum needs n_pad / 32 floats, leaf n_pad / 256.
+template <int VPT>
+__device__ __forceinline__ float cta_canonical_sum(const float (&v)[VPT], int n, float *gsum, float *leaf)
 {
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
     const int ngroups = (n + 31) >> 5, nleaf = (n + 255) >> 8;
-    __syncthreads();
-    for (int g = w; g < ngroups; g += SC_WARPS) {
-        const int i = g * 32 + l;
-        float v = i < n ? vals[i] : 0.0f;
-        v = warp_sum(v);
-        if (l == 0) gsum[g] = v;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const float s = warp_sum(v[k]);
+        if (l == 0) gsum[k * SC_WARPS + w] = s;
     }
     __syncthreads();
-    for (int L = threadIdx.x; L < nleaf; L += SC_THREADS) {
+    if ((int)threadIdx.x < nleaf) {
+        const int L = threadIdx.x;
         float p[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) p[i] = (L * 8 + i) < ngroups ? gsum[L * 8 + i] : 0.0f;
@@ -141,13 +132,9 @@ __device__ __noinline__ float block_canonical_sum(const float *vals, int n, floa
         leaf[L] = p[0];
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float total = 0.0f;
-        for (int L = 0; L < nleaf; ++L) total = __fadd_rn(total, leaf[L]);
-        sh.bcast_f[0] = total;
-    }
-    __syncthreads();
-    return sh.bcast_f[0];
+    float total = leaf[0];
+    for (int L = 1; L < nleaf; ++L) total = __fadd_rn(total, leaf[L]);
+    return total;
 }
 
 // In-place descending bitonic sort of n_pad (power of two) 64-bit keys by the whole CTA.
@@ -197,160 +184,111 @@ __device__ __forceinline__ void rank_sort_desc(u64 *cand, SCShared &sh)
     __syncthreads();
 }
 
-// Sum of one int per thread over the CTA with a single barrier: per-warp sums go to one of two
-// alternating rows of sh.red_i, so the next call never overwrites a row that is still being read.
-__device__ __forceinline__ int block_sum_int(int v, SCShared &sh, int parity)
-{
-    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-    v = __reduce_add_sync(FULL, v);
-    if (l == 0) sh.red_i[parity][w] = v;
-    __syncthreads();
-    return __reduce_add_sync(FULL, sh.red_i[parity][l]);
-}
-
-// Named barrier for the first VS_THREADS threads of the CTA (the rest do not take part).
-constexpr int VS_THREADS = 256, VS_WARPS = VS_THREADS / 32;
-__device__ __forceinline__ void vs_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(VS_THREADS) : "memory"); }
-
-// "Column sum" of the entries of vals[0..n) that `pred(bits, index)` admits, and their number; called by
-// threads 0..VS_THREADS-1 only, result in every one of them.  Fixed order: thread t adds its entries
-// t, t+256, t+512, ... in ascending order; the 32 columns of a warp are combined by the butterfly
-// 16,8,4,2,1; the 8 warp sums by the butterfly 4,2,1.  Adding an admitted entry never lowers the result
-// (every step is a monotone rounding), which is what the threshold search below relies on.
-template <typename Pred>
-__device__ __forceinline__ float column_sum(const float *vals, int n, Pred pred, SCShared &sh, int &parity, int &count)
+// The M = min(CAND, n) largest (value, lower-index-first) entries of the n values v[k] <-> index k * 1024 + tid
+// (values >= 0, entries at or beyond n hold +0), sorted descending into cand[0..CAND) (padding = 0).  `vals` is the
+// same data in shared memory.
+//
+// The value of the M-th largest entry is found two bits per step (most significant first): a candidate threshold
+// is kept when at least M entries are at or above it.  A step is one pass over the registers and one barrier, and
+// the search stops as soon as a threshold separates exactly M entries.  Entries above the threshold are then
+// compacted and ordered by rank counting.
+template <int VPT>
+__device__ __forceinline__ void select_top_sorted(const float (&v)[VPT], const float *vals, int n, u64 *cand,
+                                                  SCShared &sh, int &parity)
 {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-    float s = 0.0f;
-    int c = 0;
-    for (int b = tid; b < n; b += VS_THREADS) {
-        const float v = vals[b];
-        if (pred(__float_as_uint(v), b)) { s = __fadd_rn(s, v); ++c; }
-    }
-    s = warp_sum(s);
-    c = __reduce_add_sync(FULL, c);
-    if (lane == 0) { sh.vs_f[parity][w] = s; sh.vs_i[parity][w] = c; }
-    vs_barrier();
-    float x = lane < VS_WARPS ? sh.vs_f[parity][lane] : 0.0f;
-    int y = lane < VS_WARPS ? sh.vs_i[parity][lane] : 0;
-    parity ^= 1;
-    x = __fadd_rn(x, __shfl_xor_sync(FULL, x, 4));
-    x = __fadd_rn(x, __shfl_xor_sync(FULL, x, 2));
-    x = __fadd_rn(x, __shfl_xor_sync(FULL, x, 1));
-    count = __reduce_add_sync(FULL, y);
-    return __shfl_sync(FULL, x, 0);
-}
-
-// The M = min(CAND, n) largest (value, lower-index-first) entries of vals[0..n), vals >= 0, sorted
-// descending into cand[0..CAND) (padding = 0).  Returns M.
-//
-// The value of the M-th largest entry is found bit by bit (most significant first): a bit is kept when
-// at least M entries are >= the candidate threshold.  Each step is one pass over the values and one
-// barrier, with no shared-memory atomics, and the search stops as soon as a threshold separates exactly
-// M entries.  Entries above the threshold are then compacted and ordered by rank counting.
-__device__ __noinline__ int select_top_sorted(const float *vals, int n, u64 *cand, SCShared &sh)
-{
-    const int tid = threadIdx.x, lane = tid & 31;
-    CQA_DBG(0);
-    __syncthreads();
-    CQA_DBG(1);
     if (tid == 0) sh.counter = 0;
     for (int i = tid; i < CAND; i += SC_THREADS) cand[i] = 0ull;
     const int M = n < CAND ? n : CAND;
     if (n <= CAND) {
         __syncthreads();
-        for (int b = tid; b < n; b += SC_THREADS) cand[b] = make_key(vals[b], b);
+        if (tid < n) cand[tid] = make_key(v[0], tid);    // n <= 256: one value per thread
     } else {
         unsigned thr = 0u;
         int n_ge = n;            // entries >= thr
-        int parity = 0;
-        const int w = tid >> 5;
-        // Two bits per step: three candidate thresholds are counted at once.  Only the first 256 threads search
-        // (named barrier): a step is a short dependent chain, and with all 32 warps the issue slots of their
-        // bookkeeping cost more than the shorter element loops save.
-        if (tid < VS_THREADS) {
 #pragma unroll 1
-            for (int bit = 30; bit >= 0 && n_ge != M; bit -= 2) {
-                const bool single = bit == 0;                 // 31 value bits: the last step decides one bit
-                const int lo = single ? 0 : bit - 1;
-                const unsigned t1 = thr | (1u << lo);                              // 01 (or 1)
-                const unsigned t2 = single ? 0xFFFFFFFFu : thr | (2u << lo);       // 10
-                const unsigned t3 = single ? 0xFFFFFFFFu : thr | (3u << lo);       // 11
-                unsigned l12 = 0, l3 = 0;                     // a thread holds at most 64 entries
-                for (int b = tid; b < n; b += VS_THREADS) {
-                    const unsigned v = __float_as_uint(vals[b]);
-                    l12 += (v >= t1 ? 1u : 0u) + (v >= t2 ? 1u << 16 : 0u);
-                    l3 += v >= t3 ? 1u : 0u;
-                }
-                l12 = __reduce_add_sync(FULL, l12);
-                l3 = __reduce_add_sync(FULL, l3);
-                if (lane == 0) { sh.vs_i[parity][w] = (int)l12; sh.red_i[parity][w] = (int)l3; }
-                vs_barrier();
-                const unsigned p12 = lane < VS_WARPS ? (unsigned)sh.vs_i[parity][lane] : 0u;
-                const unsigned p3 = lane < VS_WARPS ? (unsigned)sh.red_i[parity][lane] : 0u;
-                parity ^= 1;
-                const unsigned c12 = __reduce_add_sync(FULL, p12);   // totals stay below 2^15 per field
-                const int c3 = (int)__reduce_add_sync(FULL, p3);
-                const int c1 = (int)(c12 & 0xFFFFu), c2 = (int)(c12 >> 16);
-                if (!single && c3 >= M) { thr = t3; n_ge = c3; }
-                else if (!single && c2 >= M) { thr = t2; n_ge = c2; }
-                else if (c1 >= M) { thr = t1; n_ge = c1; }
+        for (int bit = 30; bit >= 0 && n_ge != M; bit -= 2) {
+            const bool single = bit == 0;                 // 31 value bits: the last step decides one bit
+            const int lo = single ? 0 : bit - 1;
+            const unsigned t1 = thr | (1u << lo);                              // 01 (or 1)
+            const unsigned t2 = single ? 0xFFFFFFFFu : thr | (2u << lo);       // 10
+            const unsigned t3 = single ? 0xFFFFFFFFu : thr | (3u << lo);       // 11
+            unsigned l12 = 0, l3 = 0;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const unsigned x = __float_as_uint(v[k]);
+                l12 += (x >= t1 ? 1u : 0u) + (x >= t2 ? 1u << 16 : 0u);
+                l3 += x >= t3 ? 1u : 0u;
             }
-            if (tid == 0) { sh.bcast_u[1] = thr; sh.bcast_i[4] = n_ge; }
+            l12 = __reduce_add_sync(FULL, l12);
+            l3 = __reduce_add_sync(FULL, l3);
+            if (lane == 0) { sh.red_u[parity][0][w] = l12; sh.red_u[parity][1][w] = l3; }
+            __syncthreads();
+            const unsigned c12 = __reduce_add_sync(FULL, sh.red_u[parity][0][lane]);   // each field stays below 2^15
+            const int c3 = (int)__reduce_add_sync(FULL, sh.red_u[parity][1][lane]);
+            parity ^= 1;
+            const int c1 = (int)(c12 & 0xFFFFu), c2 = (int)(c12 >> 16);
+            if (!single && c3 >= M) { thr = t3; n_ge = c3; }
+            else if (!single && c2 >= M) { thr = t2; n_ge = c2; }
+            else if (c1 >= M) { thr = t1; n_ge = c1; }
         }
-        __syncthreads();
-        thr = sh.bcast_u[1];
-        n_ge = sh.bcast_i[4];
-        parity = 0;
         // n_ge == M: the entries >= thr are the answer.  Otherwise thr is the value of the M-th largest
         // entry and several entries equal it: take everything above, then the lowest block ids among the equal.
         const bool ties = n_ge != M;
-        CQA_DBG(2);
         __syncthreads();   // cand is zeroed, sh.counter is 0
-        for (int b0 = tid - lane; b0 < n; b0 += SC_THREADS) {
-            const int b = b0 + lane;
-            const unsigned bits = b < n ? __float_as_uint(vals[b]) : 0u;
-            const bool take = b < n && (ties ? bits > thr : bits >= thr);
-            const unsigned who = __ballot_sync(FULL, take);
-            if (who) {
-                int base = 0;
-                if (lane == 0) base = atomicAdd(&sh.counter, __popc(who));
-                base = __shfl_sync(FULL, base, 0);
-                if (take) cand[base + __popc(who & ((1u << lane) - 1u))] = make_key(vals[b], b);
-            }
+        unsigned take = 0;
+        int mine = 0;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const unsigned x = __float_as_uint(v[k]);
+            const bool t = (k * SC_THREADS + tid) < n && (ties ? x > thr : x >= thr);
+            take |= t ? 1u << k : 0u;
+            mine += t ? 1 : 0;
         }
-        CQA_DBG(3);
+        // exclusive scan of the per-lane counts over the warp, one atomic per warp for the base
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int x = __shfl_up_sync(FULL, incl, o);
+            if (lane >= o) incl += x;
+        }
+        const int warp_total = __shfl_sync(FULL, incl, 31);
+        int base = 0;
+        if (lane == 31 && warp_total > 0) base = atomicAdd(&sh.counter, warp_total);
+        base = __shfl_sync(FULL, base, 31);
+        int pos = base + incl - mine;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k)
+            if (take & (1u << k)) cand[pos++] = make_key(v[k], k * SC_THREADS + tid);
         if (ties) {
             // entries equal to the threshold fill the remaining places in block order: an ordered compaction,
             // 1024 consecutive blocks per round (per-warp counts, then an exclusive scan over the warps)
             __syncthreads();
             int taken = sh.counter;
+            int par = 0;
             for (int b0 = 0; b0 < n && taken < M; b0 += SC_THREADS) {
                 const int b = b0 + tid;
                 const bool eq = b < n && __float_as_uint(vals[b]) == thr;
                 const unsigned who = __ballot_sync(FULL, eq);
-                if (lane == 0) sh.red_i[parity][w] = __popc(who);
+                if (lane == 0) sh.red_i[par][w] = __popc(who);
                 __syncthreads();
-                const int cw = sh.red_i[parity][lane];
-                parity ^= 1;
-                int incl = cw;   // inclusive scan of the per-warp counts
+                const int cw = sh.red_i[par][lane];
+                par ^= 1;
+                int inc2 = cw;   // inclusive scan of the per-warp counts
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
-                    const int v = __shfl_up_sync(FULL, incl, o);
-                    if (lane >= o) incl += v;
+                    const int x = __shfl_up_sync(FULL, inc2, o);
+                    if (lane >= o) inc2 += x;
                 }
-                const int before = __shfl_sync(FULL, incl - cw, w);
-                const int pos = taken + before + __popc(who & ((1u << lane) - 1u));
-                if (eq && pos < M) cand[pos] = make_key(vals[b], b);
-                taken += __shfl_sync(FULL, incl, 31);
+                const int before = __shfl_sync(FULL, inc2 - cw, w);
+                const int p = taken + before + __popc(who & ((1u << lane) - 1u));
+                if (eq && p < M) cand[p] = make_key(vals[b], b);
+                taken += __shfl_sync(FULL, inc2, 31);
             }
         }
     }
     __syncthreads();
-    CQA_DBG(4);
     rank_sort_desc(cand, sh);
-    CQA_DBG(5);
-    return M;
 }
 
 // Descending insertion of k into a sorted list of 4.
@@ -381,22 +319,99 @@ __device__ __forceinline__ void warp_top4(u64 (&t)[4], u64 (&out)[4])
     }
 }
 
-// Dynamic shared memory: A[n_pad] B[n_pad] C[n_pad] (floats), cand[CAND] (u64), cum[CAND], gsum, leaf, mask[n_pad]
-// (bytes).  The full-sort fallbacks alias their keys over B and C.
-#ifdef CQA_WARM_REPEAT
-#define CQA_BODY_QUAL __device__ __noinline__   // instrumentation: the body runs twice, the second time with warm code
-#else
-#define CQA_BODY_QUAL __device__ __forceinline__
-#endif
+// "Column sums" of the value check, three admission thresholds at once: of the entries e[k] <-> index k * 1024 + tid
+// (entries at or beyond n hold +0 and are never admitted because thresholds are >= 1), column t (= thread t,
+// 0..1023) adds its admitted members t, t + 1024, ... in ascending order; the 32 columns of a warp are combined by
+// the butterfly 16,8,4,2,1 and the 32 warp sums by the same butterfly.  f[i] = sum of the entries with bits >= t[i],
+// c[i] = their number; results in every thread.  Adding an admitted entry never lowers a sum (every step is a
+// monotone rounding), which is what the threshold search relies on.
+template <int VPT>
+__device__ __forceinline__ void column_sums3(const float (&e)[VPT], unsigned t1, unsigned t2, unsigned t3,
+                                             SCShared &sh, int &parity, float (&f)[3], int (&c)[3])
+{
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    unsigned n12 = 0, n3 = 0;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const unsigned x = __float_as_uint(e[k]);
+        if (x >= t1) { s1 = __fadd_rn(s1, e[k]); n12 += 1u; }
+        if (x >= t2) { s2 = __fadd_rn(s2, e[k]); n12 += 1u << 16; }
+        if (x >= t3) { s3 = __fadd_rn(s3, e[k]); n3 += 1u; }
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    s3 = warp_sum(s3);
+    n12 = __reduce_add_sync(FULL, n12);
+    n3 = __reduce_add_sync(FULL, n3);
+    if (lane == 0) {
+        sh.red_f3[parity][0][w] = s1;
+        sh.red_f3[parity][1][w] = s2;
+        sh.red_f3[parity][2][w] = s3;
+        sh.red_u[parity][0][w] = n12;
+        sh.red_u[parity][1][w] = n3;
+    }
+    __syncthreads();
+    f[0] = warp_sum(sh.red_f3[parity][0][lane]);
+    f[1] = warp_sum(sh.red_f3[parity][1][lane]);
+    f[2] = warp_sum(sh.red_f3[parity][2][lane]);
+    const unsigned c12 = __reduce_add_sync(FULL, sh.red_u[parity][0][lane]);
+    c[2] = (int)__reduce_add_sync(FULL, sh.red_u[parity][1][lane]);
+    c[0] = (int)(c12 & 0xFFFFu);
+    c[1] = (int)(c12 >> 16);
+    parity ^= 1;
+}
+
+// One column sum over the entries `pred(bits, block id)` admits (same order as column_sums3).
+template <int VPT, typename Pred>
+__device__ __forceinline__ float column_sum1(const float (&e)[VPT], int n, Pred pred, SCShared &sh, int &parity, int &count)
+{
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    float s = 0.0f;
+    unsigned c = 0;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int b = k * SC_THREADS + tid;
+        if (b < n && pred(__float_as_uint(e[k]), b)) { s = __fadd_rn(s, e[k]); ++c; }
+    }
+    s = warp_sum(s);
+    c = __reduce_add_sync(FULL, c);
+    if (lane == 0) { sh.red_f3[parity][0][w] = s; sh.red_u[parity][0][w] = c; }
+    __syncthreads();
+    const float r = warp_sum(sh.red_f3[parity][0][lane]);
+    count = (int)__reduce_add_sync(FULL, sh.red_u[parity][0][lane]);
+    parity ^= 1;
+    return r;
+}
+
 template <typename T2>
-CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const cqa_workspace &ws, const void *q,
-                                int q_dtype, long nq, long nact, const float *u, long u_ld, int n_pad, int hi,
-                                int base_width, int two_level, int rk, int phases, int role_base)
+__device__ __forceinline__ void rescore_block(const cqa_cache &c, const void *q, int q_dtype, int h, long bid,
+                                              long n_scoring_tokens, float q_scale, float &s, float &lm)
+{
+    fp16_block_score_warp<T2>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
+}
+// Tier-2 dtype dispatch at run time: the re-score is a few warps of one role, the rest of the kernel does not
+// depend on the dtype.
+__device__ __noinline__ void rescore_block_any(const cqa_cache &c, const void *q, int q_dtype, int h, long bid,
+                                                  long n_scoring_tokens, float q_scale, float &s, float &lm)
+{
+    if (c.t2_dtype == CQA_BF16) rescore_block<__nv_bfloat16>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
+    else if (c.t2_dtype == CQA_F16) rescore_block<__half>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
+    else rescore_block<float>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
+}
+
+// Dynamic shared memory: A[n_pad] B[n_pad] C[n_pad] (floats), cand[CAND] (u64), cum[CAND], gsum, leaf, mask[n_pad]
+// (bytes).  The full-sort fallback aliases its keys over B and C.
+template <int VPT>
+__global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa_knobs kn, cqa_workspace ws, const void *q,
+                                                                int q_dtype, long nq, long nact, const float *u, long u_ld,
+                                                                int n_pad, int hi, int base_width, int two_level, int rk,
+                                                                int phases, int role_base)
 {
     extern __shared__ __align__(16) unsigned char dsm[];
-    float *A = reinterpret_cast<float *>(dsm);                 // m_b, later mass*eta
+    float *A = reinterpret_cast<float *>(dsm);                 // m_b (role 2: mass*eta)
     float *B = A + n_pad;                                      // block log-mass ell
-    float *C = B + n_pad;                                      // mass, then mass fraction
+    float *C = B + n_pad;                                      // mass fraction
     u64 *cand = reinterpret_cast<u64 *>(C + n_pad);
     float *cum = reinterpret_cast<float *>(cand + CAND);
     float *gsum = cum + CAND;
@@ -407,6 +422,9 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
     __shared__ float top_i8[CQA_MAX_RANKING_K], top_f16[CQA_MAX_RANKING_K], top_lm[CQA_MAX_RANKING_K];
     __shared__ float s_delta;
     __shared__ u64 s_top[SC_WARPS * 4];
+
+    grid_dependency_wait();
+    peer_wait(ws.wait_flags, ws.wait_n, ws.wait_skip, ws.wait_value, ws.wait_status, 1, ws.wait_spins);
 
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv = h / c.gqa_group;
@@ -432,105 +450,118 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
     const bool fused = (phases & PH_SELECT) != 0;
     const bool compute_frac = role == 0 || (role == 2 && fused);
     const bool have_int4 = c.values_int4_packed != nullptr && c.values_int4_errors != nullptr;
-#ifdef CQA_PHASE_CLOCKS
-    long long phase_clk[16];
-    for (int i = 0; i < 16; ++i) phase_clk[i] = 0;
-#endif
-    CQA_CLK(0);
+    int parity = 0;
 
-    // ---- one round of global loads, all issued up front: m_b, S_b; the exploration draw (role 0);
-    // eta_b and, when only certifying, the mass fractions (role 2)
-    const bool explore_on = kn.exploration_rate > 0.0f;
+    // ---- one round of global loads: m_b, S_b; the exploration uniforms (role 0); eta_b and, when only
+    // certifying, the mass fractions (role 2)
+    const bool explore_on = role == 0 && kn.exploration_rate > 0.0f;
     const float *eta = have_int4 ? c.values_int4_errors + (long)kv * (sharded_in ? ws.shard_chunk : c.max_blocks) : nullptr;
+    float m[VPT], ell[VPT], x[VPT];
+    unsigned ebits = 0;       // bit k: block k * 1024 + tid is an exploration candidate
     float mg = -INFINITY;
-    // four blocks per thread and round: all global loads of a round are issued before any is used
-    for (int b0 = tid; b0 < n_pad; b0 += 4 * SC_THREADS) {
-        float m4[4], s4[4], x4[4];
+    {
+        float s[VPT];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int b = b0 + k * SC_THREADS;
-            m4[k] = 0.0f; s4[k] = 1.0f; x4[k] = 0.0f;
+        for (int k = 0; k < VPT; ++k) {
+            const int b = k * SC_THREADS + tid;
+            m[k] = 0.0f; s[k] = 1.0f; x[k] = 0.0f;
             if (b < n) {
                 const long gb = gcol(b);
-                m4[k] = mb[gb];
-                s4[k] = sb[gb];
+                m[k] = mb[gb];
+                s[k] = sb[gb];
                 if (role == 0) {
-                    if (explore_on && u != nullptr) x4[k] = u[(long)h * u_ld + b];
+                    if (explore_on && u != nullptr) x[k] = u[(long)h * u_ld + b];
                 } else if (role == 2) {
-                    x4[k] = eta ? eta[gb] : 0.0f;
+                    x[k] = eta ? eta[gb] : 0.0f;
                 }
+            }
+        }
+        if (explore_on && u == nullptr) {
+#pragma unroll
+            for (int j = 0; j < (VPT + 3) / 4; ++j) {
+                const uint4 r = philox4(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)tid | ((unsigned)j << 10));
+                const unsigned wds[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (4 * j + i < VPT) x[4 * j + i] = uniform_of_word(wds[i]);
             }
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int b = b0 + k * SC_THREADS;
-            if (b >= n_pad) continue;
-            if (b < n) {
-                const float m = m4[k];
-                const float s = fmaxf(s4[k], 1e-30f);
-                unsigned char ebit = 0;
-                if (role == 0 && explore_on) {
-                    const float uv = u != nullptr ? x4[k]
-                                                  : philox_uniform(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)b);
-                    ebit = uv < kn.exploration_rate ? 2 : 0;
-                }
-                if (role == 2) {
-                    if (!fused) C[b] = mf[b];
-                    A[b] = x4[k];                     // eta_b: role 2 never needs m_b
+        for (int k = 0; k < VPT; ++k) {
+            const int b = k * SC_THREADS + tid;
+            if (b < n_pad) {
+                unsigned char eb = 0;
+                if (b < n) {
+                    ell[k] = __fadd_rn(clog(fmaxf(s[k], 1e-30f)), m[k]);
+                    if (explore_on && x[k] < kn.exploration_rate) { eb = 2; ebits |= 1u << k; }
+                    A[b] = role == 2 ? x[k] : m[k];
+                    B[b] = ell[k];
+                    mg = fmaxf(mg, m[k]);
                 } else {
-                    A[b] = m;
+                    ell[k] = -INFINITY;
                 }
-                B[b] = __fadd_rn(clog(s), m);
-                mask[b] = ebit;                       // bit 1: exploration candidate, bit 0: selected (set later)
-                mg = fmaxf(mg, m);
+                mask[b] = eb;                         // bit 1: exploration candidate, bit 0: selected (set later)
             } else {
-                mask[b] = 0;
+                ell[k] = -INFINITY;
             }
         }
     }
-    CQA_CLK(1);
+    float f[VPT];             // mass fractions (roles 0 and 2)
     float total = 0.0f;
     if (compute_frac) {
-        mg = block_max(mg, sh);
-        for (int b = tid; b < n; b += SC_THREADS) C[b] = cexp(__fsub_rn(B[b], mg));
-        total = fmaxf(block_canonical_sum(C, n, gsum, leaf, sh), 1e-30f);
-        for (int b = tid; b < n_pad; b += SC_THREADS) {
+        mg = cta_max(mg, sh, parity);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) f[k] = (k * SC_THREADS + tid) < n ? cexp(__fsub_rn(ell[k], mg)) : 0.0f;
+        total = fmaxf(cta_canonical_sum<VPT>(f, n, gsum, leaf), 1e-30f);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int b = k * SC_THREADS + tid;
             if (b < n) {
-                const float f = __fdiv_rn(C[b], total);
-                C[b] = f;
-                if (role == 0) mf[b] = f;
+                f[k] = __fdiv_rn(f[k], total);
+                C[b] = f[k];
+                if (role == 0) mf[b] = f[k];
             }
         }
+    } else if (role == 2) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int b = k * SC_THREADS + tid;
+            f[k] = b < n ? mf[b] : 0.0f;
+            if (b < n) C[b] = f[k];
+        }
     }
+
     if (role == 0) {
-        CQA_CLK(2);
         // the `hi` heaviest blocks, sorted
         int32_t *sidx = ws.sorted_idx + (long)h * ws.sel_width;
         float *scum = ws.sorted_cumsum + (long)h * ws.sel_width;
         const bool narrow = hi <= CAND;
         if (narrow) {
-            select_top_sorted(C, n, cand, sh);
+            __syncthreads();   // C is complete (the tie path of the search reads it)
+            select_top_sorted<VPT>(f, C, n, cand, sh, parity);
+            if (tid < CAND) cum[tid] = key_val(cand[tid]);
+            __syncthreads();
             if (tid == 0) {
-                // sequential prefix sum, eight values fetched ahead of the dependent adds
+                // sequential prefix sum in place, four values per shared-memory access
                 float run = 0.0f;
-                for (int j0 = 0; j0 < hi; j0 += 8) {
-                    float v[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = key_val(cand[j0 + i]);   // cand is padded to 256
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        run = (j0 + i) == 0 ? v[i] : __fadd_rn(run, v[i]);
-                        v[i] = run;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) cum[j0 + i] = v[i];
+                float4 *c4 = reinterpret_cast<float4 *>(cum);
+                float4 nxt = c4[0];
+                for (int j0 = 0; j0 < hi; j0 += 4) {
+                    float4 cur = nxt;
+                    if (j0 + 4 < CAND) nxt = c4[(j0 >> 2) + 1];
+                    cur.x = j0 == 0 ? cur.x : __fadd_rn(run, cur.x);
+                    cur.y = __fadd_rn(cur.x, cur.y);
+                    cur.z = __fadd_rn(cur.y, cur.z);
+                    cur.w = __fadd_rn(cur.z, cur.w);
+                    run = cur.w;
+                    c4[j0 >> 2] = cur;
                 }
+            } else if (tid >= 32 && tid < 32 + CAND) {
+                const int j = tid - 32;
+                if (j < hi) sidx[j] = key_idx(cand[j]);
             }
             __syncthreads();
-            for (int j = tid; j < hi; j += SC_THREADS) {
-                sidx[j] = key_idx(cand[j]);
-                scum[j] = cum[j];
-            }
+            if (tid < hi) scum[tid] = cum[tid];
         } else {
             // wide selections (k_max unset or very large): full sort, prefix sums straight to global memory
             u64 *keys = reinterpret_cast<u64 *>(B);   // ell and the fractions are rebuilt below
@@ -549,7 +580,6 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             }
             __syncthreads();
         }
-        CQA_CLK(3);
         // K*, Rung 1: the prefix sums are non-decreasing, so the first index with cum >= tau is the
         // number of entries below tau (one barrier-wide count each)
         const float *cs = narrow ? cum : scum;
@@ -612,33 +642,25 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             for (int j = tid; j < k_star; j += SC_THREADS) mask[sidx[j]] |= 1;
         }
         __syncthreads();
-        CQA_CLK(4);
         unsigned char *tm = ws.topk_mask + (long)h * ws.ld;
         unsigned char *em = ws.explore_mask + (long)h * ws.ld;
         int explored = 0;
         for (int b = tid; b < (int)nact; b += SC_THREADS) {
-            unsigned char m = 1, e = 0;
+            unsigned char mk1 = 1, e = 0;
             if (b < n) {
                 const unsigned char mk = mask[b];
-                m = mk & 1;
-                if (!m && (mk & 2)) { m = 1; e = 1; ++explored; }
+                mk1 = mk & 1;
+                if (!mk1 && (mk & 2)) { mk1 = 1; e = 1; ++explored; }
             }
-            tm[b] = m;
+            tm[b] = mk1;
             em[b] = e;
         }
-        if (explored) atomicAdd(&sh.counter, explored);
+        explored = __reduce_add_sync(FULL, explored);
+        if (lane == 0 && explored) atomicAdd(&sh.counter, explored);
         __syncthreads();
         if (tid == 0) ct->exploration_blocks = sh.counter;
-        if (!narrow) {
-            // the full sort overwrote ell and the fractions: rebuild them (each thread re-reads what it wrote)
-            for (int b = tid; b < n; b += SC_THREADS) {
-                B[b] = __fadd_rn(clog(fmaxf(sb[gcol(b)], 1e-30f)), A[b]);
-                C[b] = mf[b];
-            }
-        }
+        return;
     }
-    CQA_CLK(5);
-    if (role == 0) { CQA_CLK_FLUSH(1, 5); return; }
     __syncthreads();
 
     // ---- ranking / boundary / score consistency
@@ -663,9 +685,11 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             }
         } else if (rk <= 4) {
             u64 t4[4] = {0ull, 0ull, 0ull, 0ull};
-            for (int b = tid; b < n; b += SC_THREADS)
-                insert4(t4, ((u64)orderable(A[b]) << 32) | (u64)(0xFFFFFFFFu - (unsigned)b));
-            CQA_CLK(15);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int b = k * SC_THREADS + tid;
+                if (b < n) insert4(t4, ((u64)orderable(m[k]) << 32) | (u64)(0xFFFFFFFFu - (unsigned)b));
+            }
             u64 w4[4];
             warp_top4(t4, w4);
             if (lane == 0) {
@@ -698,9 +722,9 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
                     best = o > best ? o : best;
                 }
                 __syncthreads();
-                if (lane == 0) sh.red_u[warp] = best;
+                if (lane == 0) s_top[warp] = best;
                 __syncthreads();
-                best = sh.red_u[lane];
+                best = s_top[lane];
 #pragma unroll
                 for (int s = 16; s >= 1; s >>= 1) {
                     const u64 o = shfl_xor_u64(best, s);
@@ -714,7 +738,6 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             }
         }
         __syncthreads();
-        CQA_CLK(6);
         if (phases & PH_TOP_ONLY) {
             if (tid < CQA_MAX_RANKING_K) ct->top_blocks[tid] = tid < rk ? top_idx[tid] : -1;
             return;
@@ -732,7 +755,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
                 const long bl = (long)top_idx[warp] - ws.peer_first_block;
                 float s = 0.0f, lm = 0.0f;
                 if (bl >= 0 && bl < ws.peer_n_local)
-                    fp16_block_score_warp<T2>(c, q, q_dtype, h, bl, ws.peer_n_local * BS, kn.q_scale, s, lm);
+                    rescore_block_any(c, q, q_dtype, h, bl, ws.peer_n_local * BS, kn.q_scale, s, lm);
                 if (lane < ws.peer_world) {
                     float *d = ws.peer_xb[lane] + ((long)h * CQA_MAX_RANKING_K + warp) * 2;
                     d[0] = s;
@@ -740,7 +763,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
                 }
             } else if (!given) {
                 float s, lm;
-                fp16_block_score_warp<T2>(c, q, q_dtype, h, (long)top_idx[warp], nq * BS, kn.q_scale, s, lm);
+                rescore_block_any(c, q, q_dtype, h, (long)top_idx[warp], nq * BS, kn.q_scale, s, lm);
                 if (lane == 0) { top_f16[warp] = s; top_lm[warp] = lm; }
             }
         } else if (warp == rk) {
@@ -755,7 +778,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
         }
         if (overlap) {
             ubm = warp_max(ubm);
-            if (lane == 0) sh.red_f[warp] = ubm;
+            if (lane == 0) sh.red_f[0][warp] = ubm;
         }
         __syncthreads();
         if (peer_b) {
@@ -767,7 +790,7 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
                         st_release_sys(ws.peer_flags_b[p] + (long)ws.peer_rank * gridDim.x + h, ws.peer_step);
             }
             peer_wait(ws.peer_flags_b[ws.peer_rank] + h, ws.peer_world, ws.peer_rank, ws.peer_step, ws.wait_status,
-                      (long)gridDim.x);
+                      (long)gridDim.x, ws.wait_spins);
             if (tid < rk) {
                 float gs = 0.0f, gl = 0.0f;
                 for (int r = 0; r < ws.peer_world; ++r) {
@@ -780,40 +803,39 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             }
             __syncthreads();
         }
-        CQA_CLK(7);
         const float delta = s_delta;
         float ub = -INFINITY;
         if (kn.ranking_fallback) {
             if (overlap) {
-                ubm = warp_max(sh.red_f[lane]);
+                ubm = warp_max(sh.red_f[0][lane]);
             } else {
                 for (int b = tid; b < n; b += SC_THREADS) {
                     bool in_top = false;
                     for (int r = 0; r < rk; ++r) in_top |= (top_idx[r] == b);
                     if (!in_top) ubm = fmaxf(ubm, B[b]);
                 }
-                ubm = block_max(ubm, sh);
+                parity = 1;   // row 0 of red_f is not in use here, keep the two uses apart all the same
+                ubm = cta_max(ubm, sh, parity);
             }
             ub = __fadd_rn(ubm, delta);
         }
-        CQA_CLK(8);
         if (warp == 1) {
             // the certificate's per-candidate rows do not depend on the flag logic below
             ct->top_blocks[lane] = lane < rk ? top_idx[lane] : -1;
-            if (lane < CQA_LM_ROWS) ct->fp16_scores[lane] = lane < rk ? top_f16[lane] : 0.0f;
-            if (lane < CQA_LM_ROWS) ct->fp16_logmass[lane] = lane < rk ? top_lm[lane] : 0.0f;
+            ct->fp16_scores[lane] = lane < rk ? top_f16[lane] : 0.0f;
+            ct->fp16_logmass[lane] = lane < rk ? top_lm[lane] : 0.0f;
         }
         if (warp == 0) {
             // lane i owns candidate i (candidates are in INT8 order): its position in the stable
             // descending FP16 order, and in the descending FP16 log-mass order
             const bool mine = lane < rk;
-            const float f = mine ? top_f16[lane] : 0.0f;
+            const float fs = mine ? top_f16[lane] : 0.0f;
             const float lmv = mine ? top_lm[lane] : 0.0f;
             int pos16 = 0, poslm = 0;
 #pragma unroll 1
             for (int j = 0; j < rk; ++j) {
                 const float fj = top_f16[j], lj = top_lm[j];
-                pos16 += (fj > f || (fj == f && j < lane)) ? 1 : 0;
+                pos16 += (fj > fs || (fj == fs && j < lane)) ? 1 : 0;
                 poslm += (lj > lmv || (lj == lmv && j < lane)) ? 1 : 0;
             }
             const int r_main = min(kn.ranking_r, rk);
@@ -827,13 +849,13 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
             const unsigned who_2 = __ballot_sync(FULL, mine && pos16 == 1);
             float ell_r = -INFINITY;
             if (kn.ranking_fallback && r_main > 0) ell_r = __shfl_sync(FULL, lmv, __ffs(who_r) - 1);
-            const float top1 = __shfl_sync(FULL, f, __ffs(who_1) - 1);
-            const float top2 = who_2 ? __shfl_sync(FULL, f, __ffs(who_2) - 1) : top1;
+            const float top1 = __shfl_sync(FULL, fs, __ffs(who_1) - 1);
+            const float top2 = who_2 ? __shfl_sync(FULL, fs, __ffs(who_2) - 1) : top1;
             const int boundary = (kn.ranking_fallback && r_main > 0 && ub > ell_r) ? 1 : 0;
             int violation = 0;
             if (kn.score_consistency) {
                 const float thr = __fadd_rn(delta, kn.eps_guard);
-                violation = __any_sync(FULL, mine && fabsf(__fsub_rn(f, top_i8[lane])) > thr) ? 1 : 0;
+                violation = __any_sync(FULL, mine && fabsf(__fsub_rn(fs, top_i8[lane])) > thr) ? 1 : 0;
             }
             if (lane == 0) {
                 const int rung3 = (dis_main | boundary) ? 1 : 0;
@@ -868,9 +890,8 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
         ct->fp16_top1 = ct->fp16_top2 = ct->int8_top1 = 0.0f;
         for (int i = 0; i < CQA_MAX_RANKING_K; ++i) { ct->top_blocks[i] = -1; ct->fp16_scores[i] = 0.0f; ct->fp16_logmass[i] = 0.0f; }
     }
+    if (role == 1) return;
 
-    CQA_CLK(9);
-    if (role == 1) { CQA_CLK_FLUSH(6, 9); CQA_CLK_FLUSH(15, 15); return; }
     // ---- Rung-2 value check
     unsigned char *vm = ws.value_mask + (long)h * ws.ld;
     if (!have_int4) {
@@ -878,119 +899,94 @@ CQA_BODY_QUAL void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const c
         if (tid == 0) { ct->e_pre = 0.0f; ct->e_val = 0.0f; ct->value_promoted_blocks = 0; }
         return;
     }
-    __syncthreads();
-    for (int b = tid; b < n_pad; b += SC_THREADS) {
-        A[b] = b < n ? __fmul_rn(C[b], A[b]) : 0.0f;   // A held eta_b
-        mask[b] = 0;
-    }
-    CQA_CLK(10);
-    __syncthreads();
+    float e[VPT];             // contributions mass fraction * eta_b (+0 beyond n)
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) e[k] = (k * SC_THREADS + tid) < n ? __fmul_rn(f[k], x[k]) : 0.0f;
     // Greedy promotion, largest contribution first (ties: lower block id first): block b is promoted while the
     // column sum of the contributions ranked before it is below the excess.  That sum never decreases along the
     // ranking, so the promoted blocks are exactly those with contribution bits >= t0, where t0 is the largest
-    // threshold whose admitted set still sums to at least the excess; t0 is found bit by bit by the first 256
-    // threads (no sort, no serial walk).  Exact ties at t0 are resolved the same way over the block id.
-    if (tid == 0) { sh.bcast_f[1] = 0.0f; sh.bcast_f[2] = 0.0f; sh.bcast_i[1] = 0; sh.bcast_u[0] = 0xFFFFFFFFu; sh.bcast_i[3] = 0; }
-    if (tid < VS_THREADS) {
-        int parity = 0, cnt = 0;
-        const float e_pre_v = column_sum(A, n, [](unsigned, int) { return true; }, sh, parity, cnt);
-        const float excess = fmaxf(__fsub_rn(e_pre_v, kn.v_tolerance), 0.0f);
-        float promoted = 0.0f;
-        int n_prom = 0;
-        unsigned t0 = 0xFFFFFFFFu;   // nothing admitted
-        int id_bound = 0;
-        if (kn.value_mode_tight) {
-            if (excess > 0.0f) {
-                t0 = 0u;
-                int cnt_lo = cnt, cnt_hi = 0;     // entries >= t0, entries >= the upper end of the open range
-                float f_lo = e_pre_v;
+    // threshold whose admitted set still sums to at least the excess; t0 is found two bits per step (no sort, no
+    // serial walk).  Exact ties at t0 are resolved the same way over the block id.
+    int cnt = 0;
+    const float e_pre = column_sum1<VPT>(e, n, [](unsigned, int) { return true; }, sh, parity, cnt);
+    const float excess = fmaxf(__fsub_rn(e_pre, kn.v_tolerance), 0.0f);
+    float promoted = 0.0f;
+    int n_prom = 0;
+    unsigned t0 = 0xFFFFFFFFu;   // nothing admitted
+    int id_bound = 0;
+    if (kn.value_mode_tight) {
+        if (excess > 0.0f) {
+            t0 = 0u;
+            int cnt_lo = cnt, cnt_hi = 0;     // entries >= t0, entries >= the upper end of the open range
+            float f_lo = e_pre;
 #pragma unroll 1
-                for (int bit = 30; bit >= 0 && cnt_lo - cnt_hi > 1; --bit) {
-                    const unsigned trial = t0 | (1u << bit);
-                    int c = 0;
-                    const float f = column_sum(A, n, [trial](unsigned bits, int) { return bits >= trial; }, sh, parity, c);
-                    if (f >= excess) { t0 = trial; cnt_lo = c; f_lo = f; } else { cnt_hi = c; }
-                }
-                promoted = f_lo;
-                n_prom = cnt_lo;
-                id_bound = n;                     // every entry equal to t0 is admitted ...
-                if (cnt_lo - cnt_hi > 1) {
-                    // ... unless several entries equal t0: admit them in block order while the sum stays below
-                    int i0 = 0;
+            for (int bit = 30; bit >= 0 && cnt_lo - cnt_hi > 1; bit -= 2) {
+                const bool single = bit == 0;
+                const int lo = single ? 0 : bit - 1;
+                const unsigned t1 = t0 | (1u << lo);
+                const unsigned t2 = single ? 0xFFFFFFFFu : t0 | (2u << lo);
+                const unsigned t3 = single ? 0xFFFFFFFFu : t0 | (3u << lo);
+                float fs[3];
+                int cs3[3];
+                column_sums3<VPT>(e, t1, t2, t3, sh, parity, fs, cs3);
+                // thresholds ascend, their sums descend: keep the largest threshold that still reaches the excess
+                if (!single && fs[2] >= excess) { t0 = t3; cnt_lo = cs3[2]; f_lo = fs[2]; }
+                else if (!single && fs[1] >= excess) { t0 = t2; cnt_lo = cs3[1]; f_lo = fs[1]; cnt_hi = cs3[2]; }
+                else if (fs[0] >= excess) { t0 = t1; cnt_lo = cs3[0]; f_lo = fs[0]; cnt_hi = single ? cnt_hi : cs3[1]; }
+                else { cnt_hi = cs3[0]; }
+            }
+            promoted = f_lo;
+            n_prom = cnt_lo;
+            id_bound = n;                     // every entry equal to t0 is admitted ...
+            if (cnt_lo - cnt_hi > 1) {
+                // ... unless several entries equal t0: admit them in block order while the sum stays below
+                int i0 = 0;
 #pragma unroll 1
-                    for (int bit = 14; bit >= 0; --bit) {
-                        const int trial = i0 | (1 << bit);
-                        if (trial > n) continue;
-                        int c = 0;
-                        const unsigned tt = t0;
-                        const float g = column_sum(A, n, [tt, trial](unsigned bits, int b) { return bits > tt || (bits == tt && b < trial); }, sh, parity, c);
-                        if (g < excess) i0 = trial;
-                    }
-                    id_bound = i0 + 1;
+                for (int bit = 14; bit >= 0; --bit) {
+                    const int trial = i0 | (1 << bit);
+                    if (trial > n) continue;
+                    int cc = 0;
                     const unsigned tt = t0;
-                    const int ib = id_bound;
-                    promoted = column_sum(A, n, [tt, ib](unsigned bits, int b) { return bits > tt || (bits == tt && b < ib); }, sh, parity, n_prom);
+                    const float g = column_sum1<VPT>(e, n, [tt, trial](unsigned bits, int b) { return bits > tt || (bits == tt && b < trial); }, sh, parity, cc);
+                    if (g < excess) i0 = trial;
                 }
+                id_bound = i0 + 1;
+                const unsigned tt = t0;
+                const int ib = id_bound;
+                promoted = column_sum1<VPT>(e, n, [tt, ib](unsigned bits, int b) { return bits > tt || (bits == tt && b < ib); }, sh, parity, n_prom);
             }
-        } else {
-            const float vt = kn.v_tolerance;
-            promoted = column_sum(A, n, [eta, vt, &gcol](unsigned, int b) { return eta[gcol(b)] > vt; }, sh, parity, n_prom);
         }
-        if (tid == 0) {
-            sh.bcast_f[1] = promoted;
-            sh.bcast_f[2] = e_pre_v;
-            sh.bcast_i[1] = n_prom;
-            sh.bcast_u[0] = t0;
-            sh.bcast_i[3] = id_bound;
-        }
+    } else {
+        const float vt = kn.v_tolerance;
+        unsigned up = 0;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) up |= x[k] > vt ? 1u << k : 0u;
+        promoted = column_sum1<VPT>(e, n, [up, tid](unsigned, int b) { return ((up >> ((b - tid) / SC_THREADS)) & 1u) != 0; }, sh, parity, n_prom);
     }
-    __syncthreads();
-    CQA_CLK(12);
-    const float e_pre = sh.bcast_f[2];
-    {
-        const unsigned t0 = sh.bcast_u[0];
-        const int id_bound = sh.bcast_i[3];
-        for (int b = tid; b < n; b += SC_THREADS) {
-            bool up;
-            if (kn.value_mode_tight) {
-                const unsigned bits = __float_as_uint(A[b]);
-                up = t0 != 0xFFFFFFFFu && (bits > t0 || (bits == t0 && b < id_bound));
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int b = k * SC_THREADS + tid;
+        if (b < (int)nact) {
+            unsigned char upb;
+            if (b < n) {
+                if (kn.value_mode_tight) {
+                    const unsigned bits = __float_as_uint(e[k]);
+                    upb = (t0 != 0xFFFFFFFFu && (bits > t0 || (bits == t0 && b < id_bound))) ? 1 : 0;
+                } else {
+                    upb = x[k] > kn.v_tolerance ? 1 : 0;
+                }
             } else {
-                up = eta[gcol(b)] > kn.v_tolerance;
+                upb = kn.force_trailing_value_fp16 ? 1 : 0;
             }
-            mask[b] = up ? 1 : 0;
+            vm[b] = upb;
         }
     }
-    __syncthreads();
-    CQA_CLK(13);
-    for (int b = tid; b < (int)nact; b += SC_THREADS)
-        vm[b] = b < n ? mask[b] : (kn.force_trailing_value_fp16 ? 1 : 0);
     if (tid == 0) {
         ct->e_pre = e_pre;
-        ct->e_val = fmaxf(__fsub_rn(e_pre, sh.bcast_f[1]), 0.0f);
-        ct->value_promoted_blocks = sh.bcast_i[1];
-        if (sh.bcast_i[1] > 0) atomicOr(ws.any_flags + 3, 1);
+        ct->e_val = fmaxf(__fsub_rn(e_pre, promoted), 0.0f);
+        ct->value_promoted_blocks = n_prom;
+        if (n_prom > 0) atomicOr(ws.any_flags + 3, 1);
     }
-    CQA_CLK(14);
-    CQA_CLK_FLUSH(10, 14);
-#ifdef CQA_PHASE_CLOCKS
-    if (threadIdx.x == 0) for (int i = 0; i < 6; ++i) ct->fp16_scores[16 + i] = (float)(sh.dbg[i] - phase_clk[0]);
-#endif
-}
-
-template <typename T2>
-__global__ void __launch_bounds__(SC_THREADS) selcert_kernel(cqa_cache c, cqa_knobs kn, cqa_workspace ws, const void *q,
-                                                            int q_dtype, long nq, long nact, const float *u, long u_ld,
-                                                            int n_pad, int hi, int base_width, int two_level, int rk,
-                                                            int phases, int role_base)
-{
-    grid_dependency_wait();
-    peer_wait(ws.wait_flags, ws.wait_n, ws.wait_skip, ws.wait_value, ws.wait_status);
-#ifdef CQA_WARM_REPEAT
-    selcert_body<T2>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
-    __syncthreads();
-#endif
-    selcert_body<T2>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
 }
 
 static int next_pow2(long n)
@@ -1005,61 +1001,47 @@ static size_t selcert_smem(int n_pad)
     return (size_t)n_pad * 13 + (size_t)CAND * 12 + ((size_t)(n_pad >> 5) + 1 + (n_pad >> 8) + 2) * 4 + 64;
 }
 
-template <typename T2>
-static int selcert_launch_t(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q,
-                            int q_dtype, long nq, long nact, const float *u, long u_ld, int phases,
-                            cudaStream_t st)
+// Selection widths derived from the knobs (shared by the argument check and the launch).
+struct SelPlan {
+    int hi, base_width, two_level, rk;
+};
+static SelPlan sel_plan(const cqa_knobs *kn, long nq)
 {
-    const int H = c->kv_heads * c->gqa_group;
+    SelPlan p;
     const bool can_expand = kn->rung1_threshold >= 0.0f && kn->k_max > 0;
     long sel_kmax = kn->k_max;
-    int two_level = 0;
+    p.two_level = 0;
     if (can_expand) {
         long expanded = (long)ceil((double)kn->k_max * (double)kn->rung1_multiplier);
         if (expanded > nq) expanded = nq;
-        if (expanded > kn->k_max) { sel_kmax = expanded; two_level = 1; }
+        if (expanded > kn->k_max) { sel_kmax = expanded; p.two_level = 1; }
     }
-    const int hi = (int)(sel_kmax <= 0 ? nq : (sel_kmax < nq ? sel_kmax : nq));
-    const int base_width = two_level ? (int)(kn->k_max < hi ? kn->k_max : hi) : hi;
-    if ((phases & PH_SELECT) && ws->sel_width < hi) {
-        set_error("cqa_select: workspace sel_width %d < required %d", ws->sel_width, hi);
-        return CQA_ERR_INVALID;
-    }
+    p.hi = (int)(sel_kmax <= 0 ? nq : (sel_kmax < nq ? sel_kmax : nq));
+    p.base_width = p.two_level ? (int)(kn->k_max < p.hi ? kn->k_max : p.hi) : p.hi;
     int rk = kn->ranking_r > kn->top_k_fp16_keys ? kn->ranking_r : kn->top_k_fp16_keys;
     if (rk < 4) rk = 4;
     if (rk > nq) rk = (int)nq;
-    if (rk > CQA_MAX_RANKING_K - 1) {
-        set_error("cqa_certify: ranking set of %d blocks exceeds the limit %d", rk, CQA_MAX_RANKING_K - 1);
-        return CQA_ERR_TOO_LARGE;
-    }
-    const int n_pad = next_pow2(nq);
-    const size_t smem = selcert_smem(n_pad);
-    static size_t granted[SMEM_ATTR_DEVICES] = {};
-    const int rc_attr = check_cuda(ensure_dynamic_smem(selcert_kernel<T2>, smem, granted), "cudaFuncSetAttribute(selcert_kernel)");
-    if (rc_attr) return rc_attr;
-    if ((phases & PH_SELECT) && !(phases & PH_FLAGS_CLEARED)) {
-        int rc = check_cuda(cudaMemsetAsync(ws->any_flags, 0, (5 + H) * sizeof(int32_t), st),
-                            "cudaMemsetAsync(any_flags)");
-        if (rc) return rc;
-    }
-    // select only: role 0; certify only: roles 1 and 2; fused: all three
-    const int role_base = (phases & PH_SELECT) ? 0 : 1;
-    int n_roles = (phases & PH_SELECT) ? ((phases & PH_CERTIFY) ? 3 : 1) : 2;
-    if (phases & PH_GIVEN) n_roles = 1;   // role 1 alone
-    dim3 grid((unsigned)H, (unsigned)n_roles);
-    // chained to the score kernel only in the fused step (a memset precedes the launch otherwise)
-    const bool chained = (phases & PH_FLAGS_CLEARED) != 0;
-    return check_cuda(launch_chained(selcert_kernel<T2>, grid, dim3(SC_THREADS), smem, st, chained, *c, *kn, *ws, q, q_dtype,
-                                     nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base),
-                      "selcert_kernel");
+    p.rk = rk;
+    return p;
 }
 
-int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
-                   long nq, long nact, const float *u, long u_ld, int phases, cudaStream_t st)
+// Every argument check of the selector / certifier launch; nothing is launched or copied here.
+int selcert_check(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, long nq, int phases)
 {
     if (nq <= 0) { set_error("selector: needs at least one quantised block"); return CQA_ERR_INVALID; }
     if (nq > CQA_MAX_SORT_BLOCKS) {
         set_error("selector: %ld quantised blocks exceed the limit %d", nq, CQA_MAX_SORT_BLOCKS);
+        return CQA_ERR_TOO_LARGE;
+    }
+    if (nq > ws->ld && ws->shard_stride <= 0) { set_error("selector: workspace ld %ld < %ld blocks", (long)ws->ld, nq); return CQA_ERR_INVALID; }
+    if (c->t2_dtype < 0 || c->t2_dtype > 2) { set_error("selector: unknown Tier-2 dtype %d", c->t2_dtype); return CQA_ERR_INVALID; }
+    const SelPlan p = sel_plan(kn, nq);
+    if ((phases & PH_SELECT) && ws->sel_width < p.hi) {
+        set_error("cqa_select: workspace sel_width %d < required %d", ws->sel_width, p.hi);
+        return CQA_ERR_INVALID;
+    }
+    if (p.rk > CQA_MAX_RANKING_K - 1) {
+        set_error("cqa_certify: ranking set of %d blocks exceeds the limit %d", p.rk, CQA_MAX_RANKING_K - 1);
         return CQA_ERR_TOO_LARGE;
     }
     if (phases & PH_CERTIFY) {
@@ -1078,13 +1060,51 @@ int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace 
             return CQA_ERR_INVALID;
         }
     }
-    switch (c->t2_dtype) {
-    case CQA_F32: return selcert_launch_t<float>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, st);
-    case CQA_F16: return selcert_launch_t<__half>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, st);
-    case CQA_BF16: return selcert_launch_t<__nv_bfloat16>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, st);
+    return CQA_OK;
+}
+
+template <int VPT>
+static int selcert_launch_v(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q,
+                            int q_dtype, long nq, long nact, const float *u, long u_ld, int phases, int n_pad,
+                            cudaStream_t st)
+{
+    const int H = c->kv_heads * c->gqa_group;
+    const SelPlan p = sel_plan(kn, nq);
+    const size_t smem = selcert_smem(n_pad);
+    static size_t granted[SMEM_ATTR_DEVICES] = {};
+    const int rc_attr = check_cuda(ensure_dynamic_smem(selcert_kernel<VPT>, smem, granted), "cudaFuncSetAttribute(selcert_kernel)");
+    if (rc_attr) return rc_attr;
+    if ((phases & PH_SELECT) && !(phases & PH_FLAGS_CLEARED)) {
+        int rc = check_cuda(cudaMemsetAsync(ws->any_flags, 0, (5 + H) * sizeof(int32_t), st),
+                            "cudaMemsetAsync(any_flags)");
+        if (rc) return rc;
     }
-    set_error("selector: unknown Tier-2 dtype %d", c->t2_dtype);
-    return CQA_ERR_INVALID;
+    // select only: role 0; certify only: roles 1 and 2; fused: all three
+    const int role_base = (phases & PH_SELECT) ? 0 : 1;
+    int n_roles = (phases & PH_SELECT) ? ((phases & PH_CERTIFY) ? 3 : 1) : 2;
+    if (phases & PH_GIVEN) n_roles = 1;   // role 1 alone
+    dim3 grid((unsigned)H, (unsigned)n_roles);
+    // chained to the score kernel only in the fused step (a memset precedes the launch otherwise)
+    const bool chained = (phases & PH_FLAGS_CLEARED) != 0;
+    return check_cuda(launch_chained(selcert_kernel<VPT>, grid, dim3(SC_THREADS), smem, st, chained, *c, *kn, *ws, q, q_dtype,
+                                     nq, nact, u, u_ld, n_pad, p.hi, p.base_width, p.two_level, p.rk, phases, role_base),
+                      "selcert_kernel");
+}
+
+int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, int q_dtype,
+                   long nq, long nact, const float *u, long u_ld, int phases, cudaStream_t st)
+{
+    const int rc = selcert_check(c, kn, ws, q, nq, phases);
+    if (rc) return rc;
+    const int n_pad = next_pow2(nq);
+    switch (n_pad / SC_THREADS) {
+    case 0:
+    case 1: return selcert_launch_v<1>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
+    case 2: return selcert_launch_v<2>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
+    case 4: return selcert_launch_v<4>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
+    case 8: return selcert_launch_v<8>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
+    default: return selcert_launch_v<16>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
+    }
 }
 
 int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq, long nact,

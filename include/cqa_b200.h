@@ -197,7 +197,7 @@ typedef struct cqa_workspace {
     int32_t wait_n;
     int32_t wait_skip;
     int32_t wait_value;
-    int32_t reserved2;
+    int32_t wait_spins;          /* polls of one flag before giving up; 0 = the default (about half a second) */
     int32_t *wait_status;
     /* Exchange B inside the selector (cqa_sharded_layer_step): the ranking-check CTA of a head re-scores the
      * top-list blocks this rank owns ([peer_first_block, +peer_n_local), local block ids), writes (score, log-mass)

@@ -173,26 +173,26 @@ float cqa_o_canonical_sum(const float *x, long n)
 }
 
 /* "Column sum" used by the Rung-2 value check: of the values x[i] with include[i] != 0 (all when include is
- * NULL), column t (0..255) adds its members i = t, t+256, ... in ascending order; the 32 columns of each group of
- * 32 are combined by a butterfly (strides 16..1), the 8 group sums by a butterfly (strides 4,2,1).  Adding a
+ * NULL), column t (0..1023) adds its members i = t, t+1024, ... in ascending order; the 32 columns of each group
+ * of 32 are combined by a butterfly (strides 16..1), and the 32 group sums by the same butterfly.  Adding a
  * non-negative member never lowers the result. */
 float cqa_o_column_sum(const float *x, const unsigned char *include, long n)
 {
-    float col[256];
-    for (int t = 0; t < 256; ++t) {
+    float col[1024];
+    for (int t = 0; t < 1024; ++t) {
         float s = 0.0f;
-        for (long i = t; i < n; i += 256)
+        for (long i = t; i < n; i += 1024)
             if (!include || include[i]) s = s + x[i];
         col[t] = s;
     }
-    float g[8];
-    for (int w = 0; w < 8; ++w) {
+    float g[32];
+    for (int w = 0; w < 32; ++w) {
         float *p = col + w * 32;
         for (int s = 16; s >= 1; s >>= 1)
             for (int i = 0; i < s; ++i) p[i] = p[i] + p[i + s];
         g[w] = p[0];
     }
-    for (int s = 4; s >= 1; s >>= 1)
+    for (int s = 16; s >= 1; s >>= 1)
         for (int i = 0; i < s; ++i) g[i] = g[i] + g[i + s];
     return g[0];
 }

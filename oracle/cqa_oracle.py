@@ -86,7 +86,7 @@ def canonical_sum(x) -> np.float32:
 
 
 def column_sum(x, include=None) -> np.float32:
-    """Sum of x[include] in the fixed column order of the Rung-2 value check (256 columns, butterflies)."""
+    """Sum of x[include] in the fixed column order of the Rung-2 value check (1024 columns, butterflies)."""
     x = _c(x, np.float32)
     inc = None if include is None else _c(include, np.uint8)
     return f32(lib().cqa_o_column_sum(_p(x), _p(inc), C.c_long(x.size)))
@@ -428,6 +428,7 @@ def adaptive_select(m_b, S_b, tau_cov, k_min, k_max, rung1_threshold=0.02, rung1
     tau_act = np.zeros((H,), dtype=np.float32)
     trig = np.zeros((H,), dtype=bool)
     mask = np.zeros((H, nq), dtype=bool)
+    kmargin = np.full((H,), np.inf)
     for h in range(H):
         order = np.argsort(-frac[h], kind="stable")[:hi]
         cum = seq_cumsum(frac[h][order])
@@ -451,7 +452,9 @@ def adaptive_select(m_b, S_b, tau_cov, k_min, k_max, rung1_threshold=0.02, rung1
             if rung1_threshold is not None and rung1_threshold >= 0 and k_max is not None:
                 trig[h] = bool(tl_e > f32(rung1_threshold))
         mask[h, order[: k_star[h]]] = True
-    return dict(mass_frac=frac, ell=ell, m_global=mg, total=tot, sorted_idx=sorted_idx,
+        near = [abs(float(cum[j]) - float(tau32)) for j in (k_star[h] - 2, k_star[h] - 1) if 0 <= j < hi]
+        kmargin[h] = min(near) if near else np.inf
+    return dict(kstar_margin=kmargin, mass_frac=frac, ell=ell, m_global=mg, total=tot, sorted_idx=sorted_idx,
                 sorted_cumsum=sorted_cumsum, k_star=k_star, tail_mass=tail, tau_actual=tau_act,
                 rung1_trigger=trig, topk_mask=mask)
 
@@ -464,6 +467,7 @@ def value_check(frac, eta, gqa_group, v_tolerance, mode="tight"):
     e_pre = np.array([column_sum(e[h]) for h in range(H)], dtype=np.float32)
     unsafe = np.zeros((H, nq), dtype=bool)
     promoted = np.zeros((H,), dtype=np.float32)
+    margin = np.full((H,), np.inf)
     vt = f32(v_tolerance)
     if mode == "tight":
         # Greedy promotion over the descending order (ties: lower block id first): the entry at position j is
@@ -489,13 +493,17 @@ def value_check(frac, eta, gqa_group, v_tolerance, mode="tight"):
                 else:
                     hi = mid - 1
             unsafe[h, order[: lo + 1]] = True
-            promoted[h] = before(lo + 1)
+            # decision margins at the promotion boundary, relative to the excess: how far the last "still below"
+            # and the first "reached" column sums are from the excess they were compared with
+            below, reached = before(lo), before(lo + 1)
+            margin[h] = min(float(excess - below), float(reached - excess) if lo + 1 < nq else np.inf) / float(excess)
+            promoted[h] = reached
     else:
         unsafe = eta[kv_idx][:, :nq] > vt
         for h in range(H):
             promoted[h] = column_sum(e[h], unsafe[h])
     e_val = np.maximum(e_pre - promoted, f32(0.0)).astype(np.float32)
-    return dict(e=e, e_pre=e_pre, unsafe=unsafe, promoted=promoted, e_val=e_val)
+    return dict(e=e, e_pre=e_pre, unsafe=unsafe, promoted=promoted, e_val=e_val, margin=margin)
 
 
 def layer_step(cache: OracleCache, q, gqa_group, q_scale=None, *, v_tolerance, top_k_fp16_keys=0,
@@ -576,7 +584,7 @@ def layer_step(cache: OracleCache, q, gqa_group, q_scale=None, *, v_tolerance, t
     # value check (:1940-2058)
     vc = value_check(sel["mass_frac"], cache.values_int4_errors[:, :nq], gqa_group, v_tolerance,
                      value_error_mode)
-    R.update(e_pre=vc["e_pre"], e_val=vc["e_val"], value_unsafe_mask=vc["unsafe"])
+    R.update(e_pre=vc["e_pre"], e_val=vc["e_val"], value_unsafe_mask=vc["unsafe"], value_margin=vc["margin"])
     vmask = np.zeros((H, nact), dtype=bool)
     vmask[:, :nq] = vc["unsafe"]
     if trailing:
