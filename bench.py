@@ -1,17 +1,18 @@
 """Benchmark: certified quantised decode attention, µs per layer per decode step.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--context 32768] [--layers 8] [--planted 64]
+                    [--context 131072] [--layers 8] [--planted 64]
 
-Workload (N=1): the single-GPU configuration of the headline metric — Llama-3.1-8B
+Workload (N=1): the configuration the headline target is stated on - Llama-3.1-8B
 attention geometry (32 query heads, 8 KV heads, head_dim 128), batch 1,
-context 32768, bf16 Q/K/V ~ N(0,1) with 4 outlier key channels per head (x8)
+context 131072, bf16 Q/K/V ~ N(0,1) with 4 outlier key channels per head (x8)
 and 64 planted key blocks (cosine 0.9 to the query), INT8 keys / INT4 g16
 values, paper certification knobs; every decode step appends one seeded token
 and runs the certified attention chain.  A "step" is one token through
 `--layers` independent layer caches (distinct caches, so the working set
 between two visits of the same cache is far larger than L2, as in a real
-32-layer decode); the metric is step time / layers.
+32-layer decode); the metric is step time / layers.  The 32K configuration is
+measured in the same run and reported under "ctx32k".
 
 The default run prints ONE JSON line on rank 0.  `value` is the device-timed
 number with inputs resident in HBM; `e2e` is the same metric through the public
@@ -22,7 +23,7 @@ oracle (a port of the reference's algorithm) on this host.
 --impl reference times the reference's own algorithm on the host cores.  The
 reference is Python + Triton with no CPU implementation that can travel to this
 box, so that arm runs the CPU oracle port (oracle/cqa_oracle.*) with all host
-threads on the same workload.
+threads on the same workload, with the same --steps / --warmup / --layers.
 """
 from __future__ import annotations
 
@@ -50,7 +51,6 @@ PAPER_KNOBS = dict(
     eps_guard=0.01, exploration_rate=0.02, value_error_mode="tight",
 )
 METRIC = "certified_decode_attention_us_per_layer_step"
-KERNELS_PER_LAYER_STEP = 4  # append_token_kernel, score_blocks_kernel, selcert_kernel, attend_kernel
 
 
 def parse_args():
@@ -59,7 +59,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--context", type=int, default=131072)
+    ap.add_argument("--second-context", type=int, default=32768,
+                    help="a second single-GPU configuration measured in the same run (0 = skip)")
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--planted", type=int, default=64)
     ap.add_argument("--seed", type=int, default=2)
@@ -134,13 +136,13 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- workload
 
-def build_inputs(args, n_layers, rank=0):
+def build_inputs(args, n_layers, rank=0, context=None):
     from cqa_b200 import synth
 
     bases = []
     for l in range(n_layers):
-        bases.append(synth.make_layer_inputs(args.seed + 1000 * rank + l, args.context, dtype="bfloat16",
-                                             n_planted_blocks=args.planted))
+        bases.append(synth.make_layer_inputs(args.seed + 1000 * rank + l, args.context if context is None else context,
+                                             dtype="bfloat16", n_planted_blocks=args.planted))
     return bases
 
 
@@ -156,13 +158,22 @@ def step_tensors(bases, n_steps):
 
 # ----------------------------------------------------------------------------- CPU arm
 
-def cpu_baseline(args, base, n_steps, max_new):
-    """The CPU oracle port of the reference's algorithm on the host cores:
-    append + Phase 1 + selector + certificate + Phase 2 (float32) per step."""
+def cpu_threads() -> int:
+    """All host threads, set explicitly: a launcher (torchrun) exports OMP_NUM_THREADS=1."""
+    from oracle import cqa_oracle as orc
+
+    return orc.set_threads(os.cpu_count() or 1)
+
+
+def cpu_baseline(args, base, n_steps, max_new, context=None, layers=1, warmup=1):
+    """The CPU oracle port of the reference's algorithm on the host cores: append + Phase 1 + selector +
+    certificate + Phase 2 (float32) per layer-step.  A step is `layers` layer-steps (all on ONE layer cache: a
+    bounded sample, the host's caches are far smaller than a layer's Tier 1 either way).  Returns the median µs per
+    layer-step over `n_steps` steps after `warmup` untimed ones."""
     from cqa_b200 import synth
     from oracle import cqa_oracle as orc
 
-    n = args.context
+    n = args.context if context is None else context
     aligned = (n // 16) * 16
     oc = orc.OracleCache.from_fp16_cache_int4v(base.k[:, :aligned], base.v[:, :aligned], "bfloat16",
                                                max_new_tokens=max_new)
@@ -173,45 +184,64 @@ def cpu_baseline(args, base, n_steps, max_new):
     knobs = dict(PAPER_KNOBS)
     times = []
     rng = np.random.default_rng(0)
-    for s in range(n_steps + 1):
-        q, kn, vn = synth.decode_step_inputs(base, s, dtype="bfloat16")
-        t0 = time.perf_counter()
-        oc.append_token(kn, vn)
-        if (oc.num_tokens - 1) % 16 == 15:
-            vs = oc.values_int4_scales.astype(np.float32)
-            vz = oc.values_int4_zeros.astype(np.float32)
-        nq = oc.num_quantized_blocks
-        nact = oc.active_blocks
-        m_b, S_b, tok = orc.score_blocks(oc, q, 4, 1.0 / math.sqrt(128.0))
-        sel = orc.adaptive_select(m_b, S_b, knobs["tau_cov"], knobs["k_min"], knobs["k_max"],
-                                  knobs["rung1_threshold"], knobs["rung1_multiplier"])
-        mask = sel["topk_mask"]
-        u = rng.random(mask.shape, dtype=np.float32)
-        mask = mask | ((~mask) & (u < np.float32(knobs["exploration_rate"])))
-        H = mask.shape[0]
-        top_idx = np.stack([np.argsort(-m_b[h], kind="stable")[:4] for h in range(H)]).astype(np.int32)
-        orc.fp16_block_scores(oc, q, top_idx, 4, 1.0 / math.sqrt(128.0), nq)
-        orc.delta_bound(q, oc.sigma_max, 4)
-        vc = orc.value_check(sel["mass_frac"], oc.values_int4_errors[:, :nq], 4, knobs["v_tolerance"])
-        tk = np.zeros((H, nact), dtype=np.int32)
-        tk[:, :nq] = mask
-        vm = np.zeros((H, nact), dtype=np.int32)
-        vm[:, :nq] = vc["unsafe"]
-        trailing = oc.has_trailing_partial_block
-        if trailing:
-            tk[:, nq:] = 1
-            vm[:, nq:] = 1
-        lv = 16 if not trailing else oc.num_tokens - nq * 16
-        orc.attend_mixed_f32(oc, q, 4, 1.0 / math.sqrt(128.0), tok, tk, vm, nact, lv, vs, vz)
-        dt = time.perf_counter() - t0
-        if s > 0:
-            times.append(dt)
+    s = 0
+    for step in range(warmup + n_steps):
+        t_step = 0.0
+        for _ in range(layers):
+            q, kn, vn = synth.decode_step_inputs(base, s, dtype="bfloat16")
+            s += 1
+            t0 = time.perf_counter()
+            oc.append_token(kn, vn)
+            if (oc.num_tokens - 1) % 16 == 15:
+                vs = oc.values_int4_scales.astype(np.float32)
+                vz = oc.values_int4_zeros.astype(np.float32)
+            nq = oc.num_quantized_blocks
+            nact = oc.active_blocks
+            m_b, S_b, tok = orc.score_blocks(oc, q, 4, 1.0 / math.sqrt(128.0))
+            sel = orc.adaptive_select(m_b, S_b, knobs["tau_cov"], knobs["k_min"], knobs["k_max"],
+                                      knobs["rung1_threshold"], knobs["rung1_multiplier"])
+            mask = sel["topk_mask"]
+            u = rng.random(mask.shape, dtype=np.float32)
+            mask = mask | ((~mask) & (u < np.float32(knobs["exploration_rate"])))
+            H = mask.shape[0]
+            top_idx = np.stack([np.argsort(-m_b[h], kind="stable")[:4] for h in range(H)]).astype(np.int32)
+            orc.fp16_block_scores(oc, q, top_idx, 4, 1.0 / math.sqrt(128.0), nq)
+            orc.delta_bound(q, oc.sigma_max, 4)
+            vc = orc.value_check(sel["mass_frac"], oc.values_int4_errors[:, :nq], 4, knobs["v_tolerance"])
+            tk = np.zeros((H, nact), dtype=np.int32)
+            tk[:, :nq] = mask
+            vm = np.zeros((H, nact), dtype=np.int32)
+            vm[:, :nq] = vc["unsafe"]
+            trailing = oc.has_trailing_partial_block
+            if trailing:
+                tk[:, nq:] = 1
+                vm[:, nq:] = 1
+            lv = 16 if not trailing else oc.num_tokens - nq * 16
+            orc.attend_mixed_f32(oc, q, 4, 1.0 / math.sqrt(128.0), tok, tk, vm, nact, lv, vs, vz)
+            t_step += time.perf_counter() - t0
+        if step >= warmup:
+            times.append(t_step / layers)
     return float(np.median(times)) * 1e6
+
+
+def workload_text(context, planted):
+    return (f"llama3.1-8b attention geometry, batch 1, context {context}, bf16 KV, INT8K/INT4V g16, "
+            f"{planted} planted blocks, one appended token per step")
+
+
+def config_dict(context, planted, layers, world):
+    return {"workload": workload_text(context, planted), "context": context, "layers_per_step": layers,
+            "kv_heads": 8, "q_heads": 32, "head_dim": 128,
+            "knobs": "tau_cov 0.995, k 2..128, r 1, eps_guard 0.01, exploration 0.02, rung1 0.02 x2.0, v_tol 0.05",
+            "l2": "working set per step (layers x Tier-1) larger than L2",
+            "parallelism": "independent sequences per GPU" if world > 1 else "single GPU"}
 
 
 # ----------------------------------------------------------------------------- GPU arm
 
-def run_ours(args, rank, world, device_index):
+def run_ours(args, rank, world, device_index, context=None, light=False):
+    """One single-GPU measurement at `context` (default: --context).  `light`: fewer staged kernel steps and
+    end-to-end steps (the second configuration of a run)."""
     import torch
     import torch.distributed as dist
 
@@ -221,10 +251,15 @@ def run_ours(args, rank, world, device_index):
 
     torch.cuda.set_device(device_index)
     dev = torch.device("cuda", device_index)
+    from cqa_b200 import _lib as cl
+
     K, W, NL = args.steps, args.warmup, args.layers
-    total_steps = W + K + args.e2e_steps + args.kernel_steps + 4
-    bases = build_inputs(args, NL, rank)
-    n = args.context
+    context = args.context if context is None else context
+    e2e_steps = max(2, args.e2e_steps // 4) if light else args.e2e_steps
+    kernel_steps = max(1, args.kernel_steps // 8) if light else args.kernel_steps
+    total_steps = W + K + e2e_steps + kernel_steps + 4
+    bases = build_inputs(args, NL, rank, context)
+    n = context
     aligned = (n // 16) * 16
     caches = []
     for b in bases:
@@ -274,6 +309,7 @@ def run_ours(args, rank, world, device_index):
     # ---- timed region: inputs resident in HBM
     barrier()
     sampler.mark()
+    launches0 = int(cl.lib().cqa_launch_count(0))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     t_host = time.perf_counter()
@@ -284,7 +320,7 @@ def run_ours(args, rank, world, device_index):
     host_us = (time.perf_counter() - t_host) * 1e6 / (K * NL)   # CPU time to queue one layer-step
     e1.record()
     barrier()
-    clocks = sampler.stop()
+    gpu_launches = int(cl.lib().cqa_launch_count(0)) - launches0     # kernels the library launched in the timed region
     ms_total = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms_total], device=dev)
@@ -300,16 +336,16 @@ def run_ours(args, rank, world, device_index):
     # holds every layer's output.  The per-layer entry point with a stream wait after every layer-step is
     # reported beside it.
     n_in = (H + 16) * 128
-    qkv_host = torch.empty(args.e2e_steps, NL, n_in, dtype=torch.bfloat16).pin_memory()
-    for i in range(args.e2e_steps):
+    qkv_host = torch.empty(e2e_steps, NL, n_in, dtype=torch.bfloat16).pin_memory()
+    for i in range(e2e_steps):
         for l in range(NL):
             qkv_host[i, l, : H * 128] = q_host[s_idx + i, l].reshape(-1)
             qkv_host[i, l, H * 128: (H + 8) * 128] = k_host[s_idx + i, l].reshape(-1)
             qkv_host[i, l, (H + 8) * 128:] = v_host[s_idx + i, l].reshape(-1)
     out_host = torch.empty(NL, H, 128, dtype=torch.float32).pin_memory()
-    e2e_rows = [[qkv_host[i, l] for l in range(NL)] for i in range(args.e2e_steps)]
+    e2e_rows = [[qkv_host[i, l] for l in range(NL)] for i in range(e2e_steps)]
     out_rows = [out_host[l] for l in range(NL)]
-    n_waited = args.e2e_steps // 2          # first half: one wait per layer-step; second half: one per decode step
+    n_waited = e2e_steps // 2          # first half: one wait per layer-step; second half: one per decode step
 
     def e2e_loop(first, last, wait_each):
         nonlocal s_idx
@@ -330,7 +366,9 @@ def run_ours(args, rank, world, device_index):
         return sec * 1e6 / (max(1, last - first) * NL)
 
     e2e_waited_us = e2e_loop(0, n_waited, True) if n_waited > 0 else None
-    e2e_us = e2e_loop(n_waited, args.e2e_steps, False)
+    e2e_us = e2e_loop(n_waited, e2e_steps, False)
+    # the clock record covers both timed regions (device-timed steps and the end-to-end loops)
+    clocks = sampler.stop()
     if not bool(torch.isfinite(out_host).all()):
         raise RuntimeError("end-to-end loop returned non-finite attention rows")
     h2d = n_in * 2
@@ -345,7 +383,7 @@ def run_ours(args, rank, world, device_index):
     # A 512 MB fill runs ahead of every staged layer-step: it evicts L2 and keeps the GPU busy while the host
     # queues the four launches, so the events bracket kernel time and not launch latency.
     flush = torch.empty(128 * 1024 * 1024, dtype=torch.float32, device=dev)
-    for _ in range(args.kernel_steps):
+    for _ in range(kernel_steps):
         for l in range(NL):
             flush.fill_(1.0)
             layer_step(s_idx, l, collect=False, timings=phase)
@@ -369,7 +407,6 @@ def run_ours(args, rank, world, device_index):
     # ---- the two streaming kernels again, each launched back to back over the NL layer caches (NL x its bytes is
     # larger than L2 at the default sizes) between ONE pair of events: the average launch duration without the
     # event and ramp overhead that an isolated launch carries.  Every workspace still holds its last step's masks.
-    from cqa_b200 import _lib as cl
     import ctypes as C
     L = cl.lib()
     stream = cl.current_stream(dev)
@@ -408,7 +445,7 @@ def run_ours(args, rank, world, device_index):
         torch.cuda.synchronize()
         return ea.elapsed_time(eb) * 1e3 / (rounds * NL)
 
-    b2b_rounds = max(1, min(8, args.kernel_steps * 2))
+    b2b_rounds = max(1, min(8, kernel_steps * 2))
     b2b_us = {"phase1_int8_scoring": back_to_back(launch_score, b2b_rounds),
               "phase2_fused_attend": back_to_back(launch_attend, b2b_rounds)}
     peaks = {}
@@ -427,15 +464,14 @@ def run_ours(args, rank, world, device_index):
     achieved = dom_bytes / (b2b_us[dominant] * 1e-6) / 1e9
     chain_bytes = bytes_acc["total"] / n_meas
     chain_gbs = chain_bytes / (us_per_layer * 1e-6) / 1e9
-    # DRAM bytes per launch of the two streaming kernels at this workload, from one ncu capture each
-    # (dram__bytes_read.sum + dram__bytes_write.sum; profiles/ncu_decode_step_ctx32k.md)
-    ncu_traffic = {"phase1_int8_scoring": 50.39e6 + 0.23e6, "phase2_fused_attend": 36.12e6 + 0.11e6}
     roof = {
         "bound": "hbm", "kernel": {"phase1_int8_scoring": "score_blocks_kernel",
                                    "phase2_fused_attend": "attend_kernel"}[dominant],
         "achieved": round(achieved, 1), "peak": peak_gbs, "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
         "peak_source": peak_src,
-        "traffic": int(ncu_traffic[dominant]) if args.context == 32768 else None,
+        # dram__bytes_read.sum + dram__bytes_write.sum needs a profiler; a bench run does not measure it (the ncu
+        # summaries under profiles/ do)
+        "traffic": None,
         "algorithmic_bytes_per_launch": int(dom_bytes), "kernel_us": round(b2b_us[dominant], 2),
         "kernel_us_how": "average over %d back-to-back launches on %d layer caches, one event pair" % (b2b_rounds * NL, NL),
         "kernel_us_isolated": round(kern_us[dominant], 2),
@@ -450,18 +486,14 @@ def run_ours(args, rank, world, device_index):
         "metric": METRIC, "value": round(us_per_layer, 3), "unit": "us", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(ms_per_step, 5), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"llama3.1-8b attention geometry, batch 1, context {args.context}, bf16 KV, "
-                               f"INT8K/INT4V g16, {args.planted} planted blocks, one appended token per step",
-                   "context": args.context, "layers_per_step": NL, "kv_heads": 8, "q_heads": 32, "head_dim": 128,
-                   "knobs": "tau_cov 0.995, k 2..128, r 1, eps_guard 0.01, exploration 0.02, rung1 0.02 x2.0, "
-                            "v_tol 0.05", "l2": "working set per step (layers x Tier-1) larger than L2",
-                   "parallelism": "independent sequences per GPU" if world > 1 else "single GPU"},
+        "config": config_dict(context, args.planted, NL, world),
         "tokens_per_s_32layer_equiv": round(1e6 / (32.0 * us_per_layer), 2),
         "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": h2d * NL, "d2h_bytes_per_step": d2h * NL,
                 "tokens_per_s_32layer_equiv": round(1e6 / (32.0 * e2e_us), 2),
                 "waits": "one library call and one stream wait per decode step of %d layers" % NL,
                 "with_a_wait_per_layer_step": None if e2e_waited_us is None else round(e2e_waited_us, 3)},
-        "gpu_launches": KERNELS_PER_LAYER_STEP * NL * K,
+        "gpu_launches": gpu_launches,
+        "gpu_launches_how": "the library's own launch counter (cqa_launch_count) read before and after the timed region",
         "host_us_per_layer_step": round(host_us, 2),
         "clocks": clocks,
         "roofline": roof,
@@ -487,7 +519,7 @@ def run_sharded(args, rank, world, device_index):
     n, K, W = args.sharded_context, args.sharded_steps, max(3, args.warmup)
     base = synth.make_layer_inputs(args.seed + 77, n, dtype="bfloat16", n_planted_blocks=10, planted_cos=0.95,
                                    planted_depths=[i / 10.0 for i in range(10)])
-    steps = [synth.decode_step_inputs(base, s, dtype="bfloat16") for s in range(W + K)]
+    steps = [synth.decode_step_inputs(base, s, dtype="bfloat16") for s in range(W + K + 1)]
     to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).to(dev)
     qs = [to(q) for q, _, _ in steps]
     ks = [to(k.reshape(8, 1, 128)) for _, k, _ in steps]
@@ -501,15 +533,19 @@ def run_sharded(args, rank, world, device_index):
                                                       defer_int4_append_quantization=True)
     layer = ShardedCertifiedLayer(plan, cache, 4)
 
-    def timed(fn):
+    host_us = {}
+
+    def timed(fn, tag):
         for s in range(W):
             fn(s)
         dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        t_host = time.perf_counter()
         for s in range(W, W + K):
             fn(s)
+        host_us[tag] = (time.perf_counter() - t_host) * 1e6 / K    # host time to queue one sharded layer-step
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e3 / K
@@ -518,12 +554,25 @@ def run_sharded(args, rank, world, device_index):
         layer.append_token(ks[s], vs[s])
         layer.step(qs[s], None, **knobs)
 
-    us = timed(sharded_step)
+    def parity_record():
+        """One more step (index W + K) with the certificate read back: what rank 0 compares with the unsharded run."""
+        s = W + K
+        layer.append_token(ks[s], vs[s])
+        out, st = layer.step(qs[s], None, collect_stats=True, **knobs)
+        torch.cuda.synchronize()
+        nact = layer.nact
+        return {"out": out.float().cpu().numpy().copy(), "k_star": np.asarray(st["cert"]["k_star"]).copy(),
+                "rung3": np.asarray(st["cert"]["rung3"]).copy(),
+                "topk": layer.ws.topk_mask[:, :nact].cpu().numpy().copy(),
+                "vmask": layer.ws.value_mask[:, :nact].cpu().numpy().copy()}
+
+    us = timed(sharded_step, "collective")
     t = torch.tensor([us], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     us = float(t.item())
+    rec_coll = parity_record()
     # the same sequence again with peer-memory exchanges (pushes over NVLink, bounded waits on local flags)
-    us_peer, peer_status = None, None
+    us_peer, peer_status, rec_peer = None, None, None
     if args.sharded_peer:
         del layer, cache
         torch.cuda.empty_cache()
@@ -531,7 +580,8 @@ def run_sharded(args, rank, world, device_index):
                                                           max_new_tokens=(W + K + 16) if rank == plan.last else 0,
                                                           defer_int4_append_quantization=True)
         layer = ShardedCertifiedLayer(plan, cache, 4, exchange="peer")
-        us_peer = timed(sharded_step)
+        us_peer = timed(sharded_step, "peer")
+        rec_peer = parity_record()
         peer_status = layer.peer_status()
         t = torch.tensor([us_peer, float(peer_status)], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -554,10 +604,33 @@ def run_sharded(args, rank, world, device_index):
         e1.record()
         torch.cuda.synchronize()
         single = e0.elapsed_time(e1) * 1e3 / K
+        # the same extra step on the unsharded cache, and the comparison: K*, Rung-3 flags and both masks exact,
+        # output rows within 1e-5 of the row scale
+        s_par = W + K
+        full.append_token(ks[s_par], vs[s_par])
+        ref_out, _ = ca.certified_attention_layer(full, qs[s_par], 4, q_scale, False, **knobs)
+        torch.cuda.synchronize()
+        fws = full._certified_workspace["cqa_ws"]
+        fcert, _ = fws.read_cert()
+        nact = full.active_blocks
+        ref = {"out": ref_out.float().cpu().numpy().copy(), "k_star": np.asarray(fcert["k_star"]),
+               "rung3": np.asarray(fcert["rung3"]), "topk": fws.topk_mask[:, :nact].cpu().numpy(),
+               "vmask": fws.value_mask[:, :nact].cpu().numpy()}
+
+        def same(rec):
+            if rec is None:
+                return None
+            exact = all(np.array_equal(rec[k], ref[k]) for k in ("k_star", "rung3", "topk", "vmask"))
+            scale = np.abs(ref["out"]).max(axis=1, keepdims=True)
+            err = float((np.abs(rec["out"] - ref["out"]) / scale).max())
+            return {"selections_exact": bool(exact), "output_max_rel_err": err, "ok": bool(exact and err <= 1e-5)}
+
+        par_coll, par_peer = same(rec_coll), same(rec_peer)
     dist.barrier()
     if rank != 0:
         return None
     per_rank_bytes = 2304.0 * n / world
+    parity = bool(par_coll["ok"] and (par_peer is None or par_peer["ok"]))
     return {"workload": f"one layer, context {n}, 10 needle blocks (cosine 0.95), block ranges over {world} ranks, "
                         "NCCL all-gather / all-reduce exchanges", "ranks": world, "steps": K,
             "us_per_layer_step": round(us, 2), "single_gpu_us_per_layer_step": round(single, 2),
@@ -565,6 +638,11 @@ def run_sharded(args, rank, world, device_index):
             "peer_exchange_us_per_layer_step": None if us_peer is None else round(us_peer, 2),
             "peer_exchange_speedup_vs_single_gpu": None if us_peer is None else round(single / us_peer, 3),
             "peer_exchange_wait_status": peer_status,
+            "parity": parity,
+            "parity_detail": {"what": "one extra step after the timed ones: K*, Rung-3 flags, FP16-key and FP16-value "
+                                      "masks equal to the single-GPU run's, output rows within 1e-5 of the row scale",
+                              "collective": par_coll, "peer": par_peer},
+            "host_us_per_layer_step": {k: round(v, 2) for k, v in host_us.items()},
             "hbm_floor_us_per_rank": round(per_rank_bytes / 6540.2e3, 2)}
 
 
@@ -591,21 +669,19 @@ def _main(args, out):
             return 0
         from cqa_b200 import synth
 
+        cores = cpu_threads()
         base = synth.make_layer_inputs(args.seed, args.context, dtype="bfloat16", n_planted_blocks=args.planted)
-        n_cpu = max(1, min(args.steps, 8))
         t0 = time.perf_counter()
-        us = cpu_baseline(args, base, n_cpu, max_new)
-        cores = os.cpu_count() or 1
+        us = cpu_baseline(args, base, args.steps, (args.steps + args.warmup) * args.layers + 64, layers=args.layers,
+                          warmup=args.warmup)
+        sample = (f"{args.steps} decode steps of {args.layers} layer-steps each at context {args.context} (median per "
+                  f"layer-step), all on one layer cache, OpenMP over {cores} host threads, after {args.warmup} warm-up steps")
         line = {
             "impl": "reference", "metric": METRIC, "value": round(us, 1), "unit": "us", "n_gpus": args.gpus,
-            "steps": n_cpu, "warmup": 1, "ms_per_step": round(us / 1e3, 3), "higher_is_better": False,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"llama3.1-8b attention geometry, batch 1, context {args.context}, bf16 KV, "
-                                   f"INT8K/INT4V g16, {args.planted} planted blocks, one appended token per step",
-                       "context": args.context, "layers_per_step": 1},
-            "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
-                             "sample": f"{n_cpu} decode steps of one layer at context {args.context} "
-                                       f"(median), OpenMP over {cores} host threads, after 1 warm-up step"},
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(us * args.layers / 1e3, 3),
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_dict(args.context, args.planted, args.layers, max(1, args.gpus)),
+            "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": round(us, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference has no CPU implementation that runs outside its Python/Triton stack; this arm "
                     "times the CPU oracle port of its algorithm",
@@ -625,6 +701,16 @@ def _main(args, out):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     result, bases = run_ours(args, rank, world, local)
+    if args.second_context > 0 and args.second_context != args.context:
+        base0 = bases[0]
+        del bases
+        torch.cuda.empty_cache()
+        second, _ = run_ours(args, rank, world, local, context=args.second_context, light=True)
+        if rank == 0:
+            result[f"ctx{args.second_context // 1024}k"] = {
+                k: second[k] for k in ("value", "unit", "ms_per_step", "e2e", "roofline", "host_us_per_layer_step",
+                                       "selection", "gpu_launches", "config")}
+        bases = [base0]
     if world > 1 and args.sharded_context > 0:
         del bases
         torch.cuda.empty_cache()
@@ -634,8 +720,8 @@ def _main(args, out):
         bases = [None]
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
+            cores = cpu_threads()
             us = cpu_baseline(args, bases[0], args.cpu_steps, max_new)
-            cores = os.cpu_count() or 1
             result["cpu_baseline"] = {
                 "value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
                 "sample": f"{args.cpu_steps} decode steps of one layer at context {args.context} (median), "

@@ -24,6 +24,8 @@ SYMBOLS = [
     "cqa_decode_step_host", "cqa_decode_step_host_async", "cqa_decode_token_host", "cqa_hot_tier_update",
     "cqa_peer_buffer_bytes", "cqa_peer_alloc", "cqa_peer_free", "cqa_peer_export", "cqa_peer_import", "cqa_peer_close",
     "cqa_sharded_layer_step", "cqa_peer_status",
+    "cqa_hot_tier_ensure", "cqa_page_in_blocks", "cqa_page_in_by_slots", "cqa_dense_attend",
+    "cqa_launch_count",
 ]
 PARTIAL_STRIDE = 130
 
@@ -179,9 +181,15 @@ def lib() -> C.CDLL:
     L.cqa_peer_status.argtypes = [C.POINTER(CqaPeers), C.POINTER(C.c_int32), i32]
     L.cqa_sharded_layer_step.argtypes = [pc, pc, pk, pw, pw, C.POINTER(CqaPeers), vp, i32, i64, i64, i64, i64, i64, i64,
                                          i32, i64, i32, vp, vp]
+    L.cqa_dense_attend.argtypes = [pc, pw, vp, i32, i64, f32, vp]
+    L.cqa_hot_tier_ensure.argtypes = [pc, C.POINTER(CqaHotTier), i32, vp, i64, vp]
+    L.cqa_page_in_blocks.argtypes = [vp, i64, vp, i64, i32, i32, vp, vp, i64, vp, i64, vp, i64, i64, vp]
+    L.cqa_page_in_by_slots.argtypes = [vp, i64, vp, i64, i32, i32, vp, i64, i64, vp]
     for s in SYMBOLS[2:]:
         getattr(L, s).restype = C.c_int
     L.cqa_peer_buffer_bytes.restype = C.c_int64
+    L.cqa_launch_count.argtypes = [i32]
+    L.cqa_launch_count.restype = C.c_int64
     _lib = L
     return L
 

@@ -1,4 +1,5 @@
 // C ABI glue: error text, argument checks, the fused per-layer chain.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -25,6 +26,9 @@ int check_cuda(cudaError_t e, const char *what)
 
 int check_launch(const char *what) { return check_cuda(cudaGetLastError(), what); }
 
+static std::atomic<long long> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
 int score_blocks_launch(const cqa_cache *c, const void *q, int q_dtype, long nq, float q_scale, float *m_b,
                         float *s_b, long ld, float *tok, cudaStream_t st, int32_t *zero_words, int n_zero_words,
                         const ScorePush *push);
@@ -44,6 +48,8 @@ int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace 
 int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
                   long num_tokens, int last_valid, float q_scale, cudaStream_t st, bool chained);
 
+int dense_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long num_tokens, float q_scale,
+                 cudaStream_t st);
 int attend_static_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
                          long num_tokens, int last_valid, float q_scale, cudaStream_t st);
 
@@ -75,6 +81,10 @@ using namespace cqa;
 
 extern "C" const char *cqa_version(void) { return "cqa_b200 0.1 (sm_100a)"; }
 extern "C" const char *cqa_last_error(void) { return g_err; }
+extern "C" int64_t cqa_launch_count(int reset)
+{
+    return reset ? g_launches.exchange(0, std::memory_order_relaxed) : g_launches.load(std::memory_order_relaxed);
+}
 
 extern "C" int cqa_select(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace *ws, int64_t nq,
                           int64_t nact, const float *exploration_u, int64_t u_ld, void *stream)
@@ -271,6 +281,15 @@ extern "C" int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const voi
     if (rc) return rc;
     if (!q) { set_error("cqa_attend: NULL q"); return CQA_ERR_INVALID; }
     return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_block_valid, q_scale, (cudaStream_t)stream, false);
+}
+
+extern "C" int cqa_dense_attend(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype,
+                                int64_t num_tokens, float q_scale, void *stream)
+{
+    int rc = check_common(c, ws, "cqa_dense_attend");
+    if (rc) return rc;
+    if (!q) { set_error("cqa_dense_attend: NULL q"); return CQA_ERR_INVALID; }
+    return dense_launch(c, ws, q, q_dtype, num_tokens, q_scale, (cudaStream_t)stream);
 }
 
 extern "C" int cqa_attend_static(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,

@@ -778,6 +778,62 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
     }
 }
 
+// Dense recompute alone: only the pool CTAs of the kernel are launched (no split CTAs), for the heads the attached
+// certificate lists (cert[h].dense with the list in any_flags[5..], or every head when any_flags[2] is set).
+template <typename T2>
+static int dense_launch_t(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long num_tokens,
+                          float q_scale, cudaStream_t st)
+{
+    cqa_workspace w = *ws;
+    w.num_splits = 0;
+    const long nblk = (num_tokens + BS - 1) / BS;
+    dim3 grid((unsigned)DENSE_POOL_X, (unsigned)c->kv_heads);
+#define CQA_DENSE_CASE(GG)                                                                                             \
+    case GG: {                                                                                                         \
+        const size_t smem = attend_smem<GG>();                                                                         \
+        static size_t granted[SMEM_ATTR_DEVICES] = {};                                                                 \
+        const int rc = check_cuda(ensure_dynamic_smem(attend_kernel<GG, T2>, smem, granted), "cudaFuncSetAttribute(attend_kernel)"); \
+        if (rc) return rc;                                                                                             \
+        return check_cuda(launch_chained(attend_kernel<GG, T2>, grid, dim3(ATT_THREADS), smem, st, false, *c, w, q, q_dtype, \
+                                         (long)0, nblk, num_tokens, BS, q_scale, 1), "attend_kernel (dense)");         \
+    }
+    switch (c->gqa_group) {
+        CQA_DENSE_CASE(1)
+        CQA_DENSE_CASE(2)
+        CQA_DENSE_CASE(4)
+        CQA_DENSE_CASE(8)
+    }
+#undef CQA_DENSE_CASE
+    set_error("cqa_dense_attend: unsupported gqa_group %d", c->gqa_group);
+    return CQA_ERR_UNSUPPORTED;
+}
+
+int dense_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long num_tokens, float q_scale,
+                 cudaStream_t st)
+{
+    if (!ws->cert || !ws->any_flags || ws->dense_splits <= 0 || ws->dense_splits > CQA_MAX_DENSE_SPLITS || !ws->dense_m ||
+        !ws->dense_l || !ws->dense_acc || !ws->tickets || !ws->out) {
+        set_error("cqa_dense_attend: needs cert, any_flags, the dense scratch (1..%d splits), tickets and out",
+                  CQA_MAX_DENSE_SPLITS);
+        return CQA_ERR_INVALID;
+    }
+    const bool identity = c->key_slots == nullptr && c->value_slots == nullptr;
+    if (num_tokens <= 0 || (num_tokens + BS - 1) / BS > c->max_blocks ||
+        (identity && (num_tokens > c->keys_t2_rows || num_tokens > c->values_t2_rows))) {
+        set_error("cqa_dense_attend: num_tokens=%ld out of range", num_tokens);
+        return CQA_ERR_INVALID;
+    }
+    if (!c->keys_t2 || !c->values_t2) { set_error("cqa_dense_attend: Tier-2 arrays missing"); return CQA_ERR_INVALID; }
+    if (q_dtype < 0 || q_dtype > 2) { set_error("cqa_dense_attend: unknown q dtype"); return CQA_ERR_INVALID; }
+    switch (c->t2_dtype) {
+    case CQA_F32: return dense_launch_t<float>(c, ws, q, q_dtype, num_tokens, q_scale, st);
+    case CQA_F16: return dense_launch_t<__half>(c, ws, q, q_dtype, num_tokens, q_scale, st);
+    case CQA_BF16: return dense_launch_t<__nv_bfloat16>(c, ws, q, q_dtype, num_tokens, q_scale, st);
+    }
+    set_error("cqa_dense_attend: unknown Tier-2 dtype %d", c->t2_dtype);
+    return CQA_ERR_INVALID;
+}
+
 // Merge of per-rank partial rows (max, sum, acc[128]) of every head: one CTA per head, one thread per channel.
 __global__ void __launch_bounds__(D) merge_partials_kernel(const float *parts, int n_parts, int n_heads, float *out)
 {
@@ -796,7 +852,7 @@ __global__ void __launch_bounds__(D) merge_partials_kernel(const float *parts, i
 
 int merge_partials_launch(const float *parts, int n_parts, int n_heads, float *out, cudaStream_t st)
 {
-    merge_partials_kernel<<<n_heads, D, 0, st>>>(parts, n_parts, n_heads, out);
+    merge_partials_kernel<<<n_heads, D, 0, st>>>(parts, n_parts, n_heads, out); note_launch();
     return check_launch("merge_partials_kernel");
 }
 

@@ -296,6 +296,10 @@ __device__ __forceinline__ void grid_dependency_wait()
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// Every kernel launch of the library is counted (cqa_launch_count), so a caller can check that its calls ran on the
+// GPU and how many kernels a step takes.
+void note_launch(int n = 1);
+
 // Opt a kernel in to `bytes` of dynamic shared memory on the current device.  The attribute belongs to the
 // (function, device) pair, so the largest size already granted is remembered per device ordinal; `granted` is one
 // array per kernel instantiation (a function-local static of the caller).
@@ -331,6 +335,7 @@ static inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, di
     attr[0].val.programmaticStreamSerializationAllowed = chained ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    note_launch();
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

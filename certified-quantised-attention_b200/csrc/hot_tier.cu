@@ -63,6 +63,68 @@ __global__ void __launch_bounds__(256) hot_mark_kernel(cqa_hot_tier ht, cqa_work
     }
 }
 
+// The same marking for an explicit list of block ids of one tier (a caller that knows which blocks it is about to
+// read asks for them by name; reference: ensure_fp16_keys_resident / ensure_fp16_values_resident).
+__global__ void __launch_bounds__(256) hot_mark_list_kernel(cqa_hot_tier ht, int tier, const int64_t *blocks, long n,
+                                                           long max_blocks)
+{
+    const HotTierView v = tier_view(ht, tier, max_blocks);
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long b = blocks[i];
+    if (b < 0 || b >= max_blocks) return;
+    const int step = (int)ht.counters[HT_STEP];
+    const int s = v.slots[b];
+    if (s >= 0) {
+        v.stamp[s] = step;
+        atomicAdd(reinterpret_cast<unsigned long long *>(v.ctr + 0), 1ull);
+    } else {
+        const int k = atomicAdd(v.work + 0, 1);
+        v.work[2 + k] = (int)b;
+        atomicAdd(reinterpret_cast<unsigned long long *>(v.ctr + 1), 1ull);
+    }
+}
+
+// Gather of 16-row blocks from a backing array (row = token index) into the slots of a scratch array, 16 bytes per
+// thread and step.  grid (blocks, KV).  Rows at or beyond active_tokens are not copied.
+__global__ void __launch_bounds__(128) page_in_gather_kernel(const char *src, long src_rows, char *dst, long dst_rows,
+                                                            long row_bytes, const int64_t *blocks,
+                                                            const int32_t *slots, const int32_t *slot_of_block,
+                                                            long active_tokens)
+{
+    const int kv = blockIdx.y;
+    // two addressing forms: (blocks[i], slots[i]) pairs, or block i with slot slot_of_block[i]
+    const long b = blocks ? blocks[blockIdx.x] : (long)blockIdx.x;
+    const long s = blocks ? (long)slots[blockIdx.x] : (long)slot_of_block[blockIdx.x];
+    if (b < 0 || s < 0 || (s + 1) * BS > dst_rows || b * BS >= src_rows) return;
+    long rows = active_tokens - b * BS;
+    if (rows > BS) rows = BS;
+    if (rows <= 0) return;
+    const uint4 *from = reinterpret_cast<const uint4 *>(src + ((long)kv * src_rows + b * BS) * row_bytes);
+    uint4 *to = reinterpret_cast<uint4 *>(dst + ((long)kv * dst_rows + s * BS) * row_bytes);
+    const long n16 = rows * row_bytes / 16;
+    for (long k = threadIdx.x; k < n16; k += 128) to[k] = from[k];
+}
+
+__global__ void __launch_bounds__(256) slot_table_update_kernel(const int64_t *loaded_blocks, const int32_t *loaded_slots,
+                                                               long n_loaded, const int64_t *evicted_blocks,
+                                                               long n_evicted, int32_t *table, long table_size)
+{
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    // evictions first, then loads, in two grid-strided halves of the same launch would race when a block is both
+    // evicted and loaded; the loads therefore win by being applied by the same thread after its eviction
+    if (i < n_evicted) {
+        const long b = evicted_blocks[i];
+        bool reloaded = false;
+        for (long j = 0; j < n_loaded; ++j) reloaded |= loaded_blocks[j] == b;
+        if (b >= 0 && b < table_size && !reloaded) table[b] = -1;
+    }
+    if (i < n_loaded) {
+        const long b = loaded_blocks[i];
+        if (b >= 0 && b < table_size) table[b] = loaded_slots[i];
+    }
+}
+
 __global__ void __launch_bounds__(32) hot_assign_kernel(cqa_hot_tier ht, long max_blocks)
 {
     const int tier = blockIdx.x, lane = threadIdx.x;
@@ -148,6 +210,111 @@ __global__ void hot_finish_kernel(cqa_hot_tier ht, long max_blocks)
 
 using namespace cqa;
 
+static int check_hot_tier(const cqa_cache *c, const cqa_hot_tier *ht, const char *who)
+{
+    if (!ht->key_slots || !ht->value_slots || !ht->key_owner || !ht->value_owner || !ht->key_stamp || !ht->value_stamp ||
+        !ht->work || !ht->counters || ht->key_capacity_blocks <= 0 || ht->value_capacity_blocks <= 0 ||
+        ht->max_fill_blocks <= 0) {
+        set_error("%s: incomplete hot-tier state", who);
+        return CQA_ERR_INVALID;
+    }
+    if (!c->keys_t2_backing || !c->values_t2_backing || !c->keys_t2 || !c->values_t2 || c->key_slots != ht->key_slots ||
+        c->value_slots != ht->value_slots) {
+        set_error("%s: the cache is not in bounded hot-tier mode (slot tables and backing arrays)", who);
+        return CQA_ERR_INVALID;
+    }
+    if (ht->key_capacity_blocks * (int64_t)BS > c->keys_t2_rows ||
+        ht->value_capacity_blocks * (int64_t)BS > c->values_t2_rows) {
+        set_error("%s: capacity exceeds the scratch arrays", who);
+        return CQA_ERR_INVALID;
+    }
+    if (c->t2_dtype < 0 || c->t2_dtype > 2) { set_error("%s: unknown Tier-2 dtype", who); return CQA_ERR_INVALID; }
+    return CQA_OK;
+}
+
+static void launch_fill(const cqa_cache *c, const cqa_hot_tier *ht, cudaStream_t st)
+{
+    dim3 gf((unsigned)ht->max_fill_blocks, (unsigned)c->kv_heads, 2);
+    switch (c->t2_dtype) {
+    case CQA_F32: hot_fill_kernel<float><<<gf, 128, 0, st>>>(*ht, *c, c->max_blocks); note_launch(); break;
+    case CQA_F16: hot_fill_kernel<__half><<<gf, 128, 0, st>>>(*ht, *c, c->max_blocks); note_launch(); break;
+    default: hot_fill_kernel<__nv_bfloat16><<<gf, 128, 0, st>>>(*ht, *c, c->max_blocks); note_launch(); break;
+    }
+}
+
+extern "C" int cqa_hot_tier_ensure(const cqa_cache *c, const cqa_hot_tier *ht, int tier, const int64_t *block_ids,
+                                   int64_t n, void *stream)
+{
+    if (!c || !ht || (n > 0 && !block_ids)) { set_error("cqa_hot_tier_ensure: NULL pointer"); return CQA_ERR_INVALID; }
+    if (tier != 0 && tier != 1) { set_error("cqa_hot_tier_ensure: tier must be 0 (keys) or 1 (values)"); return CQA_ERR_INVALID; }
+    if (n < 0 || n > c->max_blocks) { set_error("cqa_hot_tier_ensure: %ld block ids", (long)n); return CQA_ERR_INVALID; }
+    const int rc = check_hot_tier(c, ht, "cqa_hot_tier_ensure");
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // the counters before this call, for callers that report per-call figures
+    cudaMemcpyAsync(ht->counters + 12, ht->counters, 12 * sizeof(int64_t), cudaMemcpyDeviceToDevice, st);
+    if (n > 0) {
+        hot_mark_list_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(*ht, tier, block_ids, n, c->max_blocks);
+        note_launch();
+    }
+    hot_assign_kernel<<<2, 32, 0, st>>>(*ht, c->max_blocks); note_launch();
+    launch_fill(c, ht, st);
+    hot_finish_kernel<<<1, 32, 0, st>>>(*ht, c->max_blocks); note_launch();
+    return check_launch("hot tier kernels");
+}
+
+static const char *device_view(const void *p)
+{
+    // pinned host memory is addressed through its device alias; device memory as it is
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer)
+        return static_cast<const char *>(at.devicePointer);
+    (void)cudaGetLastError();
+    return static_cast<const char *>(p);
+}
+
+extern "C" int cqa_page_in_blocks(const void *src, int64_t src_rows, void *dst, int64_t dst_rows, int kv_heads,
+                                  int row_bytes, const int64_t *loaded_blocks, const int32_t *loaded_slots,
+                                  int64_t n_loaded, const int64_t *evicted_blocks, int64_t n_evicted,
+                                  int32_t *slot_table, int64_t table_size, int64_t active_tokens, void *stream)
+{
+    if (n_loaded < 0 || n_evicted < 0 || kv_heads <= 0 || row_bytes <= 0 || (row_bytes & 15) != 0 ||
+        (n_loaded > 0 && (!src || !dst || !loaded_blocks || !loaded_slots)) || (n_evicted > 0 && !evicted_blocks)) {
+        set_error("cqa_page_in_blocks: bad arguments");
+        return CQA_ERR_INVALID;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    const long n = n_loaded > n_evicted ? n_loaded : n_evicted;
+    if (slot_table && n > 0) {
+        slot_table_update_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(loaded_blocks, loaded_slots, n_loaded,
+                                                                              evicted_blocks, n_evicted, slot_table, table_size);
+        note_launch();
+    }
+    if (n_loaded > 0) {
+        dim3 grid((unsigned)n_loaded, (unsigned)kv_heads);
+        page_in_gather_kernel<<<grid, 128, 0, st>>>(device_view(src), src_rows, static_cast<char *>(dst), dst_rows, row_bytes,
+                                                    loaded_blocks, loaded_slots, nullptr, active_tokens); note_launch();
+    }
+    return check_launch("page-in kernels");
+}
+
+extern "C" int cqa_page_in_by_slots(const void *src, int64_t src_rows, void *dst, int64_t dst_rows, int kv_heads,
+                                    int row_bytes, const int32_t *block_slots, int64_t n_blocks,
+                                    int64_t active_tokens, void *stream)
+{
+    if (n_blocks < 0 || kv_heads <= 0 || row_bytes <= 0 || (row_bytes & 15) != 0 ||
+        (n_blocks > 0 && (!src || !dst || !block_slots))) {
+        set_error("cqa_page_in_by_slots: bad arguments");
+        return CQA_ERR_INVALID;
+    }
+    if (n_blocks == 0) return CQA_OK;
+    dim3 grid((unsigned)n_blocks, (unsigned)kv_heads);
+    page_in_gather_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(device_view(src), src_rows, static_cast<char *>(dst),
+                                                                  dst_rows, row_bytes, nullptr, nullptr, block_slots,
+                                                                  active_tokens); note_launch();
+    return check_launch("page_in_gather_kernel");
+}
+
 extern "C" int cqa_hot_tier_update(const cqa_cache *c, const cqa_workspace *ws, const cqa_hot_tier *ht, int64_t nact,
                                    void *stream)
 {
@@ -172,18 +339,15 @@ extern "C" int cqa_hot_tier_update(const cqa_cache *c, const cqa_workspace *ws, 
         set_error("cqa_hot_tier_update: capacity exceeds the scratch arrays");
         return CQA_ERR_INVALID;
     }
+    if (c->t2_dtype < 0 || c->t2_dtype > 2) { set_error("cqa_hot_tier_update: unknown Tier-2 dtype"); return CQA_ERR_INVALID; }
     cudaStream_t st = (cudaStream_t)stream;
     const int H = c->kv_heads * c->gqa_group;
+    // counters[12..23] keep the values from before this step, so the host can report per-step figures
+    cudaMemcpyAsync(ht->counters + 12, ht->counters, 12 * sizeof(int64_t), cudaMemcpyDeviceToDevice, st);
     dim3 gm((unsigned)((nact + 255) / 256), 2);
-    hot_mark_kernel<<<gm, 256, 0, st>>>(*ht, *ws, H, nact, c->max_blocks);
-    hot_assign_kernel<<<2, 32, 0, st>>>(*ht, c->max_blocks);
-    dim3 gf((unsigned)ht->max_fill_blocks, (unsigned)c->kv_heads, 2);
-    switch (c->t2_dtype) {
-    case CQA_F32: hot_fill_kernel<float><<<gf, 128, 0, st>>>(*ht, *c, c->max_blocks); break;
-    case CQA_F16: hot_fill_kernel<__half><<<gf, 128, 0, st>>>(*ht, *c, c->max_blocks); break;
-    case CQA_BF16: hot_fill_kernel<__nv_bfloat16><<<gf, 128, 0, st>>>(*ht, *c, c->max_blocks); break;
-    default: set_error("cqa_hot_tier_update: unknown Tier-2 dtype"); return CQA_ERR_INVALID;
-    }
-    hot_finish_kernel<<<1, 32, 0, st>>>(*ht, c->max_blocks);
+    hot_mark_kernel<<<gm, 256, 0, st>>>(*ht, *ws, H, nact, c->max_blocks); note_launch();
+    hot_assign_kernel<<<2, 32, 0, st>>>(*ht, c->max_blocks); note_launch();
+    launch_fill(c, ht, st);
+    hot_finish_kernel<<<1, 32, 0, st>>>(*ht, c->max_blocks); note_launch();
     return check_launch("hot tier kernels");
 }

@@ -283,7 +283,7 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
         peer_push_kernel<<<grid, PUSH_THREADS, 0, st>>>(pa, xa_own, peers->chunk, L.xa + par * L.xa_parity + (long)R * slot,
                                                         peers->chunk, peers->rows, 2 * H, n_local, n_local, (long)KV * D,
                                                         L.flags + 0 * W + R, L.tickets + 0 * W, (int)step,
-                                                        L.xa + (par ^ 1) * L.xa_parity + (long)R * slot, 2 * H);
+                                                        L.xa + (par ^ 1) * L.xa_parity + (long)R * slot, 2 * H); note_launch();
         float *other = own + L.xa + (par ^ 1) * L.xa_parity + (long)R * slot + 2L * H * peers->chunk;
         rc = check_cuda(cudaMemcpyAsync(other, xa_own + 2L * H * peers->chunk, (size_t)(KV + 1) * peers->chunk * 4,
                                         cudaMemcpyDeviceToDevice, st), "copy of meta rows to the other parity");
@@ -343,6 +343,6 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     rc = attend_launch(local, &l, q, q_dtype, n_local, nact_local, num_tokens_local, last_valid, knobs->q_scale, st, false);
     if (rc) return rc;
     merge_wait_kernel<<<H, D, 0, st>>>(xc_par, W, H, out, own_i + L.flags + 2 * W, R, (int)step, own_i + L.status,
-                                       wg->wait_spins);
+                                       wg->wait_spins); note_launch();
     return check_launch("sharded step kernels");
 }

@@ -358,7 +358,7 @@ static int launch_quantize(const cqa_cache *c, const void *k, const void *v, lon
         long cnt = n - off < max_x ? n - off : max_x;
         dim3 grid((unsigned)cnt, (unsigned)c->kv_heads);
         quantize_blocks_kernel<T><<<grid, 128, 0, st>>>(*c, ks + off * BS * D, vs + off * BS * D, src_rows,
-                                                        first + off, copy);
+                                                        first + off, copy); note_launch();
     }
     return check_launch("quantize_blocks_kernel");
 }
@@ -425,9 +425,9 @@ extern "C" int cqa_int4_quantise(const void *x, int src_dtype, int64_t T, uint8_
     cudaStream_t st = (cudaStream_t)stream;
     unsigned grid = (unsigned)((T + 15) / 16);
     switch (src_dtype) {
-    case CQA_F32: int4_quantise_kernel<float><<<grid, 128, 0, st>>>((const float *)x, T, packed, scales, zeros, rel_err, abs_err); break;
-    case CQA_F16: int4_quantise_kernel<__half><<<grid, 128, 0, st>>>((const __half *)x, T, packed, scales, zeros, rel_err, abs_err); break;
-    case CQA_BF16: int4_quantise_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16 *)x, T, packed, scales, zeros, rel_err, abs_err); break;
+    case CQA_F32: int4_quantise_kernel<float><<<grid, 128, 0, st>>>((const float *)x, T, packed, scales, zeros, rel_err, abs_err); note_launch(); break;
+    case CQA_F16: int4_quantise_kernel<__half><<<grid, 128, 0, st>>>((const __half *)x, T, packed, scales, zeros, rel_err, abs_err); note_launch(); break;
+    case CQA_BF16: int4_quantise_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16 *)x, T, packed, scales, zeros, rel_err, abs_err); note_launch(); break;
     default: set_error("cqa_int4_quantise: unknown dtype %d", src_dtype); return CQA_ERR_INVALID;
     }
     return check_launch("int4_quantise_kernel");

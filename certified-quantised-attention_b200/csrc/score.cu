@@ -263,9 +263,9 @@ int rescore_owned_launch(const cqa_cache *c, const cqa_head_cert *cert, const vo
     const int H = c->kv_heads * c->gqa_group;
     dim3 grid(CQA_MAX_RANKING_K, (unsigned)H);
     switch (c->t2_dtype) {
-    case CQA_F32: rescore_owned_kernel<float><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); break;
-    case CQA_F16: rescore_owned_kernel<__half><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); break;
-    case CQA_BF16: rescore_owned_kernel<__nv_bfloat16><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); break;
+    case CQA_F32: rescore_owned_kernel<float><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); note_launch(); break;
+    case CQA_F16: rescore_owned_kernel<__half><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); note_launch(); break;
+    case CQA_BF16: rescore_owned_kernel<__nv_bfloat16><<<grid, 32, 0, st>>>(*c, cert, q, q_dtype, first_block, n_local, q_scale, out); note_launch(); break;
     default: set_error("cqa_rescore_owned: unknown Tier-2 dtype"); return CQA_ERR_INVALID;
     }
     return check_launch("rescore_owned_kernel");
@@ -352,9 +352,9 @@ extern "C" int cqa_fp16_block_scores(const cqa_cache *c, const void *q, int q_dt
     cudaStream_t st = (cudaStream_t)stream;
     const long nst = n_scoring_blocks * BS;
     switch (c->t2_dtype) {
-    case CQA_F32: fp16_block_scores_kernel<float><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); break;
-    case CQA_F16: fp16_block_scores_kernel<__half><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); break;
-    case CQA_BF16: fp16_block_scores_kernel<__nv_bfloat16><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); break;
+    case CQA_F32: fp16_block_scores_kernel<float><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); note_launch(); break;
+    case CQA_F16: fp16_block_scores_kernel<__half><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); note_launch(); break;
+    case CQA_BF16: fp16_block_scores_kernel<__nv_bfloat16><<<grid, 32, 0, st>>>(*c, q, q_dtype, idx, K, nst, q_scale, scores, logmass); note_launch(); break;
     default: set_error("cqa_fp16_block_scores: unknown Tier-2 dtype"); return CQA_ERR_INVALID;
     }
     return check_launch("fp16_block_scores_kernel");
@@ -364,6 +364,6 @@ extern "C" int cqa_delta_bound(const cqa_cache *c, const void *q, int q_dtype, f
 {
     if (!c || !q || !delta || !c->sigma_max) { set_error("cqa_delta_bound: NULL pointer"); return CQA_ERR_INVALID; }
     const int H = c->kv_heads * c->gqa_group;
-    delta_bound_kernel<<<H, 32, 0, (cudaStream_t)stream>>>(*c, q, q_dtype, delta);
+    delta_bound_kernel<<<H, 32, 0, (cudaStream_t)stream>>>(*c, q, q_dtype, delta); note_launch();
     return check_launch("delta_bound_kernel");
 }

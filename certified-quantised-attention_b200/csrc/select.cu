@@ -117,7 +117,7 @@ __device__ __forceinline__ float cta_canonical_sum(const float (&v)[VPT], int n,
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const float s = warp_sum(v[k]);
-        if (l == 0) gsum[k * SC_WARPS + w] = s;
+        if (l == 0 && k * SC_WARPS + w < ngroups) gsum[k * SC_WARPS + w] = s;   // groups beyond n hold nothing
     }
     __syncthreads();
     if ((int)threadIdx.x < nleaf) {
@@ -966,21 +966,19 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int b = k * SC_THREADS + tid;
-        if (b < (int)nact) {
+        if (b < n) {
             unsigned char upb;
-            if (b < n) {
-                if (kn.value_mode_tight) {
-                    const unsigned bits = __float_as_uint(e[k]);
-                    upb = (t0 != 0xFFFFFFFFu && (bits > t0 || (bits == t0 && b < id_bound))) ? 1 : 0;
-                } else {
-                    upb = x[k] > kn.v_tolerance ? 1 : 0;
-                }
+            if (kn.value_mode_tight) {
+                const unsigned bits = __float_as_uint(e[k]);
+                upb = (t0 != 0xFFFFFFFFu && (bits > t0 || (bits == t0 && b < id_bound))) ? 1 : 0;
             } else {
-                upb = kn.force_trailing_value_fp16 ? 1 : 0;
+                upb = x[k] > kn.v_tolerance ? 1 : 0;
             }
             vm[b] = upb;
         }
     }
+    // the trailing partial block (at most one) lies beyond the blocks the threads own
+    if (tid == 0 && (int)nact > n) vm[n] = kn.force_trailing_value_fp16 ? 1 : 0;
     if (tid == 0) {
         ct->e_pre = e_pre;
         ct->e_val = fmaxf(__fsub_rn(e_pre, promoted), 0.0f);

@@ -41,6 +41,18 @@ _CERT_F32_FIELDS = [f for f, t in _lib.CqaHeadCert._fields_ if t is C.c_float]
 class _Workspace:
     """Device buffers for one layer's step, kept in cache._certified_workspace."""
 
+    _serial = 0
+
+    def draw_seed(self) -> int:
+        """Key of this workspace's Philox stream: torch.initial_seed() mixed (splitmix64) with the workspace's
+        serial number.  Fixed at the first draw."""
+        if self.rng_seed is None:
+            z = (int(torch.initial_seed()) + 0x9E3779B97F4A7C15 * self.serial) & 0xFFFFFFFFFFFFFFFF
+            z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+            z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+            self.rng_seed = z ^ (z >> 31)
+        return self.rng_seed
+
     def __init__(self, cache: TieredKeyCacheLayer, H: int, G: int, device: torch.device, ld: int | None = None):
         self.H, self.G = H, G
         ld = int(cache.keys_scale.shape[1]) if ld is None else int(ld)
@@ -77,8 +89,12 @@ class _Workspace:
         self.cert_host = None
         self._u_flat = None
         self._step_in = None
+        # In-kernel exploration draw: torch's seed mixed with a per-workspace serial number, so that the layers of
+        # a model (one workspace each, created in layer order) draw different exploration sets, reproducibly.
         self.rng_seed = None
         self.rng_calls = 0
+        _Workspace._serial += 1
+        self.serial = _Workspace._serial
         self.struct = _lib.CqaWorkspace()
         self._struct_stale = True
 
@@ -293,9 +309,7 @@ def certified_decode_step_host(
     ws.ensure_sel_width(_selection_width(k_max, rung1_threshold, rung1_multiplier, nq), device)
     wstruct = ws.fill_struct((pos + 1 + cache.block_size - 1) // cache.block_size)
     if exploration_rate > 0.0:
-        if ws.rng_seed is None:
-            ws.rng_seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
-        wstruct.rng_seed = ws.rng_seed
+        wstruct.rng_seed = ws.draw_seed()
         wstruct.rng_offset = ws.rng_calls
         ws.rng_calls += 1
     stage = ws.step_input_buffer(n_in, qkv_host.dtype, device)
@@ -411,9 +425,7 @@ def certified_decode_token_host(
             ws.ensure_sel_width(width, device)
         wstruct = ws.fill_struct(nblocks)
         if explore:
-            if ws.rng_seed is None:
-                ws.rng_seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
-            wstruct.rng_seed = ws.rng_seed
+            wstruct.rng_seed = ws.draw_seed()
             wstruct.rng_offset = ws.rng_calls
             ws.rng_calls += 1
         call = calls[l]
@@ -463,14 +475,21 @@ def certified_attention_layer(
     """Full certified attention for one layer, all heads.
 
     Same contract as the reference (certified_attention.py:1065-1113): returns
-    (output [num_q_heads, d_v] float32, stats dict).  The output aliases a
-    reused workspace tensor; consume it before the next call on this cache.
+    (output [num_q_heads, d_v] float32, stats dict).
+
+    ONE DIFFERENCE a drop-in caller must know: the returned tensor is the
+    workspace's output buffer of this cache, not a fresh tensor.  The next
+    call on the same cache overwrites it (the kernels write their rows there
+    without an allocation or a copy per step).  A caller that keeps outputs
+    across steps must `.clone()` them; `o_proj(output)` right away, as the
+    adapter does, needs nothing.
 
     `exploration_uniforms` ([H, nq] floats in [0,1)) is an addition: when given
     it replaces the random draw so a run can be replayed exactly.  With an
     `exploration_generator` the draw is the reference's `torch.rand` from that
     generator; with neither, the selector kernel draws (Philox keyed by
-    `torch.initial_seed()` and a per-cache call counter).
+    `torch.initial_seed()`, a per-workspace serial number and a per-cache call
+    counter, so different layers draw different sets).
     """
     if not q_all.is_cuda:
         raise RuntimeError("certified_attention_layer needs CUDA tensors; there is no CPU fallback")
@@ -567,9 +586,7 @@ def certified_attention_layer(
         else:
             # no generator given: the selector draws in-kernel (Philox keyed by torch's seed and a call counter;
             # same distribution as torch.rand, one launch fewer)
-            if ws.rng_seed is None:
-                ws.rng_seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
-            wstruct.rng_seed = ws.rng_seed
+            wstruct.rng_seed = ws.draw_seed()
             wstruct.rng_offset = ws.rng_calls
             ws.rng_calls += 1
 
@@ -676,21 +693,42 @@ def _assemble_stats(cache, ws: _Workspace, H, G, nq, nact, *, has_int4, force_tr
         "h2d_key_bytes": 0, "h2d_key_blocks": 0, "h2d_value_bytes": 0, "h2d_value_blocks": 0,
         "h2d_total_bytes": 0,
     }
+    # residency figures of this step: the counters live on the device (csrc/hot_tier.cu keeps the values from
+    # before the latest update beside the running totals); a full mirror never misses
+    hot = cache.hot_tier_counters(last_call=True) if cache.bounded_hot_tier else {}
+    if hot:
+        blk_bytes = cache.kv_heads * cache.block_size * cache.head_dim * cache.keys_fp16_gpu.element_size()
+        stats["h2d_key_blocks"] = int(hot["key_pageins"])
+        stats["h2d_key_bytes"] = int(hot["key_pagein_bytes"])
+        stats["h2d_value_blocks"] = int(hot["value_pageins"])
+        stats["h2d_value_bytes"] = int(hot["value_pageins"]) * blk_bytes
+        stats["h2d_total_bytes"] = stats["h2d_key_bytes"] + stats["h2d_value_bytes"]
     if cache.fp16_key_cache_capacity is not None:
+        hits, misses = int(hot.get("key_hits", 0)), int(hot.get("key_misses", 0))
+        resident = (int((cache._hot["key_slots"] >= 0).sum().item()) if cache.bounded_hot_tier
+                    else int(len(cache._fp16_key_resident)))
         stats.update({
             "fp16_cache_capacity_blocks": int(cache.fp16_key_cache_capacity),
-            "fp16_cache_resident_blocks": int(len(cache._fp16_key_resident)),
-            "fp16_cache_hits_step": 0, "fp16_cache_misses_step": 0, "fp16_cache_evictions_step": 0,
-            "fp16_cache_needed_blocks_step": 0, "fp16_cache_hit_rate_step": 0.0,
+            "fp16_cache_resident_blocks": resident,
+            "fp16_cache_hits_step": hits, "fp16_cache_misses_step": misses,
+            "fp16_cache_evictions_step": int(hot.get("key_evictions", 0)),
+            "fp16_cache_needed_blocks_step": hits + misses,
+            "fp16_cache_hit_rate_step": float(hits) / (hits + misses) if (hits + misses) else 0.0,
         })
     if cache.fp16_value_cache_capacity is not None:
+        hits, misses = int(hot.get("value_hits", 0)), int(hot.get("value_misses", 0))
+        resident = (int((cache._hot["value_slots"] >= 0).sum().item()) if cache.bounded_hot_tier
+                    else int(len(cache._fp16_value_resident)))
         stats.update({
             "fp16_value_cache_capacity_blocks": int(cache.fp16_value_cache_capacity),
-            "fp16_value_cache_resident_blocks": int(len(cache._fp16_value_resident)),
-            "fp16_value_cache_hits_step": 0, "fp16_value_cache_misses_step": 0,
-            "fp16_value_cache_evictions_step": 0, "fp16_value_cache_needed_blocks_step": 0,
+            "fp16_value_cache_resident_blocks": resident,
+            "fp16_value_cache_hits_step": hits, "fp16_value_cache_misses_step": misses,
+            "fp16_value_cache_evictions_step": int(hot.get("value_evictions", 0)),
+            "fp16_value_cache_needed_blocks_step": hits + misses,
+            # a block that finds no free slot is read from the backing array in place: nothing overflows and the
+            # attend kernel never falls back to another code path
             "fp16_value_cache_overflow_step": 0, "mixedv_splitk_fallback_step": 0,
-            "fp16_value_cache_hit_rate_step": 0.0,
+            "fp16_value_cache_hit_rate_step": float(hits) / (hits + misses) if (hits + misses) else 0.0,
         })
     stats["vram_fp16_key_cache_bytes"] = kb
     stats["vram_fp16_value_cache_bytes"] = vb
@@ -840,6 +878,104 @@ def compute_adaptive_topk_mask(m_b, S_b, tau_cov: float = DEFAULT_TAU_COV, k_min
 def compute_block_mass_fraction(m_b, S_b):
     """Normalised per-block attention mass (reference: certified_attention.py:128-136)."""
     return compute_adaptive_topk_mask(m_b, S_b, tau_cov=1.0, k_min=1, k_max=1, return_mass_frac=True)[4]
+
+
+def compute_tier2_residual_mass(m_b, S_b, skip_mask, top_k: int = TOP_K_BLOCKS, return_details: bool = False):
+    """Per-head residual mass rho = 1 - alpha_K - beta: alpha_K = mass on the top_k blocks by m_b, beta = mass on
+    skipped blocks (reference: certified_attention.py:83-125).  The mass fractions come from the selector kernel;
+    the [H, top_k] gather and the two row sums are torch reductions over a tensor that already exists."""
+    mass_frac = compute_block_mass_fraction(m_b, S_b)
+    H, nb = m_b.shape
+    k = min(int(top_k), nb)
+    topk_idx = m_b.topk(k, dim=1).indices if k else torch.zeros(H, 0, dtype=torch.long, device=m_b.device)
+    alpha = mass_frac.gather(1, topk_idx).sum(dim=1)
+    beta = (mass_frac * skip_mask.to(mass_frac.dtype)).sum(dim=1)
+    rho = (1.0 - alpha - beta).clamp(min=0.0, max=1.0)
+    return (rho, mass_frac, topk_idx) if return_details else rho
+
+
+def _eta_per_q_head(eta_per_block, num_q_heads: int, gqa_group: int, nb: int):
+    kv_idx = (torch.arange(num_q_heads, device=eta_per_block.device) // int(gqa_group)).clamp(
+        max=eta_per_block.shape[0] - 1)
+    return eta_per_block[:, :nb][kv_idx]
+
+
+def compute_value_error_bound_for_mask(mass_frac, int4_value_mask, eta_per_block, gqa_group: int):
+    """[H]: sum over the blocks whose values stay INT4 of mass[h, b] * eta[kv(h), b]
+    (reference: certified_attention.py:139-155)."""
+    nb = min(mass_frac.shape[1], eta_per_block.shape[1])
+    eta_q = _eta_per_q_head(eta_per_block, mass_frac.shape[0], gqa_group, nb)
+    return (mass_frac[:, :nb] * int4_value_mask[:, :nb].to(mass_frac.dtype) * eta_q).sum(dim=1)
+
+
+def compute_value_error_bound(mass_frac, topk_idx, skip_mask, eta_per_block, gqa_group: int):
+    """[H]: the same sum over the residual blocks, i.e. neither in `topk_idx` nor skipped
+    (reference: certified_attention.py:158-208)."""
+    nb = min(mass_frac.shape[1], eta_per_block.shape[1])
+    residual = torch.ones(mass_frac.shape[0], nb, dtype=torch.bool, device=mass_frac.device)
+    if topk_idx.numel():
+        residual.scatter_(1, topk_idx.clamp(max=nb - 1), False)
+    residual &= ~skip_mask[:, :nb].bool()
+    eta_q = _eta_per_q_head(eta_per_block, mass_frac.shape[0], gqa_group, nb)
+    return (mass_frac[:, :nb] * eta_q * residual.to(mass_frac.dtype)).sum(dim=1)
+
+
+def _dense_rows(cache: TieredKeyCacheLayer, q_all, gqa_group: int, q_scale: float, heads: torch.Tensor | None):
+    """Dense attention over the Tier-2 keys and values of `cache` for the listed heads (all heads when `heads` is
+    None), by the dense-recompute CTAs of the attend kernel (cqa_dense_attend).  Returns float32 [H, 128]; rows of
+    heads that were not listed are undefined."""
+    if not q_all.is_cuda:
+        raise RuntimeError("dense recompute needs CUDA tensors; there is no CPU fallback")
+    G = int(gqa_group)
+    H = cache.kv_heads * G
+    dev = q_all.device
+    ws = _workspace(cache, H, G, dev)
+    # a private certificate: only the `dense` marks, the count and the list of heads are read
+    buf = torch.zeros(H * _lib.CERT_BYTES + 4 * (5 + H), dtype=torch.uint8, device=dev)
+    flags = buf[H * _lib.CERT_BYTES:].view(torch.int32)
+    if heads is None:
+        flags[2] = 1                                   # "every head": what a score-consistency violation sets
+    else:
+        hs = heads.to(device=dev, dtype=torch.int32).reshape(-1)
+        cert_i32 = buf[: H * _lib.CERT_BYTES].view(torch.int32).view(H, _lib.CERT_BYTES // 4)
+        cert_i32[hs.long(), _lib.CqaHeadCert.dense.offset // 4] = 1
+        flags[4] = int(hs.numel())
+        flags[5: 5 + hs.numel()] = hs
+    out = torch.empty(H, 128, dtype=torch.float32, device=dev)
+    w = _lib.CqaWorkspace.from_buffer_copy(bytes(ws.fill_struct(cache.active_blocks)))
+    w.cert = buf.data_ptr()
+    w.any_flags = buf.data_ptr() + H * _lib.CERT_BYTES
+    w.out = out.data_ptr()
+    q = q_all.contiguous()
+    with _lib.on_device(dev):
+        _lib.check(_lib.lib().cqa_dense_attend(
+            C.byref(cache._desc(G)), C.byref(w), q.data_ptr(), _lib.dtype_code(q.dtype), cache.num_tokens,
+            float(q_scale), _lib.current_stream(dev)), "cqa_dense_attend")
+    return out
+
+
+def recompute_heads_dense_fp16(cache: TieredKeyCacheLayer, q_all, output, head_indices, gqa_group: int,
+                               q_scale: float):
+    """Rung-3 recompute: replace output[h] for the listed heads by dense attention over the cache's Tier-2 keys and
+    values (reference: certified_attention.py:789-879).  Returns (output, h2d_key_bytes, h2d_key_blocks,
+    h2d_value_bytes, h2d_value_blocks); the byte counts are zero because nothing is staged through the host (with
+    a bounded hot tier the kernel reads non-resident blocks from the pinned backing arrays in place)."""
+    if head_indices.numel() == 0:
+        return output, 0, 0, 0, 0
+    rows = _dense_rows(cache, q_all, gqa_group, q_scale, head_indices)
+    idx = head_indices.to(device=output.device, dtype=torch.long).reshape(-1)
+    output.index_copy_(0, idx, rows.index_select(0, idx).to(output.dtype))
+    return output, 0, 0, 0, 0
+
+
+def sdpa_attend_with_skip(cache: TieredKeyCacheLayer, q_all, skip_mask, gqa_group: int, q_scale: float):
+    """Dense attention of every head over the Tier-2 keys and values, float32 [H, 128]
+    (reference: certified_attention.py:989-1062, which calls torch SDPA in the model dtype; here the dense CTAs of
+    the attend kernel accumulate in float32).  Block skipping (`skip_mask` with True entries) belongs to the
+    reference's disabled legacy path and is refused."""
+    if skip_mask is not None and bool(skip_mask.any().item()):
+        raise NotImplementedError("block skipping is not built; pass an all-False skip mask")
+    return _dense_rows(cache, q_all, gqa_group, q_scale, None)
 
 
 def compute_fp16_block_scores(cache: TieredKeyCacheLayer, q_all, block_indices, num_scoring_blocks: int,

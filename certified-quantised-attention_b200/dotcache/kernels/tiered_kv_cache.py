@@ -8,11 +8,13 @@ and counters, so callers that read the tensors keep working.  All
 quantisation and append work runs in hand-written CUDA through the C ABI of
 libcqa_b200.so; there is no PyTorch or CPU compute path.
 
-Tier 1 (INT8 per-channel keys, INT4 per-group values) and Tier 2 (the
-model-dtype originals) both live in HBM: a B200 has room for the full-context
-originals, so `keys_fp16_gpu` / `values_fp16_gpu` are full mirrors addressed
-through identity slot tables.  A bounded hot tier (capacity smaller than the
-context) is not built yet and raises NotImplementedError.
+Tier 1 (INT8 per-channel keys, INT4 per-group values) lives in HBM.  Tier 2
+(the model-dtype originals) lives in HBM too by default: a B200 has room for
+the full-context originals, so `keys_fp16_gpu` / `values_fp16_gpu` are full
+mirrors addressed through identity slot tables.  With hot-tier capacities
+below the reserved context (INT4-value caches), Tier 2 is kept in pinned host
+memory behind a device scratch of `capacity` blocks; residency tables, clock
+replacement and counters live on the device (csrc/hot_tier.cu).
 """
 from __future__ import annotations
 
@@ -197,7 +199,7 @@ class TieredKeyCacheLayer:
                 "key_owner": torch.full((kcap,), -1, **i32), "value_owner": torch.full((vcap,), -1, **i32),
                 "key_stamp": torch.full((kcap,), -1, **i32), "value_stamp": torch.full((vcap,), -1, **i32),
                 "work": torch.zeros(2 * (2 + 3 * maxblk), **i32),
-                "counters": torch.zeros(12, dtype=torch.int64, device=dev),
+                "counters": torch.zeros(24, dtype=torch.int64, device=dev),
             }
             st = _lib.CqaHotTier()
             st.key_capacity_blocks, st.value_capacity_blocks = kcap, vcap
@@ -349,12 +351,15 @@ class TieredKeyCacheLayer:
                                             stream)
         _lib.check(rc, "cqa_hot_tier_update")
 
-    def hot_tier_counters(self) -> dict:
-        """Residency telemetry since construction (synchronises): hits, misses, page-ins and evictions per tier,
-        and the bytes the page-ins moved from the backing arrays."""
+    def hot_tier_counters(self, last_call: bool = False) -> dict:
+        """Residency telemetry (synchronises): hits, misses, page-ins and evictions per tier, and the bytes the
+        page-ins moved from the backing arrays.  Totals since construction, or with `last_call` the figures of the
+        latest residency update alone (the device keeps the counters as they were before it)."""
         if self._hot is None:
             return {}
         c = self._hot["counters"].cpu().tolist()
+        if last_call:
+            c = [a - b for a, b in zip(c[:12], c[12:24])]
         blk = BLOCK * self.head_dim * self.keys_fp16_gpu.element_size() * self.kv_heads
         out = {"steps": c[0]}
         for name, o in (("key", 3), ("value", 7)):
@@ -362,6 +367,41 @@ class TieredKeyCacheLayer:
             out[f"{name}_pageins"], out[f"{name}_evictions"] = c[o + 2], c[o + 3]
             out[f"{name}_pagein_bytes"] = c[o + 2] * blk
         return out
+
+    def _ensure_resident(self, tier: int, block_ids) -> tuple[int, int, int, int]:
+        """(hits, misses, bytes paged in, evictions) of one residency request; zeros for a full mirror."""
+        if self._hot is None:
+            return (0, 0, 0, 0)
+        dev = self.keys_int8.device
+        ids = block_ids if torch.is_tensor(block_ids) else torch.as_tensor(list(block_ids), dtype=torch.int64)
+        ids = torch.unique(ids.to(device=dev, dtype=torch.int64))
+        with _lib.on_device(dev):
+            rc = _lib.lib().cqa_hot_tier_ensure(C.byref(self._desc()), C.byref(self._hot["struct"]), tier,
+                                                ids.data_ptr(), int(ids.numel()), _lib.current_stream(dev))
+        _lib.check(rc, "cqa_hot_tier_ensure")
+        d = self.hot_tier_counters(last_call=True)
+        name = "key" if tier == 0 else "value"
+        return (d[f"{name}_hits"], d[f"{name}_misses"], d[f"{name}_pagein_bytes"], d[f"{name}_evictions"])
+
+    def ensure_fp16_keys_resident(self, block_ids) -> tuple[int, int, int, int]:
+        """Bring `block_ids` into the bounded FP16 key scratch; returns (hits, misses, bytes, evictions) of this
+        call (reference: tiered_kv_cache.py:1218-1304).  A no-op returning zeros for a full mirror.  The residency
+        tables live on the device: misses are paged in by kernels from the pinned backing array, slots not used in
+        the current step are recycled in clock order, at most `max_pagein_blocks` blocks per call.  Kernels never
+        need this call (they read a non-resident block from the backing array); it is a prefetch."""
+        return self._ensure_resident(0, block_ids)
+
+    def ensure_fp16_values_resident(self, block_ids) -> tuple[int, int, int, int]:
+        """Value-tier twin of ensure_fp16_keys_resident (reference: tiered_kv_cache.py:1387-1463)."""
+        return self._ensure_resident(1, block_ids)
+
+    def ensure_fp16_keys_resident_batched(self, block_ids) -> tuple[int, int, int, int]:
+        """Reference: tiered_kv_cache.py:1306-1385; the request is always one batched device operation here."""
+        return self._ensure_resident(0, block_ids)
+
+    def ensure_fp16_values_resident_batched(self, block_ids) -> tuple[int, int, int, int]:
+        """Reference: tiered_kv_cache.py:1465-1537."""
+        return self._ensure_resident(1, block_ids)
 
     def _defers_int4(self) -> bool:
         return bool(

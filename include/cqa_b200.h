@@ -5,8 +5,10 @@
  * parameter is documented as host memory, every pointer is a DEVICE pointer.
  * Every call that launches work takes a `cudaStream_t` passed as `void*`
  * (NULL = legacy default stream), returns 0 on success or a negative
- * `cqa_status`, never throws and never allocates or frees device memory:
- * all buffers, including scratch, belong to the caller.
+ * `cqa_status` and never throws.  No compute entry point allocates or frees
+ * device memory: all buffers, including scratch, belong to the caller.  The
+ * one exception is the pair cqa_peer_alloc / cqa_peer_free, which exists to
+ * create the exchange buffer that peers map.
  *
  * Geometry is fixed to what the reference's native kernels hard-wire
  * (dotcache/backends/cuda_kernels/certified_blackwell.cpp:110,226): head_dim =
@@ -224,6 +226,8 @@ typedef struct cqa_workspace {
 const char *cqa_version(void);
 /* Text of the last error on the calling thread (host memory, valid until the next call). */
 const char *cqa_last_error(void);
+/* Kernels this library has launched in this process so far (all threads); `reset` != 0 also sets the count to 0. */
+int64_t cqa_launch_count(int reset);
 
 /* Quantise `n_blocks` complete blocks starting at block `first_block` from
  * K/V in `src_dtype` ([KV][src_rows][128], token 0 of the source = token
@@ -300,6 +304,15 @@ int cqa_certify(const cqa_cache *c, const cqa_knobs *knobs, const cqa_workspace 
 int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,
                int64_t nact, int64_t num_tokens, int last_block_valid, float q_scale, void *stream);
 
+/* Dense attention over the Tier-2 keys and values for the heads the attached certificate lists: heads with
+ * cert[h].dense set, their number in any_flags[4] and their ids in any_flags[5..]; or every head when any_flags[2]
+ * is non-zero.  Only the dense-recompute CTAs of the attend kernel run; rows of listed heads go to ws->out, other
+ * rows are left alone.  Needs cert, any_flags, dense_m/dense_l/dense_acc (dense_splits), tickets and out.
+ * Replaces recompute_heads_dense_fp16 and sdpa_attend_with_skip called on their own
+ * (kernels/certified_attention.py:789-879, 989-1062). */
+int cqa_dense_attend(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t num_tokens,
+                     float q_scale, void *stream);
+
 /* Limits of cqa_attend_static (the size of its built-in scratch). */
 #define CQA_STATIC_MAX_HEADS 64
 #define CQA_STATIC_MAX_SPLITS 128
@@ -325,10 +338,12 @@ int cqa_attend(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q
  * library.  The first call on each device looks up the device address of
  * the array (with that device current); make that first call outside any
  * stream capture.  All calls on a device share the one array and it keeps
- * whatever the previous call left there; nothing in it has to start at zero
- * (each call overwrites every partial it later reads), but two calls whose
- * kernels can overlap on the GPU (different streams) would overwrite each
- * other's partials: serialise them. */
+ * whatever the previous call left there.  The only part that has to start at
+ * zero is the row of merge tickets, and every call clears it itself with a
+ * memset queued ahead of its kernel; the partials need no clearing because
+ * each call overwrites every partial it later reads.  Two calls whose kernels
+ * can overlap on the GPU (different streams) would overwrite each other's
+ * partials and tickets: serialise them. */
 int cqa_attend_static(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, int64_t nq,
                       int64_t nact, int64_t num_tokens, int last_block_valid, float q_scale, void *stream);
 
@@ -466,11 +481,33 @@ typedef struct cqa_hot_tier {
     int32_t *key_stamp;          /* [capacity] step in which the slot was last used */
     int32_t *value_stamp;
     int32_t *work;               /* [2][2 + 3 * max_blocks] per tier: miss count, fill count, missed blocks, (block, slot) pairs */
-    int64_t *counters;           /* [12]: step, clock hands (keys, values), then per tier: hits, misses, page-ins, evictions; 1 spare */
+    int64_t *counters;           /* [24]: step, clock hands (keys, values), then per tier: hits, misses, page-ins, evictions;
+                                    1 spare; entries 12..23 repeat 0..11 as they were before the latest update call */
 } cqa_hot_tier;
 
 int cqa_hot_tier_update(const cqa_cache *c, const cqa_workspace *ws, const cqa_hot_tier *ht, int64_t nact,
                         void *stream);
+
+/* Residency request by block id (reference: TieredKeyCacheLayer.ensure_fp16_keys_resident / _values_resident,
+ * tiered_kv_cache.py:1218-1537): the `n` distinct blocks `block_ids` (device memory) of tier 0 (keys) or 1 (values) are
+ * marked as used; those not resident are paged in from the backing array into slots that were not used in the
+ * current step (at most max_fill_blocks per call).  Counters are updated as by cqa_hot_tier_update. */
+int cqa_hot_tier_ensure(const cqa_cache *c, const cqa_hot_tier *ht, int tier, const int64_t *block_ids, int64_t n,
+                        void *stream);
+
+/* Page-in primitives under the reference's native extension (dotcache/backends/cuda_pagein.py:68-149,
+ * cuda_kernels/cuda_pagein_kernel.cu): gather 16-row blocks of a backing array `src` ([KV][src_rows] rows of
+ * row_bytes bytes, device memory or pinned host memory) into 16-row slots of the scratch array `dst`
+ * ([KV][dst_rows] rows).  Rows at or beyond active_tokens are not copied.
+ * cqa_page_in_blocks: (loaded_blocks[i] -> loaded_slots[i]) pairs, after setting slot_table[evicted] = -1 and
+ * slot_table[loaded] = slot (slot_table may be NULL).  Lists are device memory.
+ * cqa_page_in_by_slots: block i goes to slot block_slots[i] for every i < n_blocks with a slot >= 0. */
+int cqa_page_in_blocks(const void *src, int64_t src_rows, void *dst, int64_t dst_rows, int kv_heads, int row_bytes,
+                       const int64_t *loaded_blocks, const int32_t *loaded_slots, int64_t n_loaded,
+                       const int64_t *evicted_blocks, int64_t n_evicted, int32_t *slot_table, int64_t table_size,
+                       int64_t active_tokens, void *stream);
+int cqa_page_in_by_slots(const void *src, int64_t src_rows, void *dst, int64_t dst_rows, int kv_heads, int row_bytes,
+                         const int32_t *block_slots, int64_t n_blocks, int64_t active_tokens, void *stream);
 
 /* Suggested split counts for a context of `nact` blocks on the current device. */
 int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int *num_splits, int *dense_splits);

@@ -50,6 +50,28 @@ static inline uint32_t f_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u
 /* exp(x): Cody-Waite reduction by ln2 (two constants), degree-5 polynomial for
  * exp(r)-1-r over r^2 (Cephes coefficients), scaling by 2^n through the
  * exponent field.  Inputs below -104 give 0. */
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+/* Number of OpenMP threads the parallel loops below use (a launcher may have exported OMP_NUM_THREADS=1). */
+void cqa_o_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+int cqa_o_max_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
 float cqa_o_exp(float x)
 {
     if (!(x > -104.0f)) return 0.0f;

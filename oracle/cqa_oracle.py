@@ -62,6 +62,13 @@ def lib():
     return _lib
 
 
+def set_threads(n: int) -> int:
+    """Use `n` OpenMP threads for the parallel loops (a launcher such as torchrun exports OMP_NUM_THREADS=1, which
+    would silently serialise them).  Returns the number now in effect."""
+    lib().cqa_o_set_threads(C.c_int(int(n)))
+    return int(lib().cqa_o_max_threads())
+
+
 def _p(a):
     return a.ctypes.data_as(C.c_void_p) if a is not None else None
 
@@ -510,10 +517,12 @@ def layer_step(cache: OracleCache, q, gqa_group, q_scale=None, *, v_tolerance, t
                ranking_fallback=False, ranking_r=1, ranking_fallback_mode="full", tau_cov=None,
                k_min=2, k_max=None, rung1_threshold=0.02, rung1_multiplier=2.0,
                score_consistency_check=True, eps_guard=0.01, exploration_rate=0.0,
-               exploration_u=None, value_error_mode="tight"):
+               exploration_u=None, value_error_mode="tight", fp16_values=False):
     """One certified decode step for one layer (adaptive K*, INT4-value cache,
     full-mirror Tier-2).  Follows certified_attention.py:1065-2790 for that
-    configuration.  Returns a dict with every intermediate."""
+    configuration.  Returns a dict with every intermediate.
+    `fp16_values`: the cache holds model-dtype values instead of INT4 (from_fp16_cache, tiered_kv_cache.py:135-286):
+    there is no value check and every block reads the original values (certified_attention.py:1827-1829)."""
     if q_scale is None:
         q_scale = 1.0 / math.sqrt(D)
     q = _c(q, np.float32)
@@ -582,13 +591,18 @@ def layer_step(cache: OracleCache, q, gqa_group, q_scale=None, *, v_tolerance, t
         return R
 
     # value check (:1940-2058)
-    vc = value_check(sel["mass_frac"], cache.values_int4_errors[:, :nq], gqa_group, v_tolerance,
-                     value_error_mode)
-    R.update(e_pre=vc["e_pre"], e_val=vc["e_val"], value_unsafe_mask=vc["unsafe"], value_margin=vc["margin"])
-    vmask = np.zeros((H, nact), dtype=bool)
-    vmask[:, :nq] = vc["unsafe"]
-    if trailing:
-        vmask[:, nq:] = True
+    if fp16_values:
+        vmask = np.ones((H, nact), dtype=bool)
+        R.update(e_pre=np.zeros(H, np.float32), e_val=np.zeros(H, np.float32),
+                 value_unsafe_mask=np.zeros((H, nq), dtype=bool))
+    else:
+        vc = value_check(sel["mass_frac"], cache.values_int4_errors[:, :nq], gqa_group, v_tolerance,
+                         value_error_mode)
+        R.update(e_pre=vc["e_pre"], e_val=vc["e_val"], value_unsafe_mask=vc["unsafe"], value_margin=vc["margin"])
+        vmask = np.zeros((H, nact), dtype=bool)
+        vmask[:, :nq] = vc["unsafe"]
+        if trailing:
+            vmask[:, nq:] = True
     R["value_fp16_mask"] = vmask
     last_valid = BS if not trailing else cache.num_tokens - nq * BS
     out, lse = attend_mixed(cache, q, gqa_group, q_scale, topk_active, vmask, nact, last_valid)

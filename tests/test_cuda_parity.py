@@ -332,13 +332,17 @@ def test_decode_step_async_layers_one_wait_per_token():
 
 def test_in_kernel_exploration_draw():
     """Without uniforms or a generator the selector draws its own: the rate is respected, the draw is a function
-    of torch's seed and the per-cache call counter only, and explored blocks are never blocks the selector chose."""
+    of torch's seed, the workspace's serial number (so the layers of a model differ) and the per-cache call counter
+    only, and explored blocks are never blocks the selector chose."""
     dtype = "bfloat16"
     base = synth.make_layer_inputs(13, 16384, dtype=dtype, n_planted_blocks=32)
     knobs = _knobs(exploration_rate=0.05)
     masks = []
-    for rep in range(2):
+    from dotcache.kernels import certified_attention as ca
+    for rep in range(3):
         torch.manual_seed(1234)
+        if rep < 2:
+            ca._Workspace._serial = 0          # as in a fresh process: the first workspace created
         cc = hz.make_cuda_cache(base.k, base.v, dtype, 16)
         per_call = []
         for call in range(2):
@@ -356,6 +360,7 @@ def test_in_kernel_exploration_draw():
         assert 0.035 < frac < 0.065, f"exploration fraction {frac}"
         assert not np.array_equal(per_call[0], per_call[1]), "the call counter must change the draw"
     assert np.array_equal(masks[0][0], masks[1][0]) and np.array_equal(masks[0][1], masks[1][1])
+    assert not np.array_equal(masks[2][0], masks[0][0]), "a second workspace (another layer) must draw another set"
 
 
 def test_decode_loop_bit_exact_selections():
