@@ -56,9 +56,15 @@ __device__ __forceinline__ uint4 philox4(unsigned long long seed, unsigned long 
     }
     return make_uint4(c0, c1, c2, c3);
 }
-// One uniform in [0, 1) per (block, head, call).  Blocks b, b + 1024, b + 2048, b + 3072 (the four a thread owns
-// in a row) share one Philox call: counter word (b mod 1024) + 1024 * (b div 4096), output word (b div 1024) mod 4.
-__device__ __forceinline__ float uniform_of_word(unsigned w) { return (float)(w >> 8) * 5.9604644775390625e-08f; }
+// The exploration draw takes one 16-bit uniform per (block, head, call): the eight blocks a thread owns in a row
+// (b, b + 1024, ..., b + 7168) share one Philox call with counter word (b mod 1024) + 1024 * (b div 8192); block
+// number i of the eight reads half (i mod 2) of output word i div 2.
+
+__device__ __forceinline__ void cp_async4(float *smem, const float *gmem)
+{
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(sa), "l"(gmem) : "memory");
+}
 
 struct SCShared {
     float red_f[2][SC_WARPS];
@@ -184,16 +190,112 @@ __device__ __forceinline__ void rank_sort_desc(u64 *cand, SCShared &sh)
     __syncthreads();
 }
 
+// Given hist[0..nbins) (nbins <= 2048, non-negative, total below 2^31), find the highest bin d whose suffix sum
+// S(d) = hist[d] + hist[d+1] + ... reaches `need` (need >= 1, S(0) >= need): returns d in every thread, with
+// `above` = S(d+1) and `in_bin` = hist[d].  Thread t scans the bins in descending order, two per thread; one
+// warp scan, one barrier, and every thread adds up the totals of the warps before its own.
+__device__ __forceinline__ int find_suffix_crossing(const int *hist, int nbins, int need, SCShared &sh, int &above,
+                                                    int &in_bin)
+{
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int r0 = 2 * tid, r1 = 2 * tid + 1;                      // ranks from the top
+    const int c0 = r0 < nbins ? hist[nbins - 1 - r0] : 0;
+    const int c1 = r1 < nbins ? hist[nbins - 1 - r1] : 0;
+    const int local = c0 + c1;
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_up_sync(FULL, incl, o);
+        if (lane >= o) incl += x;
+    }
+    if (lane == 31) sh.red_i[0][w] = incl;
+    __syncthreads();
+    const int wt = sh.red_i[0][lane];
+    int wincl = wt;                                                // inclusive scan of the warp totals
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_up_sync(FULL, wincl, o);
+        if (lane >= o) wincl += x;
+    }
+    const int base = __shfl_sync(FULL, wincl - wt, w);
+    const int excl = base + incl - local;
+    if (excl < need && need <= excl + local) {
+        const bool first = excl + c0 >= need;
+        sh.bcast_i[4] = nbins - 1 - (first ? r0 : r1);
+        sh.bcast_i[5] = first ? excl : excl + c0;
+        sh.bcast_i[6] = first ? c0 : c1;
+    }
+    __syncthreads();
+    above = sh.bcast_i[5];
+    in_bin = sh.bcast_i[6];
+    return sh.bcast_i[4];
+}
+
+// Count into hist[digit] the entries that `match`, one shared-memory atomic per entry; when every matching lane of
+// a warp has the same digit (heavily tied data) the warp adds its count with a single atomic instead.
+__device__ __forceinline__ void hist_add(int *hist, bool match, unsigned digit, int amount = 1)
+{
+    const unsigned who = __ballot_sync(FULL, match);
+    if (who == 0) return;
+    const int leader = __ffs(who) - 1;
+    const unsigned d0 = __shfl_sync(FULL, digit, leader);
+    const unsigned same = __ballot_sync(FULL, match && digit == d0);
+    if (same == who && amount == 1) {
+        if ((int)(threadIdx.x & 31) == leader) atomicAdd(&hist[d0], __popc(who));
+    } else if (match) {
+        atomicAdd(&hist[digit], amount);
+    }
+}
+
+// Bit pattern `thr` of the M-th largest of the n values v[k] <-> index k * 1024 + tid (values >= 0; 1 <= M < n) and
+// the number n_ge of entries at or above it, by a radix search: digits of 11, 11 and 9 bits from the top, each a
+// histogram in shared memory (integer atomics) and a scan for the bin that holds the M-th entry.  A pass only
+// counts the entries that fell into the previous pass's bin, and the search stops when a bin is taken whole (then
+// n_ge == M and the lower bits of thr are zero).  hist: 2048 ints.
+template <int VPT>
+__device__ __forceinline__ void radix_threshold(const float (&v)[VPT], int n, int M, int *hist, SCShared &sh,
+                                                unsigned &thr, int &n_ge)
+{
+    const int tid = threadIdx.x;
+    unsigned prefix = 0;
+    int need = M, above_total = 0;
+#pragma unroll 1
+    for (int pass = 0; pass < 3; ++pass) {
+        const int shift = pass == 0 ? 20 : (pass == 1 ? 9 : 0);
+        const int nbins = pass == 2 ? 512 : 2048;
+        const int up = pass == 0 ? 31 : (pass == 1 ? 20 : 9);        // bits at and above `up` are decided
+        hist[2 * tid] = 0;
+        hist[2 * tid + 1] = 0;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const unsigned x = __float_as_uint(v[k]);
+            const bool match = (k * SC_THREADS + tid) < n && (pass == 0 || (x >> up) == (prefix >> up));
+            hist_add(hist, match, (x >> shift) & (unsigned)(nbins - 1));
+        }
+        __syncthreads();
+        int above, in_bin;
+        const int d = find_suffix_crossing(hist, nbins, need, sh, above, in_bin);
+        prefix |= (unsigned)d << shift;
+        above_total += above;
+        need -= above;
+        __syncthreads();          // hist and the broadcast words are rewritten by the next pass
+        if (in_bin == need || pass == 2) {
+            thr = prefix;
+            n_ge = above_total + in_bin;
+            return;
+        }
+    }
+}
+
 // The M = min(CAND, n) largest (value, lower-index-first) entries of the n values v[k] <-> index k * 1024 + tid
 // (values >= 0, entries at or beyond n hold +0), sorted descending into cand[0..CAND) (padding = 0).  `vals` is the
 // same data in shared memory.
 //
-// The value of the M-th largest entry is found two bits per step (most significant first): a candidate threshold
-// is kept when at least M entries are at or above it.  A step is one pass over the registers and one barrier, and
-// the search stops as soon as a threshold separates exactly M entries.  Entries above the threshold are then
-// compacted and ordered by rank counting.
+// The value of the M-th largest entry is found by a radix search over the bit patterns (radix_threshold); entries
+// above the threshold are then compacted and ordered by rank counting.
 template <int VPT>
-__device__ __forceinline__ void select_top_sorted(const float (&v)[VPT], const float *vals, int n, u64 *cand,
+__device__ __forceinline__ void select_top_sorted(const float (&v)[VPT], const float *vals, int n, u64 *cand, int *hist,
                                                   SCShared &sh, int &parity)
 {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -206,32 +308,7 @@ __device__ __forceinline__ void select_top_sorted(const float (&v)[VPT], const f
     } else {
         unsigned thr = 0u;
         int n_ge = n;            // entries >= thr
-#pragma unroll 1
-        for (int bit = 30; bit >= 0 && n_ge != M; bit -= 2) {
-            const bool single = bit == 0;                 // 31 value bits: the last step decides one bit
-            const int lo = single ? 0 : bit - 1;
-            const unsigned t1 = thr | (1u << lo);                              // 01 (or 1)
-            const unsigned t2 = single ? 0xFFFFFFFFu : thr | (2u << lo);       // 10
-            const unsigned t3 = single ? 0xFFFFFFFFu : thr | (3u << lo);       // 11
-            unsigned l12 = 0, l3 = 0;
-#pragma unroll
-            for (int k = 0; k < VPT; ++k) {
-                const unsigned x = __float_as_uint(v[k]);
-                l12 += (x >= t1 ? 1u : 0u) + (x >= t2 ? 1u << 16 : 0u);
-                l3 += x >= t3 ? 1u : 0u;
-            }
-            l12 = __reduce_add_sync(FULL, l12);
-            l3 = __reduce_add_sync(FULL, l3);
-            if (lane == 0) { sh.red_u[parity][0][w] = l12; sh.red_u[parity][1][w] = l3; }
-            __syncthreads();
-            const unsigned c12 = __reduce_add_sync(FULL, sh.red_u[parity][0][lane]);   // each field stays below 2^15
-            const int c3 = (int)__reduce_add_sync(FULL, sh.red_u[parity][1][lane]);
-            parity ^= 1;
-            const int c1 = (int)(c12 & 0xFFFFu), c2 = (int)(c12 >> 16);
-            if (!single && c3 >= M) { thr = t3; n_ge = c3; }
-            else if (!single && c2 >= M) { thr = t2; n_ge = c2; }
-            else if (c1 >= M) { thr = t1; n_ge = c1; }
-        }
+        radix_threshold<VPT>(v, n, M, hist, sh, thr, n_ge);
         // n_ge == M: the entries >= thr are the answer.  Otherwise thr is the value of the M-th largest
         // entry and several entries equal it: take everything above, then the lowest block ids among the equal.
         const bool ties = n_ge != M;
@@ -400,8 +477,9 @@ __device__ __noinline__ void rescore_block_any(const cqa_cache &c, const void *q
     else rescore_block<float>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
 }
 
-// Dynamic shared memory: A[n_pad] B[n_pad] C[n_pad] (floats), cand[CAND] (u64), cum[CAND], gsum, leaf, mask[n_pad]
-// (bytes).  The full-sort fallback aliases its keys over B and C.
+// Dynamic shared memory: A[n_arr] B[n_arr] C[n_pad] (floats; n_arr = max(n_pad, 2048)), cand[CAND] (u64), cum[CAND],
+// gsum, leaf, mask[n_pad] (bytes).  The full-sort fallback aliases its keys over B and C; the radix searches use B
+// (and A) as histograms.
 template <int VPT>
 __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa_knobs kn, cqa_workspace ws, const void *q,
                                                                 int q_dtype, long nq, long nact, const float *u, long u_ld,
@@ -409,9 +487,10 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa
                                                                 int phases, int role_base)
 {
     extern __shared__ __align__(16) unsigned char dsm[];
-    float *A = reinterpret_cast<float *>(dsm);                 // m_b (role 2: mass*eta)
-    float *B = A + n_pad;                                      // block log-mass ell
-    float *C = B + n_pad;                                      // mass fraction
+    const int n_arr = n_pad > 2048 ? n_pad : 2048;             // A and B double as 2048-bin histograms
+    float *A = reinterpret_cast<float *>(dsm);                 // role 1: m_b
+    float *B = A + n_arr;                                      // role 1: block log-mass ell
+    float *C = B + n_arr;                                      // role 0: mass fractions
     u64 *cand = reinterpret_cast<u64 *>(C + n_pad);
     float *cum = reinterpret_cast<float *>(cand + CAND);
     float *gsum = cum + CAND;
@@ -456,70 +535,81 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa
     // certifying, the mass fractions (role 2)
     const bool explore_on = role == 0 && kn.exploration_rate > 0.0f;
     const float *eta = have_int4 ? c.values_int4_errors + (long)kv * (sharded_in ? ws.shard_chunk : c.max_blocks) : nullptr;
-    float m[VPT], ell[VPT], x[VPT];
-    unsigned ebits = 0;       // bit k: block k * 1024 + tid is an exploration candidate
+    int *hist = reinterpret_cast<int *>(B);   // 2048 bins; roles 0 and 2 do not keep block log-masses in B
+    float m[VPT], sv[VPT], x[VPT];
     float mg = -INFINITY;
+    // The rows go from global to shared memory by 4-byte asynchronous copies, all in flight at once and none of
+    // them holding a register (a thread has 64 registers here, too few to keep two dozen loads pending); the
+    // values are then read from shared memory.  A <- m_b, B <- S_b, C <- eta_b or the exploration uniforms.
     {
-        float s[VPT];
+        const float *xsrc = role == 2 ? eta : ((explore_on && u != nullptr) ? u + (long)h * u_ld : nullptr);
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
             const int b = k * SC_THREADS + tid;
-            m[k] = 0.0f; s[k] = 1.0f; x[k] = 0.0f;
             if (b < n) {
                 const long gb = gcol(b);
-                m[k] = mb[gb];
-                s[k] = sb[gb];
-                if (role == 0) {
-                    if (explore_on && u != nullptr) x[k] = u[(long)h * u_ld + b];
-                } else if (role == 2) {
-                    x[k] = eta ? eta[gb] : 0.0f;
-                }
+                cp_async4(A + b, mb + gb);
+                cp_async4(B + b, sb + gb);
+                if (xsrc) cp_async4(C + b, xsrc + (role == 2 ? gb : (long)b));
             }
         }
-        if (explore_on && u == nullptr) {
-#pragma unroll
-            for (int j = 0; j < (VPT + 3) / 4; ++j) {
-                const uint4 r = philox4(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)tid | ((unsigned)j << 10));
-                const unsigned wds[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    if (4 * j + i < VPT) x[4 * j + i] = uniform_of_word(wds[i]);
-            }
-        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        // each thread reads back only what it copied itself, so no barrier is needed here
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
             const int b = k * SC_THREADS + tid;
-            if (b < n_pad) {
-                unsigned char eb = 0;
-                if (b < n) {
-                    ell[k] = __fadd_rn(clog(fmaxf(s[k], 1e-30f)), m[k]);
-                    if (explore_on && x[k] < kn.exploration_rate) { eb = 2; ebits |= 1u << k; }
-                    A[b] = role == 2 ? x[k] : m[k];
-                    B[b] = ell[k];
-                    mg = fmaxf(mg, m[k]);
-                } else {
-                    ell[k] = -INFINITY;
+            const bool valid = b < n;
+            m[k] = valid ? A[b] : 0.0f;
+            sv[k] = valid ? fmaxf(B[b], 1e-30f) : 1.0f;
+            x[k] = (valid && xsrc) ? C[b] : 0.0f;
+        }
+        __syncthreads();   // A, B and C are reused below (histograms, block log-masses, mass fractions)
+    }
+    if (explore_on && u == nullptr) {
+        // in-kernel draw: one Philox call gives the eight 16-bit uniforms of blocks tid + 1024 * (8j .. 8j+7)
+#pragma unroll
+        for (int j = 0; j < (VPT + 7) / 8; ++j) {
+            const uint4 r = philox4(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)tid | ((unsigned)j << 10));
+            const unsigned wds[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (8 * j + i < VPT)
+                    x[8 * j + i] = (float)((wds[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu) * 1.52587890625e-05f;   // 2^-16
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int b = k * SC_THREADS + tid;
+        if (b < n_pad) {
+            unsigned char eb = 0;
+            if (b < n) {
+                if (explore_on && x[k] < kn.exploration_rate) eb = 2;
+                if (role == 1) {
+                    A[b] = m[k];
+                    B[b] = __fadd_rn(clog(sv[k]), m[k]);      // block log-mass: the boundary check needs it
                 }
-                mask[b] = eb;                         // bit 1: exploration candidate, bit 0: selected (set later)
-            } else {
-                ell[k] = -INFINITY;
+                mg = fmaxf(mg, m[k]);
             }
+            if (role == 0) mask[b] = eb;                  // bit 1: exploration candidate, bit 0: selected (set later)
         }
     }
     float f[VPT];             // mass fractions (roles 0 and 2)
     float total = 0.0f;
     if (compute_frac) {
+        // mass = S * exp(m - max m), fraction = mass * (1 / total): one exponential and one product per block
         mg = cta_max(mg, sh, parity);
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) f[k] = (k * SC_THREADS + tid) < n ? cexp(__fsub_rn(ell[k], mg)) : 0.0f;
+        for (int k = 0; k < VPT; ++k)
+            f[k] = (k * SC_THREADS + tid) < n ? __fmul_rn(sv[k], cexp(__fsub_rn(m[k], mg))) : 0.0f;
         total = fmaxf(cta_canonical_sum<VPT>(f, n, gsum, leaf), 1e-30f);
+        const float inv_total = __fdiv_rn(1.0f, total);
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
             const int b = k * SC_THREADS + tid;
             if (b < n) {
-                f[k] = __fdiv_rn(f[k], total);
-                C[b] = f[k];
-                if (role == 0) mf[b] = f[k];
+                f[k] = __fmul_rn(f[k], inv_total);
+                if (role == 0) { C[b] = f[k]; mf[b] = f[k]; }
             }
         }
     } else if (role == 2) {
@@ -527,7 +617,6 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa
         for (int k = 0; k < VPT; ++k) {
             const int b = k * SC_THREADS + tid;
             f[k] = b < n ? mf[b] : 0.0f;
-            if (b < n) C[b] = f[k];
         }
     }
 
@@ -538,7 +627,7 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa
         const bool narrow = hi <= CAND;
         if (narrow) {
             __syncthreads();   // C is complete (the tie path of the search reads it)
-            select_top_sorted<VPT>(f, C, n, cand, sh, parity);
+            select_top_sorted<VPT>(f, C, n, cand, hist, sh, parity);
             if (tid < CAND) cum[tid] = key_val(cand[tid]);
             __syncthreads();
             if (tid == 0) {
@@ -919,21 +1008,56 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa
             t0 = 0u;
             int cnt_lo = cnt, cnt_hi = 0;     // entries >= t0, entries >= the upper end of the open range
             float f_lo = e_pre;
+            int bit = 30;
+            // A hint first: 2048 bins over the top 11 bits of the contributions, each holding a fixed-point sum of its
+            // entries (integer atomics; the scale keeps the total below 2^30).  The bin where the approximate suffix
+            // sum crosses the excess is then CHECKED with exact column sums of its two edges; only if the exact sums
+            // bracket the excess does the search continue inside the bin (bits 19..0), otherwise it starts from the
+            // top as if there had been no hint.  The result never depends on the approximation.
+            float emax = 0.0f;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) emax = fmaxf(emax, e[k]);
+            emax = cta_max(emax, sh, parity);
+            if (emax > 0.0f && n > 64) {
+                int *hsum = reinterpret_cast<int *>(A);
+                hsum[2 * tid] = 0;
+                hsum[2 * tid + 1] = 0;
+                __syncthreads();
+                const float sc = __fdiv_rn(1073741824.0f, __fmul_rn((float)n, emax));     // 2^30 / (n * max)
+#pragma unroll
+                for (int k = 0; k < VPT; ++k) {
+                    const unsigned xb = __float_as_uint(e[k]);
+                    const int qv = (int)__fmul_rn(e[k], sc);
+                    hist_add(hsum, (k * SC_THREADS + tid) < n && qv > 0, xb >> 20, qv);
+                }
+                __syncthreads();
+                const int need = max(1, (int)fminf(__fmul_rn(excess, sc), 1073741824.0f));
+                // total of the bins (the crossing search needs need <= total)
+                int tot = hsum[2 * tid] + hsum[2 * tid + 1];
+                tot = __reduce_add_sync(FULL, tot);
+                if (lane == 0) sh.red_i[1][warp] = tot;
+                __syncthreads();
+                tot = __reduce_add_sync(FULL, sh.red_i[1][lane]);
+                if (need <= tot) {
+                    int above, in_bin;
+                    const int d = find_suffix_crossing(hsum, 2048, need, sh, above, in_bin);
+                    const unsigned t_lo = (unsigned)d << 20, t_hi = (unsigned)(d + 1) << 20;
+                    float fs[3];
+                    int cs3[3];
+                    column_sums3<VPT>(e, t_lo, t_hi, 0xFFFFFFFFu, sh, parity, fs, cs3);
+                    if (fs[0] >= excess && fs[1] < excess) {
+                        t0 = t_lo; cnt_lo = cs3[0]; f_lo = fs[0]; cnt_hi = cs3[1];
+                        bit = 19;
+                    }
+                }
+            }
+            // one bit per step: keep the bit when the entries at or above the trial threshold still reach the excess
 #pragma unroll 1
-            for (int bit = 30; bit >= 0 && cnt_lo - cnt_hi > 1; bit -= 2) {
-                const bool single = bit == 0;
-                const int lo = single ? 0 : bit - 1;
-                const unsigned t1 = t0 | (1u << lo);
-                const unsigned t2 = single ? 0xFFFFFFFFu : t0 | (2u << lo);
-                const unsigned t3 = single ? 0xFFFFFFFFu : t0 | (3u << lo);
-                float fs[3];
-                int cs3[3];
-                column_sums3<VPT>(e, t1, t2, t3, sh, parity, fs, cs3);
-                // thresholds ascend, their sums descend: keep the largest threshold that still reaches the excess
-                if (!single && fs[2] >= excess) { t0 = t3; cnt_lo = cs3[2]; f_lo = fs[2]; }
-                else if (!single && fs[1] >= excess) { t0 = t2; cnt_lo = cs3[1]; f_lo = fs[1]; cnt_hi = cs3[2]; }
-                else if (fs[0] >= excess) { t0 = t1; cnt_lo = cs3[0]; f_lo = fs[0]; cnt_hi = single ? cnt_hi : cs3[1]; }
-                else { cnt_hi = cs3[0]; }
+            for (; bit >= 0 && cnt_lo - cnt_hi > 1; --bit) {
+                const unsigned trial = t0 | (1u << bit);
+                int cc = 0;
+                const float fv = column_sum1<VPT>(e, n, [trial](unsigned bits, int) { return bits >= trial; }, sh, parity, cc);
+                if (fv >= excess) { t0 = trial; cnt_lo = cc; f_lo = fv; } else { cnt_hi = cc; }
             }
             promoted = f_lo;
             n_prom = cnt_lo;
@@ -942,8 +1066,8 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa
                 // ... unless several entries equal t0: admit them in block order while the sum stays below
                 int i0 = 0;
 #pragma unroll 1
-                for (int bit = 14; bit >= 0; --bit) {
-                    const int trial = i0 | (1 << bit);
+                for (int bit2 = 14; bit2 >= 0; --bit2) {
+                    const int trial = i0 | (1 << bit2);
                     if (trial > n) continue;
                     int cc = 0;
                     const unsigned tt = t0;
@@ -996,7 +1120,8 @@ static int next_pow2(long n)
 
 static size_t selcert_smem(int n_pad)
 {
-    return (size_t)n_pad * 13 + (size_t)CAND * 12 + ((size_t)(n_pad >> 5) + 1 + (n_pad >> 8) + 2) * 4 + 64;
+    const size_t n_arr = n_pad > 2048 ? n_pad : 2048;
+    return n_arr * 8 + (size_t)n_pad * 5 + (size_t)CAND * 12 + ((size_t)(n_pad >> 5) + 1 + (n_pad >> 8) + 2) * 4 + 64;
 }
 
 // Selection widths derived from the knobs (shared by the argument check and the launch).

@@ -415,9 +415,12 @@ void cqa_o_fp16_block_scores(const float *keysf, long tstride, long scratch_toke
         }
 }
 
-/* Block mass fractions per head: mass = exp((log(max(S,1e-30)) + m) - max m);
- * frac = mass / max(canonical_sum(mass), 1e-30).  certified_attention.py:345-350
- * Also returns ell = m + log(max(S,1e-30)) (block log-mass, :1683-1686). */
+/* Block mass fractions per head.  The reference computes mass = exp(log(max(S,1e-30)) + m - max m) and
+ * frac = mass / max(sum(mass), 1e-30) (certified_attention.py:345-350) without fixing the rounding of either; the
+ * canonical form here is the algebraically equal
+ *     mass = max(S,1e-30) * exp(m - max m),  frac = mass * (1 / max(canonical_sum(mass), 1e-30))
+ * (one exponential and one multiplication per block, one division per head).
+ * Also returns ell = m + log(max(S,1e-30)) (block log-mass, :1683-1686), which the boundary check uses. */
 void cqa_o_mass_frac(const float *m_b, const float *S_b, int H, long nq, float *frac, float *ell,
                      float *m_global, float *total_out)
 {
@@ -429,13 +432,13 @@ void cqa_o_mass_frac(const float *m_b, const float *S_b, int H, long nq, float *
         float *f = frac + (long)h * nq;
         for (long b = 0; b < nq; ++b) {
             float s = S[b] < 1e-30f ? 1e-30f : S[b];
-            float lm = cqa_o_log(s) + m[b];
-            if (ell) ell[(long)h * nq + b] = lm;
-            f[b] = cqa_o_exp(lm - mg);
+            if (ell) ell[(long)h * nq + b] = cqa_o_log(s) + m[b];
+            f[b] = s * cqa_o_exp(m[b] - mg);
         }
         float tot = cqa_o_canonical_sum(f, nq);
         if (tot < 1e-30f) tot = 1e-30f;
-        for (long b = 0; b < nq; ++b) f[b] = f[b] / tot;
+        const float inv = 1.0f / tot;
+        for (long b = 0; b < nq; ++b) f[b] = f[b] * inv;
         if (m_global) m_global[h] = mg;
         if (total_out) total_out[h] = tot;
     }
