@@ -25,7 +25,7 @@ SYMBOLS = [
     "cqa_peer_buffer_bytes", "cqa_peer_alloc", "cqa_peer_free", "cqa_peer_export", "cqa_peer_import", "cqa_peer_close",
     "cqa_sharded_layer_step", "cqa_peer_status",
     "cqa_hot_tier_ensure", "cqa_page_in_blocks", "cqa_page_in_by_slots", "cqa_dense_attend",
-    "cqa_launch_count",
+    "cqa_launch_count", "cqa_wait_timeouts", "cqa_layer_step_batched",
 ]
 PARTIAL_STRIDE = 130
 
@@ -124,6 +124,13 @@ class CqaLayerCall(C.Structure):
     ]
 
 
+class CqaBatchItem(C.Structure):
+    _fields_ = [
+        ("cache", CqaCache), ("ws", CqaWorkspace), ("q", vp), ("k_new", vp), ("v_new", vp),
+        ("pos", C.c_int64), ("defer_int4", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 CERT_BYTES = C.sizeof(CqaHeadCert)
 
 _lib = None
@@ -188,6 +195,8 @@ def lib() -> C.CDLL:
     for s in SYMBOLS[2:]:
         getattr(L, s).restype = C.c_int
     L.cqa_peer_buffer_bytes.restype = C.c_int64
+    L.cqa_layer_step_batched.argtypes = [C.POINTER(CqaBatchItem), i32, vp, pk, i32, i32, vp]
+    L.cqa_wait_timeouts.argtypes = [C.POINTER(C.c_int), i32]
     L.cqa_launch_count.argtypes = [i32]
     L.cqa_launch_count.restype = C.c_int64
     _lib = L

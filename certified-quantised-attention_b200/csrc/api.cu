@@ -50,6 +50,13 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
 
 int dense_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long num_tokens, float q_scale,
                  cudaStream_t st);
+int score_blocks_batched_launch(const cqa_batch_item *items_dev, int n_items, int kv_heads, int gqa_group, long max_nq,
+                                int q_dtype, float q_scale, int do_append, cudaStream_t st);
+int selcert_batched_launch(const cqa_batch_item *items_dev, int n_items, int n_heads, long max_nq, const cqa_knobs *kn,
+                           int q_dtype, int do_append, cudaStream_t st);
+int attend_batched_launch(const cqa_batch_item *items_dev, int n_items, int kv_heads, int gqa_group, int t2_dtype,
+                          int max_splits, int q_dtype, float q_scale, int do_append, cudaStream_t st);
+int append_batched_launch(const cqa_batch_item *items_dev, int n_items, int kv_heads, int t2_dtype, int src_dtype, cudaStream_t st);
 int attend_static_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, int q_dtype, long nq, long nact,
                          long num_tokens, int last_valid, float q_scale, cudaStream_t st);
 
@@ -81,6 +88,18 @@ using namespace cqa;
 
 extern "C" const char *cqa_version(void) { return "cqa_b200 0.1 (sm_100a)"; }
 extern "C" const char *cqa_last_error(void) { return g_err; }
+extern "C" int cqa_wait_timeouts(int *count, int reset)
+{
+    if (!count) { set_error("cqa_wait_timeouts: NULL pointer"); return CQA_ERR_INVALID; }
+    int a = 0, b = 0;
+    if (score_wait_timeouts(&a, reset) || attend_wait_timeouts(&b, reset)) {
+        set_error("cqa_wait_timeouts: could not read the device counters: %s", cudaGetErrorString(cudaGetLastError()));
+        return CQA_ERR_CUDA;
+    }
+    *count = a + b;
+    return CQA_OK;
+}
+
 extern "C" int64_t cqa_launch_count(int reset)
 {
     return reset ? g_launches.exchange(0, std::memory_order_relaxed) : g_launches.load(std::memory_order_relaxed);
@@ -337,6 +356,76 @@ extern "C" int cqa_layer_step(const cqa_cache *c, const cqa_knobs *knobs, const 
     rc = selcert_launch(c, knobs, ws, q, q_dtype, nq, nact, exploration_u, u_ld, 3 | 16, st);   // select + certify in one launch; flags cleared by the score kernel
     if (rc) return rc;
     return attend_launch(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, knobs->q_scale, st, true);
+}
+
+extern "C" int cqa_layer_step_batched(const cqa_batch_item *items, int n_items, void *items_dev, const cqa_knobs *knobs,
+                                      int dtype, int do_append, void *stream)
+{
+    if (!items || !items_dev || !knobs || n_items <= 0 || n_items > 65535) {
+        set_error("cqa_layer_step_batched: NULL pointer or item count %d out of range (1..65535)", n_items);
+        return CQA_ERR_INVALID;
+    }
+    if (dtype < 0 || dtype > 2) { set_error("cqa_layer_step_batched: unknown dtype %d", dtype); return CQA_ERR_INVALID; }
+    if ((uintptr_t)items_dev & 15) { set_error("cqa_layer_step_batched: items_dev must be 16-byte aligned"); return CQA_ERR_INVALID; }
+    if (!(knobs->tau_cov > 0.0f)) { set_error("cqa_layer_step_batched: tau_cov must be positive"); return CQA_ERR_INVALID; }
+    do_append = do_append ? 1 : 0;
+    const cqa_cache &c0 = items[0].cache;
+    long max_nq = 0;
+    int max_splits = 0;
+    // every check of every sequence comes before the first copy or launch
+    for (int i = 0; i < n_items; ++i) {
+        const cqa_batch_item &it = items[i];
+        int rc = check_common(&it.cache, &it.ws, "cqa_layer_step_batched");
+        if (rc) return rc;
+        if (it.cache.kv_heads != c0.kv_heads || it.cache.gqa_group != c0.gqa_group || it.cache.t2_dtype != c0.t2_dtype) {
+            set_error("cqa_layer_step_batched: item %d differs from item 0 in head geometry or Tier-2 dtype", i);
+            return CQA_ERR_INVALID;
+        }
+        rc = check_select_ws(&it.ws, "cqa_layer_step_batched");
+        if (rc) return rc;
+        if (!it.q || !it.ws.token_scores || !it.ws.value_mask) {
+            set_error("cqa_layer_step_batched: item %d has no q, token_scores or value_mask", i);
+            return CQA_ERR_INVALID;
+        }
+        if (do_append) {
+            rc = append_check(&it.cache, it.k_new, it.v_new, dtype, it.pos);
+            if (rc) return rc;
+        }
+        const long num_tokens = it.pos + do_append;
+        const long nq = num_tokens / BS, nact = (num_tokens + BS - 1) / BS;
+        if (it.pos < 0 || nq <= 0) {
+            set_error("cqa_layer_step_batched: item %d holds %ld tokens; at least one complete block is needed", i, num_tokens);
+            return CQA_ERR_INVALID;
+        }
+        rc = check_score_args(&it.cache, dtype, nq, it.ws.ld, "cqa_layer_step_batched");
+        if (rc) return rc;
+        if (nact > it.ws.ld || nact > it.cache.max_blocks) {
+            set_error("cqa_layer_step_batched: item %d: workspace ld or cache max_blocks too small", i);
+            return CQA_ERR_INVALID;
+        }
+        rc = selcert_check(&it.cache, knobs, &it.ws, it.q, nq, 3 | 16);
+        if (rc) return rc;
+        rc = attend_check(&it.cache, &it.ws, nq, nact, nact == nq ? BS : (int)(num_tokens - nq * BS));
+        if (rc) return rc;
+        if (!it.ws.out) { set_error("cqa_layer_step_batched: item %d has no output rows", i); return CQA_ERR_INVALID; }
+        if (nq > max_nq) max_nq = nq;
+        if (it.ws.num_splits > max_splits) max_splits = it.ws.num_splits;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    const cqa_batch_item *dev = static_cast<const cqa_batch_item *>(items_dev);
+    int rc = check_cuda(cudaMemcpyAsync(items_dev, items, (size_t)n_items * sizeof(cqa_batch_item), cudaMemcpyHostToDevice, st),
+                        "copy of the batch records");
+    if (rc) return rc;
+    if (do_append) {
+        rc = append_batched_launch(dev, n_items, c0.kv_heads, c0.t2_dtype, dtype, st);
+        if (rc) return rc;
+    }
+    rc = score_blocks_batched_launch(dev, n_items, c0.kv_heads, c0.gqa_group, max_nq, dtype, knobs->q_scale, do_append, st);
+    if (rc) return rc;
+    rc = selcert_batched_launch(dev, n_items, c0.kv_heads * c0.gqa_group, max_nq, knobs, dtype, do_append, st);
+    if (rc) return rc;
+    return attend_batched_launch(dev, n_items, c0.kv_heads, c0.gqa_group, c0.t2_dtype, max_splits, dtype, knobs->q_scale,
+                                 do_append, st);
 }
 
 extern "C" int cqa_suggest_splits(int kv_heads, int gqa_group, int64_t nact, int *num_splits, int *dense_splits)

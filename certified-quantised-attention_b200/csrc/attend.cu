@@ -6,8 +6,9 @@
 //     group share every value load.  A warp owns one 16-token block at a time;
 //     the block's INT4 codes, scales, zeros and cached Phase-1 token scores
 //     (1.5 KB + 64 B per head) arrive in a warp-private 4-stage shared-memory
-//     ring through 16-byte asynchronous copies, so several blocks per warp are
-//     in flight and no CTA barrier sits in the loop.  Lane L (mod 16) owns
+//     ring through bulk asynchronous copies (TMA engine: one lane issues four
+//     copies per block, completion is counted by one mbarrier per stage), so
+//     several blocks per warp are in flight and no CTA barrier sits in the loop.  Lane L (mod 16) owns
 //     output channels 8L..8L+7; half warp 0 takes the even tokens, half warp 1
 //     the odd ones (conflict-free shared-memory reads).  INT4 codes become
 //     floats with one logic op and one exact fused multiply-add each (magic
@@ -38,18 +39,6 @@ constexpr int ATT_STAGES = CQA_ATT_STAGES;
 
 __device__ __forceinline__ float fexp(float x) { return __expf(x); }
 
-__device__ __forceinline__ void att_cp16(void *smem, const void *gmem)
-{
-    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void att_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void att_wait()
-{
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
 template <int G>
 struct AttLayout {
     static constexpr int PACKED = 0;
@@ -67,54 +56,60 @@ struct AttLayout {
     // values), two tiles of true weights for those heads, and the FP16-key logits of the block being prepared
     static constexpr int W_TILE = BS * G * 8;
     static constexpr int PER_WARP = 4 * W_TILE + G * BS * 4;
-    static constexpr int TOTAL = RING_BYTES + ATT_WARPS * PER_WARP;
+    static constexpr int BARS = RING_BYTES + ATT_WARPS * PER_WARP;        // one mbarrier per (warp, stage)
+    static constexpr int TOTAL = BARS + ATT_WARPS * ATT_STAGES * 8;
 };
 
-// Per-lane source pointers of the next block to stage.  A block's stage is 1536 + 64*G bytes = packed codes
-// (two 512-byte rounds), scales+zeros (one round: lanes 0-15 scales, 16-31 zeros) and G*64 bytes of token scores.
+// Source pointers of the next block to stage.  A block's stage is 1536 + 64*G bytes: packed codes (1024), scales
+// (256), zeros (256) and G*64 bytes of token scores, four contiguous pieces in global memory, one bulk copy each.
 template <int G>
 struct AttIssuer {
-    const char *pk, *sz, *sc;   // global sources for this lane
-    long b, b_end, nq;          // block to issue next
+    const char *pk, *sc_, *zr, *sc;   // global sources of the block to issue next
+    long b, b_end, nq;
     bool have4;
 
-    __device__ __forceinline__ void init(const cqa_cache &c, const float *tok, long nq_, int kv, long b0, long bend,
-                                         int lane)
+    __device__ __forceinline__ void init(const cqa_cache &c, const float *tok, long nq_, int kv, long b0, long bend)
     {
         b = b0;
         b_end = bend;
         nq = nq_;
         have4 = c.values_int4_packed != nullptr;
         const long row0 = (long)kv * c.cap_tokens + b0 * BS;
-        pk = reinterpret_cast<const char *>(c.values_int4_packed) + row0 * (D / 2) + lane * 16;
-        const char *szb = lane < 16 ? reinterpret_cast<const char *>(c.values_int4_scales)
-                                    : reinterpret_cast<const char *>(c.values_int4_zeros);
-        sz = szb + row0 * NG * 2 + (lane & 15) * 16;
-        sc = reinterpret_cast<const char *>(tok + ((long)kv * nq_ + b0) * G * BS) + lane * 16;
+        pk = reinterpret_cast<const char *>(c.values_int4_packed) + row0 * (D / 2);
+        sc_ = reinterpret_cast<const char *>(c.values_int4_scales) + row0 * NG * 2;
+        zr = reinterpret_cast<const char *>(c.values_int4_zeros) + row0 * NG * 2;
+        sc = reinterpret_cast<const char *>(tok + ((long)kv * nq_ + b0) * G * BS);
     }
-    // Stage the block `b` (if any) and advance by one warp stride; always commits one group.  A block without
-    // INT4 data (the trailing partial block) gets zeros, so the INT4 arithmetic on it is finite.
-    __device__ __forceinline__ void issue(char *stage, int lane)
+    // Stage the block `b` (if any) and advance by one warp stride.  Exactly one arrival per call reaches the
+    // stage's mbarrier (with the bytes of the copies issued, possibly none), so every call completes one phase.
+    // A block without INT4 data (the trailing partial block, or an FP16-value cache) gets zeros, written by the
+    // lanes themselves, so the INT4 arithmetic on it is finite.
+    __device__ __forceinline__ void issue(char *stage, unsigned stage_addr, unsigned bar_addr, int lane)
     {
         using LY = AttLayout<G>;
-        if (b < b_end) {
-            if (have4 && b < nq) {
-                att_cp16(stage + lane * 16, pk);
-                att_cp16(stage + 512 + lane * 16, pk + 512);
-                att_cp16(stage + LY::SCALES + lane * 16, sz);
-                if (lane < 4 * G) att_cp16(stage + LY::SCORES + lane * 16, sc);
-            } else {
-                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4 *>(stage + lane * 16) = z;
-                *reinterpret_cast<uint4 *>(stage + 512 + lane * 16) = z;
-                *reinterpret_cast<uint4 *>(stage + LY::SCALES + lane * 16) = z;
-                if (b < nq && lane < 4 * G) att_cp16(stage + LY::SCORES + lane * 16, sc);
-            }
+        const bool live = b < b_end;
+        const bool int4 = live && have4 && b < nq;
+        const bool scores = live && b < nq;
+        if (live && !int4) {
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4 *>(stage + lane * 16) = z;
+            *reinterpret_cast<uint4 *>(stage + 512 + lane * 16) = z;
+            *reinterpret_cast<uint4 *>(stage + LY::SCALES + lane * 16) = z;
         }
-        att_commit();
+        if (lane == 0) {
+            const unsigned bytes = (int4 ? (unsigned)LY::SCORES : 0u) + (scores ? (unsigned)(G * BS * 4) : 0u);
+            mbar_arrive_expect_tx(bar_addr, bytes);
+            if (int4) {
+                bulk_copy_g2s(stage_addr + LY::PACKED, pk, BS * (D / 2), bar_addr);
+                bulk_copy_g2s(stage_addr + LY::SCALES, sc_, BS * NG * 2, bar_addr);
+                bulk_copy_g2s(stage_addr + LY::ZEROS, zr, BS * NG * 2, bar_addr);
+            }
+            if (scores) bulk_copy_g2s(stage_addr + LY::SCORES, sc, G * BS * 4, bar_addr);
+        }
         b += ATT_WARPS;
         pk += ATT_WARPS * BS * (D / 2);
-        sz += ATT_WARPS * BS * NG * 2;
+        sc_ += ATT_WARPS * BS * NG * 2;
+        zr += ATT_WARPS * BS * NG * 2;
         sc += ATT_WARPS * G * BS * 4;
     }
 };
@@ -398,9 +393,8 @@ __device__ void dense_unit(const cqa_cache &c, const cqa_workspace &ws, const vo
 constexpr int DENSE_POOL_X = 8;  // dense-recompute CTAs per KV row of the grid
 
 template <int G, typename T2>
-__global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_kernel(cqa_cache c, cqa_workspace ws, const void *q,
-                                                               int q_dtype, long nq, long nact, long num_tokens,
-                                                               int last_valid, float q_scale, int blocks_per_split)
+__device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_workspace &ws, const void *q, int q_dtype, long nq,
+                                            long nact, long num_tokens, int last_valid, float q_scale, int blocks_per_split)
 {
     using LY = AttLayout<G>;
     extern __shared__ __align__(16) char dsm[];
@@ -436,10 +430,19 @@ __global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_kernel(c
     float *sc_tile = reinterpret_cast<float *>(wpriv + 4 * LY::W_TILE);        // [G][16] FP16-key logits
 
     // start the pipeline before anything else
-    AttIssuer<G> issuer;
-    issuer.init(c, ws.token_scores, nq, kv, b_begin + warp, b_end, lane);
+    uint64_t *wbar = reinterpret_cast<uint64_t *>(dsm + LY::BARS) + warp * ATT_STAGES;
+    if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < ATT_STAGES - 1; ++s) issuer.issue(wring + s * LY::STAGE, lane);
+        for (int s = 0; s < ATT_STAGES; ++s) mbar_init(wbar + s, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    const unsigned wring_addr = smem_u32(wring), wbar_addr = smem_u32(wbar);
+    AttIssuer<G> issuer;
+    issuer.init(c, ws.token_scores, nq, kv, b_begin + warp, b_end);
+#pragma unroll
+    for (int s = 0; s < ATT_STAGES - 1; ++s)
+        issuer.issue(wring + s * LY::STAGE, wring_addr + s * LY::STAGE, wbar_addr + s * 8, lane);
 
     // Blocks of this warp: b_begin + warp + 8*it.  Lane j keeps the key / value promotion bits of the warp's
     // block (it0 + j), one bit per head of the group; they are re-read every 32 blocks.
@@ -574,16 +577,18 @@ __global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_kernel(c
 
     float alpha_cur = 1.0f;
     if (n_my > 0) {
-        att_wait<ATT_STAGES - 2>();
-        __syncwarp();
+        mbar_wait(wbar_addr, 0u);     // block 0 has landed
         alpha_cur = prepare(0, __shfl_sync(FULL, my_masks, 0));
     }
     for (int it = 0; it < n_my; ++it) {
         const long b = b_begin + warp + (long)it * ATT_WARPS;
         __syncwarp();   // every lane is done with the slot that is about to be refilled, and with w_tiles[(it+1)&1]
-        issuer.issue(wring + ((it + ATT_STAGES - 1) % ATT_STAGES) * LY::STAGE, lane);
-        att_wait<ATT_STAGES - 2>();   // block it+1 has landed
-        __syncwarp();
+        {
+            const int slot = (it + ATT_STAGES - 1) % ATT_STAGES;
+            issuer.issue(wring + slot * LY::STAGE, wring_addr + slot * LY::STAGE, wbar_addr + slot * 8, lane);
+            // block it+1 has landed: its stage barrier completes one phase per pass over the ring
+            mbar_wait(wbar_addr + ((it + 1) % ATT_STAGES) * 8, (unsigned)((it + 1) / ATT_STAGES) & 1u);
+        }
         const unsigned masks_cur = __shfl_sync(FULL, my_masks, it & 31);
         const unsigned vm = (masks_cur >> 8) & 0xFFu;
         if ((it & 31) == 31 && it + 1 < n_my) load_masks(it + 1);
@@ -662,7 +667,8 @@ __global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_kernel(c
         }
         alpha_cur = alpha_next;
     }
-    att_wait<0>();
+    // every copy that was issued has been waited for: the last blocks issued lie beyond the warp's range and
+    // carry no bytes
     // per-head (m, l) for the CTA merge: l is summed over the lanes of a head first
 #pragma unroll
     for (int o = LPH / 2; o >= 1; o >>= 1) l_mine += __shfl_xor_sync(FULL, l_mine, o);
@@ -683,6 +689,29 @@ __global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_kernel(c
     if (take_ticket(ws.tickets + kv, ns, &s_flag))
         final_merge(ws.part_m, ws.part_l, ws.part_acc, ns, kv * G, G, ws, false, reinterpret_cast<float *>(ring),
                     c.kv_heads * G);
+}
+
+template <int G, typename T2>
+__global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_kernel(cqa_cache c, cqa_workspace ws, const void *q,
+                                                               int q_dtype, long nq, long nact, long num_tokens,
+                                                               int last_valid, float q_scale, int blocks_per_split)
+{
+    attend_body<G, T2>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, blocks_per_split);
+}
+
+// Sequence blockIdx.z of a batch.  grid.x = dense pool + the largest split count of the batch; CTAs beyond a
+// sequence's own split count have nothing to do.
+template <int G, typename T2>
+__global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_batched_kernel(const cqa_batch_item *items, int q_dtype,
+                                                                                      float q_scale, int do_append)
+{
+    const cqa_batch_item &it = items[blockIdx.z];
+    const long num_tokens = it.pos + do_append;
+    const long nq = num_tokens / BS, nact = (num_tokens + BS - 1) / BS;
+    const int ns = it.ws.num_splits;
+    if ((int)blockIdx.x >= DENSE_POOL_X + ns) return;
+    const int last_valid = nact == nq ? BS : (int)(num_tokens - nq * BS);
+    attend_body<G, T2>(it.cache, it.ws, it.q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, (int)((nact + ns - 1) / ns));
 }
 
 template <int G>
@@ -727,6 +756,8 @@ static int attend_launch_t(const cqa_cache *c, const cqa_workspace *ws, const vo
     return CQA_ERR_UNSUPPORTED;
 }
 
+int attend_wait_timeouts(int *count, int reset) { return wait_timeouts_of_this_unit(count, reset); }
+
 // Argument checks of Phase 2 (also called by the fused step before its first launch).
 int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact, int last_valid)
 {
@@ -736,6 +767,11 @@ int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact
         return CQA_ERR_INVALID;
     }
     if (nq > 0 && !ws->token_scores) { set_error("cqa_attend: token_scores missing"); return CQA_ERR_INVALID; }
+    if (((uintptr_t)ws->token_scores | (uintptr_t)c->values_int4_packed | (uintptr_t)c->values_int4_scales |
+         (uintptr_t)c->values_int4_zeros) & 15) {
+        set_error("cqa_attend: token_scores and the INT4 value arrays must be 16-byte aligned (bulk copies)");
+        return CQA_ERR_INVALID;
+    }
     if (nq < 0 || nact <= 0 || nact < nq || nact > ws->ld || nact > c->max_blocks) {
         set_error("cqa_attend: nact=%ld out of range (nq=%ld, ld=%ld, max_blocks=%ld)", nact, nq, (long)ws->ld,
                   (long)c->max_blocks);
@@ -775,6 +811,45 @@ int attend_launch(const cqa_cache *c, const cqa_workspace *ws, const void *q, in
     case CQA_F32: return attend_launch_t<float>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
     case CQA_F16: return attend_launch_t<__half>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
     default: return attend_launch_t<__nv_bfloat16>(c, ws, q, q_dtype, nq, nact, num_tokens, last_valid, q_scale, st, chained);
+    }
+}
+
+template <int G, typename T2>
+static int attend_batched_launch_gt(const cqa_batch_item *items_dev, int n_items, int kv_heads, int max_splits, int q_dtype,
+                                    float q_scale, int do_append, cudaStream_t st)
+{
+    const size_t smem = attend_smem<G>();
+    static size_t granted[SMEM_ATTR_DEVICES] = {};
+    const int rc = check_cuda(ensure_dynamic_smem(attend_batched_kernel<G, T2>, smem, granted),
+                              "cudaFuncSetAttribute(attend_batched_kernel)");
+    if (rc) return rc;
+    dim3 grid((unsigned)(DENSE_POOL_X + max_splits), (unsigned)kv_heads, (unsigned)n_items);
+    return check_cuda(launch_chained(attend_batched_kernel<G, T2>, grid, dim3(ATT_THREADS), smem, st, true, items_dev, q_dtype,
+                                     q_scale, do_append), "attend_batched_kernel");
+}
+
+template <typename T2>
+static int attend_batched_launch_t(const cqa_batch_item *items_dev, int n_items, int kv_heads, int gqa_group, int max_splits,
+                                   int q_dtype, float q_scale, int do_append, cudaStream_t st)
+{
+    switch (gqa_group) {
+    case 1: return attend_batched_launch_gt<1, T2>(items_dev, n_items, kv_heads, max_splits, q_dtype, q_scale, do_append, st);
+    case 2: return attend_batched_launch_gt<2, T2>(items_dev, n_items, kv_heads, max_splits, q_dtype, q_scale, do_append, st);
+    case 4: return attend_batched_launch_gt<4, T2>(items_dev, n_items, kv_heads, max_splits, q_dtype, q_scale, do_append, st);
+    case 8: return attend_batched_launch_gt<8, T2>(items_dev, n_items, kv_heads, max_splits, q_dtype, q_scale, do_append, st);
+    }
+    set_error("cqa_layer_step_batched: unsupported gqa_group %d", gqa_group);
+    return CQA_ERR_UNSUPPORTED;
+}
+
+// Phase 2 of a batch; every item was checked by the caller (attend_check) and carries the dense scratch.
+int attend_batched_launch(const cqa_batch_item *items_dev, int n_items, int kv_heads, int gqa_group, int t2_dtype,
+                          int max_splits, int q_dtype, float q_scale, int do_append, cudaStream_t st)
+{
+    switch (t2_dtype) {
+    case CQA_F32: return attend_batched_launch_t<float>(items_dev, n_items, kv_heads, gqa_group, max_splits, q_dtype, q_scale, do_append, st);
+    case CQA_F16: return attend_batched_launch_t<__half>(items_dev, n_items, kv_heads, gqa_group, max_splits, q_dtype, q_scale, do_append, st);
+    default: return attend_batched_launch_t<__nv_bfloat16>(items_dev, n_items, kv_heads, gqa_group, max_splits, q_dtype, q_scale, do_append, st);
     }
 }
 

@@ -339,6 +339,81 @@ static inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, di
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ----------------------------------------------------------------- bulk asynchronous copies (TMA) + mbarrier
+//
+// Page tiles are staged in shared memory by the bulk-copy engine: one lane issues `cp.async.bulk` for each
+// contiguous piece of a block (the pieces land without touching a register or the load/store units of the other
+// lanes) and the copies report their bytes to an mbarrier that the consuming lanes wait on.  Plain single-CTA
+// copies from this GPU's own memory only.  Source and destination must be 16-byte aligned and sizes multiples of
+// 16 bytes.  Every wait is bounded: after BULK_WAIT_POLLS unsuccessful polls the waiter records the event in a
+// device-global counter (cqa_wait_timeouts) and carries on, so a lost copy can never hang the GPU.
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+// Makes freshly initialised barriers visible to the copy engine; call once after mbar_init, before the CTA barrier.
+__device__ __forceinline__ void mbar_init_fence()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// One arrival that also announces `bytes` of copies to come.
+// The issuing side works on 32-bit shared-memory addresses (smem_u32 of the stage and of its barrier, computed
+// once), so a copy costs the instruction itself and an add for each address.
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar_addr, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(unsigned dst_addr, const void *src_gmem, unsigned bytes, unsigned bar_addr)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_addr), "l"(src_gmem), "r"(bytes), "r"(bar_addr)
+                 : "memory");
+}
+// One poll of the barrier's phase.  The hardware may park the thread for up to `suspend_ns` before it answers, so a
+// waiting warp issues almost no instructions while its tile is in flight.
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar_addr, unsigned parity, unsigned suspend_ns = 20000u)
+{
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar_addr), "r"(parity), "r"(suspend_ns)
+                 : "memory");
+    return ok != 0;
+}
+// One counter per translation unit (the library is built without relocatable device code); cqa_wait_timeouts adds
+// them up through the accessors that the units using staged copies export.
+static __device__ int g_wait_timeouts = 0;
+constexpr int BULK_WAIT_POLLS = 50000;
+// Wait (bounded) until the phase with this parity of `bar` has completed.  A copy normally lands within a few
+// polls.  Once any wait of this unit has run out, later waits give up after a handful of polls, so that a broken
+// run ends quickly instead of paying the full limit at every stage.
+static __device__ __noinline__ void mbar_wait_slow(unsigned bar_addr, unsigned parity)
+{
+    const int limit = *reinterpret_cast<volatile int *>(&g_wait_timeouts) != 0 ? 64 : BULK_WAIT_POLLS;
+    for (int polls = 0; polls < limit; ++polls)
+        if (mbar_try_wait(bar_addr, parity)) return;
+    atomicAdd(&g_wait_timeouts, 1);
+}
+__device__ __forceinline__ void mbar_wait(unsigned bar_addr, unsigned parity)
+{
+    if (!mbar_try_wait(bar_addr, parity)) mbar_wait_slow(bar_addr, parity);
+}
+
+// Host side: read (and optionally clear) this translation unit's timeout counter on the current device.
+static inline int wait_timeouts_of_this_unit(int *count, int reset)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(count, g_wait_timeouts, sizeof(int));
+    if (e == cudaSuccess && reset) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_wait_timeouts, &zero, sizeof(int));
+    }
+    return e == cudaSuccess ? 0 : -1;
+}
+
 // ----------------------------------------------------------------- peer exchange flags
 
 __device__ __forceinline__ int ld_acquire_sys(const int32_t *p)
@@ -398,5 +473,8 @@ int check_launch(const char *what);
 int check_score_args(const cqa_cache *c, int q_dtype, long nq, long ld, const char *who);
 int selcert_check(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q, long nq, int phases);
 int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact, int last_valid);
+int append_check(const cqa_cache *c, const void *k_new, const void *v_new, int src_dtype, long pos);
+int score_wait_timeouts(int *count, int reset);
+int attend_wait_timeouts(int *count, int reset);
 
 }  // namespace cqa

@@ -199,8 +199,8 @@ __global__ void __launch_bounds__(128) quantize_blocks_kernel(cqa_cache c, const
 
 // Fused append-and-quantise of one token.  Grid: KV CTAs of 128 threads.
 template <typename T2>
-__global__ void __launch_bounds__(128) append_token_kernel(cqa_cache c, const void *k_new, const void *v_new,
-                                                          int src_dtype, long pos, int defer_int4)
+__device__ __forceinline__ void append_token_body(const cqa_cache &c, const void *k_new, const void *v_new, int src_dtype,
+                                                  long pos, int defer_int4)
 {
     __shared__ BlockQuantSmem sm;
     __shared__ float s_v[D];
@@ -284,6 +284,31 @@ __global__ void __launch_bounds__(128) append_token_kernel(cqa_cache c, const vo
         const long row0 = (long)kv * c.cap_tokens + pos;
         for (int t = 1; t < BS; ++t)
             if (pos + t < c.cap_tokens) c.keys_int8[(row0 + t) * D + tid] = (int8_t)-127;
+    }
+}
+
+template <typename T2>
+__global__ void __launch_bounds__(128) append_token_kernel(cqa_cache c, const void *k_new, const void *v_new,
+                                                          int src_dtype, long pos, int defer_int4)
+{
+    append_token_body<T2>(c, k_new, v_new, src_dtype, pos, defer_int4);
+}
+
+// One token for every sequence of a batch: grid (KV, sequences).
+template <typename T2>
+__global__ void __launch_bounds__(128) append_token_batched_kernel(const cqa_batch_item *items, int src_dtype)
+{
+    const cqa_batch_item &it = items[blockIdx.y];
+    append_token_body<T2>(it.cache, it.k_new, it.v_new, src_dtype, it.pos, it.defer_int4);
+}
+
+int append_batched_launch(const cqa_batch_item *items_dev, int n_items, int kv_heads, int t2_dtype, int src_dtype, cudaStream_t st)
+{
+    dim3 grid((unsigned)kv_heads, (unsigned)n_items);
+    switch (t2_dtype) {
+    case CQA_F32: return check_cuda(launch_chained(append_token_batched_kernel<float>, grid, dim3(128), 0, st, true, items_dev, src_dtype), "append_token_batched_kernel");
+    case CQA_F16: return check_cuda(launch_chained(append_token_batched_kernel<__half>, grid, dim3(128), 0, st, true, items_dev, src_dtype), "append_token_batched_kernel");
+    default: return check_cuda(launch_chained(append_token_batched_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, true, items_dev, src_dtype), "append_token_batched_kernel");
     }
 }
 
@@ -395,17 +420,26 @@ extern "C" int cqa_quantize_blocks(const cqa_cache *c, const void *k_src, const 
     return CQA_ERR_INVALID;
 }
 
-extern "C" int cqa_append_token(const cqa_cache *c, const void *k_new, const void *v_new, int src_dtype,
-                                int64_t pos, int defer_int4, void *stream)
+// Argument checks of the append (shared with the batched step).
+int cqa::append_check(const cqa_cache *c, const void *k_new, const void *v_new, int src_dtype, long pos)
 {
     int rc = valid_cache(c);
     if (rc) return rc;
     if (!k_new || !v_new) { set_error("cqa_append_token: NULL token"); return CQA_ERR_INVALID; }
     if (pos < 0 || pos >= c->cap_tokens || pos / BS >= c->max_blocks) {
-        set_error("cqa_append_token: position %ld beyond capacity %ld", (long)pos, (long)c->cap_tokens);
+        set_error("cqa_append_token: position %ld beyond capacity %ld", pos, (long)c->cap_tokens);
         return CQA_ERR_TOO_LARGE;
     }
     if (src_dtype < 0 || src_dtype > 2) { set_error("cqa_append_token: unknown dtype"); return CQA_ERR_INVALID; }
+    if (c->t2_dtype < 0 || c->t2_dtype > 2) { set_error("cqa_append_token: unknown Tier-2 dtype %d", c->t2_dtype); return CQA_ERR_INVALID; }
+    return CQA_OK;
+}
+
+extern "C" int cqa_append_token(const cqa_cache *c, const void *k_new, const void *v_new, int src_dtype,
+                                int64_t pos, int defer_int4, void *stream)
+{
+    int rc = append_check(c, k_new, v_new, src_dtype, pos);
+    if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     switch (c->t2_dtype) {
     case CQA_F32: rc = check_cuda(launch_chained(append_token_kernel<float>, dim3(c->kv_heads), dim3(128), 0, st, true, *c, k_new, v_new, src_dtype, pos, defer_int4), "append_token_kernel"); break;

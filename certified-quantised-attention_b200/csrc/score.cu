@@ -5,8 +5,9 @@
 // owns one 16-token block at a time.  Lane L of the half warp owns channels
 // 8L..8L+7 with q*sigma for the G heads of the group in registers, so one
 // key byte feeds G fused multiply-adds.  Key rows, scales and zero points are
-// staged in shared memory by 16-byte asynchronous copies (warp-private double
-// buffer, no CTA barrier).  Lane L walks the tokens in the order j^L, which
+// staged in shared memory by bulk asynchronous copies (TMA engine: one lane
+// issues three copies per block, 2048 + 512 + 512 bytes, which report to an
+// mbarrier; warp-private double buffer, no CTA barrier).  Lane L walks the tokens in the order j^L, which
 // makes the shared-memory reads conflict free and lets the 16-lane
 // reduce-scatter run without selects: afterwards lane L holds token L.
 //
@@ -23,38 +24,27 @@ constexpr int STAGE_HALF = BLOCK_BYTES + 2 * D * 4;       // + scale + zero poin
 constexpr int STAGE_WARP = 2 * STAGE_HALF;                // two half warps
 constexpr int SCORE_SMEM = SCORE_WARPS * 2 * STAGE_WARP;  // double buffered: 98304
 
-__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
+// Issue the copies of one warp stage: blocks b0 (lanes 0-15 consume it) and b0+1 (lanes 16-31).  A stage half is
+// the block's 2048 key bytes followed by its 128 scales and 128 zero points.  Block numbers are clamped to the
+// last block of the CTA's range, so an odd tail block is simply scored twice (only one result is stored).  One
+// lane announces the bytes to the stage's mbarrier and issues the six copies.
+__device__ __forceinline__ void score_issue(const cqa_cache &c, int kv, long b_first, long b_last, unsigned stage_addr,
+                                            unsigned bar_addr, int lane)
 {
-    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait()
-{
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
-// Issue the copies of one warp stage: blocks b0 (lanes 0-15 consume it) and b0+1 (lanes 16-31).
-// A stage half is 192 chunks of 16 B: 128 of key bytes, 32 of scales, 32 of zero points; with 32 lanes
-// every copy of the twelve is of one kind, known at compile time.  Block numbers are clamped to the last
-// block of the CTA's range, so an odd tail block is simply scored twice (only one result is stored).
-__device__ __forceinline__ void score_issue(const cqa_cache &c, int kv, long b_first, long b_last, char *stage,
-                                            int lane)
-{
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const long b = min(b_first + half, b_last);
-        const char *keys = reinterpret_cast<const char *>(c.keys_int8) + ((long)kv * c.cap_tokens + b * BS) * D + lane * 16;
-        const char *sc = reinterpret_cast<const char *>(c.keys_scale + ((long)kv * c.max_blocks + b) * D) + lane * 16;
-        const char *zp = reinterpret_cast<const char *>(c.keys_zero_points + ((long)kv * c.max_blocks + b) * D) + lane * 16;
-        char *dst = stage + half * STAGE_HALF + lane * 16;
-#pragma unroll
-        for (int r = 0; r < 4; ++r) cp_async16(dst + r * 512, keys + r * 512);
-        cp_async16(dst + BLOCK_BYTES, sc);
-        cp_async16(dst + BLOCK_BYTES + 512, zp);
+    if (lane == 0) {
+        mbar_arrive_expect_tx(bar_addr, 2 * STAGE_HALF);
+        const long b1 = min(b_first + 1, b_last);
+        const char *k0 = reinterpret_cast<const char *>(c.keys_int8) + ((long)kv * c.cap_tokens + b_first * BS) * D;
+        const char *s0 = reinterpret_cast<const char *>(c.keys_scale) + ((long)kv * c.max_blocks + b_first) * (D * 4);
+        const char *z0 = reinterpret_cast<const char *>(c.keys_zero_points) + ((long)kv * c.max_blocks + b_first) * (D * 4);
+        const long dk = (b1 - b_first) * BLOCK_BYTES, ds = (b1 - b_first) * (D * 4);
+        bulk_copy_g2s(stage_addr, k0, BLOCK_BYTES, bar_addr);
+        bulk_copy_g2s(stage_addr + BLOCK_BYTES, s0, D * 4, bar_addr);
+        bulk_copy_g2s(stage_addr + BLOCK_BYTES + D * 4, z0, D * 4, bar_addr);
+        bulk_copy_g2s(stage_addr + STAGE_HALF, k0 + dk, BLOCK_BYTES, bar_addr);
+        bulk_copy_g2s(stage_addr + STAGE_HALF + BLOCK_BYTES, s0 + ds, D * 4, bar_addr);
+        bulk_copy_g2s(stage_addr + STAGE_HALF + BLOCK_BYTES + D * 4, z0 + ds, D * 4, bar_addr);
     }
-    cp_async_commit();
 }
 
 // 8 signed bytes -> four float pairs, exactly: flip the sign bit (u = k + 128), drop each byte into the
@@ -81,11 +71,9 @@ __device__ __forceinline__ float chain8_f2(const float2 (&a)[4], const float2 (&
 }
 
 template <int G>
-__global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_cache c, const void *q, int q_dtype,
-                                                                          long nq, float q_scale, float *m_b,
-                                                                          float *s_b, long ld, float *tok,
-                                                                          int blocks_per_cta, int32_t *zero_words,
-                                                                          int n_zero_words, ScorePush push)
+__device__ __forceinline__ void score_blocks_body(const cqa_cache &c, const void *q, int q_dtype, long nq, float q_scale,
+                                                  float *m_b, float *s_b, long ld, float *tok, int blocks_per_cta,
+                                                  int32_t *zero_words, int n_zero_words, const ScorePush &push)
 {
     extern __shared__ __align__(16) char smem[];
     constexpr int GH = G >= 4 ? 4 : G;  // heads per register pass
@@ -101,24 +89,29 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
     const long b_last = b_end - 1;
     char *wbuf = smem + warp * 2 * STAGE_WARP;
     float *s_q = reinterpret_cast<float *>(smem + SCORE_SMEM);   // [G][128] query rows of this KV group
+    uint64_t *wbar = reinterpret_cast<uint64_t *>(smem + SCORE_SMEM + G * D * 4) + 2 * warp;   // one per stage
+    if (lane == 0) {
+        mbar_init(wbar, 1);
+        mbar_init(wbar + 1, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    const unsigned wbuf_addr = smem_u32(wbuf), wbar_addr = smem_u32(wbar);
 
     // Blocks of this warp: b_begin + 2*(warp + 8*it) + hw
     const long stride = 2 * SCORE_WARPS;
     long b0 = b_begin + 2 * warp;
-    int stage = 0;
-    if (b0 < b_end) score_issue(c, kv, b0, b_last, wbuf, lane);
+    int stage = 0, use = 0;
+    if (b0 < b_end) score_issue(c, kv, b0, b_last, wbuf_addr, wbar_addr, lane);
     for (int i = threadIdx.x; i < G * D; i += SCORE_WARPS * 32) s_q[i] = load_q(q, q_dtype, (long)kv * G * D + i);
     __syncthreads();
 
     for (; b0 < b_end; b0 += stride) {
         const long bn = b0 + stride;
-        if (bn < b_end) {
-            score_issue(c, kv, bn, b_last, wbuf + (stage ^ 1) * STAGE_WARP, lane);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncwarp();
+        // the other buffer was read in the previous iteration, which ended with a warp barrier
+        if (bn < b_end)
+            score_issue(c, kv, bn, b_last, wbuf_addr + (stage ^ 1) * STAGE_WARP, wbar_addr + (stage ^ 1) * 8, lane);
+        mbar_wait(wbar_addr + stage * 8, (unsigned)(use >> 1) & 1u);     // this stage's barrier completes one phase per use
         const long b = b0 + hw;
         const bool live = b < b_end;
         const char *kb = wbuf + stage * STAGE_WARP + hw * STAGE_HALF;
@@ -188,6 +181,7 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
         }
         __syncwarp();
         stage ^= 1;
+        ++use;
     }
     if (push.world > 0) {
         // the last CTA of the grid tells every rank that this rank's rows have landed
@@ -203,6 +197,31 @@ __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_c
             }
         }
     }
+}
+
+template <int G>
+__global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_kernel(cqa_cache c, const void *q, int q_dtype,
+                                                                          long nq, float q_scale, float *m_b,
+                                                                          float *s_b, long ld, float *tok,
+                                                                          int blocks_per_cta, int32_t *zero_words,
+                                                                          int n_zero_words, ScorePush push)
+{
+    score_blocks_body<G>(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, tok, blocks_per_cta, zero_words, n_zero_words, push);
+}
+
+// The same for sequence blockIdx.z of a batch; grid.x is sized for the longest sequence and every sequence splits
+// its blocks over all of grid.x.
+template <int G>
+__global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_batched_kernel(const cqa_batch_item *items, int q_dtype,
+                                                                                  float q_scale, int do_append)
+{
+    const cqa_batch_item &it = items[blockIdx.z];
+    const long nq = (it.pos + do_append) / BS;
+    long bpc = (nq + gridDim.x - 1) / gridDim.x;
+    if (bpc < 2) bpc = 2;
+    ScorePush none = {};
+    score_blocks_body<G>(it.cache, it.q, q_dtype, nq, q_scale, it.ws.m_b, it.ws.s_b, it.ws.ld, it.ws.token_scores, (int)bpc,
+                         it.ws.any_flags, 5 + it.cache.kv_heads * G, none);
 }
 
 template <typename T2>
@@ -247,7 +266,7 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
                           float *s_b, long ld, float *tok, dim3 grid, int bpc, int32_t *zero_words, int n_zero_words,
                           const ScorePush &push, cudaStream_t st)
 {
-    constexpr int SMEM = SCORE_SMEM + G * D * 4;
+    constexpr int SMEM = SCORE_SMEM + G * D * 4 + SCORE_WARPS * 2 * 8;   // stages, query rows, mbarriers
     static size_t granted[SMEM_ATTR_DEVICES] = {};
     const int rc_attr = check_cuda(ensure_dynamic_smem(score_blocks_kernel<G>, (size_t)SMEM, granted),
                                    "cudaFuncSetAttribute(score_blocks_kernel)");
@@ -255,6 +274,41 @@ static int score_launch_g(const cqa_cache *c, const void *q, int q_dtype, long n
     return check_cuda(launch_chained(score_blocks_kernel<G>, grid, dim3(SCORE_WARPS * 32), SMEM, st, true, *c, q, q_dtype,
                                      nq, q_scale, m_b, s_b, ld, tok, bpc, zero_words, n_zero_words, push),
                       "score_blocks_kernel");
+}
+
+// Phase 1 of a batch: `max_nq` = most quantised blocks of any sequence.
+int score_blocks_batched_launch(const cqa_batch_item *items_dev, int n_items, int kv_heads, int gqa_group, long max_nq,
+                                int q_dtype, float q_scale, int do_append, cudaStream_t st)
+{
+    int dev = 0, sm_count = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+    // two resident CTAs per SM over the whole batch, at least one CTA per 16 blocks of the longest sequence
+    long per_seq = ((long)sm_count * 2 + (long)kv_heads * n_items - 1) / ((long)kv_heads * n_items);
+    long by_work = (max_nq + 15) / 16;
+    long gx = per_seq < by_work ? per_seq : by_work;
+    if (gx < 1) gx = 1;
+    dim3 grid((unsigned)gx, (unsigned)kv_heads, (unsigned)n_items);
+#define CQA_SCORE_BATCH_CASE(GG)                                                                                       \
+    case GG: {                                                                                                         \
+        constexpr int SMEM = SCORE_SMEM + GG * D * 4 + SCORE_WARPS * 2 * 8;                                            \
+        static size_t granted[SMEM_ATTR_DEVICES] = {};                                                                 \
+        const int rc = check_cuda(ensure_dynamic_smem(score_blocks_batched_kernel<GG>, (size_t)SMEM, granted),         \
+                                  "cudaFuncSetAttribute(score_blocks_batched_kernel)");                                \
+        if (rc) return rc;                                                                                             \
+        return check_cuda(launch_chained(score_blocks_batched_kernel<GG>, grid, dim3(SCORE_WARPS * 32), SMEM, st, true, \
+                                         items_dev, q_dtype, q_scale, do_append), "score_blocks_batched_kernel");      \
+    }
+    switch (gqa_group) {
+        CQA_SCORE_BATCH_CASE(1)
+        CQA_SCORE_BATCH_CASE(2)
+        CQA_SCORE_BATCH_CASE(4)
+        CQA_SCORE_BATCH_CASE(8)
+    }
+#undef CQA_SCORE_BATCH_CASE
+    set_error("cqa_layer_step_batched: unsupported gqa_group %d", gqa_group);
+    return CQA_ERR_UNSUPPORTED;
 }
 
 int rescore_owned_launch(const cqa_cache *c, const cqa_head_cert *cert, const void *q, int q_dtype, long first_block,
@@ -317,6 +371,10 @@ int cqa::check_score_args(const cqa_cache *c, int q_dtype, long nq, long ld, con
         return CQA_ERR_INVALID;
     }
     if (q_dtype < 0 || q_dtype > 2) { set_error("%s: unknown q dtype %d", who, q_dtype); return CQA_ERR_INVALID; }
+    if (((uintptr_t)c->keys_int8 | (uintptr_t)c->keys_scale | (uintptr_t)c->keys_zero_points) & 15) {
+        set_error("%s: keys_int8, keys_scale and keys_zero_points must be 16-byte aligned (bulk copies)", who);
+        return CQA_ERR_INVALID;
+    }
     if (c->gqa_group != 1 && c->gqa_group != 2 && c->gqa_group != 4 && c->gqa_group != 8) {
         set_error("%s: unsupported gqa_group %d", who, c->gqa_group);
         return CQA_ERR_UNSUPPORTED;
@@ -337,6 +395,8 @@ extern "C" int cqa_score_blocks(const cqa_cache *c, const void *q, int q_dtype, 
     return score_blocks_launch(c, q, q_dtype, nq, q_scale, m_b, s_b, ld, token_scores, (cudaStream_t)stream, nullptr, 0,
                                nullptr);
 }
+
+int cqa::score_wait_timeouts(int *count, int reset) { return wait_timeouts_of_this_unit(count, reset); }
 
 extern "C" int cqa_fp16_block_scores(const cqa_cache *c, const void *q, int q_dtype, const int32_t *idx, int K,
                                      int64_t n_scoring_blocks, float q_scale, float *scores, float *logmass,

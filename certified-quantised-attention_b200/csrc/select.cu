@@ -481,10 +481,9 @@ __device__ __noinline__ void rescore_block_any(const cqa_cache &c, const void *q
 // gsum, leaf, mask[n_pad] (bytes).  The full-sort fallback aliases its keys over B and C; the radix searches use B
 // (and A) as histograms.
 template <int VPT>
-__global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa_knobs kn, cqa_workspace ws, const void *q,
-                                                                int q_dtype, long nq, long nact, const float *u, long u_ld,
-                                                                int n_pad, int hi, int base_width, int two_level, int rk,
-                                                                int phases, int role_base)
+__device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const cqa_workspace &ws, const void *q,
+                                             int q_dtype, long nq, long nact, const float *u, long u_ld, int n_pad, int hi,
+                                             int base_width, int two_level, int rk, int phases, int role_base)
 {
     extern __shared__ __align__(16) unsigned char dsm[];
     const int n_arr = n_pad > 2048 ? n_pad : 2048;             // A and B double as 2048-bin histograms
@@ -1111,24 +1110,27 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa
     }
 }
 
-static int next_pow2(long n)
+template <int VPT>
+__global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa_knobs kn, cqa_workspace ws, const void *q,
+                                                                int q_dtype, long nq, long nact, const float *u, long u_ld,
+                                                                int n_pad, int hi, int base_width, int two_level, int rk,
+                                                                int phases, int role_base)
+{
+    selcert_body<VPT>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
+}
+
+static __host__ __device__ inline int next_pow2(long n)
 {
     int p = 32;
     while (p < n) p <<= 1;
     return p;
 }
 
-static size_t selcert_smem(int n_pad)
-{
-    const size_t n_arr = n_pad > 2048 ? n_pad : 2048;
-    return n_arr * 8 + (size_t)n_pad * 5 + (size_t)CAND * 12 + ((size_t)(n_pad >> 5) + 1 + (n_pad >> 8) + 2) * 4 + 64;
-}
-
-// Selection widths derived from the knobs (shared by the argument check and the launch).
+// Selection widths derived from the knobs (shared by the argument check, the launch and the batched kernel).
 struct SelPlan {
     int hi, base_width, two_level, rk;
 };
-static SelPlan sel_plan(const cqa_knobs *kn, long nq)
+static __host__ __device__ inline SelPlan sel_plan(const cqa_knobs *kn, long nq)
 {
     SelPlan p;
     const bool can_expand = kn->rung1_threshold >= 0.0f && kn->k_max > 0;
@@ -1146,6 +1148,25 @@ static SelPlan sel_plan(const cqa_knobs *kn, long nq)
     if (rk > nq) rk = (int)nq;
     p.rk = rk;
     return p;
+}
+
+// Sequence blockIdx.z of a batch: the fused selector + certifier (all three roles) with that sequence's sizes.
+template <int VPT>
+__global__ void __launch_bounds__(SC_THREADS, 1) selcert_batched_kernel(const cqa_batch_item *items, cqa_knobs kn, int q_dtype,
+                                                                        int do_append)
+{
+    const cqa_batch_item &it = items[blockIdx.z];
+    const long num_tokens = it.pos + do_append;
+    const long nq = num_tokens / BS, nact = (num_tokens + BS - 1) / BS;
+    const SelPlan p = sel_plan(&kn, nq);
+    selcert_body<VPT>(it.cache, kn, it.ws, it.q, q_dtype, nq, nact, nullptr, 0, next_pow2(nq), p.hi, p.base_width, p.two_level,
+                      p.rk, PH_SELECT | PH_CERTIFY | PH_FLAGS_CLEARED, 0);
+}
+
+static size_t selcert_smem(int n_pad)
+{
+    const size_t n_arr = n_pad > 2048 ? n_pad : 2048;
+    return n_arr * 8 + (size_t)n_pad * 5 + (size_t)CAND * 12 + ((size_t)(n_pad >> 5) + 1 + (n_pad >> 8) + 2) * 4 + 64;
 }
 
 // Every argument check of the selector / certifier launch; nothing is launched or copied here.
@@ -1228,6 +1249,34 @@ int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace 
     case 8: return selcert_launch_v<8>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
     default: return selcert_launch_v<16>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
     }
+}
+
+// The selector of a batch; `max_nq` = most quantised blocks of any sequence (sizes the threads' register arrays and
+// the shared memory), every item checked by the caller.
+int selcert_batched_launch(const cqa_batch_item *items_dev, int n_items, int n_heads, long max_nq, const cqa_knobs *kn,
+                           int q_dtype, int do_append, cudaStream_t st)
+{
+    const int n_pad = next_pow2(max_nq);
+    const size_t smem = selcert_smem(n_pad);
+    dim3 grid((unsigned)n_heads, 3u, (unsigned)n_items);
+#define CQA_SEL_BATCH_CASE(V)                                                                                          \
+    {                                                                                                                  \
+        static size_t granted[SMEM_ATTR_DEVICES] = {};                                                                 \
+        const int rc = check_cuda(ensure_dynamic_smem(selcert_batched_kernel<V>, smem, granted),                       \
+                                  "cudaFuncSetAttribute(selcert_batched_kernel)");                                     \
+        if (rc) return rc;                                                                                             \
+        return check_cuda(launch_chained(selcert_batched_kernel<V>, grid, dim3(SC_THREADS), smem, st, true, items_dev, *kn, \
+                                         q_dtype, do_append), "selcert_batched_kernel");                               \
+    }
+    switch (n_pad / SC_THREADS) {
+    case 0:
+    case 1: CQA_SEL_BATCH_CASE(1)
+    case 2: CQA_SEL_BATCH_CASE(2)
+    case 4: CQA_SEL_BATCH_CASE(4)
+    case 8: CQA_SEL_BATCH_CASE(8)
+    default: CQA_SEL_BATCH_CASE(16)
+    }
+#undef CQA_SEL_BATCH_CASE
 }
 
 int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq, long nact,

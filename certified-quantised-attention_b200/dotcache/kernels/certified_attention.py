@@ -446,6 +446,131 @@ def certified_decode_token_host(
     return out_host
 
 
+def certified_attention_batch(
+    caches,
+    q_all: torch.Tensor,
+    gqa_group: int,
+    q_scale: float | None = None,
+    *,
+    new_keys: torch.Tensor | None = None,
+    new_values: torch.Tensor | None = None,
+    num_splits: int | None = None,
+    v_tolerance: float,
+    top_k_fp16_keys: int = 4,
+    ranking_fallback: bool = True,
+    ranking_r: int = 1,
+    ranking_fallback_mode: str = "full",
+    tau_cov: float = 0.995,
+    k_min: int = DEFAULT_K_MIN,
+    k_max: int | None = DEFAULT_K_MAX,
+    rung1_threshold: float = DEFAULT_RUNG1_THRESHOLD,
+    rung1_multiplier: float = DEFAULT_RUNG1_MULTIPLIER,
+    score_consistency_check: bool = False,
+    eps_guard: float = 0.01,
+    exploration_rate: float = 0.0,
+    value_error_mode: str = "tight",
+) -> torch.Tensor:
+    """One certified decode step of one layer for a BATCH of sequences, each with its own cache: the (optional)
+    append and the three kernels of the step run once, with the sequences on the grid (cqa_layer_step_batched).
+    The reference is batch-1 only (its adapter raises otherwise, integrations/llama.py:717-718); a caller with B
+    sequences would loop.  An addition, no reference counterpart.
+
+    `caches`: the B layer caches (same head geometry and dtype; lengths may differ).  `q_all`: [B, H, 128] on the
+    GPU in the caches' dtype (or float32).  `new_keys` / `new_values`: [B, KV, 128]; when given, every sequence's
+    token is appended first (`cache.append_token`) inside the same call.  Returns float32 [B, H, 128]; row b equals
+    what `certified_attention_layer(caches[b], q_all[b], ...)` returns when both use the same `num_splits` (the
+    split count fixes the summation order of Phase 2).  The tensor is reused by the next call with the same caches.
+    Certificates stay in each cache's workspace (`cache._certified_workspace["cqa_ws"].read_cert()`)."""
+    B = len(caches)
+    if B == 0:
+        raise ValueError("certified_attention_batch needs at least one cache")
+    if not q_all.is_cuda:
+        raise RuntimeError("certified_attention_batch needs CUDA tensors; there is no CPU fallback")
+    first = caches[0]
+    G = int(gqa_group)
+    H = first.kv_heads * G
+    KV = first.kv_heads
+    if tuple(q_all.shape) != (B, H, first.head_dim):
+        raise ValueError(f"q_all must have shape {(B, H, first.head_dim)}, got {tuple(q_all.shape)}")
+    do_append = new_keys is not None
+    if do_append != (new_values is not None):
+        raise ValueError("new_keys and new_values go together")
+    if do_append and (tuple(new_keys.shape) != (B, KV, first.head_dim) or tuple(new_values.shape) != (B, KV, first.head_dim)):
+        raise ValueError(f"new_keys / new_values must have shape {(B, KV, first.head_dim)}")
+    device = q_all.device
+    if q_scale is None:
+        q_scale = 1.0 / (first.head_dim ** 0.5)
+    q = q_all.contiguous()
+    if do_append:
+        new_keys = new_keys.to(q.dtype).contiguous()
+        new_values = new_values.to(q.dtype).contiguous()
+    knobs = _make_knobs(
+        q_scale=q_scale, tau_cov=tau_cov, k_min=k_min, k_max=k_max, rung1_threshold=rung1_threshold,
+        rung1_multiplier=rung1_multiplier, eps_guard=eps_guard, exploration_rate=exploration_rate,
+        v_tolerance=v_tolerance, ranking_r=ranking_r, top_k_fp16_keys=top_k_fp16_keys,
+        ranking_fallback=ranking_fallback, ranking_fallback_mode=ranking_fallback_mode,
+        score_consistency_check=score_consistency_check, value_error_mode=value_error_mode,
+        force_trailing_value_fp16=True,
+    )
+    key = (tuple(id(c) for c in caches), G)
+    plan = getattr(first, "_batch_plan", None)
+    if plan is None or plan[0] != key:
+        items = (_lib.CqaBatchItem * B)()
+        items_dev = torch.empty(C.sizeof(items) + 16, dtype=torch.uint8, device=device)
+        out = torch.empty(B, H, first.head_dim, dtype=torch.float32, device=device)
+        plan = (key, items, items_dev, out)
+        first._batch_plan = plan
+    _, items, items_dev, out = plan
+    esz = q.element_size()
+    row_q, row_kv = H * first.head_dim * esz, KV * first.head_dim * esz
+    block = first.block_size
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    positions = []
+    for b, cache in enumerate(caches):
+        if (cache.kv_heads, cache.head_dim, cache.keys_int8.device) != (KV, first.head_dim, first.keys_int8.device):
+            raise ValueError("all caches of a batch must share geometry and device")
+        pos = cache.num_tokens
+        if do_append and pos >= cache.keys_int8.shape[1]:
+            raise ValueError(f"cache capacity {cache.keys_int8.shape[1]} exhausted")
+        n_tok = pos + (1 if do_append else 0)
+        nq, nact = n_tok // block, (n_tok + block - 1) // block
+        if nq <= 0:
+            raise NotImplementedError("the certified path needs at least one complete block per sequence")
+        ws = _workspace(cache, H, G, device)
+        ws.ensure_sel_width(_selection_width(k_max, rung1_threshold, rung1_multiplier, nq), device)
+        w = ws.fill_struct(nact)
+        # splits: the whole batch should put about two CTAs on every SM; never more than a sequence's own limit
+        ns = int(num_splits) if num_splits else max(1, (2 * sms + KV * B - 1) // (KV * B))
+        w.num_splits = max(1, min(ns, w.num_splits, nact))
+        if exploration_rate > 0.0:
+            w.rng_seed = ws.draw_seed()
+            w.rng_offset = ws.rng_calls
+            ws.rng_calls += 1
+        it = items[b]
+        C.memmove(C.byref(it.cache), C.byref(cache._desc(G)), C.sizeof(_lib.CqaCache))
+        C.memmove(C.byref(it.ws), C.byref(w), C.sizeof(_lib.CqaWorkspace))
+        it.ws.out = out.data_ptr() + b * H * first.head_dim * 4
+        it.q = q.data_ptr() + b * row_q
+        it.k_new = new_keys.data_ptr() + b * row_kv if do_append else None
+        it.v_new = new_values.data_ptr() + b * row_kv if do_append else None
+        it.pos = pos
+        it.defer_int4 = 1 if cache._defers_int4() else 0
+        positions.append(pos)
+    dev_ptr = (items_dev.data_ptr() + 15) & ~15
+    stream = _lib.current_stream(device)
+    with _lib.on_device(device):
+        _lib.check(_lib.lib().cqa_layer_step_batched(items, B, dev_ptr, C.byref(knobs), _lib.dtype_code(q.dtype),
+                                                     1 if do_append else 0, stream), "cqa_layer_step_batched")
+        for b, cache in enumerate(caches):
+            if cache.bounded_hot_tier:
+                n_tok = positions[b] + (1 if do_append else 0)
+                cache._hot_tier_update(cache._desc(G), items[b].ws, (n_tok + block - 1) // block, stream)
+    if do_append:
+        for b, cache in enumerate(caches):
+            cache._advance_after_append(positions[b])
+    return out
+
+
 def certified_attention_layer(
     cache: TieredKeyCacheLayer,
     q_all: torch.Tensor,

@@ -226,6 +226,10 @@ typedef struct cqa_workspace {
 const char *cqa_version(void);
 /* Text of the last error on the calling thread (host memory, valid until the next call). */
 const char *cqa_last_error(void);
+/* Number of bounded device-side waits on staged copies that ran out on the current device since the library was
+ * loaded (0 in a healthy run; a non-zero count means results of the affected calls are invalid).  Synchronises with
+ * the device.  `reset` != 0 clears the counter. */
+int cqa_wait_timeouts(int *count, int reset);
 /* Kernels this library has launched in this process so far (all threads); `reset` != 0 also sets the count to 0. */
 int64_t cqa_launch_count(int reset);
 
@@ -395,6 +399,33 @@ typedef struct cqa_layer_call {
 
 int cqa_decode_token_host(const cqa_layer_call *layers, int n_layers, const cqa_knobs *knobs, void *qkv_dev, int dtype,
                           void *stream);
+
+/* ---- batches: several sequences in one launch of each kernel ----
+ * The reference runs batch 1 only (its adapter raises on anything else, dotcache/integrations/llama.py:717-718), so a
+ * batch of B sequences costs it B serial kernel chains per layer.  cqa_layer_step_batched puts (sequence, KV head,
+ * block range) on the grid of each of the kernels, so that many short sequences fill the GPU together.  Each sequence
+ * gets exactly the arithmetic of its own cqa_append_token + cqa_layer_step call: results are bit-identical to the
+ * one-sequence entry points when ws.num_splits is the same.  No reference counterpart.
+ *
+ * One record per sequence; all caches of a call share kv_heads, gqa_group and t2_dtype; every workspace carries the
+ * dense scratch.  The exploration draw is the in-kernel one (ws.rng_seed / ws.rng_offset of each record). */
+typedef struct cqa_batch_item {
+    cqa_cache cache;
+    cqa_workspace ws;
+    const void *q;        /* [H][128] elements of the call's dtype (device) */
+    const void *k_new;    /* [KV][128] key row of the token to append (device); unused when do_append == 0 */
+    const void *v_new;
+    int64_t pos;          /* tokens in the cache before this step's append (the step attends pos + do_append tokens) */
+    int32_t defer_int4;
+    int32_t reserved;
+} cqa_batch_item;
+
+/* `items_host` (host memory, n_items records) is copied to `items_dev` (device scratch of the same size, 16-byte
+ * aligned) on the stream; then, with grid.z = sequence: the fused append (when do_append != 0), Phase 1, the
+ * selector / certifier and Phase 2.  Limits: n_items <= 65535, every sequence at least one complete block after the
+ * append. */
+int cqa_layer_step_batched(const cqa_batch_item *items_host, int n_items, void *items_dev, const cqa_knobs *knobs,
+                           int dtype, int do_append, void *stream);
 
 /* ---- sequence sharding: every rank owns a contiguous range of blocks ----
  * The reference runs one cache per process; these entry points let P ranks that each

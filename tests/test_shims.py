@@ -586,3 +586,78 @@ def test_bounded_wait_runs_out_and_reports():
     out2, _ = ca.certified_attention_layer(cc, q, 4, None, False, **dict(gc.PAPER_KNOBS, exploration_rate=0.0))
     torch.cuda.synchronize()
     assert bool(torch.isfinite(out2).all())
+
+
+def test_no_staged_copy_wait_ran_out():
+    """After everything above, the library's counter of bounded waits on staged (bulk-copy) tiles that ran out is
+    zero: every tile of every score and attend launch arrived."""
+    n = C.c_int(-1)
+    with torch.cuda.device(0):
+        assert _lib.lib().cqa_wait_timeouts(C.byref(n), 0) == 0
+    assert n.value == 0
+
+
+# ----------------------------------------------------------------------------- batches
+
+def test_batched_layer_step_equals_single_sequence_runs():
+    """cqa_layer_step_batched: several sequences of different lengths in one launch of each kernel.  Every
+    sequence's masks, certificate, appended bytes and output rows equal its own one-sequence run bit for bit (same
+    split count), over steps that cross a block completion; an oracle check pins one of them."""
+    dtype = DTYPE
+    lengths = [1024 + 3, 4096, 2048 + 15, 512]
+    knobs = dict(gc.PAPER_KNOBS, exploration_rate=0.0)
+    bases = [synth.make_layer_inputs(60 + i, n + 24, dtype=dtype, n_planted_blocks=4) for i, n in enumerate(lengths)]
+
+    def build(i):
+        n = lengths[i]
+        al = (n // 16) * 16
+        c = hz.make_cuda_cache(bases[i].k[:, :al], bases[i].v[:, :al], dtype, 64)
+        for t in range(al, n):
+            c.append_token(hz.to_dev(bases[i].k[:, t:t + 1], dtype), hz.to_dev(bases[i].v[:, t:t + 1], dtype))
+        return c
+
+    solo = [build(i) for i in range(4)]
+    batch = [build(i) for i in range(4)]
+    oc = hz.make_oracle_cache(bases[1].k[:, :4096], bases[1].v[:, :4096], dtype, 64)
+    for step in range(20):
+        qs, ks, vs = [], [], []
+        for i in range(4):
+            q, kn, vn = synth.decode_step_inputs(bases[i], step, dtype=dtype)
+            qs.append(q), ks.append(kn.reshape(8, 128)), vs.append(vn.reshape(8, 128))
+        oc.append_token(ks[1].reshape(8, 1, 128), vs[1].reshape(8, 1, 128))
+        qd = hz.to_dev(np.stack(qs), dtype)
+        kd, vd = hz.to_dev(np.stack(ks), dtype), hz.to_dev(np.stack(vs), dtype)
+        out_b = ca.certified_attention_batch(batch, qd, 4, None, new_keys=kd, new_values=vd, num_splits=6, **knobs)
+        torch.cuda.synchronize()
+        for i in range(4):
+            solo[i].append_token(kd[i].reshape(8, 1, 128), vd[i].reshape(8, 1, 128))
+            ws = solo[i]._certified_workspace.get("cqa_ws") or ca._workspace(solo[i], 32, 4, qd.device)
+            # the same split count as the batch call used for this sequence
+            nact = solo[i].active_blocks
+            want_ns = max(1, min(6, max(1, min(ws.num_splits, (nact + 7) // 8)), nact))
+            keep = ws.num_splits
+            ws.num_splits = want_ns
+            out_s, _ = ca.certified_attention_layer(solo[i], qd[i], 4, None, False, **knobs)
+            torch.cuda.synchronize()
+            ws.num_splits = keep
+            assert torch.equal(out_b[i], out_s), f"step {step} sequence {i}: output rows differ"
+            wb = batch[i]._certified_workspace["cqa_ws"]
+            for name in ("topk_mask", "value_mask", "explore_mask", "m_b", "s_b", "mass_frac"):
+                assert torch.equal(getattr(wb, name)[:, :nact], getattr(ws, name)[:, :nact]), f"{name} seq {i} step {step}"
+            cb_, fb = wb.read_cert()
+            cs_, fs = ws.read_cert()
+            assert fb[:5] == fs[:5]
+            for key in ("k_star", "rung3", "dense", "value_promoted_blocks", "delta", "e_val", "tail_mass"):
+                assert np.array_equal(np.asarray(cb_[key]).view(np.uint8), np.asarray(cs_[key]).view(np.uint8)), key
+            assert batch[i].num_tokens == solo[i].num_tokens
+        if step in (0, 15, 19):
+            R = orc.layer_step(oc, qs[1], 4, exploration_u=None, **knobs)
+            hz.compare_step(batch[1], R, out_b[1].cpu().numpy(), f"batched sequence 1 step {step}")
+    for i in range(4):
+        for name in ("keys_int8", "keys_scale", "values_int4_packed", "values_int4_errors", "keys_fp16_gpu"):
+            assert torch.equal(getattr(batch[i], name), getattr(solo[i], name)), f"{name} of sequence {i}"
+    # attend only (no append) on the same caches
+    prev = out_b.clone()
+    out_n = ca.certified_attention_batch(batch, qd, 4, None, num_splits=6, **knobs)
+    torch.cuda.synchronize()
+    assert torch.equal(out_n, prev)
