@@ -72,6 +72,9 @@ def parse_args():
     ap.add_argument("--sharded-context", type=int, default=131072,
                     help="context of the sequence-sharded measurement taken when --gpus > 1 (0 = skip)")
     ap.add_argument("--sharded-steps", type=int, default=64)
+    ap.add_argument("--batched-sweep", action="store_true",
+                    help="instead of the headline run: batch x context sweep of one layer (batched launch against a loop "
+                         "of one-sequence calls, full Tier-2 mirror and a hot tier capped at 2048 tokens)")
     ap.add_argument("--sharded-peer", type=int, default=1,
                     help="also time the sharded step with peer-memory exchanges (0 = collectives only)")
     return ap.parse_args()
@@ -646,6 +649,94 @@ def run_sharded(args, rank, world, device_index):
             "hbm_floor_us_per_rank": round(per_rank_bytes / 6540.2e3, 2)}
 
 
+def run_batched_sweep(args, device_index):
+    """Capped-hot-tier sweep shape (batch x context, one layer): µs per sequence-layer-step of the batched launch
+    (cqa_layer_step_batched) against a loop of one-sequence calls on the same caches, with the full Tier-2 mirror
+    and with the hot tier capped at 2048 tokens (128 blocks; Tier 2 in pinned host memory), where the residency
+    counters give hit rate and page-in bytes per step."""
+    import torch
+
+    from cqa_b200 import synth
+    from dotcache.kernels import certified_attention as ca
+    from dotcache.kernels.tiered_kv_cache import TieredKeyCacheLayer
+
+    torch.cuda.set_device(device_index)
+    dev = torch.device("cuda", device_index)
+    K, W = max(4, min(args.steps, 32)), max(3, min(args.warmup, 8))
+    q_scale = 1.0 / math.sqrt(128.0)
+    rows = []
+    for context in (8192, 32768, 131072):
+        base = synth.make_layer_inputs(args.seed, context, dtype="bfloat16", n_planted_blocks=args.planted)
+        kd = torch.from_numpy(base.k).to(torch.bfloat16).to(dev)
+        vd = torch.from_numpy(base.v).to(torch.bfloat16).to(dev)
+        steps = [synth.decode_step_inputs(base, s, dtype="bfloat16") for s in range(2 * (W + K))]
+        for v_tol in (0.05, 0.02):
+            knobs = dict(PAPER_KNOBS, v_tolerance=v_tol)
+            for capped in (0, 128, 2048):     # blocks of 16 tokens in each hot tier; 0 = full mirror in HBM
+                for B in (1, 8, 32, 64):
+                    if context == 131072 and B > 8:
+                        continue
+                    if capped and (B > 8 or v_tol != 0.05 or (capped == 2048 and (B > 1 or context == 8192))):
+                        continue     # the pinned backing arrays of larger batches do not fit the time budget of a sweep
+                    if not capped and v_tol != 0.05 and B not in (1, 32):
+                        continue
+                    kw = dict(max_new_tokens=2 * (W + K) + 16, defer_int4_append_quantization=not capped)
+                    if capped:
+                        kw.update(fp16_key_cache_capacity=capped, fp16_value_cache_capacity=capped, max_pagein_blocks=64)
+                    caches = [TieredKeyCacheLayer.from_fp16_cache_int4v(kd, vd, **kw) for _ in range(B)]
+                    qs = [torch.from_numpy(np.stack([steps[s][0]] * B)).to(torch.bfloat16).to(dev) for s in range(2 * (W + K))]
+                    ks = [torch.from_numpy(np.stack([steps[s][1].reshape(8, 128)] * B)).to(torch.bfloat16).to(dev)
+                          for s in range(2 * (W + K))]
+                    vs = [torch.from_numpy(np.stack([steps[s][2].reshape(8, 128)] * B)).to(torch.bfloat16).to(dev)
+                          for s in range(2 * (W + K))]
+
+                    def batched(s):
+                        ca.certified_attention_batch(caches, qs[s], 4, q_scale, new_keys=ks[s], new_values=vs[s], **knobs)
+
+                    def looped(s):
+                        for b in range(B):
+                            caches[b].append_token(ks[s][b].reshape(8, 1, 128), vs[s][b].reshape(8, 1, 128))
+                            ca.certified_attention_layer(caches[b], qs[s][b], 4, q_scale, False, **knobs)
+
+                    def timed(fn, first):
+                        for s in range(first, first + W):
+                            fn(s)
+                        torch.cuda.synchronize()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        for s in range(first + W, first + W + K):
+                            fn(s)
+                        e1.record()
+                        torch.cuda.synchronize()
+                        return e0.elapsed_time(e1) * 1e3 / (K * B)
+
+                    us_loop = timed(looped, 0)
+                    before = caches[0].hot_tier_counters() if capped else {}
+                    us_batch = timed(batched, W + K)
+                    row = {"context": context, "batch": B, "v_tolerance": v_tol, "hot_tier_tokens": capped * 16 if capped else None,
+                           "us_per_sequence_layer_step_batched": round(us_batch, 2),
+                           "us_per_sequence_layer_step_looped": round(us_loop, 2),
+                           "speedup_of_batching": round(us_loop / us_batch, 2)}
+                    if capped:
+                        after = caches[0].hot_tier_counters()
+                        d = {k: after[k] - before.get(k, 0) for k in after}
+                        n_steps = max(1, d["steps"])
+                        for tier in ("key", "value"):
+                            tot = d[f"{tier}_hits"] + d[f"{tier}_misses"]
+                            row[f"{tier}_hit_rate"] = round(d[f"{tier}_hits"] / tot, 4) if tot else None
+                            row[f"{tier}_pagein_bytes_per_step"] = int(d[f"{tier}_pagein_bytes"] / n_steps)
+                    rows.append(row)
+                    print(json.dumps(row), file=sys.stderr, flush=True)
+                    del caches, qs, ks, vs
+                    torch.cuda.empty_cache()
+        del kd, vd
+    return {"metric": "certified_decode_attention_us_per_sequence_layer_step", "unit": "us", "n_gpus": 1,
+            "steps": K, "warmup": W, "higher_is_better": False, "data": "synthetic", "dtype": "f32",
+            "config": {"workload": "batch x context sweep, one layer, llama3.1-8b attention geometry, bf16 KV, "
+                                   "INT8K/INT4V g16, one appended token per sequence and step"},
+            "batched_sweep": rows}
+
+
 def main():
     args = parse_args()
     # Libraries (NCCL prints its version on start-up) write to file descriptor 1; the one JSON line the caller
@@ -695,6 +786,10 @@ def _main(args, out):
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device: bench.py --impl ours needs a B200; there is no CPU fallback"}), file=out)
         return 1
+    if args.batched_sweep:
+        if rank == 0:
+            print(json.dumps(run_batched_sweep(args, local)), file=out, flush=True)
+        return 0
     if world > 1:
         import torch.distributed as dist
 

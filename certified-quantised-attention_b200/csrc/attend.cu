@@ -6,9 +6,11 @@
 //     group share every value load.  A warp owns one 16-token block at a time;
 //     the block's INT4 codes, scales, zeros and cached Phase-1 token scores
 //     (1.5 KB + 64 B per head) arrive in a warp-private 4-stage shared-memory
-//     ring through bulk asynchronous copies (TMA engine: one lane issues four
-//     copies per block, completion is counted by one mbarrier per stage), so
-//     several blocks per warp are in flight and no CTA barrier sits in the loop.  Lane L (mod 16) owns
+//     ring through 16-byte asynchronous copies, so several blocks per warp are
+//     in flight and no CTA barrier sits in the loop.  (The pieces of a block are
+//     small here - 1024, 256, 256 and 64 bytes per head - and bulk copies through
+//     the TMA engine measured 3-7 % slower for them than per-lane 16-byte copies;
+//     the score kernel, whose pieces are 2 KB and 512 bytes, stages by TMA.)  Lane L (mod 16) owns
 //     output channels 8L..8L+7; half warp 0 takes the even tokens, half warp 1
 //     the odd ones (conflict-free shared-memory reads).  INT4 codes become
 //     floats with one logic op and one exact fused multiply-add each (magic
@@ -39,6 +41,18 @@ constexpr int ATT_STAGES = CQA_ATT_STAGES;
 
 __device__ __forceinline__ float fexp(float x) { return __expf(x); }
 
+__device__ __forceinline__ void att_cp16(void *smem, const void *gmem)
+{
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void att_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void att_wait()
+{
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
 template <int G>
 struct AttLayout {
     static constexpr int PACKED = 0;
@@ -56,60 +70,54 @@ struct AttLayout {
     // values), two tiles of true weights for those heads, and the FP16-key logits of the block being prepared
     static constexpr int W_TILE = BS * G * 8;
     static constexpr int PER_WARP = 4 * W_TILE + G * BS * 4;
-    static constexpr int BARS = RING_BYTES + ATT_WARPS * PER_WARP;        // one mbarrier per (warp, stage)
-    static constexpr int TOTAL = BARS + ATT_WARPS * ATT_STAGES * 8;
+    static constexpr int TOTAL = RING_BYTES + ATT_WARPS * PER_WARP;
 };
 
-// Source pointers of the next block to stage.  A block's stage is 1536 + 64*G bytes: packed codes (1024), scales
-// (256), zeros (256) and G*64 bytes of token scores, four contiguous pieces in global memory, one bulk copy each.
+// Per-lane source pointers of the next block to stage.  A block's stage is 1536 + 64*G bytes = packed codes
+// (two 512-byte rounds), scales+zeros (one round: lanes 0-15 scales, 16-31 zeros) and G*64 bytes of token scores.
 template <int G>
 struct AttIssuer {
-    const char *pk, *sc_, *zr, *sc;   // global sources of the block to issue next
-    long b, b_end, nq;
+    const char *pk, *sz, *sc;   // global sources for this lane
+    long b, b_end, nq;          // block to issue next
     bool have4;
 
-    __device__ __forceinline__ void init(const cqa_cache &c, const float *tok, long nq_, int kv, long b0, long bend)
+    __device__ __forceinline__ void init(const cqa_cache &c, const float *tok, long nq_, int kv, long b0, long bend,
+                                         int lane)
     {
         b = b0;
         b_end = bend;
         nq = nq_;
         have4 = c.values_int4_packed != nullptr;
         const long row0 = (long)kv * c.cap_tokens + b0 * BS;
-        pk = reinterpret_cast<const char *>(c.values_int4_packed) + row0 * (D / 2);
-        sc_ = reinterpret_cast<const char *>(c.values_int4_scales) + row0 * NG * 2;
-        zr = reinterpret_cast<const char *>(c.values_int4_zeros) + row0 * NG * 2;
-        sc = reinterpret_cast<const char *>(tok + ((long)kv * nq_ + b0) * G * BS);
+        pk = reinterpret_cast<const char *>(c.values_int4_packed) + row0 * (D / 2) + lane * 16;
+        const char *szb = lane < 16 ? reinterpret_cast<const char *>(c.values_int4_scales)
+                                    : reinterpret_cast<const char *>(c.values_int4_zeros);
+        sz = szb + row0 * NG * 2 + (lane & 15) * 16;
+        sc = reinterpret_cast<const char *>(tok + ((long)kv * nq_ + b0) * G * BS) + lane * 16;
     }
-    // Stage the block `b` (if any) and advance by one warp stride.  Exactly one arrival per call reaches the
-    // stage's mbarrier (with the bytes of the copies issued, possibly none), so every call completes one phase.
-    // A block without INT4 data (the trailing partial block, or an FP16-value cache) gets zeros, written by the
-    // lanes themselves, so the INT4 arithmetic on it is finite.
-    __device__ __forceinline__ void issue(char *stage, unsigned stage_addr, unsigned bar_addr, int lane)
+    // Stage the block `b` (if any) and advance by one warp stride; always commits one group.  A block without
+    // INT4 data (the trailing partial block) gets zeros, so the INT4 arithmetic on it is finite.
+    __device__ __forceinline__ void issue(char *stage, int lane)
     {
         using LY = AttLayout<G>;
-        const bool live = b < b_end;
-        const bool int4 = live && have4 && b < nq;
-        const bool scores = live && b < nq;
-        if (live && !int4) {
-            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4 *>(stage + lane * 16) = z;
-            *reinterpret_cast<uint4 *>(stage + 512 + lane * 16) = z;
-            *reinterpret_cast<uint4 *>(stage + LY::SCALES + lane * 16) = z;
-        }
-        if (lane == 0) {
-            const unsigned bytes = (int4 ? (unsigned)LY::SCORES : 0u) + (scores ? (unsigned)(G * BS * 4) : 0u);
-            mbar_arrive_expect_tx(bar_addr, bytes);
-            if (int4) {
-                bulk_copy_g2s(stage_addr + LY::PACKED, pk, BS * (D / 2), bar_addr);
-                bulk_copy_g2s(stage_addr + LY::SCALES, sc_, BS * NG * 2, bar_addr);
-                bulk_copy_g2s(stage_addr + LY::ZEROS, zr, BS * NG * 2, bar_addr);
+        if (b < b_end) {
+            if (have4 && b < nq) {
+                att_cp16(stage + lane * 16, pk);
+                att_cp16(stage + 512 + lane * 16, pk + 512);
+                att_cp16(stage + LY::SCALES + lane * 16, sz);
+                if (lane < 4 * G) att_cp16(stage + LY::SCORES + lane * 16, sc);
+            } else {
+                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4 *>(stage + lane * 16) = z;
+                *reinterpret_cast<uint4 *>(stage + 512 + lane * 16) = z;
+                *reinterpret_cast<uint4 *>(stage + LY::SCALES + lane * 16) = z;
+                if (b < nq && lane < 4 * G) att_cp16(stage + LY::SCORES + lane * 16, sc);
             }
-            if (scores) bulk_copy_g2s(stage_addr + LY::SCORES, sc, G * BS * 4, bar_addr);
         }
+        att_commit();
         b += ATT_WARPS;
         pk += ATT_WARPS * BS * (D / 2);
-        sc_ += ATT_WARPS * BS * NG * 2;
-        zr += ATT_WARPS * BS * NG * 2;
+        sz += ATT_WARPS * BS * NG * 2;
         sc += ATT_WARPS * G * BS * 4;
     }
 };
@@ -430,19 +438,10 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
     float *sc_tile = reinterpret_cast<float *>(wpriv + 4 * LY::W_TILE);        // [G][16] FP16-key logits
 
     // start the pipeline before anything else
-    uint64_t *wbar = reinterpret_cast<uint64_t *>(dsm + LY::BARS) + warp * ATT_STAGES;
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < ATT_STAGES; ++s) mbar_init(wbar + s, 1);
-        mbar_init_fence();
-    }
-    __syncwarp();
-    const unsigned wring_addr = smem_u32(wring), wbar_addr = smem_u32(wbar);
     AttIssuer<G> issuer;
-    issuer.init(c, ws.token_scores, nq, kv, b_begin + warp, b_end);
+    issuer.init(c, ws.token_scores, nq, kv, b_begin + warp, b_end, lane);
 #pragma unroll
-    for (int s = 0; s < ATT_STAGES - 1; ++s)
-        issuer.issue(wring + s * LY::STAGE, wring_addr + s * LY::STAGE, wbar_addr + s * 8, lane);
+    for (int s = 0; s < ATT_STAGES - 1; ++s) issuer.issue(wring + s * LY::STAGE, lane);
 
     // Blocks of this warp: b_begin + warp + 8*it.  Lane j keeps the key / value promotion bits of the warp's
     // block (it0 + j), one bit per head of the group; they are re-read every 32 blocks.
@@ -577,18 +576,16 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
 
     float alpha_cur = 1.0f;
     if (n_my > 0) {
-        mbar_wait(wbar_addr, 0u);     // block 0 has landed
+        att_wait<ATT_STAGES - 2>();
+        __syncwarp();
         alpha_cur = prepare(0, __shfl_sync(FULL, my_masks, 0));
     }
     for (int it = 0; it < n_my; ++it) {
         const long b = b_begin + warp + (long)it * ATT_WARPS;
         __syncwarp();   // every lane is done with the slot that is about to be refilled, and with w_tiles[(it+1)&1]
-        {
-            const int slot = (it + ATT_STAGES - 1) % ATT_STAGES;
-            issuer.issue(wring + slot * LY::STAGE, wring_addr + slot * LY::STAGE, wbar_addr + slot * 8, lane);
-            // block it+1 has landed: its stage barrier completes one phase per pass over the ring
-            mbar_wait(wbar_addr + ((it + 1) % ATT_STAGES) * 8, (unsigned)((it + 1) / ATT_STAGES) & 1u);
-        }
+        issuer.issue(wring + ((it + ATT_STAGES - 1) % ATT_STAGES) * LY::STAGE, lane);
+        att_wait<ATT_STAGES - 2>();   // block it+1 has landed
+        __syncwarp();
         const unsigned masks_cur = __shfl_sync(FULL, my_masks, it & 31);
         const unsigned vm = (masks_cur >> 8) & 0xFFu;
         if ((it & 31) == 31 && it + 1 < n_my) load_masks(it + 1);
@@ -667,8 +664,7 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
         }
         alpha_cur = alpha_next;
     }
-    // every copy that was issued has been waited for: the last blocks issued lie beyond the warp's range and
-    // carry no bytes
+    att_wait<0>();
     // per-head (m, l) for the CTA merge: l is summed over the lanes of a head first
 #pragma unroll
     for (int o = LPH / 2; o >= 1; o >>= 1) l_mine += __shfl_xor_sync(FULL, l_mine, o);
@@ -705,7 +701,7 @@ template <int G, typename T2>
 __global__ void __launch_bounds__(ATT_THREADS, CQA_ATT_MIN_CTAS) attend_batched_kernel(const cqa_batch_item *items, int q_dtype,
                                                                                       float q_scale, int do_append)
 {
-    const cqa_batch_item &it = items[blockIdx.z];
+    const cqa_batch_item &it = *stage_batch_item(items + blockIdx.z);
     const long num_tokens = it.pos + do_append;
     const long nq = num_tokens / BS, nact = (num_tokens + BS - 1) / BS;
     const int ns = it.ws.num_splits;
@@ -756,8 +752,6 @@ static int attend_launch_t(const cqa_cache *c, const cqa_workspace *ws, const vo
     return CQA_ERR_UNSUPPORTED;
 }
 
-int attend_wait_timeouts(int *count, int reset) { return wait_timeouts_of_this_unit(count, reset); }
-
 // Argument checks of Phase 2 (also called by the fused step before its first launch).
 int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact, int last_valid)
 {
@@ -769,7 +763,7 @@ int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact
     if (nq > 0 && !ws->token_scores) { set_error("cqa_attend: token_scores missing"); return CQA_ERR_INVALID; }
     if (((uintptr_t)ws->token_scores | (uintptr_t)c->values_int4_packed | (uintptr_t)c->values_int4_scales |
          (uintptr_t)c->values_int4_zeros) & 15) {
-        set_error("cqa_attend: token_scores and the INT4 value arrays must be 16-byte aligned (bulk copies)");
+        set_error("cqa_attend: token_scores and the INT4 value arrays must be 16-byte aligned (16-byte copies)");
         return CQA_ERR_INVALID;
     }
     if (nq < 0 || nact <= 0 || nact < nq || nact > ws->ld || nact > c->max_blocks) {

@@ -391,16 +391,13 @@ constexpr int BULK_WAIT_POLLS = 50000;
 // Wait (bounded) until the phase with this parity of `bar` has completed.  A copy normally lands within a few
 // polls.  Once any wait of this unit has run out, later waits give up after a handful of polls, so that a broken
 // run ends quickly instead of paying the full limit at every stage.
-static __device__ __noinline__ void mbar_wait_slow(unsigned bar_addr, unsigned parity)
+__device__ __forceinline__ void mbar_wait(unsigned bar_addr, unsigned parity)
 {
+    if (mbar_try_wait(bar_addr, parity)) return;
     const int limit = *reinterpret_cast<volatile int *>(&g_wait_timeouts) != 0 ? 64 : BULK_WAIT_POLLS;
     for (int polls = 0; polls < limit; ++polls)
         if (mbar_try_wait(bar_addr, parity)) return;
     atomicAdd(&g_wait_timeouts, 1);
-}
-__device__ __forceinline__ void mbar_wait(unsigned bar_addr, unsigned parity)
-{
-    if (!mbar_try_wait(bar_addr, parity)) mbar_wait_slow(bar_addr, parity);
 }
 
 // Host side: read (and optionally clear) this translation unit's timeout counter on the current device.
@@ -462,6 +459,21 @@ __device__ __forceinline__ void peer_wait(const int32_t *flags, int n, int skip,
     __syncthreads();
 }
 
+// ----------------------------------------------------------------- batches
+
+// A batched kernel's CTA copies the record of its sequence from global to shared memory once and works from that
+// copy (the one-sequence kernels get the same structs as kernel parameters).  Ends with a CTA barrier.
+__device__ __forceinline__ const cqa_batch_item *stage_batch_item(const cqa_batch_item *src)
+{
+    __shared__ __align__(16) cqa_batch_item s_item;
+    static_assert(sizeof(cqa_batch_item) % 4 == 0, "record is copied in 32-bit words");
+    const int *from = reinterpret_cast<const int *>(src);
+    int *to = reinterpret_cast<int *>(&s_item);
+    for (int i = threadIdx.x; i < (int)(sizeof(cqa_batch_item) / 4); i += blockDim.x) to[i] = from[i];
+    __syncthreads();
+    return &s_item;
+}
+
 // ----------------------------------------------------------------- errors
 
 void set_error(const char *fmt, ...);
@@ -475,6 +487,5 @@ int selcert_check(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *
 int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact, int last_valid);
 int append_check(const cqa_cache *c, const void *k_new, const void *v_new, int src_dtype, long pos);
 int score_wait_timeouts(int *count, int reset);
-int attend_wait_timeouts(int *count, int reset);
 
 }  // namespace cqa

@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(128) append_token_kernel(cqa_cache c, const vo
 template <typename T2>
 __global__ void __launch_bounds__(128) append_token_batched_kernel(const cqa_batch_item *items, int src_dtype)
 {
-    const cqa_batch_item &it = items[blockIdx.y];
+    const cqa_batch_item &it = *stage_batch_item(items + blockIdx.y);
     append_token_body<T2>(it.cache, it.k_new, it.v_new, src_dtype, it.pos, it.defer_int4);
 }
 

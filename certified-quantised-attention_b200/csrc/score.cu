@@ -24,26 +24,26 @@ constexpr int STAGE_HALF = BLOCK_BYTES + 2 * D * 4;       // + scale + zero poin
 constexpr int STAGE_WARP = 2 * STAGE_HALF;                // two half warps
 constexpr int SCORE_SMEM = SCORE_WARPS * 2 * STAGE_WARP;  // double buffered: 98304
 
-// Issue the copies of one warp stage: blocks b0 (lanes 0-15 consume it) and b0+1 (lanes 16-31).  A stage half is
-// the block's 2048 key bytes followed by its 128 scales and 128 zero points.  Block numbers are clamped to the
-// last block of the CTA's range, so an odd tail block is simply scored twice (only one result is stored).  One
-// lane announces the bytes to the stage's mbarrier and issues the six copies.
+// Issue the copies of one warp stage: blocks b0 (lanes 0-15 consume it) and b0+1 (lanes 16-31).  The two blocks are
+// neighbours in every array, so a stage is three bulk copies: 4096 key bytes, 2 x 128 scales, 2 x 128 zero points
+// (laid out [keys b0 | keys b0+1 | scales b0 | scales b0+1 | zero points b0 | zero points b0+1]).  An odd tail block
+// has no neighbour: then the copies are half as long and both half warps read the first half (the block is scored
+// twice, one result is stored).  One lane announces the bytes to the stage's mbarrier and issues the copies.
+constexpr int ST_SCALES = 2 * BLOCK_BYTES, ST_ZEROS = ST_SCALES + 2 * D * 4;
 __device__ __forceinline__ void score_issue(const cqa_cache &c, int kv, long b_first, long b_last, unsigned stage_addr,
                                             unsigned bar_addr, int lane)
 {
+    // the addresses are the same for every lane (computed outside the one-lane region, where the compiler can
+    // keep them on the uniform datapath); only the copy instructions themselves are issued by one lane
+    const unsigned nblk = b_first < b_last ? 2u : 1u;
+    const char *k0 = reinterpret_cast<const char *>(c.keys_int8) + ((long)kv * c.cap_tokens + b_first * BS) * D;
+    const char *s0 = reinterpret_cast<const char *>(c.keys_scale) + ((long)kv * c.max_blocks + b_first) * (D * 4);
+    const char *z0 = reinterpret_cast<const char *>(c.keys_zero_points) + ((long)kv * c.max_blocks + b_first) * (D * 4);
     if (lane == 0) {
-        mbar_arrive_expect_tx(bar_addr, 2 * STAGE_HALF);
-        const long b1 = min(b_first + 1, b_last);
-        const char *k0 = reinterpret_cast<const char *>(c.keys_int8) + ((long)kv * c.cap_tokens + b_first * BS) * D;
-        const char *s0 = reinterpret_cast<const char *>(c.keys_scale) + ((long)kv * c.max_blocks + b_first) * (D * 4);
-        const char *z0 = reinterpret_cast<const char *>(c.keys_zero_points) + ((long)kv * c.max_blocks + b_first) * (D * 4);
-        const long dk = (b1 - b_first) * BLOCK_BYTES, ds = (b1 - b_first) * (D * 4);
-        bulk_copy_g2s(stage_addr, k0, BLOCK_BYTES, bar_addr);
-        bulk_copy_g2s(stage_addr + BLOCK_BYTES, s0, D * 4, bar_addr);
-        bulk_copy_g2s(stage_addr + BLOCK_BYTES + D * 4, z0, D * 4, bar_addr);
-        bulk_copy_g2s(stage_addr + STAGE_HALF, k0 + dk, BLOCK_BYTES, bar_addr);
-        bulk_copy_g2s(stage_addr + STAGE_HALF + BLOCK_BYTES, s0 + ds, D * 4, bar_addr);
-        bulk_copy_g2s(stage_addr + STAGE_HALF + BLOCK_BYTES + D * 4, z0 + ds, D * 4, bar_addr);
+        mbar_arrive_expect_tx(bar_addr, nblk * STAGE_HALF);
+        bulk_copy_g2s(stage_addr, k0, nblk * BLOCK_BYTES, bar_addr);
+        bulk_copy_g2s(stage_addr + ST_SCALES, s0, nblk * (D * 4), bar_addr);
+        bulk_copy_g2s(stage_addr + ST_ZEROS, z0, nblk * (D * 4), bar_addr);
     }
 }
 
@@ -114,9 +114,11 @@ __device__ __forceinline__ void score_blocks_body(const cqa_cache &c, const void
         mbar_wait(wbar_addr + stage * 8, (unsigned)(use >> 1) & 1u);     // this stage's barrier completes one phase per use
         const long b = b0 + hw;
         const bool live = b < b_end;
-        const char *kb = wbuf + stage * STAGE_WARP + hw * STAGE_HALF;
-        const float *sc = reinterpret_cast<const float *>(kb + BLOCK_BYTES);
-        const float *zp = sc + D;
+        const int half = live ? hw : 0;        // an odd tail has one block in the stage
+        const char *sbase = wbuf + stage * STAGE_WARP;
+        const char *kb = sbase + half * BLOCK_BYTES;
+        const float *sc = reinterpret_cast<const float *>(sbase + ST_SCALES) + half * D;
+        const float *zp = reinterpret_cast<const float *>(sbase + ST_ZEROS) + half * D;
 #pragma unroll
         for (int pass = 0; pass < G / GH; ++pass) {
             float2 qs[GH][4];
@@ -215,7 +217,7 @@ template <int G>
 __global__ void __launch_bounds__(SCORE_WARPS * 32, 2) score_blocks_batched_kernel(const cqa_batch_item *items, int q_dtype,
                                                                                   float q_scale, int do_append)
 {
-    const cqa_batch_item &it = items[blockIdx.z];
+    const cqa_batch_item &it = *stage_batch_item(items + blockIdx.z);
     const long nq = (it.pos + do_append) / BS;
     long bpc = (nq + gridDim.x - 1) / gridDim.x;
     if (bpc < 2) bpc = 2;

@@ -1155,7 +1155,7 @@ template <int VPT>
 __global__ void __launch_bounds__(SC_THREADS, 1) selcert_batched_kernel(const cqa_batch_item *items, cqa_knobs kn, int q_dtype,
                                                                         int do_append)
 {
-    const cqa_batch_item &it = items[blockIdx.z];
+    const cqa_batch_item &it = *stage_batch_item(items + blockIdx.z);
     const long num_tokens = it.pos + do_append;
     const long nq = num_tokens / BS, nact = (num_tokens + BS - 1) / BS;
     const SelPlan p = sel_plan(&kn, nq);
