@@ -513,11 +513,14 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     const long row_ld = sharded_in ? ws.shard_chunk : ws.ld;
     const float *mb = ws.m_b + (long)h * row_ld;
     const float *sb = ws.s_b + (long)h * row_ld;
+    // 32-bit arithmetic on purpose: the mapping runs once per block and thread, and a 64-bit division there costs
+    // more than everything else in the loop
+    const int sh_stride = sharded_in ? (int)ws.shard_stride : 1, sh_last = ws.shard_ranks - 1;
+    const long sh_rank_stride = ws.shard_rank_stride;
     auto gcol = [&](int b) -> long {
-        if (!sharded_in) return b;
-        long r = b / ws.shard_stride;
-        if (r > ws.shard_ranks - 1) r = ws.shard_ranks - 1;
-        return r * ws.shard_rank_stride + (b - r * ws.shard_stride);
+        int r = b / sh_stride;
+        if (r > sh_last) r = sh_last;
+        return (long)r * sh_rank_stride + (b - r * sh_stride);
     };
     float *mf = ws.mass_frac + (long)h * ws.ld;
     cqa_head_cert *ct = ws.cert + h;
@@ -542,14 +545,26 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     // values are then read from shared memory.  A <- m_b, B <- S_b, C <- eta_b or the exploration uniforms.
     {
         const float *xsrc = role == 2 ? eta : ((explore_on && u != nullptr) ? u + (long)h * u_ld : nullptr);
+        if (!sharded_in) {
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            const int b = k * SC_THREADS + tid;
-            if (b < n) {
-                const long gb = gcol(b);
-                cp_async4(A + b, mb + gb);
-                cp_async4(B + b, sb + gb);
-                if (xsrc) cp_async4(C + b, xsrc + (role == 2 ? gb : (long)b));
+            for (int k = 0; k < VPT; ++k) {
+                const int b = k * SC_THREADS + tid;
+                if (b < n) {
+                    cp_async4(A + b, mb + b);
+                    cp_async4(B + b, sb + b);
+                    if (xsrc) cp_async4(C + b, xsrc + b);
+                }
+            }
+        } else {
+#pragma unroll 1
+            for (int k = 0; k < VPT; ++k) {
+                const int b = k * SC_THREADS + tid;
+                if (b < n) {
+                    const long gb = gcol(b);
+                    cp_async4(A + b, mb + gb);
+                    cp_async4(B + b, sb + gb);
+                    if (xsrc) cp_async4(C + b, xsrc + (role == 2 ? gb : (long)b));
+                }
             }
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
