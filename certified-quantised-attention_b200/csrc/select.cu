@@ -1,14 +1,14 @@
 // Selector and certifier: one CTA of 1024 threads per (query head, role).
 //
 // A thread owns the blocks b = tid, tid + 1024, ... (at most 16 at the limit of
-// 16384 blocks) and keeps their values in registers, so the searches below are
-// passes over registers with one CTA barrier each; shared memory holds a copy
-// for the few steps that index by block id.
+// 16384 blocks).  The per-block values live in shared-memory arrays and every
+// phase is a short rolled loop over them with one CTA barrier: the executed
+// code is small on purpose, because ~100 CTAs start the same code at the same
+// moment and an unrolled form of these loops was bound by instruction fetch.
 //
 //   role 0 (select) : block log-masses and mass fractions (canonical sum), the
-//            256 heaviest blocks (ties -> lower block id) by a threshold search
-//            on the float bit patterns, two bits per step, ordered by rank
-//            counting; sequential cumulative mass; K* with the Rung-1
+//            256 heaviest blocks (ties -> lower block id) by a radix search
+//            on the float bit patterns, ordered by rank counting; sequential cumulative mass; K* with the Rung-1
 //            expansion; exploration draw; FP16-key mask.
 //   role 1 (ranking): top-4 blocks by m_b (per-thread lists merged by
 //            shuffles), FP16 re-score by four warps while the other warps take
@@ -16,7 +16,8 @@
 //            score-consistency flags, work list of the dense recompute.
 //   role 2 (values) : Rung-2 value check: the promoted blocks are those whose
 //            contribution mass*eta is at or above a threshold found by a search
-//            over "column sums" (two bits per step), no sort and no serial walk.
+//            over "column sums" (histogram hint, then one bit per step), no sort
+//            and no serial walk.
 //
 // cqa_select, cqa_certify and the fused cqa_layer_step all launch the same
 // kernel with a phase mask.  Sums over blocks use the canonical orders
@@ -112,33 +113,38 @@ __device__ __forceinline__ float cta_max(float v, SCShared &sh, int &parity)
     return r;
 }
 
-// Canonical sum of the n values held one per (thread, k) as v[k] <-> index k * 1024 + tid (entries at or beyond n
-// must be +0): 32 consecutive values by a warp butterfly (16..1), 8 such sums by a butterfly (4,2,1) = one leaf of
-// 256 values, leaves added left to right.  Result in every thread.  gsum needs n_pad / 32 floats, leaf n_pad / 256.
-template <int VPT>
-__device__ __forceinline__ float cta_canonical_sum(const float (&v)[VPT], int n, float *gsum, float *leaf)
+// Every per-block loop of this kernel is a ROLLED loop over shared-memory arrays ("for k < nk: b = k * 1024 + tid").
+// The code of a phase is then a few dozen instructions that stay in the instruction cache, instead of the same
+// instructions unrolled once per block a thread owns: with ~100 CTAs starting the same straight-line code at the same
+// moment, fetching instructions through the L2 was what bounded the unrolled form.
+
+// Canonical sum of vals[0..n) (shared memory): 32 consecutive values by a warp butterfly (16..1), 8 such sums by a
+// butterfly (4,2,1) = one leaf of 256 values, leaves added left to right.  Result in every thread.  gsum needs
+// n_pad / 32 floats, leaf n_pad / 256.
+__device__ __forceinline__ float cta_canonical_sum(const float *vals, int n, int nk, float *gsum, float *leaf)
 {
-    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    const int tid = threadIdx.x, w = tid >> 5, l = tid & 31;
     const int ngroups = (n + 31) >> 5, nleaf = (n + 255) >> 8;
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-        const float s = warp_sum(v[k]);
+#pragma unroll 1
+    for (int k = 0; k < nk; ++k) {
+        const int b = k * SC_THREADS + tid;
+        const float s = warp_sum(b < n ? vals[b] : 0.0f);
         if (l == 0 && k * SC_WARPS + w < ngroups) gsum[k * SC_WARPS + w] = s;   // groups beyond n hold nothing
     }
     __syncthreads();
-    if ((int)threadIdx.x < nleaf) {
-        const int L = threadIdx.x;
+    if (tid < nleaf) {
         float p[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) p[i] = (L * 8 + i) < ngroups ? gsum[L * 8 + i] : 0.0f;
+        for (int i = 0; i < 8; ++i) p[i] = (tid * 8 + i) < ngroups ? gsum[tid * 8 + i] : 0.0f;
 #pragma unroll
         for (int s = 4; s >= 1; s >>= 1)
 #pragma unroll
             for (int i = 0; i < s; ++i) p[i] = __fadd_rn(p[i], p[i + s]);
-        leaf[L] = p[0];
+        leaf[tid] = p[0];
     }
     __syncthreads();
     float total = leaf[0];
+#pragma unroll 1
     for (int L = 1; L < nleaf; ++L) total = __fadd_rn(total, leaf[L]);
     return total;
 }
@@ -193,7 +199,7 @@ __device__ __forceinline__ void rank_sort_desc(u64 *cand, SCShared &sh)
 // Given hist[0..nbins) (nbins <= 2048, non-negative, total below 2^31), find the highest bin d whose suffix sum
 // S(d) = hist[d] + hist[d+1] + ... reaches `need` (need >= 1, S(0) >= need): returns d in every thread, with
 // `above` = S(d+1) and `in_bin` = hist[d].  Thread t scans the bins in descending order, two per thread; one
-// warp scan, one barrier, and every thread adds up the totals of the warps before its own.
+// warp scan, one barrier, a second scan over the warp totals.
 __device__ __forceinline__ int find_suffix_crossing(const int *hist, int nbins, int need, SCShared &sh, int &above,
                                                     int &in_bin)
 {
@@ -247,13 +253,12 @@ __device__ __forceinline__ void hist_add(int *hist, bool match, unsigned digit, 
     }
 }
 
-// Bit pattern `thr` of the M-th largest of the n values v[k] <-> index k * 1024 + tid (values >= 0; 1 <= M < n) and
-// the number n_ge of entries at or above it, by a radix search: digits of 11, 11 and 9 bits from the top, each a
-// histogram in shared memory (integer atomics) and a scan for the bin that holds the M-th entry.  A pass only
-// counts the entries that fell into the previous pass's bin, and the search stops when a bin is taken whole (then
-// n_ge == M and the lower bits of thr are zero).  hist: 2048 ints.
-template <int VPT>
-__device__ __forceinline__ void radix_threshold(const float (&v)[VPT], int n, int M, int *hist, SCShared &sh,
+// Bit pattern `thr` of the M-th largest of vals[0..n) (shared memory, values >= 0; 1 <= M < n) and the number n_ge of
+// entries at or above it, by a radix search: digits of 11, 11 and 9 bits from the top, each a histogram in shared
+// memory (integer atomics) and a scan for the bin that holds the M-th entry.  A pass only counts the entries that
+// fell into the previous pass's bin, and the search stops when a bin is taken whole (then n_ge == M and the lower
+// bits of thr are zero).  hist: 2048 ints.
+__device__ __forceinline__ void radix_threshold(const float *vals, int n, int nk, int M, int *hist, SCShared &sh,
                                                 unsigned &thr, int &n_ge)
 {
     const int tid = threadIdx.x;
@@ -267,10 +272,11 @@ __device__ __forceinline__ void radix_threshold(const float (&v)[VPT], int n, in
         hist[2 * tid] = 0;
         hist[2 * tid + 1] = 0;
         __syncthreads();
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            const unsigned x = __float_as_uint(v[k]);
-            const bool match = (k * SC_THREADS + tid) < n && (pass == 0 || (x >> up) == (prefix >> up));
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
+            const int b = k * SC_THREADS + tid;
+            const unsigned x = b < n ? __float_as_uint(vals[b]) : 0u;
+            const bool match = b < n && (pass == 0 || (x >> up) == (prefix >> up));
             hist_add(hist, match, (x >> shift) & (unsigned)(nbins - 1));
         }
         __syncthreads();
@@ -288,15 +294,10 @@ __device__ __forceinline__ void radix_threshold(const float (&v)[VPT], int n, in
     }
 }
 
-// The M = min(CAND, n) largest (value, lower-index-first) entries of the n values v[k] <-> index k * 1024 + tid
-// (values >= 0, entries at or beyond n hold +0), sorted descending into cand[0..CAND) (padding = 0).  `vals` is the
-// same data in shared memory.
-//
-// The value of the M-th largest entry is found by a radix search over the bit patterns (radix_threshold); entries
-// above the threshold are then compacted and ordered by rank counting.
-template <int VPT>
-__device__ __forceinline__ void select_top_sorted(const float (&v)[VPT], const float *vals, int n, u64 *cand, int *hist,
-                                                  SCShared &sh, int &parity)
+// The M = min(CAND, n) largest (value, lower-index-first) entries of vals[0..n) (shared memory, values >= 0), sorted
+// descending into cand[0..CAND) (padding = 0).  The value of the M-th largest entry is found by a radix search over
+// the bit patterns (radix_threshold); entries above the threshold are then compacted and ordered by rank counting.
+__device__ __forceinline__ void select_top_sorted(const float *vals, int n, int nk, u64 *cand, int *hist, SCShared &sh)
 {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     if (tid == 0) sh.counter = 0;
@@ -304,25 +305,23 @@ __device__ __forceinline__ void select_top_sorted(const float (&v)[VPT], const f
     const int M = n < CAND ? n : CAND;
     if (n <= CAND) {
         __syncthreads();
-        if (tid < n) cand[tid] = make_key(v[0], tid);    // n <= 256: one value per thread
+        if (tid < n) cand[tid] = make_key(vals[tid], tid);
     } else {
         unsigned thr = 0u;
         int n_ge = n;            // entries >= thr
-        radix_threshold<VPT>(v, n, M, hist, sh, thr, n_ge);
+        radix_threshold(vals, n, nk, M, hist, sh, thr, n_ge);
         // n_ge == M: the entries >= thr are the answer.  Otherwise thr is the value of the M-th largest
         // entry and several entries equal it: take everything above, then the lowest block ids among the equal.
         const bool ties = n_ge != M;
         __syncthreads();   // cand is zeroed, sh.counter is 0
-        unsigned take = 0;
+        // first the number of entries each thread takes, then one atomic per warp for the base, then the copies
         int mine = 0;
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            const unsigned x = __float_as_uint(v[k]);
-            const bool t = (k * SC_THREADS + tid) < n && (ties ? x > thr : x >= thr);
-            take |= t ? 1u << k : 0u;
-            mine += t ? 1 : 0;
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
+            const int b = k * SC_THREADS + tid;
+            const unsigned x = b < n ? __float_as_uint(vals[b]) : 0u;
+            mine += (b < n && (ties ? x > thr : x >= thr)) ? 1 : 0;
         }
-        // exclusive scan of the per-lane counts over the warp, one atomic per warp for the base
         int incl = mine;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -334,9 +333,17 @@ __device__ __forceinline__ void select_top_sorted(const float (&v)[VPT], const f
         if (lane == 31 && warp_total > 0) base = atomicAdd(&sh.counter, warp_total);
         base = __shfl_sync(FULL, base, 31);
         int pos = base + incl - mine;
-#pragma unroll
-        for (int k = 0; k < VPT; ++k)
-            if (take & (1u << k)) cand[pos++] = make_key(v[k], k * SC_THREADS + tid);
+        if (mine) {
+#pragma unroll 1
+            for (int k = 0; k < nk; ++k) {
+                const int b = k * SC_THREADS + tid;
+                if (b < n) {
+                    const float v = vals[b];
+                    const unsigned x = __float_as_uint(v);
+                    if (ties ? x > thr : x >= thr) cand[pos++] = make_key(v, b);
+                }
+            }
+        }
         if (ties) {
             // entries equal to the threshold fill the remaining places in block order: an ordered compaction,
             // 1024 consecutive blocks per round (per-warp counts, then an exclusive scan over the warps)
@@ -381,9 +388,9 @@ __device__ __forceinline__ void insert4(u64 (&t)[4], u64 k)
 }
 // The four largest keys held by a warp, given one descending 4-list per lane (keys distinct, zero is
 // padding): four rounds of a warp-wide maximum over the list heads; the lane that wins pops its list.
-__device__ __forceinline__ void warp_top4(u64 (&t)[4], u64 (&out)[4])
+__device__ __noinline__ void warp_top4(u64 (&t)[4], u64 (&out)[4])
 {
-#pragma unroll
+#pragma unroll 1
     for (int r = 0; r < 4; ++r) {
         u64 best = t[0];
 #pragma unroll
@@ -396,25 +403,28 @@ __device__ __forceinline__ void warp_top4(u64 (&t)[4], u64 (&out)[4])
     }
 }
 
-// "Column sums" of the value check, three admission thresholds at once: of the entries e[k] <-> index k * 1024 + tid
-// (entries at or beyond n hold +0 and are never admitted because thresholds are >= 1), column t (= thread t,
-// 0..1023) adds its admitted members t, t + 1024, ... in ascending order; the 32 columns of a warp are combined by
-// the butterfly 16,8,4,2,1 and the 32 warp sums by the same butterfly.  f[i] = sum of the entries with bits >= t[i],
-// c[i] = their number; results in every thread.  Adding an admitted entry never lowers a sum (every step is a
-// monotone rounding), which is what the threshold search relies on.
-template <int VPT>
-__device__ __forceinline__ void column_sums3(const float (&e)[VPT], unsigned t1, unsigned t2, unsigned t3,
+// "Column sums" of the value check for up to three admission thresholds at once: of the entries e[0..n) (shared
+// memory), column t (= thread t, 0..1023) adds its admitted
+// members t, t + 1024, ... in ascending order; the 32 columns of a warp are combined by the butterfly 16,8,4,2,1 and
+// the 32 warp sums by the same butterfly.  f[i] = sum of the entries with bits >= t[i], c[i] = their number; results
+// in every thread.  Adding an admitted entry never lowers a sum (every step is a monotone rounding), which is what
+// the threshold search relies on.  A threshold of 0xFFFFFFFF admits nothing.
+__device__ __forceinline__ void column_sums3(const float *e, int n, int nk, unsigned t1, unsigned t2, unsigned t3,
                                              SCShared &sh, int &parity, float (&f)[3], int (&c)[3])
 {
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
     unsigned n12 = 0, n3 = 0;
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-        const unsigned x = __float_as_uint(e[k]);
-        if (x >= t1) { s1 = __fadd_rn(s1, e[k]); n12 += 1u; }
-        if (x >= t2) { s2 = __fadd_rn(s2, e[k]); n12 += 1u << 16; }
-        if (x >= t3) { s3 = __fadd_rn(s3, e[k]); n3 += 1u; }
+#pragma unroll 1
+    for (int k = 0; k < nk; ++k) {
+        const int b = k * SC_THREADS + tid;
+        if (b < n) {
+            const float v = e[b];
+            const unsigned x = __float_as_uint(v);
+            if (x >= t1) { s1 = __fadd_rn(s1, v); n12 += 1u; }
+            if (x >= t2) { s2 = __fadd_rn(s2, v); n12 += 1u << 16; }
+            if (x >= t3) { s3 = __fadd_rn(s3, v); n3 += 1u; }
+        }
     }
     s1 = warp_sum(s1);
     s2 = warp_sum(s2);
@@ -439,17 +449,22 @@ __device__ __forceinline__ void column_sums3(const float (&e)[VPT], unsigned t1,
     parity ^= 1;
 }
 
-// One column sum over the entries `pred(bits, block id)` admits (same order as column_sums3).
-template <int VPT, typename Pred>
-__device__ __forceinline__ float column_sum1(const float (&e)[VPT], int n, Pred pred, SCShared &sh, int &parity, int &count)
+// One column sum (same order as column_sums3) over the entries with bits > t_gt, or bits == t_gt and block id below
+// id_lt.  (t_gt = t - 1, id_lt = 0 admits the entries with bits >= t; t_gt = 0, id_lt = n admits everything.)
+__device__ __forceinline__ float column_sum1(const float *e, int n, int nk, unsigned t_gt, int id_lt, SCShared &sh,
+                                             int &parity, int &count)
 {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     float s = 0.0f;
     unsigned c = 0;
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
+#pragma unroll 1
+    for (int k = 0; k < nk; ++k) {
         const int b = k * SC_THREADS + tid;
-        if (b < n && pred(__float_as_uint(e[k]), b)) { s = __fadd_rn(s, e[k]); ++c; }
+        if (b < n) {
+            const float v = e[b];
+            const unsigned x = __float_as_uint(v);
+            if (x > t_gt || (x == t_gt && b < id_lt)) { s = __fadd_rn(s, v); ++c; }
+        }
     }
     s = warp_sum(s);
     c = __reduce_add_sync(FULL, c);
@@ -470,7 +485,7 @@ __device__ __forceinline__ void rescore_block(const cqa_cache &c, const void *q,
 // Tier-2 dtype dispatch at run time: the re-score is a few warps of one role, the rest of the kernel does not
 // depend on the dtype.
 __device__ __noinline__ void rescore_block_any(const cqa_cache &c, const void *q, int q_dtype, int h, long bid,
-                                                  long n_scoring_tokens, float q_scale, float &s, float &lm)
+                                               long n_scoring_tokens, float q_scale, float &s, float &lm)
 {
     if (c.t2_dtype == CQA_BF16) rescore_block<__nv_bfloat16>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
     else if (c.t2_dtype == CQA_F16) rescore_block<__half>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
@@ -478,18 +493,17 @@ __device__ __noinline__ void rescore_block_any(const cqa_cache &c, const void *q
 }
 
 // Dynamic shared memory: A[n_arr] B[n_arr] C[n_pad] (floats; n_arr = max(n_pad, 2048)), cand[CAND] (u64), cum[CAND],
-// gsum, leaf, mask[n_pad] (bytes).  The full-sort fallback aliases its keys over B and C; the radix searches use B
-// (and A) as histograms.
-template <int VPT>
+// gsum, leaf, mask[n_pad] (bytes).  The full-sort fallback aliases its keys over A and B; the radix searches use the
+// array that is free at that point as their histogram.
 __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs &kn, const cqa_workspace &ws, const void *q,
                                              int q_dtype, long nq, long nact, const float *u, long u_ld, int n_pad, int hi,
                                              int base_width, int two_level, int rk, int phases, int role_base)
 {
     extern __shared__ __align__(16) unsigned char dsm[];
-    const int n_arr = n_pad > 2048 ? n_pad : 2048;             // A and B double as 2048-bin histograms
-    float *A = reinterpret_cast<float *>(dsm);                 // role 1: m_b
-    float *B = A + n_arr;                                      // role 1: block log-mass ell
-    float *C = B + n_arr;                                      // role 0: mass fractions
+    const int n_arr = n_pad > 2048 ? n_pad : 2048;
+    float *A = reinterpret_cast<float *>(dsm);                 // m_b; role 2 later: contributions mass * eta
+    float *B = A + n_arr;                                      // S_b; then mass / block log-mass / histogram
+    float *C = B + n_arr;                                      // uniforms or eta_b; then mass fractions / histogram
     u64 *cand = reinterpret_cast<u64 *>(C + n_pad);
     float *cum = reinterpret_cast<float *>(cand + CAND);
     float *gsum = cum + CAND;
@@ -507,21 +521,16 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv = h / c.gqa_group;
     const int n = (int)nq;
+    const int nk = (n + SC_THREADS - 1) / SC_THREADS;          // blocks per thread: b = k * 1024 + tid, k < nk
     // Plain layout: row h of an [H][ld] array.  Sharded layout: row h of rank r's slot in the all-gather buffer,
-    // [rank][row][chunk]; `gcol` maps a global block to its offset from the row start of rank 0.
+    // [rank][row][chunk]; global block b sits at rank r = min(b / stride, ranks - 1), column b - r * stride.
     const bool sharded_in = ws.shard_stride > 0;
     const long row_ld = sharded_in ? ws.shard_chunk : ws.ld;
     const float *mb = ws.m_b + (long)h * row_ld;
     const float *sb = ws.s_b + (long)h * row_ld;
-    // 32-bit arithmetic on purpose: the mapping runs once per block and thread, and a 64-bit division there costs
-    // more than everything else in the loop
+    // 32-bit arithmetic on purpose: the mapping runs once per block and thread
     const int sh_stride = sharded_in ? (int)ws.shard_stride : 1, sh_last = ws.shard_ranks - 1;
     const long sh_rank_stride = ws.shard_rank_stride;
-    auto gcol = [&](int b) -> long {
-        int r = b / sh_stride;
-        if (r > sh_last) r = sh_last;
-        return (long)r * sh_rank_stride + (b - r * sh_stride);
-    };
     float *mf = ws.mass_frac + (long)h * ws.ld;
     cqa_head_cert *ct = ws.cert + h;
     // Three independent roles per head run as separate CTAs (grid.y): 0 = selector, 1 = ranking /
@@ -533,106 +542,101 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     const bool have_int4 = c.values_int4_packed != nullptr && c.values_int4_errors != nullptr;
     int parity = 0;
 
-    // ---- one round of global loads: m_b, S_b; the exploration uniforms (role 0); eta_b and, when only
-    // certifying, the mass fractions (role 2)
+    // ---- the rows go from global to shared memory by 4-byte asynchronous copies, all in flight at once and none of
+    // them holding a register: A <- m_b, B <- S_b, C <- eta_b (role 2) or the exploration uniforms (role 0)
     const bool explore_on = role == 0 && kn.exploration_rate > 0.0f;
     const float *eta = have_int4 ? c.values_int4_errors + (long)kv * (sharded_in ? ws.shard_chunk : c.max_blocks) : nullptr;
-    int *hist = reinterpret_cast<int *>(B);   // 2048 bins; roles 0 and 2 do not keep block log-masses in B
-    float m[VPT], sv[VPT], x[VPT];
-    float mg = -INFINITY;
-    // The rows go from global to shared memory by 4-byte asynchronous copies, all in flight at once and none of
-    // them holding a register (a thread has 64 registers here, too few to keep two dozen loads pending); the
-    // values are then read from shared memory.  A <- m_b, B <- S_b, C <- eta_b or the exploration uniforms.
-    {
-        const float *xsrc = role == 2 ? eta : ((explore_on && u != nullptr) ? u + (long)h * u_ld : nullptr);
-        if (!sharded_in) {
-#pragma unroll
-            for (int k = 0; k < VPT; ++k) {
-                const int b = k * SC_THREADS + tid;
-                if (b < n) {
-                    cp_async4(A + b, mb + b);
-                    cp_async4(B + b, sb + b);
-                    if (xsrc) cp_async4(C + b, xsrc + b);
-                }
-            }
-        } else {
+    const bool frac_given = role == 2 && !fused;
+    const float *xsrc = role == 2 ? eta : ((explore_on && u != nullptr) ? u + (long)h * u_ld : nullptr);
 #pragma unroll 1
-            for (int k = 0; k < VPT; ++k) {
-                const int b = k * SC_THREADS + tid;
-                if (b < n) {
-                    const long gb = gcol(b);
-                    cp_async4(A + b, mb + gb);
-                    cp_async4(B + b, sb + gb);
-                    if (xsrc) cp_async4(C + b, xsrc + (role == 2 ? gb : (long)b));
-                }
-            }
-        }
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-        // each thread reads back only what it copied itself, so no barrier is needed here
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            const int b = k * SC_THREADS + tid;
-            const bool valid = b < n;
-            m[k] = valid ? A[b] : 0.0f;
-            sv[k] = valid ? fmaxf(B[b], 1e-30f) : 1.0f;
-            x[k] = (valid && xsrc) ? C[b] : 0.0f;
-        }
-        __syncthreads();   // A, B and C are reused below (histograms, block log-masses, mass fractions)
-    }
-    if (explore_on && u == nullptr) {
-        // in-kernel draw: one Philox call gives the eight 16-bit uniforms of blocks tid + 1024 * (8j .. 8j+7)
-#pragma unroll
-        for (int j = 0; j < (VPT + 7) / 8; ++j) {
-            const uint4 r = philox4(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)tid | ((unsigned)j << 10));
-            const unsigned wds[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                if (8 * j + i < VPT)
-                    x[8 * j + i] = (float)((wds[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu) * 1.52587890625e-05f;   // 2^-16
-        }
-    }
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
+    for (int k = 0; k < nk; ++k) {
         const int b = k * SC_THREADS + tid;
-        if (b < n_pad) {
-            unsigned char eb = 0;
-            if (b < n) {
-                if (explore_on && x[k] < kn.exploration_rate) eb = 2;
-                if (role == 1) {
-                    A[b] = m[k];
-                    B[b] = __fadd_rn(clog(sv[k]), m[k]);      // block log-mass: the boundary check needs it
-                }
-                mg = fmaxf(mg, m[k]);
+        if (b < n) {
+            long gb = b;
+            if (sharded_in) {
+                int r = b / sh_stride;
+                if (r > sh_last) r = sh_last;
+                gb = (long)r * sh_rank_stride + (b - r * sh_stride);
             }
-            if (role == 0) mask[b] = eb;                  // bit 1: exploration candidate, bit 0: selected (set later)
+            cp_async4(A + b, mb + gb);
+            // certifying only: the mass fractions were computed by the selector call and take the place of S_b
+            cp_async4(B + b, frac_given ? mf + b : sb + gb);
+            if (xsrc) cp_async4(C + b, xsrc + (role == 2 ? gb : (long)b));
         }
     }
-    float f[VPT];             // mass fractions (roles 0 and 2)
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    // each thread reads back only what it copied itself until the next barrier
+
+    // ---- per-block preparation: the head's largest m_b; exploration bits (role 0); block log-masses (role 1)
+    float mg = -INFINITY;
+    if (role == 0) {
+        if (explore_on && u == nullptr) {
+            // in-kernel draw: one Philox call gives the eight 16-bit uniforms of blocks tid + 1024 * (8j .. 8j+7)
+#pragma unroll 1
+            for (int j = 0; j * 8 < nk; ++j) {
+                const uint4 r = philox4(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)tid | ((unsigned)j << 10));
+                const unsigned wds[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int b = (8 * j + i) * SC_THREADS + tid;
+                    if (8 * j + i < nk && b < n)
+                        C[b] = (float)((wds[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu) * 1.52587890625e-05f;   // 2^-16
+                }
+            }
+        }
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
+            const int b = k * SC_THREADS + tid;
+            if (b < n_pad) {
+                unsigned char eb = 0;
+                if (b < n) {
+                    if (explore_on && C[b] < kn.exploration_rate) eb = 2;
+                    mg = fmaxf(mg, A[b]);
+                }
+                mask[b] = eb;                             // bit 1: exploration candidate, bit 0: selected (set later)
+            }
+        }
+    } else {
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
+            const int b = k * SC_THREADS + tid;
+            if (b < n) {
+                const float m = A[b];
+                mg = fmaxf(mg, m);
+                if (role == 1) B[b] = __fadd_rn(clog(fmaxf(B[b], 1e-30f)), m);   // block log-mass for the boundary check
+            }
+        }
+    }
     float total = 0.0f;
     if (compute_frac) {
-        // mass = S * exp(m - max m), fraction = mass * (1 / total): one exponential and one product per block
+        // mass = S * exp(m - max m) into B, fraction = mass * (1 / total): role 0 into C (and global memory),
+        // role 2 straight into the contributions
         mg = cta_max(mg, sh, parity);
-#pragma unroll
-        for (int k = 0; k < VPT; ++k)
-            f[k] = (k * SC_THREADS + tid) < n ? __fmul_rn(sv[k], cexp(__fsub_rn(m[k], mg))) : 0.0f;
-        total = fmaxf(cta_canonical_sum<VPT>(f, n, gsum, leaf), 1e-30f);
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
+            const int b = k * SC_THREADS + tid;
+            if (b < n) B[b] = __fmul_rn(fmaxf(B[b], 1e-30f), cexp(__fsub_rn(A[b], mg)));
+        }
+        total = fmaxf(cta_canonical_sum(B, n, nk, gsum, leaf), 1e-30f);
         const float inv_total = __fdiv_rn(1.0f, total);
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) {
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
             const int b = k * SC_THREADS + tid;
             if (b < n) {
-                f[k] = __fmul_rn(f[k], inv_total);
-                if (role == 0) { C[b] = f[k]; mf[b] = f[k]; }
+                const float f = __fmul_rn(B[b], inv_total);
+                if (role == 0) { C[b] = f; mf[b] = f; }
+                else A[b] = __fmul_rn(f, C[b]);           // role 2: contribution = mass fraction * eta_b
             }
         }
     } else if (role == 2) {
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) {
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
             const int b = k * SC_THREADS + tid;
-            f[k] = b < n ? mf[b] : 0.0f;
+            if (b < n) A[b] = __fmul_rn(B[b], C[b]);
         }
     }
+    __syncthreads();
 
     if (role == 0) {
         // the `hi` heaviest blocks, sorted
@@ -640,8 +644,7 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
         float *scum = ws.sorted_cumsum + (long)h * ws.sel_width;
         const bool narrow = hi <= CAND;
         if (narrow) {
-            __syncthreads();   // C is complete (the tie path of the search reads it)
-            select_top_sorted<VPT>(f, C, n, cand, hist, sh, parity);
+            select_top_sorted(C, n, nk, cand, reinterpret_cast<int *>(B), sh);
             if (tid < CAND) cum[tid] = key_val(cand[tid]);
             __syncthreads();
             if (tid == 0) {
@@ -649,6 +652,7 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
                 float run = 0.0f;
                 float4 *c4 = reinterpret_cast<float4 *>(cum);
                 float4 nxt = c4[0];
+#pragma unroll 1
                 for (int j0 = 0; j0 < hi; j0 += 4) {
                     float4 cur = nxt;
                     if (j0 + 4 < CAND) nxt = c4[(j0 >> 2) + 1];
@@ -667,9 +671,8 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
             if (tid < hi) scum[tid] = cum[tid];
         } else {
             // wide selections (k_max unset or very large): full sort, prefix sums straight to global memory
-            u64 *keys = reinterpret_cast<u64 *>(B);   // ell and the fractions are rebuilt below
-            __syncthreads();
-            for (int b = tid; b < n_pad; b += SC_THREADS) keys[b] = b < n ? make_key(mf[b], b) : 0ull;
+            u64 *keys = reinterpret_cast<u64 *>(A);   // m_b and the masses are not needed any more
+            for (int b = tid; b < n_pad; b += SC_THREADS) keys[b] = b < n ? make_key(C[b], b) : 0ull;
             __syncthreads();
             bitonic_sort_desc(keys, n_pad);
             if (tid == 0) {
@@ -748,6 +751,7 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
         unsigned char *tm = ws.topk_mask + (long)h * ws.ld;
         unsigned char *em = ws.explore_mask + (long)h * ws.ld;
         int explored = 0;
+#pragma unroll 1
         for (int b = tid; b < (int)nact; b += SC_THREADS) {
             unsigned char mk1 = 1, e = 0;
             if (b < n) {
@@ -764,7 +768,6 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
         if (tid == 0) ct->exploration_blocks = sh.counter;
         return;
     }
-    __syncthreads();
 
     // ---- ranking / boundary / score consistency
     const bool need_fp16 = (kn.ranking_fallback || kn.score_consistency) && n > 0;
@@ -788,10 +791,10 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
             }
         } else if (rk <= 4) {
             u64 t4[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-            for (int k = 0; k < VPT; ++k) {
+#pragma unroll 1
+            for (int k = 0; k < nk; ++k) {
                 const int b = k * SC_THREADS + tid;
-                if (b < n) insert4(t4, ((u64)orderable(m[k]) << 32) | (u64)(0xFFFFFFFFu - (unsigned)b));
+                if (b < n) insert4(t4, ((u64)orderable(A[b]) << 32) | (u64)(0xFFFFFFFFu - (unsigned)b));
             }
             u64 w4[4];
             warp_top4(t4, w4);
@@ -873,6 +876,7 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
             const float d = delta_bound_warp(c, q, q_dtype, h, sharded_in ? ws.shard_ranks : 1, ws.shard_rank_stride);
             if (lane == 0) s_delta = d;
         } else if (overlap && kn.ranking_fallback) {
+#pragma unroll 1
             for (int b = (warp - ub_first) * 32 + lane; b < n; b += ub_warps * 32) {
                 bool in_top = false;
                 for (int r = 0; r < rk; ++r) in_top |= (top_idx[r] == b);
@@ -995,23 +999,21 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     }
     if (role == 1) return;
 
-    // ---- Rung-2 value check
+    // ---- Rung-2 value check (A holds the contributions mass fraction * eta_b, C still holds eta_b)
     unsigned char *vm = ws.value_mask + (long)h * ws.ld;
     if (!have_int4) {
         for (int b = tid; b < (int)nact; b += SC_THREADS) vm[b] = 1;   // FP16-value cache: every block reads Tier 2
         if (tid == 0) { ct->e_pre = 0.0f; ct->e_val = 0.0f; ct->value_promoted_blocks = 0; }
         return;
     }
-    float e[VPT];             // contributions mass fraction * eta_b (+0 beyond n)
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) e[k] = (k * SC_THREADS + tid) < n ? __fmul_rn(f[k], x[k]) : 0.0f;
+    const float *e = A;
     // Greedy promotion, largest contribution first (ties: lower block id first): block b is promoted while the
     // column sum of the contributions ranked before it is below the excess.  That sum never decreases along the
     // ranking, so the promoted blocks are exactly those with contribution bits >= t0, where t0 is the largest
-    // threshold whose admitted set still sums to at least the excess; t0 is found two bits per step (no sort, no
-    // serial walk).  Exact ties at t0 are resolved the same way over the block id.
+    // threshold whose admitted set still sums to at least the excess (no sort, no serial walk).  Exact ties at t0
+    // are resolved the same way over the block id.
     int cnt = 0;
-    const float e_pre = column_sum1<VPT>(e, n, [](unsigned, int) { return true; }, sh, parity, cnt);
+    const float e_pre = column_sum1(e, n, nk, 0u, n, sh, parity, cnt);     // every entry
     const float excess = fmaxf(__fsub_rn(e_pre, kn.v_tolerance), 0.0f);
     float promoted = 0.0f;
     int n_prom = 0;
@@ -1029,20 +1031,24 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
             // bracket the excess does the search continue inside the bin (bits 19..0), otherwise it starts from the
             // top as if there had been no hint.  The result never depends on the approximation.
             float emax = 0.0f;
-#pragma unroll
-            for (int k = 0; k < VPT; ++k) emax = fmaxf(emax, e[k]);
+#pragma unroll 1
+            for (int k = 0; k < nk; ++k) {
+                const int b = k * SC_THREADS + tid;
+                if (b < n) emax = fmaxf(emax, e[b]);
+            }
             emax = cta_max(emax, sh, parity);
             if (emax > 0.0f && n > 64) {
-                int *hsum = reinterpret_cast<int *>(A);
+                int *hsum = reinterpret_cast<int *>(B);
                 hsum[2 * tid] = 0;
                 hsum[2 * tid + 1] = 0;
                 __syncthreads();
                 const float sc = __fdiv_rn(1073741824.0f, __fmul_rn((float)n, emax));     // 2^30 / (n * max)
-#pragma unroll
-                for (int k = 0; k < VPT; ++k) {
-                    const unsigned xb = __float_as_uint(e[k]);
-                    const int qv = (int)__fmul_rn(e[k], sc);
-                    hist_add(hsum, (k * SC_THREADS + tid) < n && qv > 0, xb >> 20, qv);
+#pragma unroll 1
+                for (int k = 0; k < nk; ++k) {
+                    const int b = k * SC_THREADS + tid;
+                    const float v = b < n ? e[b] : 0.0f;
+                    const int qv = (int)__fmul_rn(v, sc);
+                    hist_add(hsum, qv > 0, __float_as_uint(v) >> 20, qv);
                 }
                 __syncthreads();
                 const int need = max(1, (int)fminf(__fmul_rn(excess, sc), 1073741824.0f));
@@ -1058,7 +1064,7 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
                     const unsigned t_lo = (unsigned)d << 20, t_hi = (unsigned)(d + 1) << 20;
                     float fs[3];
                     int cs3[3];
-                    column_sums3<VPT>(e, t_lo, t_hi, 0xFFFFFFFFu, sh, parity, fs, cs3);
+                    column_sums3(e, n, nk, t_lo, t_hi, 0xFFFFFFFFu, sh, parity, fs, cs3);
                     if (fs[0] >= excess && fs[1] < excess) {
                         t0 = t_lo; cnt_lo = cs3[0]; f_lo = fs[0]; cnt_hi = cs3[1];
                         bit = 19;
@@ -1070,7 +1076,7 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
             for (; bit >= 0 && cnt_lo - cnt_hi > 1; --bit) {
                 const unsigned trial = t0 | (1u << bit);
                 int cc = 0;
-                const float fv = column_sum1<VPT>(e, n, [trial](unsigned bits, int) { return bits >= trial; }, sh, parity, cc);
+                const float fv = column_sum1(e, n, nk, trial - 1u, 0, sh, parity, cc);
                 if (fv >= excess) { t0 = trial; cnt_lo = cc; f_lo = fv; } else { cnt_hi = cc; }
             }
             promoted = f_lo;
@@ -1084,33 +1090,42 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
                     const int trial = i0 | (1 << bit2);
                     if (trial > n) continue;
                     int cc = 0;
-                    const unsigned tt = t0;
-                    const float g = column_sum1<VPT>(e, n, [tt, trial](unsigned bits, int b) { return bits > tt || (bits == tt && b < trial); }, sh, parity, cc);
+                    const float g = column_sum1(e, n, nk, t0, trial, sh, parity, cc);
                     if (g < excess) i0 = trial;
                 }
                 id_bound = i0 + 1;
-                const unsigned tt = t0;
-                const int ib = id_bound;
-                promoted = column_sum1<VPT>(e, n, [tt, ib](unsigned bits, int b) { return bits > tt || (bits == tt && b < ib); }, sh, parity, n_prom);
+                promoted = column_sum1(e, n, nk, t0, id_bound, sh, parity, n_prom);
             }
         }
     } else {
+        // loose mode: every block whose eta_b exceeds the tolerance
         const float vt = kn.v_tolerance;
-        unsigned up = 0;
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) up |= x[k] > vt ? 1u << k : 0u;
-        promoted = column_sum1<VPT>(e, n, [up, tid](unsigned, int b) { return ((up >> ((b - tid) / SC_THREADS)) & 1u) != 0; }, sh, parity, n_prom);
+        const int lane_ = tid & 31, w_ = tid >> 5;
+        float s = 0.0f;
+        unsigned cc = 0;
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
+            const int b = k * SC_THREADS + tid;
+            if (b < n && C[b] > vt) { s = __fadd_rn(s, e[b]); ++cc; }
+        }
+        s = warp_sum(s);
+        cc = __reduce_add_sync(FULL, cc);
+        if (lane_ == 0) { sh.red_f3[parity][0][w_] = s; sh.red_u[parity][0][w_] = cc; }
+        __syncthreads();
+        promoted = warp_sum(sh.red_f3[parity][0][lane_]);
+        n_prom = (int)__reduce_add_sync(FULL, sh.red_u[parity][0][lane_]);
+        parity ^= 1;
     }
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
+#pragma unroll 1
+    for (int k = 0; k < nk; ++k) {
         const int b = k * SC_THREADS + tid;
         if (b < n) {
             unsigned char upb;
             if (kn.value_mode_tight) {
-                const unsigned bits = __float_as_uint(e[k]);
+                const unsigned bits = __float_as_uint(e[b]);
                 upb = (t0 != 0xFFFFFFFFu && (bits > t0 || (bits == t0 && b < id_bound))) ? 1 : 0;
             } else {
-                upb = x[k] > kn.v_tolerance ? 1 : 0;
+                upb = C[b] > kn.v_tolerance ? 1 : 0;
             }
             vm[b] = upb;
         }
@@ -1125,13 +1140,12 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     }
 }
 
-template <int VPT>
 __global__ void __launch_bounds__(SC_THREADS, 1) selcert_kernel(cqa_cache c, cqa_knobs kn, cqa_workspace ws, const void *q,
                                                                 int q_dtype, long nq, long nact, const float *u, long u_ld,
                                                                 int n_pad, int hi, int base_width, int two_level, int rk,
                                                                 int phases, int role_base)
 {
-    selcert_body<VPT>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
+    selcert_body(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, n_pad, hi, base_width, two_level, rk, phases, role_base);
 }
 
 static __host__ __device__ inline int next_pow2(long n)
@@ -1166,7 +1180,6 @@ static __host__ __device__ inline SelPlan sel_plan(const cqa_knobs *kn, long nq)
 }
 
 // Sequence blockIdx.z of a batch: the fused selector + certifier (all three roles) with that sequence's sizes.
-template <int VPT>
 __global__ void __launch_bounds__(SC_THREADS, 1) selcert_batched_kernel(const cqa_batch_item *items, cqa_knobs kn, int q_dtype,
                                                                         int do_append)
 {
@@ -1174,7 +1187,7 @@ __global__ void __launch_bounds__(SC_THREADS, 1) selcert_batched_kernel(const cq
     const long num_tokens = it.pos + do_append;
     const long nq = num_tokens / BS, nact = (num_tokens + BS - 1) / BS;
     const SelPlan p = sel_plan(&kn, nq);
-    selcert_body<VPT>(it.cache, kn, it.ws, it.q, q_dtype, nq, nact, nullptr, 0, next_pow2(nq), p.hi, p.base_width, p.two_level,
+    selcert_body(it.cache, kn, it.ws, it.q, q_dtype, nq, nact, nullptr, 0, next_pow2(nq), p.hi, p.base_width, p.two_level,
                       p.rk, PH_SELECT | PH_CERTIFY | PH_FLAGS_CLEARED, 0);
 }
 
@@ -1222,7 +1235,6 @@ int selcert_check(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *
     return CQA_OK;
 }
 
-template <int VPT>
 static int selcert_launch_v(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, const void *q,
                             int q_dtype, long nq, long nact, const float *u, long u_ld, int phases, int n_pad,
                             cudaStream_t st)
@@ -1231,7 +1243,7 @@ static int selcert_launch_v(const cqa_cache *c, const cqa_knobs *kn, const cqa_w
     const SelPlan p = sel_plan(kn, nq);
     const size_t smem = selcert_smem(n_pad);
     static size_t granted[SMEM_ATTR_DEVICES] = {};
-    const int rc_attr = check_cuda(ensure_dynamic_smem(selcert_kernel<VPT>, smem, granted), "cudaFuncSetAttribute(selcert_kernel)");
+    const int rc_attr = check_cuda(ensure_dynamic_smem(selcert_kernel, smem, granted), "cudaFuncSetAttribute(selcert_kernel)");
     if (rc_attr) return rc_attr;
     if ((phases & PH_SELECT) && !(phases & PH_FLAGS_CLEARED)) {
         int rc = check_cuda(cudaMemsetAsync(ws->any_flags, 0, (5 + H) * sizeof(int32_t), st),
@@ -1245,7 +1257,7 @@ static int selcert_launch_v(const cqa_cache *c, const cqa_knobs *kn, const cqa_w
     dim3 grid((unsigned)H, (unsigned)n_roles);
     // chained to the score kernel only in the fused step (a memset precedes the launch otherwise)
     const bool chained = (phases & PH_FLAGS_CLEARED) != 0;
-    return check_cuda(launch_chained(selcert_kernel<VPT>, grid, dim3(SC_THREADS), smem, st, chained, *c, *kn, *ws, q, q_dtype,
+    return check_cuda(launch_chained(selcert_kernel, grid, dim3(SC_THREADS), smem, st, chained, *c, *kn, *ws, q, q_dtype,
                                      nq, nact, u, u_ld, n_pad, p.hi, p.base_width, p.two_level, p.rk, phases, role_base),
                       "selcert_kernel");
 }
@@ -1256,42 +1268,22 @@ int selcert_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace 
     const int rc = selcert_check(c, kn, ws, q, nq, phases);
     if (rc) return rc;
     const int n_pad = next_pow2(nq);
-    switch (n_pad / SC_THREADS) {
-    case 0:
-    case 1: return selcert_launch_v<1>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
-    case 2: return selcert_launch_v<2>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
-    case 4: return selcert_launch_v<4>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
-    case 8: return selcert_launch_v<8>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
-    default: return selcert_launch_v<16>(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
-    }
+    return selcert_launch_v(c, kn, ws, q, q_dtype, nq, nact, u, u_ld, phases, n_pad, st);
 }
 
-// The selector of a batch; `max_nq` = most quantised blocks of any sequence (sizes the threads' register arrays and
-// the shared memory), every item checked by the caller.
+// The selector of a batch; `max_nq` = most quantised blocks of any sequence (sizes the shared memory), every item checked by the caller.
 int selcert_batched_launch(const cqa_batch_item *items_dev, int n_items, int n_heads, long max_nq, const cqa_knobs *kn,
                            int q_dtype, int do_append, cudaStream_t st)
 {
     const int n_pad = next_pow2(max_nq);
     const size_t smem = selcert_smem(n_pad);
     dim3 grid((unsigned)n_heads, 3u, (unsigned)n_items);
-#define CQA_SEL_BATCH_CASE(V)                                                                                          \
-    {                                                                                                                  \
-        static size_t granted[SMEM_ATTR_DEVICES] = {};                                                                 \
-        const int rc = check_cuda(ensure_dynamic_smem(selcert_batched_kernel<V>, smem, granted),                       \
-                                  "cudaFuncSetAttribute(selcert_batched_kernel)");                                     \
-        if (rc) return rc;                                                                                             \
-        return check_cuda(launch_chained(selcert_batched_kernel<V>, grid, dim3(SC_THREADS), smem, st, true, items_dev, *kn, \
-                                         q_dtype, do_append), "selcert_batched_kernel");                               \
-    }
-    switch (n_pad / SC_THREADS) {
-    case 0:
-    case 1: CQA_SEL_BATCH_CASE(1)
-    case 2: CQA_SEL_BATCH_CASE(2)
-    case 4: CQA_SEL_BATCH_CASE(4)
-    case 8: CQA_SEL_BATCH_CASE(8)
-    default: CQA_SEL_BATCH_CASE(16)
-    }
-#undef CQA_SEL_BATCH_CASE
+    static size_t granted[SMEM_ATTR_DEVICES] = {};
+    const int rc = check_cuda(ensure_dynamic_smem(selcert_batched_kernel, smem, granted),
+                              "cudaFuncSetAttribute(selcert_batched_kernel)");
+    if (rc) return rc;
+    return check_cuda(launch_chained(selcert_batched_kernel, grid, dim3(SC_THREADS), smem, st, true, items_dev, *kn, q_dtype,
+                                     do_append), "selcert_batched_kernel");
 }
 
 int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq, long nact,
