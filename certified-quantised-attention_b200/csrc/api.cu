@@ -91,12 +91,12 @@ extern "C" const char *cqa_last_error(void) { return g_err; }
 extern "C" int cqa_wait_timeouts(int *count, int reset)
 {
     if (!count) { set_error("cqa_wait_timeouts: NULL pointer"); return CQA_ERR_INVALID; }
-    int a = 0;
-    if (score_wait_timeouts(&a, reset)) {
+    int a = 0, b = 0;
+    if (score_wait_timeouts(&a, reset) || selcert_wait_timeouts(&b, reset)) {
         set_error("cqa_wait_timeouts: could not read the device counters: %s", cudaGetErrorString(cudaGetLastError()));
         return CQA_ERR_CUDA;
     }
-    *count = a;
+    *count = a + b;
     return CQA_OK;
 }
 

@@ -487,5 +487,6 @@ int selcert_check(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *
 int attend_check(const cqa_cache *c, const cqa_workspace *ws, long nq, long nact, int last_valid);
 int append_check(const cqa_cache *c, const void *k_new, const void *v_new, int src_dtype, long pos);
 int score_wait_timeouts(int *count, int reset);
+int selcert_wait_timeouts(int *count, int reset);
 
 }  // namespace cqa

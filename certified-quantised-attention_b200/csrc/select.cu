@@ -515,6 +515,13 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     __shared__ float s_delta;
     __shared__ u64 s_top[SC_WARPS * 4];
 
+    __shared__ __align__(8) uint64_t row_bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&row_bar, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();   // before the wait on the previous kernel: this part overlaps its tail
+
     grid_dependency_wait();
     peer_wait(ws.wait_flags, ws.wait_n, ws.wait_skip, ws.wait_value, ws.wait_status, 1, ws.wait_spins);
 
@@ -542,16 +549,30 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     const bool have_int4 = c.values_int4_packed != nullptr && c.values_int4_errors != nullptr;
     int parity = 0;
 
-    // ---- the rows go from global to shared memory by 4-byte asynchronous copies, all in flight at once and none of
-    // them holding a register: A <- m_b, B <- S_b, C <- eta_b (role 2) or the exploration uniforms (role 0)
+    // ---- the rows go from global to shared memory without passing through registers:
+    // A <- m_b, B <- S_b, C <- eta_b (role 2) or the exploration uniforms (role 0)
     const bool explore_on = role == 0 && kn.exploration_rate > 0.0f;
     const float *eta = have_int4 ? c.values_int4_errors + (long)kv * (sharded_in ? ws.shard_chunk : c.max_blocks) : nullptr;
     const bool frac_given = role == 2 && !fused;
     const float *xsrc = role == 2 ? eta : ((explore_on && u != nullptr) ? u + (long)h * u_ld : nullptr);
+    // Plain rows that start on a 16-byte boundary are fetched by the bulk-copy engine: one thread issues three copies
+    // and every thread waits on the barrier they report to (bounded).  The last n % 4 blocks, rows of the sharded
+    // layout and unaligned rows go by 4-byte asynchronous copies, each thread copying the blocks it owns.
+    const float *bsrc = frac_given ? mf : sb;
+    const int n4 = n & ~3;
+    const bool bulk = !sharded_in && n4 > 0 &&
+                      (((uintptr_t)mb | (uintptr_t)bsrc | (uintptr_t)(xsrc ? xsrc : mb)) & 15u) == 0;
+    if (bulk && tid == 0) {
+        const unsigned bar = smem_u32(&row_bar), bytes = (unsigned)n4 * 4u;
+        mbar_arrive_expect_tx(bar, bytes * (xsrc ? 3u : 2u));
+        bulk_copy_g2s(smem_u32(A), mb, bytes, bar);
+        bulk_copy_g2s(smem_u32(B), bsrc, bytes, bar);
+        if (xsrc) bulk_copy_g2s(smem_u32(C), xsrc, bytes, bar);
+    }
 #pragma unroll 1
-    for (int k = 0; k < nk; ++k) {
+    for (int k = bulk ? n4 / SC_THREADS : 0; k < nk; ++k) {
         const int b = k * SC_THREADS + tid;
-        if (b < n) {
+        if (b < n && !(bulk && b < n4)) {
             long gb = b;
             if (sharded_in) {
                 int r = b / sh_stride;
@@ -566,6 +587,7 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    if (bulk) mbar_wait(smem_u32(&row_bar), 0u);
     // each thread reads back only what it copied itself until the next barrier
 
     // ---- per-block preparation: the head's largest m_b; exploration bits (role 0); block log-masses (role 1)
@@ -1285,6 +1307,8 @@ int selcert_batched_launch(const cqa_batch_item *items_dev, int n_items, int n_h
     return check_cuda(launch_chained(selcert_batched_kernel, grid, dim3(SC_THREADS), smem, st, true, items_dev, *kn, q_dtype,
                                      do_append), "selcert_batched_kernel");
 }
+
+int selcert_wait_timeouts(int *count, int reset) { return wait_timeouts_of_this_unit(count, reset); }
 
 int select_launch(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *ws, long nq, long nact,
                   const float *u, long u_ld, cudaStream_t st)
