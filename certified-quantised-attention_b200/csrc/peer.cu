@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(D) merge_wait_kernel(const float *parts, int n
                                                       const int32_t *flags, int skip, int value, int32_t *status,
                                                       int spins)
 {
+    grid_dependency_wait();   // this rank's own rows come from the attend kernel before it on the stream
     peer_wait(flags, n_parts, skip, value, status, 1, spins);
     const int h = blockIdx.x, ch = threadIdx.x;
     float M = -INFINITY;
@@ -268,7 +269,7 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
         sp.step = (int)step;
     }
     rc = score_blocks_launch(local, q, q_dtype, n_local, knobs->q_scale, xa_own, xa_own + (long)H * peers->chunk,
-                                 peers->chunk, wl->token_scores, st, nullptr, 0, push_meta ? nullptr : &sp);
+                                 peers->chunk, wl->token_scores, st, wg->any_flags, 5 + H, push_meta ? nullptr : &sp);
     if (rc) return rc;
     if (push_meta) {
         // eta rows and the row of scale maxima follow the 2H score rows; both parities get them
@@ -319,7 +320,7 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     cqa_cache gv = *global_view;
     gv.values_int4_errors = xa_par + 2L * H * peers->chunk;
     gv.sigma_max = xa_par + (2L * H + KV) * peers->chunk;
-    rc = selcert_launch(&gv, knobs, &g, q, q_dtype, nq_global, nact_global, nullptr, 0, 1 | 2 | 64, st);
+    rc = selcert_launch(&gv, knobs, &g, q, q_dtype, nq_global, nact_global, nullptr, 0, 1 | 2 | 16 | 64, st);
     if (rc) return rc;
     // 6. Phase 2 over the local blocks; un-normalised partial rows go to this rank's slot of xc
     cqa_workspace l = *wl;
@@ -340,9 +341,11 @@ extern "C" int cqa_sharded_layer_step(const cqa_cache *local, const cqa_cache *g
     l.peer_world = W;
     l.peer_rank = R;
     l.peer_step = (int)step;
-    rc = attend_launch(local, &l, q, q_dtype, n_local, nact_local, num_tokens_local, last_valid, knobs->q_scale, st, false);
+    rc = attend_launch(local, &l, q, q_dtype, n_local, nact_local, num_tokens_local, last_valid, knobs->q_scale, st, true);
     if (rc) return rc;
-    merge_wait_kernel<<<H, D, 0, st>>>(xc_par, W, H, out, own_i + L.flags + 2 * W, R, (int)step, own_i + L.status,
-                                       wg->wait_spins); note_launch();
-    return check_launch("sharded step kernels");
+    // the four kernels are chained by programmatic dependent launch, like the single-GPU step: each one is scheduled
+    // while the previous one drains and waits for it on the device (the score kernel cleared the certifier's flags)
+    return check_cuda(launch_chained(merge_wait_kernel, dim3(H), dim3(D), 0, st, true, (const float *)xc_par, W, H, out,
+                                     (const int32_t *)(own_i + L.flags + 2 * W), R, (int)step, own_i + L.status,
+                                     wg->wait_spins), "sharded step kernels");
 }

@@ -172,11 +172,6 @@ __device__ __forceinline__ void score_blocks_body(const cqa_cache &c, const void
                         const long o = (long)(kv * G + gg) * ld + b;
                         m_b[o] = mx;
                         s_b[o] = ssum;
-                        for (int p = 0; p < push.world; ++p) {
-                            if (p == push.rank) continue;
-                            push.mb[p][o] = mx;
-                            push.sb[p][o] = ssum;
-                        }
                     }
                 }
             }
@@ -186,6 +181,22 @@ __device__ __forceinline__ void score_blocks_body(const cqa_cache &c, const void
         ++use;
     }
     if (push.world > 0) {
+        // This CTA's results (G rows of b_end - b_begin consecutive blocks, for m_b and for S_b) go to the other ranks
+        // as runs of consecutive words, a warp storing 128 contiguous bytes at a time: a remote store of a single word
+        // costs a whole link packet, so the rows are not pushed from the scoring loop.  The values are read back
+        // from this GPU's L2 after the CTA barrier.
+        __syncthreads();
+        const int nb = (int)(b_end - b_begin);
+        if (nb > 0) {
+            for (int i = threadIdx.x; i < 2 * G * nb; i += SCORE_WARPS * 32) {
+                const int row = i / nb, col = i - row * nb;              // rows 0..G-1: m_b, G..2G-1: S_b
+                const int gg = row < G ? row : row - G;
+                const long o = (long)(kv * G + gg) * ld + b_begin + col;
+                const float v = __ldcg((row < G ? m_b : s_b) + o);
+                for (int p = 0; p < push.world; ++p)
+                    if (p != push.rank) (row < G ? push.mb[p] : push.sb[p])[o] = v;
+            }
+        }
         // the last CTA of the grid tells every rank that this rank's rows have landed
         __syncthreads();
         if (threadIdx.x == 0) {

@@ -388,9 +388,9 @@ __device__ __forceinline__ void insert4(u64 (&t)[4], u64 k)
 }
 // The four largest keys held by a warp, given one descending 4-list per lane (keys distinct, zero is
 // padding): four rounds of a warp-wide maximum over the list heads; the lane that wins pops its list.
-__device__ __noinline__ void warp_top4(u64 (&t)[4], u64 (&out)[4])
+__device__ __forceinline__ void warp_top4(u64 (&t)[4], u64 (&out)[4])
 {
-#pragma unroll 1
+#pragma unroll
     for (int r = 0; r < 4; ++r) {
         u64 best = t[0];
 #pragma unroll
@@ -522,9 +522,6 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     }
     __syncthreads();   // before the wait on the previous kernel: this part overlaps its tail
 
-    grid_dependency_wait();
-    peer_wait(ws.wait_flags, ws.wait_n, ws.wait_skip, ws.wait_value, ws.wait_status, 1, ws.wait_spins);
-
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv = h / c.gqa_group;
     const int n = (int)nq;
@@ -555,19 +552,54 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     const float *eta = have_int4 ? c.values_int4_errors + (long)kv * (sharded_in ? ws.shard_chunk : c.max_blocks) : nullptr;
     const bool frac_given = role == 2 && !fused;
     const float *xsrc = role == 2 ? eta : ((explore_on && u != nullptr) ? u + (long)h * u_ld : nullptr);
-    // Plain rows that start on a 16-byte boundary are fetched by the bulk-copy engine: one thread issues three copies
-    // and every thread waits on the barrier they report to (bounded).  The last n % 4 blocks, rows of the sharded
-    // layout and unaligned rows go by 4-byte asynchronous copies, each thread copying the blocks it owns.
+    // Rows that start on a 16-byte boundary are fetched by the bulk-copy engine: one thread issues the copies (one
+    // per array, or one per array and rank in the sharded layout, whose per-rank pieces are contiguous) and every
+    // thread waits on the barrier they report to (bounded).  The last n % 4 blocks and unaligned rows go by 4-byte
+    // asynchronous copies, each thread copying the blocks it owns.
     const float *bsrc = frac_given ? mf : sb;
     const int n4 = n & ~3;
-    const bool bulk = !sharded_in && n4 > 0 &&
+    const int nseg = sharded_in ? ws.shard_ranks : 1;
+    const int last_first = (nseg - 1) * sh_stride;             // first block of the last piece
+    const bool pieces_ok = !sharded_in || (((sh_stride | (int)(sh_rank_stride & 0x7fffffff)) & 3) == 0 && n > last_first);
+    const bool bulk = pieces_ok && n4 > 0 &&
                       (((uintptr_t)mb | (uintptr_t)bsrc | (uintptr_t)(xsrc ? xsrc : mb)) & 15u) == 0;
+    // Still nothing of the previous kernel has been read: the exploration bits depend on the seed alone and are drawn
+    // while that kernel drains.  One Philox call gives the eight 16-bit uniforms of blocks tid + 1024 * (8j .. 8j+7).
+    const bool drawn = explore_on && u == nullptr;
+    if (drawn) {
+        const int nkp = n_pad > SC_THREADS ? n_pad / SC_THREADS : 1;
+#pragma unroll 1
+        for (int j = 0; j * 8 < nkp; ++j) {
+            const uint4 r = philox4(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)tid | ((unsigned)j << 10));
+            const unsigned wds[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int b = (8 * j + i) * SC_THREADS + tid;
+                if (8 * j + i < nkp && b < n_pad) {
+                    const float uni = (float)((wds[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu) * 1.52587890625e-05f;   // 2^-16
+                    mask[b] = (b < n && uni < kn.exploration_rate) ? 2 : 0;   // bit 1: exploration candidate
+                }
+            }
+        }
+    }
+
+    grid_dependency_wait();
+    peer_wait(ws.wait_flags, ws.wait_n, ws.wait_skip, ws.wait_value, ws.wait_status, 1, ws.wait_spins);
+
     if (bulk && tid == 0) {
-        const unsigned bar = smem_u32(&row_bar), bytes = (unsigned)n4 * 4u;
-        mbar_arrive_expect_tx(bar, bytes * (xsrc ? 3u : 2u));
-        bulk_copy_g2s(smem_u32(A), mb, bytes, bar);
-        bulk_copy_g2s(smem_u32(B), bsrc, bytes, bar);
-        if (xsrc) bulk_copy_g2s(smem_u32(C), xsrc, bytes, bar);
+        const unsigned bar = smem_u32(&row_bar);
+        mbar_arrive_expect_tx(bar, (unsigned)n4 * 4u * (xsrc ? 3u : 2u));
+#pragma unroll 1
+        for (int r = 0; r < nseg; ++r) {
+            const int first = r * sh_stride;
+            const int cnt = (r == nseg - 1 ? n4 : first + sh_stride) - first;     // blocks of this piece, a multiple of 4
+            if (cnt <= 0) continue;
+            const long go = sharded_in ? (long)r * sh_rank_stride : 0;
+            const unsigned bytes = (unsigned)cnt * 4u;
+            bulk_copy_g2s(smem_u32(A + first), mb + go, bytes, bar);
+            bulk_copy_g2s(smem_u32(B + first), frac_given ? mf + first : sb + go, bytes, bar);
+            if (xsrc) bulk_copy_g2s(smem_u32(C + first), role == 2 ? xsrc + go : xsrc + first, bytes, bar);
+        }
     }
 #pragma unroll 1
     for (int k = bulk ? n4 / SC_THREADS : 0; k < nk; ++k) {
@@ -593,30 +625,13 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     // ---- per-block preparation: the head's largest m_b; exploration bits (role 0); block log-masses (role 1)
     float mg = -INFINITY;
     if (role == 0) {
-        if (explore_on && u == nullptr) {
-            // in-kernel draw: one Philox call gives the eight 16-bit uniforms of blocks tid + 1024 * (8j .. 8j+7)
-#pragma unroll 1
-            for (int j = 0; j * 8 < nk; ++j) {
-                const uint4 r = philox4(ws.rng_seed, ws.rng_offset, (unsigned)h, (unsigned)tid | ((unsigned)j << 10));
-                const unsigned wds[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int b = (8 * j + i) * SC_THREADS + tid;
-                    if (8 * j + i < nk && b < n)
-                        C[b] = (float)((wds[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu) * 1.52587890625e-05f;   // 2^-16
-                }
-            }
-        }
 #pragma unroll 1
         for (int k = 0; k < nk; ++k) {
             const int b = k * SC_THREADS + tid;
             if (b < n_pad) {
-                unsigned char eb = 0;
-                if (b < n) {
-                    if (explore_on && C[b] < kn.exploration_rate) eb = 2;
-                    mg = fmaxf(mg, A[b]);
-                }
-                mask[b] = eb;                             // bit 1: exploration candidate, bit 0: selected (set later)
+                if (!drawn)   // bit 1: exploration candidate (uniforms given by the caller), bit 0: selected (set later)
+                    mask[b] = (explore_on && b < n && C[b] < kn.exploration_rate) ? 2 : 0;
+                if (b < n) mg = fmaxf(mg, A[b]);
             }
         }
     } else {
@@ -670,20 +685,24 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
             if (tid < CAND) cum[tid] = key_val(cand[tid]);
             __syncthreads();
             if (tid == 0) {
-                // sequential prefix sum in place, four values per shared-memory access
+                // sequential prefix sum in place; 32 values are fetched at a time so that only the additions are serial
                 float run = 0.0f;
                 float4 *c4 = reinterpret_cast<float4 *>(cum);
-                float4 nxt = c4[0];
 #pragma unroll 1
-                for (int j0 = 0; j0 < hi; j0 += 4) {
-                    float4 cur = nxt;
-                    if (j0 + 4 < CAND) nxt = c4[(j0 >> 2) + 1];
-                    cur.x = j0 == 0 ? cur.x : __fadd_rn(run, cur.x);
-                    cur.y = __fadd_rn(cur.x, cur.y);
-                    cur.z = __fadd_rn(cur.y, cur.z);
-                    cur.w = __fadd_rn(cur.z, cur.w);
-                    run = cur.w;
-                    c4[j0 >> 2] = cur;
+                for (int j0 = 0; j0 < hi; j0 += 32) {
+                    float4 v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = c4[(j0 >> 2) + i];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        v[i].x = (j0 == 0 && i == 0) ? v[i].x : __fadd_rn(run, v[i].x);
+                        v[i].y = __fadd_rn(v[i].x, v[i].y);
+                        v[i].z = __fadd_rn(v[i].y, v[i].z);
+                        v[i].w = __fadd_rn(v[i].z, v[i].w);
+                        run = v[i].w;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) c4[(j0 >> 2) + i] = v[i];
                 }
             } else if (tid >= 32 && tid < 32 + CAND) {
                 const int j = tid - 32;

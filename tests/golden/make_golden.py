@@ -68,6 +68,11 @@ CASES = {
         seed=21, n_tokens=8192, kv_heads=8, gqa_group=4, dtype="bfloat16",
         planted=32, appends=0, call_after=[0], knobs={},
     ),
+    # the 32K workload bench.py measures as its second configuration (seed 2, 64 planted blocks, bf16)
+    "planted_32k_bf16": dict(
+        seed=2, n_tokens=32768, kv_heads=8, gqa_group=4, dtype="bfloat16",
+        planted=64, appends=0, call_after=[0], knobs={},
+    ),
 }
 
 TORCH_DTYPE = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}

@@ -226,6 +226,9 @@ def test_sharded_step_matches_unsharded(world, knobs):
 
 # ----------------------------------------------------------------------------- CUDA, real ranks over NCCL
 
+NCCL_STEPS = 24     # crosses a block completion (step 16): the eta rows and scale maxima are exchanged again there
+
+
 def _nccl_rank(rank, world, port, ret, exchange="collective"):
     import sys
     from pathlib import Path
@@ -254,7 +257,7 @@ def _nccl_rank(rank, world, port, ret, exchange="collective"):
             layer = ShardedCertifiedLayer(plan, cache, G, exchange=exchange)
             rng = np.random.default_rng(33)
             outs, ks = [], []
-            for s in range(4):
+            for s in range(NCCL_STEPS):
                 q, knew, vnew = synth.decode_step_inputs(base, s, dtype=dtype)
                 layer.append_token(hz.to_dev(knew, dtype).cuda(rank), hz.to_dev(vnew, dtype).cuda(rank))
                 u = rng.random((H, layer.nq), dtype=np.float32)
@@ -286,20 +289,24 @@ def test_sharded_step_over_nccl(exchange):
         pytest.skip("needs two GPUs")
     world = 4 if n_gpus >= 4 else 2
     ctx = mp.get_context("spawn")
-    ret = ctx.SimpleQueue()
+    ret = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, ret, exchange)) for r in range(world)]
     for p in procs:
         p.start()
-    outs, ks = ret.get()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
+    try:
+        outs, ks = ret.get(timeout=600)      # a rank that died leaves the queue empty: fail, do not hang
+    finally:
+        for p in procs:
+            p.join(timeout=300)
+            if p.is_alive():
+                p.kill()
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     dtype = "bfloat16"
     base = synth.make_layer_inputs(33, 16384, dtype=dtype, n_planted_blocks=16)
     cc = hz.make_cuda_cache(base.k, base.v, dtype, 64)
     rng = np.random.default_rng(33)
-    for s in range(4):
+    for s in range(NCCL_STEPS):
         q, knew, vnew = synth.decode_step_inputs(base, s, dtype=dtype)
         cc.append_token(hz.to_dev(knew, dtype), hz.to_dev(vnew, dtype))
         u = rng.random((H, cc.num_quantized_blocks), dtype=np.float32)
