@@ -25,7 +25,7 @@ SYMBOLS = [
     "cqa_peer_buffer_bytes", "cqa_peer_alloc", "cqa_peer_free", "cqa_peer_export", "cqa_peer_import", "cqa_peer_close",
     "cqa_sharded_layer_step", "cqa_peer_status",
     "cqa_hot_tier_ensure", "cqa_page_in_blocks", "cqa_page_in_by_slots", "cqa_dense_attend",
-    "cqa_launch_count", "cqa_wait_timeouts", "cqa_layer_step_batched",
+    "cqa_launch_count", "cqa_wait_timeouts", "cqa_layer_step_batched", "cqa_prefill_encode",
 ]
 PARTIAL_STRIDE = 130
 
@@ -131,6 +131,13 @@ class CqaBatchItem(C.Structure):
     ]
 
 
+class CqaPrefillItem(C.Structure):
+    _fields_ = [
+        ("cache", CqaCache), ("k_src", vp), ("v_src", vp), ("src_rows", C.c_int64), ("n_tokens", C.c_int64),
+        ("defer_int4", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 CERT_BYTES = C.sizeof(CqaHeadCert)
 
 _lib = None
@@ -195,6 +202,7 @@ def lib() -> C.CDLL:
     for s in SYMBOLS[2:]:
         getattr(L, s).restype = C.c_int
     L.cqa_peer_buffer_bytes.restype = C.c_int64
+    L.cqa_prefill_encode.argtypes = [C.POINTER(CqaPrefillItem), i32, i32, vp]
     L.cqa_layer_step_batched.argtypes = [C.POINTER(CqaBatchItem), i32, vp, pk, i32, i32, vp]
     L.cqa_wait_timeouts.argtypes = [C.POINTER(C.c_int), i32]
     L.cqa_launch_count.argtypes = [i32]

@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(128) quantize_blocks_kernel(cqa_cache c, const
 // Fused append-and-quantise of one token.  Grid: KV CTAs of 128 threads.
 template <typename T2>
 __device__ __forceinline__ void append_token_body(const cqa_cache &c, const void *k_new, const void *v_new, int src_dtype,
-                                                  long pos, int defer_int4)
+                                                  long pos, int defer_int4, long kv_stride = D, long tok_off = 0)
 {
     __shared__ BlockQuantSmem sm;
     __shared__ float s_v[D];
@@ -214,8 +214,8 @@ __device__ __forceinline__ void append_token_body(const cqa_cache &c, const void
     if (c.key_slots) { int s = c.key_slots[blk]; krow = s < 0 ? -1 : (long)s * BS + pib; }
     if (c.value_slots) { int s = c.value_slots[blk]; vrow = s < 0 ? -1 : (long)s * BS + pib; }
 
-    T2 kq = Cvt<T2>::from_f(load_q(k_new, src_dtype, (long)kv * D + tid));
-    T2 vq = Cvt<T2>::from_f(load_q(v_new, src_dtype, (long)kv * D + tid));
+    T2 kq = Cvt<T2>::from_f(load_q(k_new, src_dtype, (long)kv * kv_stride + tok_off + tid));
+    T2 vq = Cvt<T2>::from_f(load_q(v_new, src_dtype, (long)kv * kv_stride + tok_off + tid));
     T2 *kt2 = reinterpret_cast<T2 *>(c.keys_t2);
     T2 *vt2 = reinterpret_cast<T2 *>(c.values_t2);
     if (kt2 && krow >= 0) kt2[((long)kv * c.keys_t2_rows + krow) * D + tid] = kq;
@@ -292,6 +292,19 @@ __global__ void __launch_bounds__(128) append_token_kernel(cqa_cache c, const vo
                                                           int src_dtype, long pos, int defer_int4)
 {
     append_token_body<T2>(c, k_new, v_new, src_dtype, pos, defer_int4);
+}
+
+// The ragged tail of a prefill: tokens [first_pos, first_pos + n_tail) of a [KV][src_rows][128] source, appended one
+// after the other by the CTA of their KV head (the per-block running maxima and error sums are read-modify-write, so
+// the tokens of one head stay in order; different heads share nothing).
+template <typename T2>
+__global__ void __launch_bounds__(128) append_tail_kernel(cqa_cache c, const void *k_src, const void *v_src, int src_dtype,
+                                                         long src_rows, long first_pos, int n_tail, int defer_int4)
+{
+    for (int t = 0; t < n_tail; ++t) {
+        append_token_body<T2>(c, k_src, v_src, src_dtype, first_pos + t, defer_int4, src_rows * D, (first_pos + t) * D);
+        __syncthreads();   // the staging arrays of the body are reused by the next token
+    }
 }
 
 // One token for every sequence of a batch: grid (KV, sequences).
@@ -448,6 +461,54 @@ extern "C" int cqa_append_token(const cqa_cache *c, const void *k_new, const voi
     default: set_error("cqa_append_token: unknown Tier-2 dtype %d", c->t2_dtype); return CQA_ERR_INVALID;
     }
     return rc;
+}
+
+extern "C" int cqa_prefill_encode(const cqa_prefill_item *items, int n_items, int src_dtype, void *stream)
+{
+    if (!items || n_items <= 0) { set_error("cqa_prefill_encode: no items"); return CQA_ERR_INVALID; }
+    if (src_dtype < 0 || src_dtype > 2) { set_error("cqa_prefill_encode: unknown dtype %d", src_dtype); return CQA_ERR_INVALID; }
+    // every check before the first launch
+    for (int i = 0; i < n_items; ++i) {
+        const cqa_prefill_item &it = items[i];
+        int rc = valid_cache(&it.cache);
+        if (rc) return rc;
+        if (!it.k_src || !it.v_src || it.n_tokens < 0 || it.src_rows < it.n_tokens) {
+            set_error("cqa_prefill_encode: item %d: bad source (%ld tokens in %ld rows)", i, (long)it.n_tokens, (long)it.src_rows);
+            return CQA_ERR_INVALID;
+        }
+        const long nblk = (it.n_tokens + BS - 1) / BS;
+        if (it.n_tokens > it.cache.cap_tokens || nblk > it.cache.max_blocks) {
+            set_error("cqa_prefill_encode: item %d: %ld tokens exceed the cache capacity %ld", i, (long)it.n_tokens,
+                      (long)it.cache.cap_tokens);
+            return CQA_ERR_TOO_LARGE;
+        }
+        if ((it.cache.keys_t2 || it.cache.values_t2) && src_dtype != it.cache.t2_dtype) {
+            set_error("cqa_prefill_encode: item %d: source dtype %d must equal the cache's Tier-2 dtype %d", i, src_dtype,
+                      it.cache.t2_dtype);
+            return CQA_ERR_UNSUPPORTED;
+        }
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    for (int i = 0; i < n_items; ++i) {
+        const cqa_prefill_item &it = items[i];
+        const long full = it.n_tokens / BS;
+        const int tail = (int)(it.n_tokens - full * BS);
+        if (full > 0) {
+            int rc = cqa_quantize_blocks(&it.cache, it.k_src, it.v_src, src_dtype, it.src_rows, 0, full, stream);
+            if (rc) return rc;
+        }
+        if (tail > 0) {
+            const cqa_cache *c = &it.cache;
+            int rc;
+            switch (c->t2_dtype) {
+            case CQA_F32: rc = check_cuda(launch_chained(append_tail_kernel<float>, dim3(c->kv_heads), dim3(128), 0, st, false, *c, it.k_src, it.v_src, src_dtype, (long)it.src_rows, full * BS, tail, (int)it.defer_int4), "append_tail_kernel"); break;
+            case CQA_F16: rc = check_cuda(launch_chained(append_tail_kernel<__half>, dim3(c->kv_heads), dim3(128), 0, st, false, *c, it.k_src, it.v_src, src_dtype, (long)it.src_rows, full * BS, tail, (int)it.defer_int4), "append_tail_kernel"); break;
+            default: rc = check_cuda(launch_chained(append_tail_kernel<__nv_bfloat16>, dim3(c->kv_heads), dim3(128), 0, st, false, *c, it.k_src, it.v_src, src_dtype, (long)it.src_rows, full * BS, tail, (int)it.defer_int4), "append_tail_kernel"); break;
+            }
+            if (rc) return rc;
+        }
+    }
+    return CQA_OK;
 }
 
 extern "C" int cqa_int4_quantise(const void *x, int src_dtype, int64_t T, uint8_t *packed, uint16_t *scales,

@@ -248,8 +248,9 @@ class TieredKeyCacheLayer:
     @classmethod
     def from_fp16_cache(cls, keys_fp16: torch.Tensor, values_fp16: torch.Tensor, block_size: int = 16,
                         max_pagein_blocks: int = 64, max_new_tokens: int = 512,
-                        fp16_key_cache_capacity: int | None = None) -> "TieredKeyCacheLayer":
-        """INT8 keys + model-dtype values (reference: tiered_kv_cache.py:135-286)."""
+                        fp16_key_cache_capacity: int | None = None, _encode: bool = True) -> "TieredKeyCacheLayer":
+        """INT8 keys + model-dtype values (reference: tiered_kv_cache.py:135-286).  `_encode=False` only allocates
+        (the whole-model constructors encode every layer in one library call afterwards)."""
         self = cls._allocate(keys_fp16, values_fp16, block_size, max_pagein_blocks, max_new_tokens,
                              int4=False, group_size=16)
         cap = cls._check_capacity(fp16_key_cache_capacity, self.keys_scale.shape[1], "fp16_key_cache_capacity")
@@ -257,7 +258,8 @@ class TieredKeyCacheLayer:
             raise NotImplementedError(
                 "a bounded FP16-key scratch is built for the INT4-value cache (from_fp16_cache_int4v) only; "
                 "pass None or a capacity that covers the reserved context")
-        self._quantize_prefill(keys_fp16, values_fp16)
+        if _encode:
+            self._quantize_prefill(keys_fp16, values_fp16)
         if cap is not None:
             self.fp16_key_cache_capacity = cap
             self.static_resident_key_cache = True
@@ -269,8 +271,9 @@ class TieredKeyCacheLayer:
                               group_size: int = 16, max_pagein_blocks: int = 64, max_new_tokens: int = 512,
                               fp16_key_cache_capacity: int | None = None,
                               fp16_value_cache_capacity: int | None = None,
-                              defer_int4_append_quantization: bool = False) -> "TieredKeyCacheLayer":
-        """INT8 keys + INT4 g16 values (reference: tiered_kv_cache.py:289-405)."""
+                              defer_int4_append_quantization: bool = False,
+                              _encode: bool = True) -> "TieredKeyCacheLayer":
+        """INT8 keys + INT4 g16 values (reference: tiered_kv_cache.py:289-405).  `_encode=False` only allocates."""
         nb0 = keys_fp16.shape[1] // BLOCK
         maxblk = nb0 + (max_new_tokens + BLOCK - 1) // BLOCK
         kcap = cls._check_capacity(fp16_key_cache_capacity, maxblk, "fp16_key_cache_capacity")
@@ -286,12 +289,14 @@ class TieredKeyCacheLayer:
                              int4=True, group_size=group_size, hot_blocks=hot_blocks)
         if bounded:
             self.defer_int4_append_quantization = bool(defer_int4_append_quantization)
-            self._quantize_prefill(keys_fp16, values_fp16)
+            if _encode:
+                self._quantize_prefill(keys_fp16, values_fp16)
             self._fp16_key_resident = OrderedDict()
             self._fp16_value_resident = OrderedDict()
             return self
         self.defer_int4_append_quantization = bool(defer_int4_append_quantization)
-        self._quantize_prefill(keys_fp16, values_fp16)
+        if _encode:
+            self._quantize_prefill(keys_fp16, values_fp16)
         if kcap is not None:
             self.fp16_key_cache_capacity = kcap
             self.static_resident_key_cache = True
@@ -326,11 +331,7 @@ class TieredKeyCacheLayer:
             k = k.contiguous()
         if not v.is_contiguous():
             v = v.contiguous()
-        defer = bool(
-            self.defer_int4_append_quantization
-            and self.values_fp16_gpu is not None
-            and (self.fp16_value_cache_capacity is None or self.static_resident_value_cache)
-        )
+        defer = self._defer_int4_flag()
         dev = k.device
         with _lib.on_device(dev):
             rc = _lib.lib().cqa_append_token(
@@ -404,6 +405,14 @@ class TieredKeyCacheLayer:
         return self._ensure_resident(1, block_ids)
 
     def _defers_int4(self) -> bool:
+        return bool(
+            self.defer_int4_append_quantization
+            and self.values_fp16_gpu is not None
+            and (self.fp16_value_cache_capacity is None or self.static_resident_value_cache)
+        )
+
+    def _defer_int4_flag(self) -> bool:
+        """INT4 quantisation of appended values waits for block completion (reference: tiered_kv_cache.py:947-952)."""
         return bool(
             self.defer_int4_append_quantization
             and self.values_fp16_gpu is not None
@@ -527,10 +536,41 @@ def _layer_kv(past_kv, layer_id: int):
     return past_kv[layer_id][0][0], past_kv[layer_id][1][0]
 
 
-def _poison_padding(cache: TieredKeyCacheLayer) -> None:
-    at, nt = cache.aligned_tokens, cache.num_tokens
-    if at > nt:
-        cache.keys_int8[:, nt:at, :] = -127
+def _encode_prefill_layers(entries) -> None:
+    """entries: (cache, keys [KV, seq, 128], values, seq_len) per layer, caches allocated but empty.  One library
+    call per (device, dtype) group quantises every layer's complete blocks straight from the prefill tensors and
+    appends each ragged remainder with one launch (reference: the per-layer, per-token loop of
+    tiered_kv_cache.py:1579-1701)."""
+    groups: dict = {}
+    for cache, keys, values, seq_len in entries:
+        if values.dtype != keys.dtype:
+            values = values.to(keys.dtype)
+        # rows of 128 contiguous elements with one row stride per KV head are read in place (a slice of a longer
+        # [KV, rows, 128] buffer, as HF caches hand out); anything else is copied once
+        def row_stride(t):
+            ok = t.stride(2) == 1 and t.stride(1) == HEAD_DIM and t.stride(0) % HEAD_DIM == 0
+            return t.stride(0) // HEAD_DIM if ok and t.stride(0) >= t.shape[1] * HEAD_DIM else None
+        rk, rv = row_stride(keys), row_stride(values)
+        if rk is None or rk != rv:
+            keys, values = keys.contiguous(), values.contiguous()
+            rk = keys.shape[1]
+        groups.setdefault((keys.device, keys.dtype), []).append((cache, keys, values, seq_len, rk))
+    for (dev, dtype), group in groups.items():
+        items = (_lib.CqaPrefillItem * len(group))()
+        for i, (cache, keys, values, seq_len, rows) in enumerate(group):
+            items[i].cache = cache._desc()
+            items[i].k_src = keys.data_ptr()
+            items[i].v_src = values.data_ptr()
+            items[i].src_rows = rows
+            items[i].n_tokens = seq_len
+            items[i].defer_int4 = 1 if cache._defer_int4_flag() else 0
+        with _lib.on_device(dev):
+            rc = _lib.lib().cqa_prefill_encode(items, len(group), _lib.dtype_code(dtype), _lib.current_stream(dev))
+        _lib.check(rc, "cqa_prefill_encode")
+        for cache, _k, _v, seq_len, _rows in group:
+            cache.num_tokens = seq_len
+            cache.num_blocks = (seq_len + BLOCK - 1) // BLOCK
+            cache.num_quantized_blocks = seq_len // BLOCK
 
 
 def create_tiered_cache_int4v_from_model(past_kv, layer_ids: list, block_size: int = 16, group_size: int = 16,
@@ -539,44 +579,45 @@ def create_tiered_cache_int4v_from_model(past_kv, layer_ids: list, block_size: i
                                          fp16_value_cache_capacity: int | None = None,
                                          defer_int4_append_quantization: bool | None = None) -> dict:
     """Per-layer INT8K/INT4V caches from HF past_key_values
-    (reference: tiered_kv_cache.py:1579-1641)."""
+    (reference: tiered_kv_cache.py:1579-1641).  Every layer is allocated first, then all of them are encoded by one
+    library call, ragged remainders included."""
     if defer_int4_append_quantization is None:
         defer_int4_append_quantization = fp16_value_cache_capacity is None
-    caches = {}
+    caches, entries = {}, []
     for layer_id in layer_ids:
         keys, values = _layer_kv(past_kv, layer_id)
         seq_len = keys.shape[1]
         aligned = (seq_len // block_size) * block_size
         cache = TieredKeyCacheLayer.from_fp16_cache_int4v(
-            keys[:, :aligned, :].contiguous(), values[:, :aligned, :].contiguous(),
+            keys[:, :aligned, :], values[:, :aligned, :],
             block_size=block_size, group_size=group_size,
             max_new_tokens=max_new_tokens + (seq_len - aligned),
             fp16_key_cache_capacity=fp16_key_cache_capacity,
             fp16_value_cache_capacity=fp16_value_cache_capacity,
-            defer_int4_append_quantization=bool(defer_int4_append_quantization),
+            defer_int4_append_quantization=bool(defer_int4_append_quantization), _encode=False,
         )
-        for t in range(aligned, seq_len):
-            cache.append_token(keys[:, t:t + 1, :], values[:, t:t + 1, :])
-        _poison_padding(cache)
+        cache.num_tokens = cache.num_blocks = cache.num_quantized_blocks = 0
+        entries.append((cache, keys, values, seq_len))
         caches[layer_id] = cache
+    _encode_prefill_layers(entries)
     return caches
 
 
 def create_tiered_cache_from_model(past_kv, layer_ids: list, block_size: int = 16, max_new_tokens: int = 512,
                                    fp16_key_cache_capacity: int | None = None) -> dict:
     """Per-layer INT8-key / model-dtype-value caches (reference: tiered_kv_cache.py:1644-1701)."""
-    caches = {}
+    caches, entries = {}, []
     for layer_id in layer_ids:
         keys, values = _layer_kv(past_kv, layer_id)
         seq_len = keys.shape[1]
         aligned = (seq_len // block_size) * block_size
         cache = TieredKeyCacheLayer.from_fp16_cache(
-            keys[:, :aligned, :].contiguous(), values[:, :aligned, :].contiguous(),
+            keys[:, :aligned, :], values[:, :aligned, :],
             block_size=block_size, max_new_tokens=max_new_tokens + (seq_len - aligned),
-            fp16_key_cache_capacity=fp16_key_cache_capacity,
+            fp16_key_cache_capacity=fp16_key_cache_capacity, _encode=False,
         )
-        for t in range(aligned, seq_len):
-            cache.append_token(keys[:, t:t + 1, :], values[:, t:t + 1, :])
-        _poison_padding(cache)
+        cache.num_tokens = cache.num_blocks = cache.num_quantized_blocks = 0
+        entries.append((cache, keys, values, seq_len))
         caches[layer_id] = cache
+    _encode_prefill_layers(entries)
     return caches

@@ -244,6 +244,25 @@ int64_t cqa_launch_count(int reset);
 int cqa_quantize_blocks(const cqa_cache *c, const void *k_src, const void *v_src, int src_dtype,
                         int64_t src_rows, int64_t first_block, int64_t n_blocks, void *stream);
 
+/* Whole-model prefill encode in one call: for each item (one layer's cache) the complete 16-token blocks of
+ * its n_tokens source rows are quantised as by cqa_quantize_blocks, straight from the strided
+ * [KV][src_rows][128] prefill tensors (no contiguous copy of the aligned prefix), and the ragged remainder
+ * (n_tokens % 16 tokens) is appended by ONE launch whose CTAs walk the tokens of their KV head in order, with the
+ * arithmetic of cqa_append_token.  `items` is a host array; every item is checked before the first launch.
+ * Replaces the per-layer loop of create_tiered_cache_int4v_from_model / create_tiered_cache_from_model
+ * (tiered_kv_cache.py:1579-1701), which quantises layer by layer and appends the remainder token by token
+ * from Python. */
+typedef struct {
+    cqa_cache cache;
+    const void *k_src;    /* [KV][src_rows][128] of the call's src_dtype (device) */
+    const void *v_src;
+    int64_t src_rows;     /* rows per KV head in the source tensors */
+    int64_t n_tokens;     /* tokens to encode (<= src_rows) */
+    int32_t defer_int4;   /* as in cqa_append_token, for the remainder */
+    int32_t reserved;
+} cqa_prefill_item;
+int cqa_prefill_encode(const cqa_prefill_item *items, int n_items, int src_dtype, void *stream);
+
 /* Fused append-and-quantise of one token at position `pos` for every KV head:
  * Tier-2 rows, nu_b, per-token INT4 (unless `defer_int4`), and, when the token
  * completes a block, the block's INT8 keys and (deferred) INT4 values with

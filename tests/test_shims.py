@@ -449,6 +449,50 @@ def test_fp16_value_cache_end_to_end(dtype):
     assert c4.values_int4_packed is not None and c4.num_tokens == n and c4.num_quantized_blocks == n // 16
 
 
+@pytest.mark.parametrize("dtype,defer", [("bfloat16", None), ("float32", False)])
+def test_whole_model_prefill_encode(dtype, defer):
+    """create_tiered_cache_int4v_from_model: three layers with ragged lengths go through ONE library call (complete
+    blocks quantised from the strided [1, KV, seq, 128] tensors, the remainder appended by one launch per layer);
+    every array equals the oracle cache built block-wise + token by token, and decoding continues from there."""
+    lens = [16 * 37 + 11, 16 * 37 + 11, 16 * 37 + 11]
+    layers, bases = [], []
+    for i, n in enumerate(lens):
+        base = synth.make_layer_inputs(70 + i, n + 40, dtype=dtype, n_planted_blocks=4)
+        bases.append(base)
+        # a [1, KV, seq + 40, 128] buffer of which the first n rows are the prompt: non-trivial KV stride
+        kfull, vfull = hz.to_dev(base.k, dtype).unsqueeze(0), hz.to_dev(base.v, dtype).unsqueeze(0)
+        layers.append(_Layer(kfull[:, :, :n], vfull[:, :, :n]))
+    before = _lib.lib().cqa_launch_count(0)
+    caches = create_tiered_cache_int4v_from_model(_PastKV(layers), [0, 1, 2], max_new_tokens=48,
+                                                  defer_int4_append_quantization=defer)
+    launched = _lib.lib().cqa_launch_count(0) - before
+    assert launched == 2 * len(lens), f"{launched} launches for {len(lens)} layers"
+    for i, n in enumerate(lens):
+        cc, base = caches[i], bases[i]
+        al = (n // 16) * 16
+        oc = hz.make_oracle_cache(base.k[:, :al], base.v[:, :al], dtype, 48 + n - al, defer=cc._defer_int4_flag())
+        for t in range(al, n):
+            oc.append_token(base.k[:, t:t + 1], base.v[:, t:t + 1])
+        hz.compare_caches(cc, oc, f"layer {i} after the prefill encode")
+        for step in range(8):     # crosses the completion of the ragged block
+            q, kn, vn = synth.decode_step_inputs(base, step, dtype=dtype)
+            cc.append_token(hz.to_dev(kn, dtype), hz.to_dev(vn, dtype))
+            oc.append_token(kn, vn)
+        hz.compare_caches(cc, oc, f"layer {i} after 8 appends")
+
+
+def test_prefill_encode_refuses_bad_items():
+    base = synth.make_layer_inputs(75, 256, kv_heads=2, dtype="bfloat16")
+    cc = hz.make_cuda_cache(base.k, base.v, "bfloat16", 16)
+    it = (_lib.CqaPrefillItem * 1)()
+    it[0].cache = cc._desc()
+    it[0].k_src, it[0].v_src = cc.keys_fp16_gpu.data_ptr(), cc.values_fp16_gpu.data_ptr()
+    it[0].src_rows, it[0].n_tokens = 256, 100000          # more tokens than the cache holds
+    before = _lib.lib().cqa_launch_count(0)
+    rc = _lib.lib().cqa_prefill_encode(it, 1, _lib.CQA_BF16, None)
+    assert rc != 0 and _lib.lib().cqa_launch_count(0) == before
+
+
 # ----------------------------------------------------------------------------- page-in module and residency API
 
 def test_cuda_pagein_module():
