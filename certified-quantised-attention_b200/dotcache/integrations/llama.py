@@ -17,8 +17,13 @@ reference's names and argument meaning:
   model's own prefill KV (reference: `create_tiered_cache_int4v_from_model`,
   tiered_kv_cache.py:1579-1641).
 
-Prefill and any call that is not a batch-1 single-token decode go through the
-wrapped HF attention unchanged.
+* batch > 1 (an addition; the reference raises on it, llama.py:717-718): with
+  `CertifiedAttentionState.batch_caches` (one cache per layer and sequence) a
+  single-token decode call of B sequences runs each layer's append and
+  certified step as ONE batched launch chain (`certified_attention_batch`).
+
+Prefill and any call that is not a single-token decode go through the wrapped
+HF attention unchanged.
 """
 from __future__ import annotations
 
@@ -27,7 +32,7 @@ from dataclasses import dataclass, field
 import torch
 from torch import nn
 
-from ..kernels.certified_attention import certified_attention_layer
+from ..kernels.certified_attention import certified_attention_batch, certified_attention_layer
 from ..kernels.tiered_kv_cache import TieredKeyCacheLayer, create_tiered_cache_int4v_from_model
 
 
@@ -59,6 +64,9 @@ class CertifiedAttentionState:
     _clear_seq: int = 0
     phase_timings: dict | None = None
     _score_consistency_step: int = 0
+    # batch > 1 (an addition; the reference raises, llama.py:717-718): layer_id -> list of one cache per sequence.
+    # A decode call with B sequences then runs each layer's step as ONE batched launch chain.
+    batch_caches: dict | None = None
 
     def __post_init__(self):
         if self.step_stats is None:
@@ -112,11 +120,13 @@ class CertifiedLlamaAttention(nn.Module):
 
     def _forward_certified(self, hidden_states, position_embeddings=None):
         """One decode step of this layer (reference: llama.py:710-797)."""
-        if tuple(hidden_states.shape[:2]) != (1, 1):
-            raise ValueError("Certified decode mode only supports batch=1 and query_len=1")
+        if hidden_states.shape[1] != 1:
+            raise ValueError("Certified decode mode only supports query_len=1")
         if position_embeddings is None:
             raise ValueError("position_embeddings are required for the Llama attention path")
         st = self.certified_state
+        if hidden_states.shape[0] != 1:
+            return self._forward_certified_batch(hidden_states, position_embeddings)
         cache = st.tiered_caches.get(self.layer_idx)
         if cache is None:
             raise ValueError(f"No tiered cache for layer {self.layer_idx}")
@@ -141,10 +151,36 @@ class CertifiedLlamaAttention(nn.Module):
         ctx = context.to(dtype=hidden_states.dtype).reshape(1, 1, -1)
         return self.base_attention.o_proj(ctx), None
 
+    def _forward_certified_batch(self, hidden_states, position_embeddings):
+        """One decode step of this layer for B sequences with their own caches: one append and one chain of three
+        kernels for the whole batch (certified_attention_batch).  Per-layer stats are not collected here; the
+        certificates stay in each cache's workspace."""
+        st = self.certified_state
+        caches = (st.batch_caches or {}).get(self.layer_idx)
+        B = hidden_states.shape[0]
+        if caches is None or len(caches) != B:
+            raise ValueError(f"No batch of {B} tiered caches for layer {self.layer_idx}")
+        q, k, v = self._project_qkv(hidden_states, position_embeddings)
+        gqa_group = self.config.num_attention_heads // self.config.num_key_value_heads
+        context = certified_attention_batch(
+            caches, q[:, :, 0, :], gqa_group, float(self.base_attention.scaling),
+            new_keys=k[:, :, 0, :] if st.append_kv else None, new_values=v[:, :, 0, :] if st.append_kv else None,
+            v_tolerance=st.v_tolerance, top_k_fp16_keys=st.top_k_fp16_keys,
+            ranking_fallback=st.ranking_fallback, ranking_r=st.ranking_r,
+            ranking_fallback_mode=st.ranking_fallback_mode, tau_cov=st.tau_cov, k_min=st.k_min, k_max=st.k_max,
+            rung1_threshold=st.rung1_threshold, rung1_multiplier=st.rung1_multiplier,
+            score_consistency_check=st.score_consistency_enabled_for_layer(self.layer_idx),
+            eps_guard=st.eps_guard, exploration_rate=st.exploration_rate, value_error_mode=st.value_error_mode,
+        )
+        ctx = context.to(dtype=hidden_states.dtype).reshape(B, 1, -1)
+        return self.base_attention.o_proj(ctx), None
+
     def forward(self, hidden_states, position_embeddings=None, attention_mask=None, past_key_values=None, **kwargs):
         st = self.certified_state
-        decode = (tuple(hidden_states.shape[:2]) == (1, 1) and st is not None
-                  and self.layer_idx in st.tiered_caches)
+        B = hidden_states.shape[0]
+        decode = st is not None and hidden_states.shape[1] == 1 and (
+            (B == 1 and self.layer_idx in st.tiered_caches)
+            or (B > 1 and st.batch_caches is not None and len(st.batch_caches.get(self.layer_idx, ())) == B))
         if decode:
             return self._forward_certified(hidden_states, position_embeddings)
         return self.base_attention(hidden_states, position_embeddings=position_embeddings,
@@ -160,7 +196,7 @@ def install_certified_attention(model: nn.Module, state: CertifiedAttentionState
             attn.certified_state = state
             wrappers.append(attn)
             continue
-        if int(attn.layer_idx) in state.tiered_caches:
+        if int(attn.layer_idx) in state.tiered_caches or int(attn.layer_idx) in (state.batch_caches or {}):
             w = CertifiedLlamaAttention(attn, state)
             layer.self_attn = w
             wrappers.append(w)
@@ -177,12 +213,24 @@ def build_certified_state_from_prefill(past_key_values, layer_ids: list[int], *,
                                        fp16_key_cache_capacity: int | None = None,
                                        fp16_value_cache_capacity: int | None = None,
                                        **state_kwargs) -> CertifiedAttentionState:
-    """INT8-key / INT4-value caches from a prefill's KV (batch 1), wrapped in a state with the paper's knobs
+    """INT8-key / INT4-value caches from a prefill's KV (one cache per layer; with a batch of prompts one per layer
+    and sequence, in `batch_caches`), wrapped in a state with the paper's knobs
     unless overridden: tau_cov 0.995, k in [2, 128], ranking fallback r = 1, v_tolerance 0.05, append_kv on."""
-    caches = create_tiered_cache_int4v_from_model(
-        past_key_values, layer_ids, max_new_tokens=max_new_tokens,
-        fp16_key_cache_capacity=fp16_key_cache_capacity, fp16_value_cache_capacity=fp16_value_cache_capacity)
     knobs = dict(append_kv=True, tau_cov=0.995, k_min=2, k_max=128, ranking_fallback=True, ranking_r=1,
                  v_tolerance=0.05, score_consistency_check=False, collect_stats=False)
     knobs.update(state_kwargs)
-    return CertifiedAttentionState(tiered_caches=caches, **knobs)
+    batch = _prefill_batch_size(past_key_values, layer_ids[0])
+    per_seq = [create_tiered_cache_int4v_from_model(
+        past_key_values, layer_ids, max_new_tokens=max_new_tokens, fp16_key_cache_capacity=fp16_key_cache_capacity,
+        fp16_value_cache_capacity=fp16_value_cache_capacity, batch_index=b) for b in range(batch)]
+    if batch == 1:
+        return CertifiedAttentionState(tiered_caches=per_seq[0], **knobs)
+    # a batch of prompts (all of the prefill's length): one cache per (layer, sequence)
+    return CertifiedAttentionState(tiered_caches={}, batch_caches={l: [c[l] for c in per_seq] for l in layer_ids},
+                                   **knobs)
+
+
+def _prefill_batch_size(past_kv, layer_id: int) -> int:
+    if hasattr(past_kv, "layers"):
+        return int(past_kv.layers[layer_id].keys.shape[0])
+    return int(past_kv[layer_id][0].shape[0])

@@ -530,10 +530,10 @@ class TieredKeyCacheLayer:
         return codes * s + z
 
 
-def _layer_kv(past_kv, layer_id: int):
+def _layer_kv(past_kv, layer_id: int, batch_index: int = 0):
     if hasattr(past_kv, "layers"):
-        return past_kv.layers[layer_id].keys[0], past_kv.layers[layer_id].values[0]
-    return past_kv[layer_id][0][0], past_kv[layer_id][1][0]
+        return past_kv.layers[layer_id].keys[batch_index], past_kv.layers[layer_id].values[batch_index]
+    return past_kv[layer_id][0][batch_index], past_kv[layer_id][1][batch_index]
 
 
 def _encode_prefill_layers(entries) -> None:
@@ -577,15 +577,16 @@ def create_tiered_cache_int4v_from_model(past_kv, layer_ids: list, block_size: i
                                          max_new_tokens: int = 512,
                                          fp16_key_cache_capacity: int | None = None,
                                          fp16_value_cache_capacity: int | None = None,
-                                         defer_int4_append_quantization: bool | None = None) -> dict:
-    """Per-layer INT8K/INT4V caches from HF past_key_values
-    (reference: tiered_kv_cache.py:1579-1641).  Every layer is allocated first, then all of them are encoded by one
+                                         defer_int4_append_quantization: bool | None = None,
+                                         batch_index: int = 0) -> dict:
+    """Per-layer INT8K/INT4V caches from HF past_key_values, sequence `batch_index` of the prefill's batch
+    (reference: tiered_kv_cache.py:1579-1641, which takes sequence 0).  Every layer is allocated first, then all of them are encoded by one
     library call, ragged remainders included."""
     if defer_int4_append_quantization is None:
         defer_int4_append_quantization = fp16_value_cache_capacity is None
     caches, entries = {}, []
     for layer_id in layer_ids:
-        keys, values = _layer_kv(past_kv, layer_id)
+        keys, values = _layer_kv(past_kv, layer_id, batch_index)
         seq_len = keys.shape[1]
         aligned = (seq_len // block_size) * block_size
         cache = TieredKeyCacheLayer.from_fp16_cache_int4v(

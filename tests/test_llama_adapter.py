@@ -69,3 +69,49 @@ def test_tiny_llama_decodes_through_the_certified_path():
         rel = ((d - c).norm() / d.norm()).item()
         assert cos > 0.999 and rel < 5e-2, f"step {s}: cosine {cos}, relative error {rel}"
         assert d.argmax().item() == c.argmax().item() or (d.max() - d[c.argmax()]).item() < 0.05
+
+
+@pytest.mark.gpu
+def test_tiny_llama_batch_of_two_decodes_in_one_launch_chain_per_layer():
+    """Batch 2 (the reference raises on it): every layer's append + certified step is one batched chain of four
+    launches for both sequences; logits stay close to the model's own dense batch decode."""
+    import copy
+
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from cqa_b200 import _lib
+
+    torch.manual_seed(1)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=4096,
+                      rms_norm_eps=1e-5, tie_word_embeddings=False)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).cuda().eval()
+    T, steps, B = 768 + 9, 12, 2
+    ids = torch.randint(0, cfg.vocab_size, (B, T + steps), device="cuda")
+    with torch.no_grad():
+        past = model(input_ids=ids[:, :T], use_cache=True).past_key_values
+        dense_past = copy.deepcopy(past)
+        dense_logits = []
+        for s in range(steps):
+            out = model(input_ids=ids[:, T + s: T + s + 1], past_key_values=dense_past, use_cache=True)
+            dense_logits.append(out.logits[:, -1].float())
+        state = build_certified_state_from_prefill(past, [0, 1], max_new_tokens=64)
+        assert state.batch_caches is not None and all(len(v) == B for v in state.batch_caches.values())
+        install_certified_attention(model, state)
+        cert_logits, launches = [], []
+        for s in range(steps):
+            state.begin_decode_step()
+            pos = torch.full((B, 1), T + s, device="cuda")
+            before = _lib.lib().cqa_launch_count(0)
+            out = model(input_ids=ids[:, T + s: T + s + 1], position_ids=pos, use_cache=False)
+            launches.append(_lib.lib().cqa_launch_count(0) - before)
+            cert_logits.append(out.logits[:, -1].float())
+        remove_certified_attention(model)
+    assert all(c.num_tokens == T + steps for cs in state.batch_caches.values() for c in cs)
+    assert all(n == 2 * 4 for n in launches), launches      # 2 layers x (append, score, selector, attend)
+    for s in range(steps):
+        for b in range(B):
+            d, c = dense_logits[s][b], cert_logits[s][b]
+            cos = torch.nn.functional.cosine_similarity(d, c, dim=0).item()
+            rel = ((d - c).norm() / d.norm()).item()
+            assert cos > 0.999 and rel < 5e-2, f"step {s} sequence {b}: cosine {cos}, relative error {rel}"
