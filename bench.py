@@ -75,6 +75,16 @@ def parse_args():
     ap.add_argument("--batched-sweep", action="store_true",
                     help="instead of the headline run: batch x context sweep of one layer (batched launch against a loop "
                          "of one-sequence calls, full Tier-2 mirror and a hot tier capped at 2048 tokens)")
+    ap.add_argument("--decoder", action="store_true",
+                    help="instead of the headline run: a whole random-init Llama-3.1-8B-shaped decoder (32 layers, "
+                         "hidden 4096, 32/8 heads, FFN 14336, vocab 128256), a batch of prompts prefilled by the "
+                         "model itself, then greedy decoding through the certified path")
+    ap.add_argument("--decoder-layers", type=int, default=32)
+    ap.add_argument("--decoder-batch", type=int, default=4)
+    ap.add_argument("--decoder-prompt", type=int, default=65536)
+    ap.add_argument("--decoder-steps", type=int, default=256)
+    ap.add_argument("--decoder-dense-steps", type=int, default=8,
+                    help="steps of the model's own dense decode (HF cache, torch SDPA) timed for comparison (0 = skip)")
     ap.add_argument("--sharded-peer", type=int, default=1,
                     help="also time the sharded step with peer-memory exchanges (0 = collectives only)")
     return ap.parse_args()
@@ -649,6 +659,123 @@ def run_sharded(args, rank, world, device_index):
             "hbm_floor_us_per_rank": round(per_rank_bytes / 6540.2e3, 2)}
 
 
+def run_decoder(args, device_index):
+    """A whole decoder with random-init bf16 weights: prefill of a batch of uniform-random prompts by the model itself
+    (chunked, its own SDPA attention), per-(layer, sequence) certified caches built from that prefill by one library
+    call per sequence, then greedy decoding with every layer's attention going through the certified batched step.
+    Reports end-to-end decode tokens/s (all sequences) and the model's own dense decode beside it."""
+    import torch
+    from transformers import DynamicCache, LlamaConfig, LlamaForCausalLM
+
+    from cqa_b200 import _lib as cl
+    from dotcache.integrations.llama import (build_certified_state_from_prefill, install_certified_attention,
+                                             remove_certified_attention)
+
+    torch.cuda.set_device(device_index)
+    dev = torch.device("cuda", device_index)
+    torch.manual_seed(args.seed)
+    NL, B, P, S = args.decoder_layers, args.decoder_batch, args.decoder_prompt, args.decoder_steps
+    cfg = LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=NL,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                      max_position_embeddings=P + S + 64, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      tie_word_embeddings=False)
+    with torch.device(dev):
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    ids = torch.randint(0, cfg.vocab_size, (B, P), device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    with torch.no_grad():
+        past = DynamicCache()
+        t0 = time.perf_counter()
+        chunk = 4096
+        for c0 in range(0, P, chunk):
+            out = model.model(input_ids=ids[:, c0:c0 + chunk], past_key_values=past, use_cache=True)
+        tok = model.lm_head(out.last_hidden_state[:, -1:]).argmax(dim=-1)          # [B, 1]
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t0
+        first_tok = tok.clone()
+        dense = None
+        if args.decoder_dense_steps > 0:
+            e0, e1 = ev(), ev()
+            dtok = first_tok.clone()
+            for s in range(args.decoder_dense_steps + 2):
+                if s == 2:
+                    e0.record()
+                o = model(input_ids=dtok, past_key_values=past, use_cache=True)
+                dtok = o.logits[:, -1:].argmax(dim=-1)
+            e1.record()
+            torch.cuda.synchronize()
+            dense_ms = e0.elapsed_time(e1) / args.decoder_dense_steps
+            dense = {"ms_per_step": round(dense_ms, 3), "tokens_per_s": round(B * 1e3 / dense_ms, 1),
+                     "what": "the same model's dense decode: HF DynamicCache (grows by concatenation) + torch SDPA, "
+                             f"{args.decoder_dense_steps} steps"}
+            past.crop(P)
+        t0 = time.perf_counter()
+        state = build_certified_state_from_prefill(past, list(range(NL)), max_new_tokens=S + 32)
+        torch.cuda.synchronize()
+        encode_s = time.perf_counter() - t0
+        del past, out
+        torch.cuda.empty_cache()
+        install_certified_attention(model, state)
+        warm = 4
+        e0, e1 = ev(), ev()
+        tok = first_tok
+        sampler = ClockSampler(device_index)
+        launches0 = 0
+        for s in range(warm + S):
+            if s == warm:
+                torch.cuda.synchronize()
+                sampler.start()
+                launches0 = cl.lib().cqa_launch_count(0)
+                e0.record()
+            state.begin_decode_step()
+            pos = torch.full((B, 1), P + s, device=dev)
+            o = model(input_ids=tok, position_ids=pos, use_cache=False)
+            tok = o.logits[:, -1:].argmax(dim=-1)
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        launches = cl.lib().cqa_launch_count(0) - launches0
+        remove_certified_attention(model)
+        caches = state.batch_caches if state.batch_caches else {l: [c] for l, c in state.tiered_caches.items()}
+        # the attention part alone: the batched certified step of every layer in turn (no append), one event pair
+        from dotcache.kernels import certified_attention as ca
+
+        qb = torch.randn(B, 32, 128, device=dev).to(torch.bfloat16)
+        kn = dict(v_tolerance=state.v_tolerance, top_k_fp16_keys=state.top_k_fp16_keys,
+                  ranking_fallback=state.ranking_fallback, ranking_r=state.ranking_r, tau_cov=state.tau_cov,
+                  k_min=state.k_min, k_max=state.k_max)
+        a0, a1 = ev(), ev()
+        for rep in range(3):
+            if rep == 1:
+                a0.record()
+            for l in range(NL):
+                if B > 1:
+                    ca.certified_attention_batch(caches[l], qb, 4, None, **kn)
+                else:
+                    ca.certified_attention_layer(caches[l][0], qb[0], 4, None, False, **kn)
+        a1.record()
+        torch.cuda.synchronize()
+        attn_ms = a0.elapsed_time(a1) / 2
+    ms = e0.elapsed_time(e1) / S
+    tier1 = sum(c.keys_int8.numel() + c.values_int4_packed.numel() for cs in caches.values() for c in cs)
+    return {
+        "metric": "certified_decode_tokens_per_s", "value": round(B * 1e3 / ms, 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": S, "warmup": warm, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"Llama-3.1-8B-shaped decoder, random-init bf16 weights, {NL} layers, batch {B}, prompt "
+                               f"{P} uniform token ids, {S} greedy steps, INT8K/INT4V g16 certified attention in every "
+                               "layer (one batched launch chain per layer), projections / MLP / lm_head by torch",
+                   "layers": NL, "batch": B, "prompt": P, "knobs": "tau_cov 0.995, k 2..128, r 1, v_tol 0.05"},
+        "us_per_sequence_layer_step": round(ms * 1e3 / (NL * B), 2),
+        "attention_only": {"ms_per_step": round(attn_ms, 3), "us_per_sequence_layer_step": round(attn_ms * 1e3 / (NL * B), 2),
+                           "what": "the certified step of all layers back to back on the final caches, no model around it"},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "prefill_s": round(prefill_s, 1), "cache_encode_s": round(encode_s, 2),
+        "tier1_bytes_int8k_int4v": int(tier1), "dense_decode": dense,
+        "hbm_gb_allocated": round(torch.cuda.max_memory_allocated(dev) / 2**30, 1),
+    }
+
+
 def run_batched_sweep(args, device_index):
     """Capped-hot-tier sweep shape (batch x context, one layer): µs per sequence-layer-step of the batched launch
     (cqa_layer_step_batched) against a loop of one-sequence calls on the same caches, with the full Tier-2 mirror
@@ -786,6 +913,10 @@ def _main(args, out):
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device: bench.py --impl ours needs a B200; there is no CPU fallback"}), file=out)
         return 1
+    if args.decoder:
+        if rank == 0:
+            print(json.dumps(run_decoder(args, local)), file=out, flush=True)
+        return 0
     if args.batched_sweep:
         if rank == 0:
             print(json.dumps(run_batched_sweep(args, local)), file=out, flush=True)
