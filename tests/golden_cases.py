@@ -30,7 +30,7 @@ PAPER_KNOBS = dict(
 )
 
 SMALL_CASES = ["small_fp32", "small_vtol0", "planted_bf16_append", "planted_fp16_g2"]
-LARGE_CASES = ["config1_8k", "planted_8k_bf16"]
+LARGE_CASES = ["config1_8k", "planted_8k_bf16", "planted_32k_bf16"]
 
 
 def available(names):
