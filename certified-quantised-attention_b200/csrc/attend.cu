@@ -66,9 +66,12 @@ struct AttLayout {
     static constexpr int MERGE_B = (2 * G * CQA_MAX_SPLITS + G + 4 + ATT_WARPS * D) * 4;
     static constexpr int MERGE = MERGE_A > MERGE_B ? MERGE_A : MERGE_B;
     static constexpr int RING_BYTES = RING > MERGE ? RING : MERGE;
-    // per warp: two weight tiles [16 tokens][G] of (w, w) pairs (INT4 part, zero where a head reads Tier-2
-    // values), two tiles of true weights for those heads, and the FP16-key logits of the block being prepared
-    static constexpr int W_TILE = BS * G * 8;
+    // per warp: two weight tiles [16 tokens][GP] of (w, w) pairs (INT4 part, zero where a head reads Tier-2
+    // values), two tiles of true weights for those heads, and the FP16-key logits of the block being prepared.
+    // A token's row is padded to GP = G + 2 pairs: with the lanes of a head holding tokens sub, sub + LPH, ... the
+    // 8-byte stores of a half warp then fall into 16 different bank pairs (rows of G pairs collide four ways).
+    static constexpr int GP = G >= 2 ? G + 2 : G;
+    static constexpr int W_TILE = BS * GP * 8;
     static constexpr int PER_WARP = 4 * W_TILE + G * BS * 4;
     static constexpr int TOTAL = RING_BYTES + ATT_WARPS * PER_WARP;
 };
@@ -433,8 +436,8 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
     const long b_end = min(nact, b_begin + (long)blocks_per_split);
     char *wring = ring + warp * ATT_STAGES * LY::STAGE;
     char *wpriv = dsm + LY::RING_BYTES + warp * LY::PER_WARP;
-    float2 *w_tiles = reinterpret_cast<float2 *>(wpriv);                       // [2][16][G] INT4-part weights
-    float2 *w16_tiles = reinterpret_cast<float2 *>(wpriv + 2 * LY::W_TILE);    // [2][16][G] true weights (Tier-2 values)
+    float2 *w_tiles = reinterpret_cast<float2 *>(wpriv);                       // [2][16][GP] INT4-part weights
+    float2 *w16_tiles = reinterpret_cast<float2 *>(wpriv + 2 * LY::W_TILE);    // [2][16][GP] true weights (Tier-2 values)
     float *sc_tile = reinterpret_cast<float *>(wpriv + 4 * LY::W_TILE);        // [G][16] FP16-key logits
 
     // start the pipeline before anything else
@@ -487,6 +490,7 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
     // Softmax bookkeeping layout: LPH lanes per head, each lane holds TPL tokens of its head `gl`.
     constexpr int LPH = G >= 8 ? 4 : (G == 4 ? 8 : 16);
     constexpr int TPL = BS / LPH;
+    constexpr int GP = LY::GP;           // pairs per token row of a weight tile (padded)
     const int gl = lane / LPH, sub = lane % LPH;
     const bool gl_valid = gl < G;
 
@@ -534,7 +538,7 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
         float sv_[TPL];
 #pragma unroll
         for (int i = 0; i < TPL; ++i) {
-            const int t = sub * TPL + i;
+            const int t = sub + LPH * i;
             float x = -INFINITY;
             if (gl_valid && t < n_valid) x = ((km >> gl) & 1u) ? sc_tile[gl * BS + t] : st_sc[gl * BS + t];
             sv_[i] = x;
@@ -553,7 +557,7 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
             m_mine = m_up;
         }
         const float m_new = m_mine;
-        float2 *wt = w_tiles + (it & 1) * BS * G;
+        float2 *wt = w_tiles + (it & 1) * BS * GP;
         const bool v16 = (vm >> gl) & 1u;
         float ls = 0.0f;
 #pragma unroll
@@ -561,13 +565,13 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
             const float w = sv_[i] == -INFINITY ? 0.0f : fexp(sv_[i] - m_new);
             ls += w;
             const float w4 = v16 ? 0.0f : w;
-            if (gl_valid) wt[(sub * TPL + i) * G + gl] = make_float2(w4, w4);
+            if (gl_valid) wt[(sub + LPH * i) * GP + gl] = make_float2(w4, w4);
         }
         if (vm) {
 #pragma unroll
             for (int i = 0; i < TPL; ++i) {
                 const float w = sv_[i] == -INFINITY ? 0.0f : fexp(sv_[i] - m_new);
-                if (gl_valid) w16_tiles[((it & 1) * BS + sub * TPL + i) * G + gl] = make_float2(w, w);
+                if (gl_valid) w16_tiles[((it & 1) * BS + sub + LPH * i) * GP + gl] = make_float2(w, w);
             }
         }
         l_mine = fmaf(l_mine, alpha, ls);
@@ -601,7 +605,7 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
             }
         }
         const char *st = wring + (it % ATT_STAGES) * LY::STAGE;
-        const float2 *wt = w_tiles + (it & 1) * BS * G;
+        const float2 *wt = w_tiles + (it & 1) * BS * GP;
         // ---- INT4 values of block `it` (zero weights where a head reads Tier-2 values or the token is padding);
         // this half warp takes tokens t = 2i + hw
         if (have4) {
@@ -620,12 +624,12 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
                 if constexpr (G % 2 == 0) {
 #pragma unroll
                     for (int g = 0; g < G; g += 2) {
-                        const float4 ww = *reinterpret_cast<const float4 *>(wt + t * G + g);
+                        const float4 ww = *reinterpret_cast<const float4 *>(wt + t * GP + g);
                         w2[g] = make_float2(ww.x, ww.y);
                         w2[g + 1] = make_float2(ww.z, ww.w);
                     }
                 } else {
-                    w2[0] = wt[t * G];
+                    w2[0] = wt[t * GP];
                 }
 #pragma unroll
                 for (int g = 0; g < G; ++g)
@@ -655,7 +659,7 @@ __device__ __forceinline__ void attend_body(const cqa_cache &c, const cqa_worksp
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     if (!(vm & (1u << g))) continue;
-                    const float2 w2 = w16_tiles[((it & 1) * BS + t) * G + g];
+                    const float2 w2 = w16_tiles[((it & 1) * BS + t) * GP + g];
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         acc2[g][k] = __ffma2_rn(w2, make_float2(v16[2 * k], v16[2 * k + 1]), acc2[g][k]);
