@@ -13,14 +13,21 @@ namespace cqa {
 template <typename T2>
 __device__ __forceinline__ void fp16_block_score_warp(const cqa_cache &c, const void *q, int q_dtype, int h,
                                                       long bid, long n_scoring_tokens, float q_scale,
-                                                      float &score_out, float &logmass_out)
+                                                      float &score_out, float &logmass_out,
+                                                      const float *q_row = nullptr)
 {
     const int lane = threadIdx.x & 31, L = lane & 15, hw = lane >> 4;
     const int kv = h / c.gqa_group;
     const bool valid_block = bid >= 0 && bid * BS < n_scoring_tokens;
     const T2 *base = valid_block ? t2_key_block<T2>(c, kv, bid) : nullptr;   // hot slot or backing array
+    // q_row: the head's 128 query values already converted to float (shared memory), fetched by the caller ahead of time
     float qv[8];
-    load_q8(q, q_dtype, (long)h * D + 8 * L, qv);
+    if (q_row != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qv[i] = q_row[8 * L + i];
+    } else {
+        load_q8(q, q_dtype, (long)h * D + 8 * L, qv);
+    }
     float lg[8];  // this half warp's tokens hw*8 .. hw*8+7 (all lanes hold all 8)
     // issue the eight row loads together, then reduce (small code: this runs once per launch)
     Raw8<T2> raw[8];

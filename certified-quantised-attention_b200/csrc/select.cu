@@ -478,18 +478,51 @@ __device__ __forceinline__ float column_sum1(const float *e, int n, int nk, unsi
 
 template <typename T2>
 __device__ __forceinline__ void rescore_block(const cqa_cache &c, const void *q, int q_dtype, int h, long bid,
-                                              long n_scoring_tokens, float q_scale, float &s, float &lm)
+                                              long n_scoring_tokens, float q_scale, float &s, float &lm, const float *q_row)
 {
-    fp16_block_score_warp<T2>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
+    fp16_block_score_warp<T2>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm, q_row);
 }
+// Address of token t of Tier-2 key block `bid` as seen by this lane (its 8 channels), or NULL when the token does not
+// take part (beyond the scoring range, or a block held by neither tier).
+__device__ __forceinline__ const void *t2_token_row(const cqa_cache &c, int kv, long bid, int t, long n_scoring_tokens)
+{
+    const int L = threadIdx.x & 15;
+    if (bid < 0 || bid * BS + t >= n_scoring_tokens) return nullptr;
+    const size_t esz = c.t2_dtype == CQA_F32 ? 4 : 2;
+    const char *base = c.t2_dtype == CQA_BF16  ? reinterpret_cast<const char *>(t2_key_block<__nv_bfloat16>(c, kv, bid))
+                       : c.t2_dtype == CQA_F16 ? reinterpret_cast<const char *>(t2_key_block<__half>(c, kv, bid))
+                                               : reinterpret_cast<const char *>(t2_key_block<float>(c, kv, bid));
+    return base ? base + ((size_t)t * D + 8 * L) * esz : nullptr;
+}
+// The logit of one token, by the 16 lanes of a half warp (same arithmetic as fp16_block_score_warp).
+template <typename T2>
+__device__ __forceinline__ float token_logit_t(const void *row, const float *q_row, float q_scale)
+{
+    const int L = threadIdx.x & 15;
+    const Raw8<T2> raw = row ? raw_load8<T2>(reinterpret_cast<const T2 *>(row)) : raw_zero8<T2>();
+    float kf[8], qv[8];
+    raw_to_f(raw, kf);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qv[i] = q_row[8 * L + i];
+    const float d = hw_sum(chain8(kf, qv));
+    return row ? __fmul_rn(d, q_scale) : -INFINITY;
+}
+__device__ __forceinline__ float token_logit(const cqa_cache &c, const void *row, const float *q_row, float q_scale)
+{
+    if (c.t2_dtype == CQA_BF16) return token_logit_t<__nv_bfloat16>(row, q_row, q_scale);
+    if (c.t2_dtype == CQA_F16) return token_logit_t<__half>(row, q_row, q_scale);
+    return token_logit_t<float>(row, q_row, q_scale);
+}
+
 // Tier-2 dtype dispatch at run time: the re-score is a few warps of one role, the rest of the kernel does not
 // depend on the dtype.
 __device__ __noinline__ void rescore_block_any(const cqa_cache &c, const void *q, int q_dtype, int h, long bid,
-                                               long n_scoring_tokens, float q_scale, float &s, float &lm)
+                                               long n_scoring_tokens, float q_scale, float &s, float &lm,
+                                               const float *q_row)
 {
-    if (c.t2_dtype == CQA_BF16) rescore_block<__nv_bfloat16>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
-    else if (c.t2_dtype == CQA_F16) rescore_block<__half>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
-    else rescore_block<float>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm);
+    if (c.t2_dtype == CQA_BF16) rescore_block<__nv_bfloat16>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm, q_row);
+    else if (c.t2_dtype == CQA_F16) rescore_block<__half>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm, q_row);
+    else rescore_block<float>(c, q, q_dtype, h, bid, n_scoring_tokens, q_scale, s, lm, q_row);
 }
 
 // Dynamic shared memory: A[n_arr] B[n_arr] C[n_pad] (floats; n_arr = max(n_pad, 2048)), cand[CAND] (u64), cum[CAND],
@@ -513,6 +546,7 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
     __shared__ int top_idx[CQA_MAX_RANKING_K];
     __shared__ float top_i8[CQA_MAX_RANKING_K], top_f16[CQA_MAX_RANKING_K], top_lm[CQA_MAX_RANKING_K];
     __shared__ float s_delta;
+    __shared__ float s_q[D];           // role 1: the head's query row as floats
     __shared__ u64 s_top[SC_WARPS * 4];
 
     __shared__ __align__(8) uint64_t row_bar;
@@ -580,6 +614,20 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
                     mask[b] = (b < n && uni < kn.exploration_rate) ? 2 : 0;   // bit 1: exploration candidate
                 }
             }
+        }
+    }
+
+    // Role 1, also ahead of the wait: the query row and Delta depend on q and on the per-channel scale maxima, both
+    // complete before the score kernel started (the scale maxima of a sharded run arrive with the exchange and are
+    // read after it).  The re-scoring warps later find q in shared memory and have one round trip to DRAM less.
+    const bool rank_checks = role == 1 && (kn.ranking_fallback || kn.score_consistency) && n > 0 && q != nullptr;
+    const bool delta_early = rank_checks && !sharded_in && !(phases & PH_TOP_ONLY) && c.sigma_max != nullptr;
+    if (rank_checks) {
+        if (warp == 0)
+            for (int i = lane; i < D; i += 32) s_q[i] = load_q(q, q_dtype, (long)h * D + i);
+        if (warp == 1 && delta_early) {
+            const float d = delta_bound_warp(c, q, q_dtype, h);
+            if (lane == 0) s_delta = d;
         }
     }
 
@@ -893,16 +941,61 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
         // so it equals (max ell_b) + delta; the maximum is taken by the warps that neither re-score a block
         // nor compute delta, while those wait for Tier-2 rows.
         const int ub_first = rk + 1, ub_warps = SC_WARPS - ub_first;
-        const bool overlap = ub_warps >= 8;
-        float ubm = -INFINITY;
         const bool peer_b = (phases & PH_PEER_B) != 0;
-        if (warp < rk) {
+        // With at most four candidates and Delta already known, a candidate block is re-scored by EIGHT warps (warp
+        // 8j + p takes tokens p and p + 8 of candidate j, one per half warp): a single warp walking all 16 tokens is a
+        // chain of ~600 dependent instructions behind a DRAM round trip, run once, and was the longest step of this role.
+        const bool spread = !peer_b && !given && rk <= 4 && delta_early;
+        const bool overlap = spread || ub_warps >= 8;
+        float ubm = -INFINITY;
+        if (spread) {
+            const int j = warp >> 3, part = warp & 7, hw = lane >> 4;
+            const int t = part + 8 * hw;
+            const void *row = j < rk ? t2_token_row(c, kv, (long)top_idx[j], t, nq * BS) : nullptr;
+            if (row && c.key_slots == nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(row));   // device memory only
+            if (kn.ranking_fallback) {
+                // the boundary maximum while the rows are on their way
+#pragma unroll 1
+                for (int b = tid; b < n; b += SC_THREADS) {
+                    bool in_top = false;
+                    for (int r = 0; r < rk; ++r) in_top |= (top_idx[r] == b);
+                    if (!in_top) ubm = fmaxf(ubm, B[b]);
+                }
+            }
+            float *s_lg = reinterpret_cast<float *>(s_top);          // [4][16] logits, then [4][8] pair sums behind them
+            float *s_pair = s_lg + 4 * BS;
+            if (j < rk) {
+                const float lg = token_logit(c, row, s_q, kn.q_scale);
+                if ((lane & 15) == 0) s_lg[j * BS + t] = lg;
+            }
+            __syncthreads();
+            float mx = -INFINITY;
+            if (j < rk) {
+                const float mine = s_lg[j * BS + t];
+                mx = s_lg[j * BS + (lane & 15)];
+#pragma unroll
+                for (int o = 8; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
+                float e = mine == -INFINITY ? 0.0f : cexp(__fsub_rn(mine, mx));
+                e = __fadd_rn(e, __shfl_xor_sync(FULL, e, 16));       // token p + token p + 8
+                if (lane == 0) s_pair[j * 8 + part] = e;
+            }
+            __syncthreads();
+            if (j < rk && part == 0 && lane == 0) {
+                // the 16-token butterfly finished in its fixed order: (i, i+4), then (0,2) and (1,3), then the two
+                const float *pp = s_pair + j * 8;
+                const float q0 = __fadd_rn(pp[0], pp[4]), q1 = __fadd_rn(pp[1], pp[5]);
+                const float q2 = __fadd_rn(pp[2], pp[6]), q3 = __fadd_rn(pp[3], pp[7]);
+                const float l = fmaxf(__fadd_rn(__fadd_rn(q0, q2), __fadd_rn(q1, q3)), 1e-30f);
+                top_f16[j] = mx;
+                top_lm[j] = mx == -INFINITY ? -INFINITY : __fadd_rn(mx, clog(l));
+            }
+        } else if (warp < rk) {
             if (peer_b) {
                 // re-score the block if this rank owns it (local block ids), zeros otherwise; every rank gets the row
                 const long bl = (long)top_idx[warp] - ws.peer_first_block;
                 float s = 0.0f, lm = 0.0f;
                 if (bl >= 0 && bl < ws.peer_n_local)
-                    rescore_block_any(c, q, q_dtype, h, bl, ws.peer_n_local * BS, kn.q_scale, s, lm);
+                    rescore_block_any(c, q, q_dtype, h, bl, ws.peer_n_local * BS, kn.q_scale, s, lm, s_q);
                 if (lane < ws.peer_world) {
                     float *d = ws.peer_xb[lane] + ((long)h * CQA_MAX_RANKING_K + warp) * 2;
                     d[0] = s;
@@ -910,12 +1003,14 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
                 }
             } else if (!given) {
                 float s, lm;
-                rescore_block_any(c, q, q_dtype, h, (long)top_idx[warp], nq * BS, kn.q_scale, s, lm);
+                rescore_block_any(c, q, q_dtype, h, (long)top_idx[warp], nq * BS, kn.q_scale, s, lm, s_q);
                 if (lane == 0) { top_f16[warp] = s; top_lm[warp] = lm; }
             }
         } else if (warp == rk) {
-            const float d = delta_bound_warp(c, q, q_dtype, h, sharded_in ? ws.shard_ranks : 1, ws.shard_rank_stride);
-            if (lane == 0) s_delta = d;
+            if (!delta_early) {
+                const float d = delta_bound_warp(c, q, q_dtype, h, sharded_in ? ws.shard_ranks : 1, ws.shard_rank_stride);
+                if (lane == 0) s_delta = d;
+            }
         } else if (overlap && kn.ranking_fallback) {
 #pragma unroll 1
             for (int b = (warp - ub_first) * 32 + lane; b < n; b += ub_warps * 32) {
