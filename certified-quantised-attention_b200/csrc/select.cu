@@ -840,8 +840,20 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
         unsigned char *tm = ws.topk_mask + (long)h * ws.ld;
         unsigned char *em = ws.explore_mask + (long)h * ws.ld;
         int explored = 0;
+        // four blocks per thread and store when the rows allow it (mask[] is 4-byte aligned, n_pad a multiple of 32)
+        const int n4w = ((((uintptr_t)tm | (uintptr_t)em) & 3u) == 0) ? (n & ~3) : 0;
+        const unsigned *mask4 = reinterpret_cast<const unsigned *>(mask);
 #pragma unroll 1
-        for (int b = tid; b < (int)nact; b += SC_THREADS) {
+        for (int b = 4 * tid; b < n4w; b += 4 * SC_THREADS) {
+            const unsigned mk = mask4[b >> 2];
+            const unsigned sel = mk & 0x01010101u;                       // selected by K*
+            const unsigned exp = ((mk >> 1) & 0x01010101u) & ~sel;       // exploration candidates not already selected
+            explored += __popc(exp);
+            *reinterpret_cast<unsigned *>(tm + b) = sel | exp;
+            *reinterpret_cast<unsigned *>(em + b) = exp;
+        }
+#pragma unroll 1
+        for (int b = n4w + tid; b < (int)nact; b += SC_THREADS) {
             unsigned char mk1 = 1, e = 0;
             if (b < n) {
                 const unsigned char mk = mask[b];
