@@ -6,14 +6,16 @@
 // code is small on purpose, because ~100 CTAs start the same code at the same
 // moment and an unrolled form of these loops was bound by instruction fetch.
 //
-//   role 0 (select) : block log-masses and mass fractions (canonical sum), the
-//            256 heaviest blocks (ties -> lower block id) by a radix search
-//            on the float bit patterns, ordered by rank counting; sequential cumulative mass; K* with the Rung-1
-//            expansion; exploration draw; FP16-key mask.
-//   role 1 (ranking): top-4 blocks by m_b (per-thread lists merged by
-//            shuffles), FP16 re-score by four warps while the other warps take
-//            the boundary maximum, Delta, ranking / boundary /
-//            score-consistency flags, work list of the dense recompute.
+//   role 0 (select) : exploration bits (drawn before the wait on the score
+//            kernel), block masses and mass fractions (canonical sum), the 256
+//            heaviest blocks (ties -> lower block id) by a radix search on the
+//            float bit patterns, ordered by rank counting; sequential cumulative
+//            mass; K* with the Rung-1 expansion; FP16-key mask.
+//   role 1 (ranking): query row and Delta (before the wait), top-4 blocks by
+//            m_b (per-thread lists merged by shuffles), FP16 re-score of each
+//            candidate by eight warps while the boundary maximum is taken,
+//            ranking / boundary / score-consistency flags, work list of the
+//            dense recompute.
 //   role 2 (values) : Rung-2 value check: the promoted blocks are those whose
 //            contribution mass*eta is at or above a threshold found by a search
 //            over "column sums" (histogram hint, then one bit per step), no sort
