@@ -176,6 +176,36 @@ def test_full_size_128k_needles_vs_oracle():
     print(f"128K needles: k*={stats['k_star_mean']:.1f} out_err={err:.2e}")
 
 
+def test_maximum_size_and_one_block_more():
+    """The selector's limit: 16384 quantised blocks (262144 tokens; every thread of a selector CTA owns 16 blocks),
+    here with two KV heads, exploration on and a trailing partial block.  Bit-exact against the oracle like any other
+    size; one block more is refused with CQA_ERR_TOO_LARGE before anything is launched."""
+    dtype = "bfloat16"
+    n_tokens = 16384 * 16 + 5
+    base = synth.make_layer_inputs(78, n_tokens + 16, kv_heads=2, dtype=dtype, n_planted_blocks=24)
+    cc = hz.make_cuda_cache(base.k[:, :16384 * 16], base.v[:, :16384 * 16], dtype, 48)
+    oc = hz.make_oracle_cache(base.k[:, :16384 * 16], base.v[:, :16384 * 16], dtype, 48)
+    for t in range(16384 * 16, n_tokens):
+        cc.append_token(hz.to_dev(base.k[:, t:t + 1], dtype), hz.to_dev(base.v[:, t:t + 1], dtype))
+        oc.append_token(base.k[:, t:t + 1], base.v[:, t:t + 1])
+    knobs = _knobs()
+    rng = np.random.default_rng(78)
+    u = rng.random((8, oc.num_quantized_blocks), dtype=np.float32)
+    R = orc.layer_step(oc, base.q, 4, **_oracle_knobs(knobs, u))
+    out, stats = hz.cuda_step(cc, base.q, dtype, 4, knobs, u)
+    err = hz.compare_step(cc, R, out, "16384 blocks")
+    assert err < 1e-3
+    # eleven more tokens complete block 16385: beyond the limit
+    for t in range(n_tokens, n_tokens + 11):
+        cc.append_token(hz.to_dev(base.k[:, t:t + 1], dtype), hz.to_dev(base.v[:, t:t + 1], dtype))
+    assert cc.num_quantized_blocks == 16385
+    from cqa_b200 import _lib
+    before = _lib.lib().cqa_launch_count(0)
+    with pytest.raises((ValueError, RuntimeError), match="exceed the limit"):
+        hz.cuda_step(cc, base.q, dtype, 4, knobs, None)
+    assert _lib.lib().cqa_launch_count(0) == before
+
+
 def test_exact_ties_take_lowest_block_ids():
     """Every 16-token block repeats the same keys and values, so all mass fractions and all value-error
     terms tie exactly: the selector, the top-4 list and the value check must break the ties by block id
