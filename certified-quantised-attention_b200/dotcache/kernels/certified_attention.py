@@ -446,6 +446,20 @@ def certified_decode_token_host(
     return out_host
 
 
+def _batch_splits(slots: int, heads: int, nact: int, limit: int) -> int:
+    """Phase-2 splits per (sequence, KV head) of a batch: the count that minimises (waves of `slots` resident CTAs)
+    x (blocks per CTA + the fixed cost of a CTA, worth about 64 blocks: merges, partial rows, ticket).  Rounding the
+    per-head share UP to fill the GPU puts a few CTAs into a second, nearly empty wave; this picks the lower count or
+    a multi-wave split instead."""
+    best_p, best = 1, None
+    for p in range(1, max(1, min(limit, nact // 8 if nact >= 8 else 1)) + 1):
+        waves = -(-heads * p // slots)
+        cost = waves * (-(-nact // p) + 64)
+        if best is None or cost < best:
+            best_p, best = p, cost
+    return best_p
+
+
 def certified_attention_batch(
     caches,
     q_all: torch.Tensor,
@@ -539,8 +553,8 @@ def certified_attention_batch(
         ws = _workspace(cache, H, G, device)
         ws.ensure_sel_width(_selection_width(k_max, rung1_threshold, rung1_multiplier, nq), device)
         w = ws.fill_struct(nact)
-        # splits: the whole batch should put about two CTAs on every SM; never more than a sequence's own limit
-        ns = int(num_splits) if num_splits else max(1, (2 * sms + KV * B - 1) // (KV * B))
+        # splits per sequence: never more than the sequence's own limit (its partial buffers)
+        ns = int(num_splits) if num_splits else _batch_splits(2 * sms, KV * B, nact, w.num_splits)
         w.num_splits = max(1, min(ns, w.num_splits, nact))
         if exploration_rate > 0.0:
             w.rng_seed = ws.draw_seed()
