@@ -70,17 +70,23 @@ __device__ __forceinline__ void fp16_block_score_warp(const cqa_cache &c, const 
 __device__ __forceinline__ float delta_bound_warp(const cqa_cache &c, const void *q, int q_dtype, int h, int ranks = 1,
                                                   long rank_stride = 0)
 {
-    const int L = threadIdx.x & 15;
+    const int L = threadIdx.x & 15, hw = (threadIdx.x >> 4) & 1;
     const int kv = h / c.gqa_group;
     float qa[8], sg[8];
     load_q8(q, q_dtype, (long)h * D + 8 * L, qa);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        qa[i] = fabsf(qa[i]);
-        float sv = c.sigma_max[kv * D + 8 * L + i];
-        for (int r = 1; r < ranks; ++r) sv = fmaxf(sv, c.sigma_max[r * rank_stride + kv * D + 8 * L + i]);
-        sg[i] = sv;
+    for (int i = 0; i < 8; ++i) { qa[i] = fabsf(qa[i]); sg[i] = 0.0f; }      // scales are positive
+    // the ranks' rows are split over the two half warps and fetched four ranks at a time (a chain of dependent
+    // loads, one rank after the other, was several microseconds long with eight ranks)
+#pragma unroll 4
+    for (int r = hw; r < ranks; r += 2) {
+        const float4 *row = reinterpret_cast<const float4 *>(c.sigma_max + (long)r * rank_stride + kv * D + 8 * L);
+        const float4 a = row[0], b = row[1];
+        sg[0] = fmaxf(sg[0], a.x); sg[1] = fmaxf(sg[1], a.y); sg[2] = fmaxf(sg[2], a.z); sg[3] = fmaxf(sg[3], a.w);
+        sg[4] = fmaxf(sg[4], b.x); sg[5] = fmaxf(sg[5], b.y); sg[6] = fmaxf(sg[6], b.z); sg[7] = fmaxf(sg[7], b.w);
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sg[i] = fmaxf(sg[i], __shfl_xor_sync(0xFFFFFFFFu, sg[i], 16));
     const float denom = 22.627416997969522f;  // 2*sqrt(128) rounded to binary32
     return __fdiv_rn(hw_sum(chain8(qa, sg)), denom);
 }

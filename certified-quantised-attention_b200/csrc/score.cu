@@ -447,6 +447,7 @@ extern "C" int cqa_fp16_block_scores(const cqa_cache *c, const void *q, int q_dt
 extern "C" int cqa_delta_bound(const cqa_cache *c, const void *q, int q_dtype, float *delta, void *stream)
 {
     if (!c || !q || !delta || !c->sigma_max) { set_error("cqa_delta_bound: NULL pointer"); return CQA_ERR_INVALID; }
+    if ((uintptr_t)c->sigma_max & 15) { set_error("cqa_delta_bound: sigma_max must be 16-byte aligned"); return CQA_ERR_INVALID; }
     const int H = c->kv_heads * c->gqa_group;
     delta_bound_kernel<<<H, 32, 0, (cudaStream_t)stream>>>(*c, q, q_dtype, delta); note_launch();
     return check_launch("delta_bound_kernel");

@@ -959,13 +959,17 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
         // With at most four candidates and Delta already known, a candidate block is re-scored by EIGHT warps (warp
         // 8j + p takes tokens p and p + 8 of candidate j, one per half warp): a single warp walking all 16 tokens is a
         // chain of ~600 dependent instructions behind a DRAM round trip, run once, and was the longest step of this role.
-        const bool spread = !peer_b && !given && rk <= 4 && delta_early;
+        const bool spread = !given && rk <= 4 && (delta_early || peer_b);
         const bool overlap = spread || ub_warps >= 8;
         float ubm = -INFINITY;
         if (spread) {
             const int j = warp >> 3, part = warp & 7, hw = lane >> 4;
             const int t = part + 8 * hw;
-            const void *row = j < rk ? t2_token_row(c, kv, (long)top_idx[j], t, nq * BS) : nullptr;
+            // sharded by block range: this rank re-scores the candidates it owns (local block ids) and sends zeros for
+            // the others, so that the sum over the ranks' rows is the owner's row
+            const long bid = j < rk ? (long)top_idx[j] - (peer_b ? ws.peer_first_block : 0) : -1;
+            const bool owned = j < rk && (!peer_b || (bid >= 0 && bid < ws.peer_n_local));
+            const void *row = owned ? t2_token_row(c, kv, bid, t, peer_b ? ws.peer_n_local * BS : nq * BS) : nullptr;
             if (row && c.key_slots == nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(row));   // device memory only
             if (kn.ranking_fallback) {
                 // the boundary maximum while the rows are on their way
@@ -994,14 +998,27 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
                 if (lane == 0) s_pair[j * 8 + part] = e;
             }
             __syncthreads();
-            if (j < rk && part == 0 && lane == 0) {
+            if (j < rk && part == 0) {
                 // the 16-token butterfly finished in its fixed order: (i, i+4), then (0,2) and (1,3), then the two
                 const float *pp = s_pair + j * 8;
                 const float q0 = __fadd_rn(pp[0], pp[4]), q1 = __fadd_rn(pp[1], pp[5]);
                 const float q2 = __fadd_rn(pp[2], pp[6]), q3 = __fadd_rn(pp[3], pp[7]);
                 const float l = fmaxf(__fadd_rn(__fadd_rn(q0, q2), __fadd_rn(q1, q3)), 1e-30f);
-                top_f16[j] = mx;
-                top_lm[j] = mx == -INFINITY ? -INFINITY : __fadd_rn(mx, clog(l));
+                const float sc = owned ? mx : 0.0f;
+                const float lm = !owned ? 0.0f : (mx == -INFINITY ? -INFINITY : __fadd_rn(mx, clog(l)));
+                if (peer_b) {
+                    if (lane < ws.peer_world) {       // one lane per destination rank
+                        float *d = ws.peer_xb[lane] + ((long)h * CQA_MAX_RANKING_K + j) * 2;
+                        d[0] = sc;
+                        d[1] = lm;
+                    }
+                } else if (lane == 0) {
+                    top_f16[j] = sc;
+                    top_lm[j] = lm;
+                }
+            } else if (warp == 1 && !delta_early) {
+                const float d = delta_bound_warp(c, q, q_dtype, h, sharded_in ? ws.shard_ranks : 1, ws.shard_rank_stride);
+                if (lane == 0) s_delta = d;
             }
         } else if (warp < rk) {
             if (peer_b) {
@@ -1371,6 +1388,10 @@ int selcert_check(const cqa_cache *c, const cqa_knobs *kn, const cqa_workspace *
         const bool local_keys = !(phases & (PH_TOP_ONLY | PH_GIVEN));
         if ((phases & PH_PEER_B) && (ws->peer_world < 2 || ws->peer_world > 8 || !ws->given_fp16 || ws->peer_step < 1)) {
             set_error("selector: incomplete peer description for the in-kernel exchange");
+            return CQA_ERR_INVALID;
+        }
+        if (need_fp16 && c->sigma_max && ((uintptr_t)c->sigma_max & 15)) {
+            set_error("cqa_certify: sigma_max must be 16-byte aligned");
             return CQA_ERR_INVALID;
         }
         if (need_fp16 && local_keys && (!c->keys_t2 || !c->sigma_max || !q)) {
