@@ -18,7 +18,7 @@
 //            dense recompute.
 //   role 2 (values) : Rung-2 value check: the promoted blocks are those whose
 //            contribution mass*eta is at or above a threshold found by a search
-//            over "column sums" (histogram hint, then one bit per step), no sort
+//            over "column sums" (histogram hint, then two bits per step), no sort
 //            and no serial walk.
 //
 // cqa_select, cqa_certify and the fused cqa_layer_step all launch the same
@@ -1235,13 +1235,38 @@ __device__ __forceinline__ void selcert_body(const cqa_cache &c, const cqa_knobs
                     if (fs[0] >= excess && fs[1] < excess) {
                         t0 = t_lo; cnt_lo = cs3[0]; f_lo = fs[0]; cnt_hi = cs3[1];
                         bit = 19;
+                    } else {
+                        // the fixed-point sums put the crossing one bin off: look at the neighbour on that side
+                        const unsigned t_dn = d > 0 ? (unsigned)(d - 1) << 20 : 0u;
+                        const unsigned t_up = d + 2 < 2048 ? (unsigned)(d + 2) << 20 : 0xFFFFFFFFu;
+                        float gs[3];
+                        int gc[3];
+                        column_sums3(e, n, nk, t_dn, t_up, 0xFFFFFFFFu, sh, parity, gs, gc);
+                        if (d > 0 && fs[0] < excess && gs[0] >= excess) {
+                            t0 = t_dn; cnt_lo = gc[0]; f_lo = gs[0]; cnt_hi = cs3[0];
+                            bit = 19;
+                        } else if (fs[1] >= excess && gs[1] < excess) {
+                            t0 = t_hi; cnt_lo = cs3[1]; f_lo = fs[1]; cnt_hi = gc[1];
+                            bit = 19;
+                        }
                     }
                 }
             }
-            // one bit per step: keep the bit when the entries at or above the trial threshold still reach the excess
+            // two bits per step: of the three trial thresholds t0 + {1,2,3} << (bit-1), keep the highest whose admitted
+            // entries still reach the excess (the sums fall as the threshold rises)
 #pragma unroll 1
-            for (; bit >= 0 && cnt_lo - cnt_hi > 1; --bit) {
-                const unsigned trial = t0 | (1u << bit);
+            for (; bit >= 1 && cnt_lo - cnt_hi > 1; bit -= 2) {
+                const unsigned s1 = t0 | (1u << (bit - 1)), s2 = t0 | (2u << (bit - 1)), s3 = t0 | (3u << (bit - 1));
+                float fs[3];
+                int cs3[3];
+                column_sums3(e, n, nk, s1, s2, s3, sh, parity, fs, cs3);
+                if (fs[2] >= excess) { t0 = s3; cnt_lo = cs3[2]; f_lo = fs[2]; }
+                else if (fs[1] >= excess) { t0 = s2; cnt_lo = cs3[1]; f_lo = fs[1]; cnt_hi = cs3[2]; }
+                else if (fs[0] >= excess) { t0 = s1; cnt_lo = cs3[0]; f_lo = fs[0]; cnt_hi = cs3[1]; }
+                else cnt_hi = cs3[0];
+            }
+            if (bit == 0 && cnt_lo - cnt_hi > 1) {      // an odd number of bits was open (search from the top: 31)
+                const unsigned trial = t0 | 1u;
                 int cc = 0;
                 const float fv = column_sum1(e, n, nk, trial - 1u, 0, sh, parity, cc);
                 if (fv >= excess) { t0 = trial; cnt_lo = cc; f_lo = fv; } else { cnt_hi = cc; }
