@@ -116,3 +116,21 @@ def test_roofline_bytes():
     assert b2["fp16_key_bytes"] == 16 * 256
     assert b2["fp16_value_bytes"] == 16 * 256 and b2["int4_value_bytes"] == 2 * nq * 16 * 96
     assert b2["attend"] == 16 * 256 + 16 * 256 + 2 * nq * 16 * 96 + 2 * 5 * 512
+
+
+def test_batch_split_policy_avoids_a_nearly_empty_wave():
+    """Phase-2 splits per (sequence, KV head) of a batch: never more than the sequence's limit or one split per 8
+    blocks, one sequence keeps the one-sequence split, and a batch is never given a count that spills a few CTAs
+    into a second wave when one fewer per head fits in one (8 sequences x 8 KV heads on 296 slots: 4, not 5)."""
+    from dotcache.kernels.certified_attention import _batch_splits
+
+    slots = 296
+    assert _batch_splits(slots, 8, 8193, 37) == 37
+    for heads, nact in ((64, 2049), (64, 8193), (256, 2049), (512, 513), (32, 4097)):
+        p = _batch_splits(slots, heads, nact, 37)
+        assert 1 <= p <= min(37, max(1, nact // 8))
+        waves = -(-heads * p // slots)
+        fill = heads * p / (waves * slots)
+        assert waves >= 4 or fill > 0.8 or p == 1, (heads, nact, p, waves, fill)
+    assert _batch_splits(slots, 64, 2049, 37) == 4
+    assert _batch_splits(slots, 8, 40, 37) <= 5
