@@ -67,7 +67,8 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=2)
     ap.add_argument("--e2e-steps", type=int, default=64)
     ap.add_argument("--kernel-steps", type=int, default=32)
-    ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--cpu-steps", type=int, default=96,
+                    help="decode steps of the bounded CPU sample (about 10 s of host work at 128K on 16 threads)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sharded-context", type=int, default=131072,
                     help="context of the sequence-sharded measurement taken when --gpus > 1 (0 = skip)")
@@ -947,7 +948,7 @@ def _main(args, out):
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             cores = cpu_threads()
-            us = cpu_baseline(args, bases[0], args.cpu_steps, max_new)
+            us = cpu_baseline(args, bases[0], args.cpu_steps, max(max_new, args.cpu_steps + 32))
             result["cpu_baseline"] = {
                 "value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
                 "sample": f"{args.cpu_steps} decode steps of one layer at context {args.context} (median), "
